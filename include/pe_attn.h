@@ -1,0 +1,158 @@
+/*
+ * pe_attn.h -- C ABI of the fused positional-encoding causal attention forward
+ * for NVIDIA B200 (sm_100a).
+ *
+ * One call computes, for every (batch, head), the attention core that the
+ * reference's attention modules run between their input projections and their
+ * output projection: the positional transform of Q and K, softmax_causal(scale *
+ * Q K^T [+ bias]) and the product with V.  Nothing but the output is written to
+ * device memory: no transformed Q/K, no GQA copy, no score matrix.
+ *
+ * What each entry point replaces in the reference (paths inside that project):
+ *   pe_attn_forward, variant PE_ATTN_NOPE / PE_ATTN_ROTARY
+ *       src/model/attention.py:77-96   (rope.py:35-57 rotation, QKNorm, GQA repeat,
+ *                                       F.scaled_dot_product_attention)
+ *   pe_attn_forward, variant PE_ATTN_ALIBI
+ *       src/model/alibi.py:137-160     (QKNorm, GQA repeat, scores + bias, mask,
+ *                                       softmax, @ V)
+ *   pe_attn_forward, variant PE_ATTN_POPE
+ *       src/model/fpope_attention.py:145-177 with src/model/pope.py:124-183 or
+ *       src/model/fpope.py:107-146,266-338 (softplus magnitudes, position x
+ *       frequency phases, clamped key phase bias, cos/sin expansion, concat, GQA
+ *       repeat, F.scaled_dot_product_attention)
+ *   The reference's own native ABI for this path (extension "fpope_cuda",
+ *   setup.py:36-46, Python-level fpope_attention_forward(q, k, v, freqs,
+ *   phase_bias, start_pos, causal), tests/test_fpope.py:222-226) is no longer in
+ *   its tree; this header is what a binding for the path links against instead.
+ *
+ * Conventions
+ *   - All tensor pointers are DEVICE pointers owned by the caller; the library
+ *     allocates no device memory.  Work is enqueued on the given stream and the
+ *     call does not synchronise.
+ *   - Tensors are addressed as base + b*stride[0] + h*stride[1] + s*stride[2] + d
+ *     in ELEMENTS, innermost dimension contiguous.  Both [B,S,H,d] and [B,H,S,d]
+ *     storage are therefore accepted without a copy.
+ *   - Query head h reads key/value head h / (H / Hkv)  (repeat_interleave
+ *     semantics, src/model/attention.py:87-89).
+ *   - Query row r sits at position q_pos0 + r, key row s at k_pos0 + s; key s is
+ *     visible to query r iff s <= r + (Sk - Sq).
+ *   - Return value: 0 on success, otherwise a pe_attn_status code; a message for
+ *     the calling thread's last failure is available from pe_attn_last_error().
+ */
+#ifndef PE_ATTN_H_
+#define PE_ATTN_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PE_ATTN_ABI_VERSION 1
+
+typedef enum pe_attn_variant {
+  PE_ATTN_NOPE = 0,   /* no positional transform                                            */
+  PE_ATTN_ROTARY = 1, /* interleaved-pair rotation by a (cos, sin) table: RoPE, NTK, YaRN,    */
+                      /* FoPE-rotary                                                        */
+  PE_ATTN_ALIBI = 2,  /* logits - slope[h] * |t - s|                                        */
+  PE_ATTN_POPE = 3    /* content half + softplus-magnitude / phase half: PoPE, PoPE-floor,  */
+                      /* FoPE+PoPE                                                          */
+} pe_attn_variant;
+
+typedef enum pe_attn_dtype {
+  PE_ATTN_BF16 = 0, /* bf16 tensors, tcgen05 tensor-core path, fp32 accumulate and softmax  */
+  PE_ATTN_FP32 = 1  /* fp32 tensors, FFMA path in the reference's fp32 operation order      */
+} pe_attn_dtype;
+
+enum pe_attn_flags {
+  PE_ATTN_QK_NORM = 1 << 0,           /* x / (||x||_2 + eps) on q and k rows, after the rotation   */
+  PE_ATTN_FOURIER_MIX = 1 << 1,       /* POPE: freqs[] are base frequencies; mix them with         */
+                                      /* fourier_coeffs[] inside the kernel (fpope.py:107-146)     */
+  PE_ATTN_FOURIER_NORMALIZE = 1 << 2, /* L1-normalise each row of coefficients first               */
+  PE_ATTN_FOURIER_CEILING = 1 << 3,   /* clamp effective frequencies to +-ceil_freq                */
+  PE_ATTN_SIMT_CHECK = 1 << 8         /* bf16 only: run the FFMA kernel on the bf16 tensors (an    */
+                                      /* on-device cross-check for the tensor-core kernel)         */
+};
+
+typedef enum pe_attn_status {
+  PE_ATTN_OK = 0,
+  PE_ATTN_ERR_NULL = 1,        /* a required pointer is null                                */
+  PE_ATTN_ERR_VARIANT = 2,     /* unknown variant / dtype / struct size                     */
+  PE_ATTN_ERR_SHAPE = 3,       /* unsupported or inconsistent dimensions                    */
+  PE_ATTN_ERR_ALIGNMENT = 4,   /* base pointer or stride not 16-byte aligned                */
+  PE_ATTN_ERR_LAUNCH = 5,      /* CUDA reported an error at launch or descriptor encoding   */
+  PE_ATTN_ERR_DEVICE = 6,      /* no sm_100 device current                                  */
+  PE_ATTN_ERR_TOO_LARGE = 7    /* a size exceeds what an entry point supports               */
+} pe_attn_status;
+
+typedef struct pe_attn_args {
+  uint32_t struct_size; /* sizeof(pe_attn_args), checked                                    */
+  int32_t variant;      /* pe_attn_variant                                                  */
+  int32_t dtype;        /* pe_attn_dtype                                                    */
+  uint32_t flags;       /* pe_attn_flags                                                    */
+
+  int32_t B, H, Hkv;    /* batch, query heads, key/value heads (H % Hkv == 0)               */
+  int32_t Sq, Sk;       /* query rows, key rows (Sk >= Sq)                                  */
+  int32_t d_c;          /* content (or plain) head dim of q and k; 0 = position-only PoPE   */
+  int32_t d_r;          /* PoPE position dim BEFORE the cos/sin expansion; 0 otherwise      */
+  int32_t d_v;          /* value / output head dim                                          */
+  int32_t q_pos0;       /* position of query row 0 (the reference's start_pos)              */
+  int32_t k_pos0;       /* position of key row 0                                            */
+
+  float scale;          /* logit scale, e.g. (d_c + 2 d_r)^-1/2                             */
+  float qk_norm_eps;    /* QKNorm epsilon (reference: 1e-6)                                 */
+  float mscale;         /* ROTARY: q and k are multiplied by this after rotation (YaRN); 1  */
+
+  const void* q;        /* [B,H,Sq,d_c]  content / plain queries (null if d_c == 0)         */
+  const void* k;        /* [B,Hkv,Sk,d_c]                                                   */
+  const void* v;        /* [B,Hkv,Sk,d_v]                                                   */
+  void* out;            /* [B,H,Sq,d_v]                                                     */
+  const void* q_r;      /* POPE: [B,H,Sq,d_r] position queries, pre-softplus                */
+  const void* k_r;      /* POPE: [B,Hkv,Sk,d_r]                                             */
+  int64_t q_stride[3], k_stride[3], v_stride[3], out_stride[3], qr_stride[3], kr_stride[3];
+
+  const float* rotary_table;  /* ROTARY: [table_rows, d_c/2, 2] fp32 (cos, sin); row i is     */
+  int32_t table_pos0;         /* position table_pos0 + i                                     */
+  int32_t table_rows;
+  const float* alibi_slopes;  /* ALIBI: [H] fp32                                             */
+  const float* freqs;         /* POPE: [d_r] fp32 effective (or, with FOURIER_MIX, base)     */
+  const float* delta;         /* POPE: [d_r] fp32 raw key phase bias (clamped to [-2pi, 0]   */
+                              /* inside, as the reference does at use); null = 0             */
+  const float* fourier_coeffs;/* POPE + FOURIER_MIX: [d_r, n_fourier] fp32                   */
+  int32_t n_fourier;
+  float floor_freq;           /* FOURIER_MIX: |eff| < floor_freq -> 0  (2 pi / T)            */
+  float ceil_freq;            /* FOURIER_CEILING: clamp bound (2 pi)                         */
+
+  int32_t* device_status;     /* optional [1] int32 on the device: the tensor-core kernel     */
+                              /* ORs a non-zero code into it if one of its bounded waits      */
+                              /* expires (the output is then invalid); never written on      */
+                              /* success.  May be null.                                      */
+} pe_attn_args;
+
+/* ABI version of the loaded library (PE_ATTN_ABI_VERSION at build time). */
+int pe_attn_version(void);
+
+/* Validate ``args`` and enqueue the forward on ``stream`` (a cudaStream_t; null = default
+ * stream) of the current device.  Replaces the reference code listed at the top. */
+int pe_attn_forward(const pe_attn_args* args, void* stream);
+
+/* Validate only: same checks and return codes as pe_attn_forward, touches no GPU. */
+int pe_attn_validate(const pe_attn_args* args);
+
+/* Name of the kernel family pe_attn_forward would pick for ``args``: "tcgen05" or "ffma";
+ * null if ``args`` does not validate. */
+const char* pe_attn_kernel_name(const pe_attn_args* args);
+
+/* Message for the calling thread's most recent non-zero return ("" if none). */
+const char* pe_attn_last_error(void);
+
+/* Static name of a status code. */
+const char* pe_attn_status_string(int status);
+
+/* Algorithmic FLOPs of one call: B * H * (causal pairs) * 2 * (d_c + 2 d_r + d_v). */
+double pe_attn_flops(const pe_attn_args* args);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PE_ATTN_H_ */

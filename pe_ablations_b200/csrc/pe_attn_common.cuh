@@ -1,0 +1,88 @@
+// Shared definitions of the PE-attention kernels: the device-side argument block
+// and the positional-encoding math both kernel families use.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/pe_attn.h"
+
+namespace pe_attn {
+
+// A [B, H, S, d] tensor addressed by element strides, innermost contiguous.
+struct TensorRef {
+  const void* ptr;
+  long long sb, sh, ss;
+};
+
+// Device-side copy of the validated arguments (passed to kernels by value).
+struct KParams {
+  int variant;
+  unsigned flags;
+  int B, H, Hkv, groups;
+  int Sq, Sk;
+  int d_c, d_r, d_v, d_qk;
+  int q_pos0, k_pos0;
+  int causal_off;  // key s visible to query row r iff s <= r + causal_off
+  float scale, eps, mscale;
+  TensorRef q, k, v, out, qr, kr;
+  const float* table;
+  int table_pos0, table_rows;
+  const float* slopes;
+  const float* freqs;
+  const float* delta;
+  const float* coeffs;
+  int n_fourier;
+  float floor_freq, ceil_freq;
+  int* status;
+};
+
+constexpr float kTwoPi = 6.283185307179586f;
+
+// Effective frequency of PoPE dimension c.  Without FOURIER_MIX this is freqs[c].
+// With it, the FoPE collapse of the reference (src/model/fpope.py:116-146):
+//   eff = base * sum_j a^_j * j + base,  a^ = a / (sum_j |a_j| + 1e-8) when normalising,
+//   |eff| < floor -> 0, optional clamp to +-ceil.
+// The sum is accumulated in fp64 and rounded once, which lands within an ulp of any
+// fp32 summation order.
+__device__ __forceinline__ float effective_freq(const KParams& p, int c) {
+  const float base = p.freqs[c];
+  if (!(p.flags & PE_ATTN_FOURIER_MIX)) return base;
+  const float* a = p.coeffs + (size_t)c * p.n_fourier;
+  float denom = 1.0f;
+  if (p.flags & PE_ATTN_FOURIER_NORMALIZE) {
+    double s = 0.0;
+    for (int j = 0; j < p.n_fourier; ++j) s += fabs((double)a[j]);
+    denom = __fadd_rn((float)s, 1e-8f);
+  }
+  double acc = 0.0;
+  for (int j = 0; j < p.n_fourier; ++j) {
+    const float an = (p.flags & PE_ATTN_FOURIER_NORMALIZE) ? __fdiv_rn(a[j], denom) : a[j];
+    const float sj = __fmul_rn(base, (float)(j + 1));
+    acc += (double)__fmul_rn(an, sj);
+  }
+  float eff = __fadd_rn((float)acc, base);
+  if (fabsf(eff) < p.floor_freq) eff = 0.0f;
+  if (p.flags & PE_ATTN_FOURIER_CEILING) eff = fminf(fmaxf(eff, -p.ceil_freq), p.ceil_freq);
+  return eff;
+}
+
+// Key phase bias as used: clamp(delta, -2 pi, 0) (src/model/pope.py:172, src/model/fpope.py:328).
+__device__ __forceinline__ float clamped_delta(const KParams& p, int c) {
+  if (p.delta == nullptr) return 0.0f;
+  return fminf(fmaxf(p.delta[c], -kTwoPi), 0.0f);
+}
+
+// softplus with torch's defaults (beta 1, threshold 20), accurate libm calls.
+__device__ __forceinline__ float softplus_accurate(float x) {
+  return x > 20.0f ? x : log1pf(expf(x));
+}
+
+int launch_simt(const KParams& p, int dtype, cudaStream_t stream);
+int launch_tc(const KParams& p, cudaStream_t stream);
+bool tc_supports(const KParams& p);
+
+void set_error(const char* fmt, ...);
+
+}  // namespace pe_attn

@@ -1,0 +1,297 @@
+// FFMA (CUDA-core) fused PE-attention forward.
+//
+// This is the fp32 path: every positional transform follows the reference's fp32
+// operation order (separately rounded position*frequency product, then the phase
+// bias, accurate sin/cos/exp/log1p), because tensor cores at tf32 precision cannot
+// hold the 1e-4 tolerance of the fp32 configurations.  Instantiated for bf16
+// tensors too, where it serves as an on-device cross-check of the tcgen05 kernel.
+//
+// One CTA owns 64 query rows of one (batch, head) and streams 64-key tiles:
+//   load + transform K tile -> S = Q K^T (4x4 per thread) -> online softmax with
+//   16-lane shuffle reductions -> P to shared memory -> O += P V.
+// Shared memory: Q operand [64][d_qk+1], K operand [64][d_qk+1], V [64][d_v],
+// P [64][65], per-dimension frequency / phase-bias vectors.
+#include "pe_attn_common.cuh"
+
+namespace pe_attn {
+namespace {
+
+constexpr int BM = 64;
+constexpr int BN = 64;
+constexpr int NTHREADS = 256;
+constexpr int MAX_VC = 8;  // d_v <= 128: up to 8 output columns per thread (stride 16)
+
+template <typename T>
+__device__ __forceinline__ float load_elem(const void* base, long long off) {
+  return static_cast<float>(reinterpret_cast<const T*>(base)[off]);
+}
+template <>
+__device__ __forceinline__ float load_elem<__nv_bfloat16>(const void* base, long long off) {
+  return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[off]);
+}
+
+template <bool ROUND>
+__device__ __forceinline__ float round_op(float x) {
+  if constexpr (ROUND) return __bfloat162float(__float2bfloat16_rn(x));
+  return x;
+}
+
+// Fill one 64-row operand tile (Q or K) in shared memory with the transformed rows.
+// dst[row][0 .. d_qk) ; rows at or past n_rows are zero.
+template <typename T, bool ROUND>
+__device__ void build_operand_tile(const KParams& p, float* dst, int ld, const TensorRef& content,
+                                   const TensorRef& posi, int b, int head, int row0, int n_rows, int pos0,
+                                   bool is_key, const float* freq_s, const float* delta_s) {
+  const int tid = threadIdx.x;
+  const int d_c = p.d_c, d_r = p.d_r;
+  if (p.variant == PE_ATTN_ROTARY) {
+    const int half = d_c >> 1;
+    for (int idx = tid; idx < BM * half; idx += NTHREADS) {
+      const int r = idx / half, i = idx - r * half;
+      const int row = row0 + r;
+      float o0 = 0.f, o1 = 0.f;
+      if (row < n_rows) {
+        const long long off = (long long)b * content.sb + (long long)head * content.sh + (long long)row * content.ss;
+        const float x0 = load_elem<T>(content.ptr, off + 2 * i);
+        const float x1 = load_elem<T>(content.ptr, off + 2 * i + 1);
+        const int trow = pos0 + row - p.table_pos0;
+        const float2 cs = reinterpret_cast<const float2*>(p.table)[(size_t)trow * half + i];
+        // complex product (x0 + i x1)(cos + i sin), each term rounded separately
+        o0 = __fsub_rn(__fmul_rn(x0, cs.x), __fmul_rn(x1, cs.y));
+        o1 = __fadd_rn(__fmul_rn(x0, cs.y), __fmul_rn(x1, cs.x));
+        o0 = round_op<ROUND>(o0);
+        o1 = round_op<ROUND>(o1);
+        if (p.mscale != 1.0f) {
+          o0 = round_op<ROUND>(__fmul_rn(o0, p.mscale));
+          o1 = round_op<ROUND>(__fmul_rn(o1, p.mscale));
+        }
+      }
+      dst[r * ld + 2 * i] = o0;
+      dst[r * ld + 2 * i + 1] = o1;
+    }
+  } else {
+    for (int idx = tid; idx < BM * d_c; idx += NTHREADS) {
+      const int r = idx / d_c, c = idx - r * d_c;
+      const int row = row0 + r;
+      float x = 0.f;
+      if (row < n_rows) {
+        const long long off = (long long)b * content.sb + (long long)head * content.sh + (long long)row * content.ss;
+        x = load_elem<T>(content.ptr, off + c);
+      }
+      dst[r * ld + c] = x;
+    }
+  }
+  if (p.variant == PE_ATTN_POPE) {
+    for (int idx = tid; idx < BM * d_r; idx += NTHREADS) {
+      const int r = idx / d_r, c = idx - r * d_r;
+      const int row = row0 + r;
+      float oc = 0.f, os = 0.f;
+      if (row < n_rows) {
+        const long long off = (long long)b * posi.sb + (long long)head * posi.sh + (long long)row * posi.ss;
+        const float x = load_elem<T>(posi.ptr, off + c);
+        const float mu = softplus_accurate(x);
+        // phase = fl(fl(pos * freq) + delta): product and sum rounded separately, as the
+        // reference's tensor ops do
+        float phase = __fmul_rn((float)(pos0 + row), freq_s[c]);
+        if (is_key) phase = __fadd_rn(phase, delta_s[c]);
+        oc = round_op<ROUND>(__fmul_rn(mu, cosf(phase)));
+        os = round_op<ROUND>(__fmul_rn(mu, sinf(phase)));
+      }
+      dst[r * ld + d_c + c] = oc;
+      dst[r * ld + d_c + d_r + c] = os;
+    }
+  }
+  if (p.flags & PE_ATTN_QK_NORM) {
+    __syncthreads();
+    // x / (||x||_2 + eps) per row, 4 threads per row
+    const int r = tid >> 2, q4 = tid & 3;
+    float ss = 0.f;
+    for (int c = q4; c < p.d_qk; c += 4) {
+      const float x = dst[r * ld + c];
+      ss = fmaf(x, x, ss);
+    }
+    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+    const float denom = __fadd_rn(sqrtf(ss), p.eps);
+    for (int c = q4; c < p.d_qk; c += 4) dst[r * ld + c] = round_op<ROUND>(__fdiv_rn(dst[r * ld + c], denom));
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void store_elem(void* base, long long off, float x) {
+  reinterpret_cast<T*>(base)[off] = static_cast<T>(x);
+}
+template <>
+__device__ __forceinline__ void store_elem<__nv_bfloat16>(void* base, long long off, float x) {
+  reinterpret_cast<__nv_bfloat16*>(base)[off] = __float2bfloat16_rn(x);
+}
+
+template <typename T, bool ROUND>
+__global__ void __launch_bounds__(NTHREADS) pe_attn_simt_kernel(const KParams p) {
+  extern __shared__ float smem[];
+  const int dqk = p.d_qk, dv = p.d_v;
+  const int ld = dqk + 1;
+  float* Qs = smem;
+  float* Ks = Qs + BM * ld;
+  float* Vs = Ks + BN * ld;
+  float* Ps = Vs + BN * dv;
+  float* freq_s = Ps + BM * (BN + 1);
+  float* delta_s = freq_s + (p.d_r > 0 ? p.d_r : 1);
+
+  const int tid = threadIdx.x;
+  const int ty = tid >> 4, tx = tid & 15;
+  const int n_qblk = (p.Sq + BM - 1) / BM;
+  const int qblk = n_qblk - 1 - (int)blockIdx.x;  // heaviest (last) query blocks first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / p.groups;
+  const int m0 = qblk * BM;
+
+  if (p.variant == PE_ATTN_POPE) {
+    for (int c = tid; c < p.d_r; c += NTHREADS) {
+      freq_s[c] = effective_freq(p, c);
+      delta_s[c] = clamped_delta(p, c);
+    }
+    __syncthreads();
+  }
+  build_operand_tile<T, ROUND>(p, Qs, ld, p.q, p.qr, b, h, m0, p.Sq, p.q_pos0, false, freq_s, delta_s);
+
+  float m_run[4], l_run[4], o_acc[4][MAX_VC];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    m_run[i] = -INFINITY;
+    l_run[i] = 0.f;
+#pragma unroll
+    for (int c = 0; c < MAX_VC; ++c) o_acc[i][c] = 0.f;
+  }
+  const float slope = (p.variant == PE_ATTN_ALIBI) ? p.slopes[h] : 0.f;
+
+  int k_end = m0 + BM + p.causal_off;
+  if (k_end > p.Sk) k_end = p.Sk;
+  for (int n0 = 0; n0 < k_end; n0 += BN) {
+    __syncthreads();  // previous tile's reads of Ks / Vs / Ps are done (and Qs is complete)
+    build_operand_tile<T, ROUND>(p, Ks, ld, p.k, p.kr, b, hk, n0, p.Sk, p.k_pos0, true, freq_s, delta_s);
+    for (int idx = tid; idx < BN * dv; idx += NTHREADS) {
+      const int r = idx / dv, c = idx - r * dv;
+      const int row = n0 + r;
+      float x = 0.f;
+      if (row < p.Sk) x = load_elem<T>(p.v.ptr, (long long)b * p.v.sb + (long long)hk * p.v.sh + (long long)row * p.v.ss + c);
+      Vs[r * dv + c] = x;
+    }
+    __syncthreads();
+
+    float s[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+    for (int kk = 0; kk < dqk; ++kk) {
+      float a[4], bb[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = Qs[(ty + 16 * i) * ld + kk];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) bb[j] = Ks[(tx + 16 * j) * ld + kk];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s[i][j] = fmaf(a[i], bb[j], s[i][j]);
+    }
+
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = m0 + ty + 16 * i;
+      float tmax = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int col = n0 + tx + 16 * j;
+        const int rel = col - (row + p.causal_off);
+        float x = s[i][j] * p.scale;
+        if (p.variant == PE_ATTN_ALIBI) x = x - slope * fabsf((float)rel);
+        if (rel > 0 || col >= p.Sk) x = -INFINITY;
+        s[i][j] = x;
+        tmax = fmaxf(tmax, x);
+      }
+#pragma unroll
+      for (int d = 1; d < 16; d <<= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, d));
+      const float m_new = fmaxf(m_run[i], tmax);
+      const float alpha = (m_new == -INFINITY) ? 1.f : expf(m_run[i] - m_new);
+      float psum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float pj = (m_new == -INFINITY) ? 0.f : expf(s[i][j] - m_new);
+        psum += pj;
+        Ps[(ty + 16 * i) * (BN + 1) + tx + 16 * j] = pj;
+      }
+#pragma unroll
+      for (int d = 1; d < 16; d <<= 1) psum += __shfl_xor_sync(0xffffffffu, psum, d);
+      l_run[i] = l_run[i] * alpha + psum;
+      m_run[i] = m_new;
+#pragma unroll
+      for (int c = 0; c < MAX_VC; ++c) o_acc[i][c] *= alpha;
+    }
+    __syncthreads();
+
+    for (int j = 0; j < BN; ++j) {
+      float a[4], vv[MAX_VC];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = Ps[(ty + 16 * i) * (BN + 1) + j];
+#pragma unroll
+      for (int c = 0; c < MAX_VC; ++c) {
+        const int col = tx + 16 * c;
+        vv[c] = col < dv ? Vs[j * dv + col] : 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int c = 0; c < MAX_VC; ++c) o_acc[i][c] = fmaf(a[i], vv[c], o_acc[i][c]);
+    }
+  }
+
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int row = m0 + ty + 16 * i;
+    if (row >= p.Sq) continue;
+    const float inv = 1.f / l_run[i];
+    const long long off = (long long)b * p.out.sb + (long long)h * p.out.sh + (long long)row * p.out.ss;
+#pragma unroll
+    for (int c = 0; c < MAX_VC; ++c) {
+      const int col = tx + 16 * c;
+      if (col < dv) store_elem<T>(const_cast<void*>(p.out.ptr), off + col, o_acc[i][c] * inv);
+    }
+  }
+}
+
+}  // namespace
+
+size_t simt_smem_bytes(const KParams& p) {
+  const size_t ld = p.d_qk + 1;
+  const size_t nfl = 2 * (size_t)BM * ld + (size_t)BN * p.d_v + (size_t)BM * (BN + 1) + 2 * (size_t)(p.d_r > 0 ? p.d_r : 1);
+  return nfl * sizeof(float);
+}
+
+int launch_simt(const KParams& p, int dtype, cudaStream_t stream) {
+  const size_t smem = simt_smem_bytes(p);
+  dim3 grid((p.Sq + BM - 1) / BM, p.H, p.B), block(NTHREADS);
+  cudaError_t e;
+  if (dtype == PE_ATTN_FP32) {
+    auto kern = pe_attn_simt_kernel<float, false>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) {
+      kern<<<grid, block, smem, stream>>>(p);
+      e = cudaGetLastError();
+    }
+  } else {
+    auto kern = pe_attn_simt_kernel<__nv_bfloat16, true>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) {
+      kern<<<grid, block, smem, stream>>>(p);
+      e = cudaGetLastError();
+    }
+  }
+  if (e != cudaSuccess) {
+    set_error("ffma kernel launch failed: %s", cudaGetErrorString(e));
+    return PE_ATTN_ERR_LAUNCH;
+  }
+  return PE_ATTN_OK;
+}
+
+}  // namespace pe_attn

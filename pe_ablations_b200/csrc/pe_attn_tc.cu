@@ -1,0 +1,679 @@
+// tcgen05 / TMEM / TMA fused PE-attention forward for bf16 tensors (sm_100a).
+//
+// One CTA (512 threads, 1 per SM) owns 256 query rows of one (batch, head) as two
+// 128-row tiles and streams 64-key tiles through a 2-stage shared-memory ring:
+//
+//   warp 0        TMA producer: content halves of Q and K, and V, as 128B-swizzled tiles
+//   warp 1        MMA issuer:   S_i = Q_i K^T  (SS, M128 N64 K16 x d_qk/16) into TMEM,
+//                               O_i += P_i V   (TS: P read from TMEM, V from smem, N = d_v)
+//   warp 2        TMEM allocation / release (512 columns)
+//   warps 4-7     softmax of query tile 0: TMEM -> registers, running max / sum, P (bf16)
+//   warps 8-11    softmax of query tile 1          back into TMEM over its own S buffer
+//   warps 12-15   positional transform of every K tile, written straight into the
+//                 swizzled K-major operand layout the MMA reads
+// The softmax warpgroups also build the positional part of their own Q tile once.
+//
+// Nothing positional ever goes to global memory: RoPE-family rotation (from the (cos, sin)
+// table), QKNorm, and the PoPE expansion [softplus(x) cos(phi), softplus(x) sin(phi)] with
+// phi = pos * freq (+ clamped key phase bias) are computed in registers from the raw
+// projections and stored as bf16 MMA operands in shared memory.  The FoPE frequency mix
+// and floor clipping run in the kernel prologue.
+//
+// TMEM map (columns): S/P buffers (tile i, buffer b) at (2 i + b) * 64, 64 fp32 columns
+// each (P reuses the first 32 as packed bf16 pairs); O_i at 256 + i * d_v.
+//
+// Every mbarrier wait is bounded; on expiry the CTA ORs a code into the caller's status
+// word, lets its copies land, frees its TMEM and returns.
+#include <cuda.h>
+
+#include "pe_attn_common.cuh"
+#include "pe_attn_ptx.cuh"
+
+namespace pe_attn {
+namespace {
+
+using namespace ptx;
+
+constexpr int BLOCK_M = 128;   // query rows per tile (TMEM lanes)
+constexpr int Q_TILES = 2;     // query tiles per CTA
+constexpr int BLOCK_N = 64;    // keys per tile
+constexpr int KV_STAGES = 2;
+constexpr int NTHREADS = 512;
+constexpr int TMEM_COLS = 512;
+constexpr int TAIL_BYTES = 1024;  // barriers, TMEM base, frequency / phase-bias vectors
+
+enum Mode { MODE_PLAIN = 0, MODE_XFORM = 1, MODE_POPE = 2 };
+
+// status codes ORed into the caller's device status word
+enum : int {
+  ST_WAIT_QFULL = 1 << 0, ST_WAIT_KFULL = 1 << 1, ST_WAIT_VFULL = 1 << 2, ST_WAIT_KEMPTY = 1 << 3,
+  ST_WAIT_VEMPTY = 1 << 4, ST_WAIT_SFULL = 1 << 5, ST_WAIT_PREADY = 1 << 6, ST_WAIT_PVDONE = 1 << 7,
+  ST_WAIT_MMADONE = 1 << 8
+};
+
+enum : int {
+  BAR_QFULL = 0, BAR_KFULL = 2, BAR_KEMPTY = 4, BAR_VFULL = 6, BAR_VEMPTY = 8, BAR_SFULL = 10, BAR_PREADY = 14,
+  BAR_PVDONE = 18, BAR_MMADONE = 22, NUM_BARS = 23
+};
+
+template <int DC, int DR, int DV>
+struct Cfg {
+  static constexpr int DQK = DC + 2 * DR;
+  static constexpr int NCHUNK = DQK / 64;  // 64-column (128-byte) operand chunks
+  static constexpr int NCC = DC / 64;      // chunks that are plain content (TMA-loaded)
+  static constexpr int VCH = DV / 64;
+  static constexpr int Q_CHUNK_BYTES = BLOCK_M * 128;
+  static constexpr int K_CHUNK_BYTES = BLOCK_N * 128;
+  static constexpr int V_CHUNK_BYTES = BLOCK_N * 128;
+  static constexpr int Q_TILE_BYTES = NCHUNK * Q_CHUNK_BYTES;
+  static constexpr int K_STAGE_BYTES = NCHUNK * K_CHUNK_BYTES;
+  static constexpr int V_STAGE_BYTES = VCH * V_CHUNK_BYTES;
+  static constexpr int Q_OFF = TAIL_BYTES;
+  static constexpr int K_OFF = Q_OFF + Q_TILES * Q_TILE_BYTES;
+  static constexpr int V_OFF = K_OFF + KV_STAGES * K_STAGE_BYTES;
+  static constexpr int SMEM_USED = V_OFF + KV_STAGES * V_STAGE_BYTES;
+  static constexpr int SMEM_BYTES = SMEM_USED + 1024;  // slack to align the base to 1024
+  static_assert(DQK % 64 == 0 && DQK >= 64 && DQK <= 256, "d_qk must be 64..256 in steps of 64");
+  static_assert(DV == 64 || DV == 128, "d_v must be 64 or 128");
+  static_assert(SMEM_BYTES <= 232448, "shared memory budget exceeded");
+};
+
+// softplus with the special-function unit: max(x, 0) + log1p(exp(-|x|))
+__device__ __forceinline__ float softplus_fast(float x) {
+  const float e = ex2_approx(-fabsf(x) * 1.4426950408889634f);
+  return fmaxf(x, 0.f) + lg2_approx(1.0f + e) * 0.6931471805599453f;
+}
+
+// sin / cos of a large fp32 angle: two-term Cody-Waite reduction by 2 pi, then MUFU
+__device__ __forceinline__ void sincos_reduced(float x, float* s, float* c) {
+  const float k = rintf(x * 0.15915494309189535f);
+  float r = fmaf(k, -6.2831854820251465f, x);
+  r = fmaf(k, 1.7484556000744883e-7f, r);
+  *s = __sinf(r);
+  *c = __cosf(r);
+}
+
+// byte offset of the 16-byte slot ``slot`` (0..7) of row ``r`` inside a 128B-swizzled chunk
+__device__ __forceinline__ uint32_t swz(int r, int slot) { return (uint32_t)(r * 128 + ((slot ^ (r & 7)) << 4)); }
+
+// Build 64 operand rows (positional / transformed columns only) in shared memory with a
+// group of 128 threads (tg = 0..127).  ``base`` is the shared address of chunk 0 at the
+// slab's first row (1024-byte aligned), chunks are ``chunk_stride`` bytes apart.
+//   MODE_POPE : columns [DC, DC + 2 DR): softplus magnitude x (cos, sin) of the phase
+//   MODE_XFORM: columns [0, DC): optional pair rotation, mscale, optional L2 normalisation
+template <int DC, int DR, int MODE>
+__device__ __forceinline__ void build_slab(const KParams& p, uint32_t base, uint32_t chunk_stride,
+                                           const TensorRef& content, const TensorRef& posi, int b, int head,
+                                           int row0, int n_rows, int pos_row0, bool is_key, const float* freq_s,
+                                           const float* delta_s, int tg) {
+  if constexpr (MODE == MODE_POPE) {
+    constexpr int VPR = DR / 8;            // 16-byte vectors per row
+    constexpr int RPP = 128 / VPR;         // rows per pass
+    constexpr int PASSES = BLOCK_N / RPP;
+    const int cv = tg % VPR, r_in = tg / VPR;
+    float f[8], dl[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      f[e] = freq_s[cv * 8 + e];
+      dl[e] = is_key ? delta_s[cv * 8 + e] : 0.f;
+    }
+    const char* src = reinterpret_cast<const char*>(posi.ptr) +
+                      2 * ((long long)b * posi.sb + (long long)head * posi.sh + (long long)cv * 8);
+    uint4 raw[PASSES];
+#pragma unroll
+    for (int k = 0; k < PASSES; ++k) {
+      const int grow = row0 + r_in + k * RPP;
+      raw[k] = make_uint4(0, 0, 0, 0);
+      if (grow < n_rows) raw[k] = ldg_nc_v4(src + 2 * (long long)grow * posi.ss);
+    }
+#pragma unroll
+    for (int k = 0; k < PASSES; ++k) {
+      const int r = r_in + k * RPP;
+      const bool live = (row0 + r) < n_rows;
+      const float pos = (float)(pos_row0 + r);
+      const uint32_t w[4] = {raw[k].x, raw[k].y, raw[k].z, raw[k].w};
+      float oc[8], os[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float x = (e & 1) ? bf16_hi(w[e >> 1]) : bf16_lo(w[e >> 1]);
+        const float mu = live ? softplus_fast(x) : 0.f;
+        // phase = fl(fl(pos * freq) + delta), the reference's rounding order
+        const float ph = __fadd_rn(__fmul_rn(pos, f[e]), dl[e]);
+        float sn, cs;
+        sincos_reduced(ph, &sn, &cs);
+        oc[e] = mu * cs;
+        os[e] = mu * sn;
+      }
+      const uint4 vc = make_uint4(pack_bf16x2(oc[0], oc[1]), pack_bf16x2(oc[2], oc[3]), pack_bf16x2(oc[4], oc[5]),
+                                  pack_bf16x2(oc[6], oc[7]));
+      const uint4 vs = make_uint4(pack_bf16x2(os[0], os[1]), pack_bf16x2(os[2], os[3]), pack_bf16x2(os[4], os[5]),
+                                  pack_bf16x2(os[6], os[7]));
+      const int col_c = DC + cv * 8, col_s = DC + DR + cv * 8;
+      sts_v4(base + (col_c / 64) * chunk_stride + swz(r, (col_c % 64) / 8), vc);
+      sts_v4(base + (col_s / 64) * chunk_stride + swz(r, (col_s % 64) / 8), vs);
+    }
+  } else if constexpr (MODE == MODE_XFORM) {
+    constexpr int VPR = DC / 8;
+    constexpr int RPP = 128 / VPR;
+    constexpr int PASSES = BLOCK_N / RPP;
+    const int cv = tg % VPR, r_in = tg / VPR;
+    const bool rotary = p.variant == PE_ATTN_ROTARY;
+    const bool norm = (p.flags & PE_ATTN_QK_NORM) != 0;
+    const char* src = reinterpret_cast<const char*>(content.ptr) +
+                      2 * ((long long)b * content.sb + (long long)head * content.sh + (long long)cv * 8);
+    uint4 pk[PASSES];
+    float ss[PASSES];
+#pragma unroll
+    for (int k = 0; k < PASSES; ++k) {
+      const int grow = row0 + r_in + k * RPP;
+      pk[k] = make_uint4(0, 0, 0, 0);
+      if (grow < n_rows) pk[k] = ldg_nc_v4(src + 2 * (long long)grow * content.ss);
+    }
+#pragma unroll
+    for (int k = 0; k < PASSES; ++k) {
+      const int r = r_in + k * RPP;
+      const bool live = (row0 + r) < n_rows;
+      uint32_t w[4] = {pk[k].x, pk[k].y, pk[k].z, pk[k].w};
+      if (rotary && live) {
+        const int trow = pos_row0 + r - p.table_pos0;
+        const float4* tp = reinterpret_cast<const float4*>(p.table + ((size_t)trow * (DC / 2) + cv * 4) * 2);
+        const float4 t0 = __ldg(tp), t1 = __ldg(tp + 1);
+        const float cs[4] = {t0.x, t0.z, t1.x, t1.z}, sn[4] = {t0.y, t0.w, t1.y, t1.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float x0 = bf16_lo(w[e]), x1 = bf16_hi(w[e]);
+          const float o0 = x0 * cs[e] - x1 * sn[e];
+          const float o1 = x0 * sn[e] + x1 * cs[e];
+          w[e] = pack_bf16x2(o0, o1);
+          if (p.mscale != 1.0f) w[e] = pack_bf16x2(bf16_lo(w[e]) * p.mscale, bf16_hi(w[e]) * p.mscale);
+        }
+      }
+      float acc = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float x0 = bf16_lo(w[e]), x1 = bf16_hi(w[e]);
+        acc = fmaf(x0, x0, acc);
+        acc = fmaf(x1, x1, acc);
+      }
+      ss[k] = acc;
+      pk[k] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    if (norm) {
+      // row sum of squares across the VPR lanes that share a row (warp-level reduction)
+#pragma unroll
+      for (int k = 0; k < PASSES; ++k) {
+#pragma unroll
+        for (int d = 1; d < VPR; d <<= 1) ss[k] += __shfl_xor_sync(0xffffffffu, ss[k], d);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < PASSES; ++k) {
+      const int r = r_in + k * RPP;
+      uint32_t w[4] = {pk[k].x, pk[k].y, pk[k].z, pk[k].w};
+      if (norm) {
+        const float inv = 1.0f / (sqrtf(ss[k]) + p.eps);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) w[e] = pack_bf16x2(bf16_lo(w[e]) * inv, bf16_hi(w[e]) * inv);
+      }
+      const int col = cv * 8;
+      sts_v4(base + (col / 64) * chunk_stride + swz(r, (col % 64) / 8), make_uint4(w[0], w[1], w[2], w[3]));
+    }
+  }
+}
+
+template <int DC, int DR, int DV, int MODE, bool ALIBI>
+__global__ void __launch_bounds__(NTHREADS, 1)
+pe_attn_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                  const __grid_constant__ CUtensorMap tmV) {
+  using C = Cfg<DC, DR, DV>;
+  constexpr bool HAS_TMA_QK = (MODE == MODE_PLAIN) || (MODE == MODE_POPE && DC > 0);
+  constexpr bool HAS_XFORM = MODE != MODE_PLAIN;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bars = smem_base;                       // NUM_BARS x 8 bytes
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + 256);
+  volatile uint32_t* abort_slot = reinterpret_cast<volatile uint32_t*>(smem + 260);
+  float* freq_s = reinterpret_cast<float*>(smem + 512);   // [64]
+  float* delta_s = reinterpret_cast<float*>(smem + 768);  // [64]
+  auto bar = [&](int idx) -> uint32_t { return bars + 8u * (uint32_t)idx; };
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_qblk = (p.Sq + Q_TILES * BLOCK_M - 1) / (Q_TILES * BLOCK_M);
+  const int qblk = n_qblk - 1 - (int)blockIdx.x;  // longest (last) query blocks are scheduled first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / p.groups;
+  const int m0 = qblk * Q_TILES * BLOCK_M;
+
+  // key tiles each query tile needs (causal): keys [0, min(Sk, last row + 1 + off))
+  int nt[Q_TILES];
+#pragma unroll
+  for (int i = 0; i < Q_TILES; ++i) {
+    const int first = m0 + i * BLOCK_M;
+    int kend = first + BLOCK_M + p.causal_off;
+    if (kend > p.Sk) kend = p.Sk;
+    nt[i] = first < p.Sq ? (kend + BLOCK_N - 1) / BLOCK_N : 0;
+  }
+  const int n_tiles = nt[1] > nt[0] ? nt[1] : nt[0];
+
+  auto fail = [&](int code) {
+    if (p.status != nullptr) atomicOr(p.status, code);
+  };
+
+  if (tid == 0) {
+    // a CTA that starts after another one reported a failure does no work
+    *abort_slot = (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1u : 0u;
+    const uint32_t n_xf = HAS_XFORM ? 4u : 0u;
+    const uint32_t n_tma = HAS_TMA_QK ? 1u : 0u;
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(BAR_QFULL + i), n_tma + n_xf);
+      mbar_init(bar(BAR_KFULL + i), n_tma + n_xf);
+      mbar_init(bar(BAR_KEMPTY + i), 1);
+      mbar_init(bar(BAR_VFULL + i), 1);
+      mbar_init(bar(BAR_VEMPTY + i), 1);
+    }
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(bar(BAR_SFULL + i), 1);
+      mbar_init(bar(BAR_PREADY + i), BLOCK_M);
+      mbar_init(bar(BAR_PVDONE + i), 1);
+    }
+    mbar_init(bar(BAR_MMADONE), 1);
+    mbar_fence_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+    tmem_relinquish();
+  }
+  if constexpr (MODE == MODE_POPE) {
+    if (tid >= 128 && tid < 128 + DR) {
+      freq_s[tid - 128] = effective_freq(p, tid - 128);
+      delta_s[tid - 128] = clamped_delta(p, tid - 128);
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const bool run = *abort_slot == 0;
+
+  const uint32_t q_smem = smem_base + C::Q_OFF;
+  const uint32_t k_smem = smem_base + C::K_OFF;
+  const uint32_t v_smem = smem_base + C::V_OFF;
+
+  if (!run) {
+    // nothing to do
+  } else if (warp == 0) {
+    // ===================== TMA producer =====================
+    if (lane == 0) {
+      tma_prefetch_desc(&tmV);
+      if constexpr (HAS_TMA_QK) {
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        for (int i = 0; i < Q_TILES; ++i) {
+          if (nt[i] == 0) continue;
+          mbar_arrive_expect_tx(bar(BAR_QFULL + i), C::NCC * C::Q_CHUNK_BYTES);
+          for (int c = 0; c < C::NCC; ++c)
+            tma_load_4d(q_smem + i * C::Q_TILE_BYTES + c * C::Q_CHUNK_BYTES, &tmQ, bar(BAR_QFULL + i), c * 64,
+                        m0 + i * BLOCK_M, h, b);
+        }
+      }
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (uint32_t)((j >> 1) & 1);
+        if constexpr (HAS_TMA_QK) {
+          if (!mbar_wait(bar(BAR_KEMPTY + s), ph ^ 1u)) { fail(ST_WAIT_KEMPTY); break; }
+          mbar_arrive_expect_tx(bar(BAR_KFULL + s), C::NCC * C::K_CHUNK_BYTES);
+          for (int c = 0; c < C::NCC; ++c)
+            tma_load_4d(k_smem + s * C::K_STAGE_BYTES + c * C::K_CHUNK_BYTES, &tmK, bar(BAR_KFULL + s), c * 64,
+                        j * BLOCK_N, hk, b);
+        }
+        if (!mbar_wait(bar(BAR_VEMPTY + s), ph ^ 1u)) { fail(ST_WAIT_VEMPTY); break; }
+        mbar_arrive_expect_tx(bar(BAR_VFULL + s), C::V_STAGE_BYTES);
+        for (int c = 0; c < C::VCH; ++c)
+          tma_load_4d(v_smem + s * C::V_STAGE_BYTES + c * C::V_CHUNK_BYTES, &tmV, bar(BAR_VFULL + s), c * 64,
+                      j * BLOCK_N, hk, b);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ===================== MMA issuer =====================
+    if (lane == 0) {
+      constexpr uint32_t IDESC_QK = make_idesc_bf16(BLOCK_M, BLOCK_N, false);
+      constexpr uint32_t IDESC_PV = make_idesc_bf16(BLOCK_M, DV, true);
+      bool ok = true;
+      for (int i = 0; i < Q_TILES && ok; ++i)
+        if (nt[i] > 0 && !mbar_wait(bar(BAR_QFULL + i), 0)) { fail(ST_WAIT_QFULL); ok = false; }
+
+      auto issue_qk = [&](int j) -> bool {
+        const int s = j & 1;
+        if (!mbar_wait(bar(BAR_KFULL + s), (uint32_t)((j >> 1) & 1))) { fail(ST_WAIT_KFULL); return false; }
+        tc_fence_after_sync();
+        for (int i = 0; i < Q_TILES; ++i) {
+          if (j >= nt[i]) continue;
+          const uint32_t d = tmem_base + (uint32_t)((2 * i + (j & 1)) * BLOCK_N);
+#pragma unroll
+          for (int kk = 0; kk < C::DQK / 16; ++kk) {
+            const uint64_t ad = make_smem_desc(
+                q_smem + i * C::Q_TILE_BYTES + (kk >> 2) * C::Q_CHUNK_BYTES + (kk & 3) * 32, 16, 1024);
+            const uint64_t bd = make_smem_desc(
+                k_smem + s * C::K_STAGE_BYTES + (kk >> 2) * C::K_CHUNK_BYTES + (kk & 3) * 32, 16, 1024);
+            mma_ss(d, ad, bd, IDESC_QK, kk > 0 ? 1u : 0u);
+          }
+          tc_commit(bar(BAR_SFULL + 2 * i + (j & 1)));
+        }
+        tc_commit(bar(BAR_KEMPTY + s));
+        return true;
+      };
+      auto issue_pv = [&](int j) -> bool {
+        const int s = j & 1;
+        const uint32_t ph = (uint32_t)((j >> 1) & 1);
+        if (!mbar_wait(bar(BAR_VFULL + s), ph)) { fail(ST_WAIT_VFULL); return false; }
+        for (int i = 0; i < Q_TILES; ++i) {
+          if (j >= nt[i]) continue;
+          if (!mbar_wait(bar(BAR_PREADY + 2 * i + (j & 1)), ph)) { fail(ST_WAIT_PREADY); return false; }
+          tc_fence_after_sync();
+          const uint32_t d = tmem_base + 256u + (uint32_t)(i * DV);
+          const uint32_t a = tmem_base + (uint32_t)((2 * i + (j & 1)) * BLOCK_N);
+#pragma unroll
+          for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
+            const uint64_t bd = make_smem_desc(v_smem + s * C::V_STAGE_BYTES + kk * 16 * 128, C::V_CHUNK_BYTES, 1024);
+            mma_ts(d, a + (uint32_t)(kk * 8), bd, IDESC_PV, (j > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(bar(BAR_PVDONE + 2 * i + (j & 1)));
+        }
+        tc_commit(bar(BAR_VEMPTY + s));
+        return true;
+      };
+
+      if (ok && n_tiles > 0) ok = issue_qk(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) ok = issue_qk(j + 1);
+        if (ok) ok = issue_pv(j);
+      }
+      // every MMA, and with it every barrier arrival they trigger, has landed before the CTA exits
+      tc_commit(bar(BAR_MMADONE));
+      if (!mbar_wait(bar(BAR_MMADONE), 0)) fail(ST_WAIT_MMADONE);
+    }
+    __syncwarp();
+  } else if (warp >= 4 && warp < 12) {
+    // ===================== softmax warpgroups =====================
+    const int i = (warp - 4) >> 2;
+    const int tg = tid - 128 - i * BLOCK_M;
+    const int ntile = nt[i];
+    if (ntile > 0) {
+      if constexpr (HAS_XFORM) {
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+          const int r0 = m0 + i * BLOCK_M + half * 64;
+          build_slab<DC, DR, MODE>(p, q_smem + i * C::Q_TILE_BYTES + half * 64 * 128, C::Q_CHUNK_BYTES, p.q, p.qr, b,
+                                   h, r0, p.Sq, p.q_pos0 + r0, false, freq_s, delta_s, tg);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(BAR_QFULL + i));
+      }
+      const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+      const int row = m0 + i * BLOCK_M + tg;
+      const int row_lim = row + p.causal_off;  // last visible key
+      const float c2 = p.scale * 1.4426950408889634f;
+      float slope2 = 0.f;
+      if constexpr (ALIBI) slope2 = p.slopes[h] * 1.4426950408889634f;
+      float m_used = -INFINITY, l_sum = 0.f;
+      bool ok = true;
+
+#pragma unroll 1
+      for (int j = 0; j < ntile; ++j) {
+        const int bsel = 2 * i + (j & 1);
+        const uint32_t ph = (uint32_t)((j >> 1) & 1);
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_SFULL + bsel), ph));
+        if (!ok) { fail(ST_WAIT_SFULL); break; }
+        tc_fence_after_sync();
+        const uint32_t s_addr = tmem_base + lane_sel + (uint32_t)(bsel * BLOCK_N);
+        uint32_t sr[2][32];
+        tmem_ld32(s_addr, sr[0]);
+        tmem_ld32(s_addr + 32, sr[1]);
+        tmem_wait_ld();
+
+        float t[64];
+#pragma unroll
+        for (int c = 0; c < 64; ++c) t[c] = __uint_as_float(sr[c >> 5][c & 31]);
+        const int key0 = j * BLOCK_N;
+        if constexpr (ALIBI) {
+          // logit (log2 units) = s * c2 - slope2 * (row_lim - key)
+          const float base = slope2 * (float)(key0 - row_lim);
+#pragma unroll
+          for (int c = 0; c < 64; ++c) t[c] = fmaf(t[c], c2, fmaf((float)c, slope2, base));
+        }
+        const bool need_mask = (key0 + BLOCK_N - 1 > m0 + i * BLOCK_M + p.causal_off) || (key0 + BLOCK_N > p.Sk);
+        if (need_mask) {
+#pragma unroll
+          for (int c = 0; c < 64; ++c)
+            if (key0 + c > row_lim || key0 + c >= p.Sk) t[c] = -INFINITY;
+        }
+        float mx0 = t[0], mx1 = t[1], mx2 = t[2], mx3 = t[3];
+#pragma unroll
+        for (int c = 4; c < 64; c += 4) {
+          mx0 = fmaxf(mx0, t[c]);
+          mx1 = fmaxf(mx1, t[c + 1]);
+          mx2 = fmaxf(mx2, t[c + 2]);
+          mx3 = fmaxf(mx3, t[c + 3]);
+        }
+        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        const float kf = ALIBI ? 1.0f : c2;  // t is already in log2 units with ALiBi
+        // lazy rescale: move the reference maximum only when it grows by more than 2^8
+        const bool need = (mx - m_used) * kf > 8.0f;
+        if (__any_sync(0xffffffffu, need)) {
+          const float alpha = need ? ex2_approx((m_used - mx) * kf) : 1.0f;
+          if (j > 0) {
+            const int pb = 2 * i + ((j - 1) & 1);
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_PVDONE + pb), (uint32_t)(((j - 1) >> 1) & 1)));
+            if (!ok) { fail(ST_WAIT_PVDONE); break; }
+            tc_fence_after_sync();
+            const uint32_t o_addr = tmem_base + lane_sel + 256u + (uint32_t)(i * DV);
+#pragma unroll
+            for (int cb = 0; cb < DV / 32; ++cb) {
+              uint32_t orow[32];
+              tmem_ld32(o_addr + cb * 32, orow);
+              tmem_wait_ld();
+#pragma unroll
+              for (int c = 0; c < 32; ++c) orow[c] = __float_as_uint(__uint_as_float(orow[c]) * alpha);
+              tmem_st32(o_addr + cb * 32, orow);
+            }
+            tmem_wait_st();
+          }
+          l_sum *= alpha;
+          if (need) m_used = mx;
+        }
+        const float neg_m = -m_used * kf;
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        uint32_t pk[32];
+#pragma unroll
+        for (int c = 0; c < 64; c += 4) {
+          const float p0 = ex2_approx(fmaf(t[c], kf, neg_m));
+          const float p1 = ex2_approx(fmaf(t[c + 1], kf, neg_m));
+          const float p2 = ex2_approx(fmaf(t[c + 2], kf, neg_m));
+          const float p3 = ex2_approx(fmaf(t[c + 3], kf, neg_m));
+          a0 += p0; a1 += p1; a2 += p2; a3 += p3;
+          pk[c >> 1] = pack_bf16x2(p0, p1);
+          pk[(c >> 1) + 1] = pack_bf16x2(p2, p3);
+        }
+        l_sum += (a0 + a1) + (a2 + a3);
+        tmem_st32(s_addr, pk);  // P over the first 32 columns of this S buffer
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(bar(BAR_PREADY + bsel));
+      }
+
+      if (ok) {
+        const int lb = 2 * i + ((ntile - 1) & 1);
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_PVDONE + lb), (uint32_t)(((ntile - 1) >> 1) & 1)));
+        if (!ok) fail(ST_WAIT_PVDONE);
+      }
+      if (ok) {
+        tc_fence_after_sync();
+        const float inv_l = 1.0f / l_sum;
+        const uint32_t o_addr = tmem_base + lane_sel + 256u + (uint32_t)(i * DV);
+        char* dst = reinterpret_cast<char*>(const_cast<void*>(p.out.ptr)) +
+                    2 * ((long long)b * p.out.sb + (long long)h * p.out.sh + (long long)row * p.out.ss);
+#pragma unroll
+        for (int cb = 0; cb < DV / 32; ++cb) {
+          uint32_t orow[32];
+          tmem_ld32(o_addr + cb * 32, orow);
+          tmem_wait_ld();
+          if (row < p.Sq) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(orow[v * 8 + 0]) * inv_l, __uint_as_float(orow[v * 8 + 1]) * inv_l);
+              o.y = pack_bf16x2(__uint_as_float(orow[v * 8 + 2]) * inv_l, __uint_as_float(orow[v * 8 + 3]) * inv_l);
+              o.z = pack_bf16x2(__uint_as_float(orow[v * 8 + 4]) * inv_l, __uint_as_float(orow[v * 8 + 5]) * inv_l);
+              o.w = pack_bf16x2(__uint_as_float(orow[v * 8 + 6]) * inv_l, __uint_as_float(orow[v * 8 + 7]) * inv_l);
+              *reinterpret_cast<uint4*>(dst + (cb * 32 + v * 8) * 2) = o;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp >= 12) {
+    // ===================== K-tile positional transform =====================
+    if constexpr (HAS_XFORM) {
+      const int tg = tid - 384;
+#pragma unroll 1
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j & 1;
+        const bool ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_KEMPTY + s), (uint32_t)(((j >> 1) & 1) ^ 1)));
+        if (!ok) { fail(ST_WAIT_KEMPTY); break; }
+        build_slab<DC, DR, MODE>(p, k_smem + s * C::K_STAGE_BYTES, C::K_CHUNK_BYTES, p.k, p.kr, b, hk, j * BLOCK_N,
+                                 p.Sk, p.k_pos0 + j * BLOCK_N, true, freq_s, delta_s, tg);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(BAR_KFULL + s));
+      }
+    }
+  }
+
+  // common exit: after a failed wait give copies in flight time to land before the
+  // shared memory and TMEM are released
+  if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 200000) {
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- host side --------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// [B, H, S, d] bf16 tensor viewed as a 4-D TMA tensor (d, S, H, B) with a (64 x rows) box,
+// 128-byte swizzle, zero fill outside the tensor.
+bool encode_map(CUtensorMap* map, const TensorRef& t, int d, int S, int H, int B, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)t.ss * 2, (cuuint64_t)t.sh * 2, (cuuint64_t)t.sb * 2};
+  // a size-1 dimension may carry any stride; TMA still wants a multiple of 16 bytes
+  for (int i = 0; i < 3; ++i)
+    if (strides[i] == 0 || strides[i] % 16 != 0) strides[i] = (cuuint64_t)d * 2;
+  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(t.ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+template <int DC, int DR, int DV, int MODE, bool ALIBI>
+int launch_instance(const KParams& p, cudaStream_t stream) {
+  using C = Cfg<DC, DR, DV>;
+  auto kern = pe_attn_tc_kernel<DC, DR, DV, MODE, ALIBI>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (e != cudaSuccess) {
+      set_error("cudaFuncSetAttribute(%d bytes) failed: %s", C::SMEM_BYTES, cudaGetErrorString(e));
+      return PE_ATTN_ERR_LAUNCH;
+    }
+    configured = true;
+  }
+  CUtensorMap tmQ, tmK, tmV;
+  memset(&tmQ, 0, sizeof(tmQ));
+  memset(&tmK, 0, sizeof(tmK));
+  if (!encode_map(&tmV, p.v, DV, p.Sk, p.Hkv, p.B, BLOCK_N)) {
+    set_error("cuTensorMapEncodeTiled failed for v");
+    return PE_ATTN_ERR_LAUNCH;
+  }
+  if constexpr (MODE == MODE_PLAIN || (MODE == MODE_POPE && DC > 0)) {
+    if (!encode_map(&tmQ, p.q, DC, p.Sq, p.H, p.B, BLOCK_M) || !encode_map(&tmK, p.k, DC, p.Sk, p.Hkv, p.B, BLOCK_N)) {
+      set_error("cuTensorMapEncodeTiled failed for q / k");
+      return PE_ATTN_ERR_LAUNCH;
+    }
+  }
+  const int n_qblk = (p.Sq + Q_TILES * BLOCK_M - 1) / (Q_TILES * BLOCK_M);
+  dim3 grid(n_qblk, p.H, p.B), block(NTHREADS);
+  kern<<<grid, block, C::SMEM_BYTES, stream>>>(p, tmQ, tmK, tmV);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("tcgen05 kernel launch failed: %s", cudaGetErrorString(e));
+    return PE_ATTN_ERR_LAUNCH;
+  }
+  return PE_ATTN_OK;
+}
+
+template <int DC, int DR, int DV, int MODE>
+int launch_alibi(const KParams& p, cudaStream_t stream) {
+  if (p.variant == PE_ATTN_ALIBI) return launch_instance<DC, DR, DV, MODE, true>(p, stream);
+  return launch_instance<DC, DR, DV, MODE, false>(p, stream);
+}
+
+}  // namespace
+
+bool tc_supports(const KParams& p) {
+  if (p.variant == PE_ATTN_POPE) {
+    return (p.d_c == 64 && p.d_r == 32 && p.d_v == 64) || (p.d_c == 128 && p.d_r == 64 && p.d_v == 128) ||
+           (p.d_c == 128 && p.d_r == 32 && p.d_v == 128) || (p.d_c == 0 && p.d_r == 32 && p.d_v == 64) ||
+           (p.d_c == 0 && p.d_r == 64 && p.d_v == 128);
+  }
+  return (p.d_c == 64 && p.d_v == 64) || (p.d_c == 128 && p.d_v == 128);
+}
+
+int launch_tc(const KParams& p, cudaStream_t stream) {
+  if (p.variant == PE_ATTN_POPE) {
+    if (p.d_c == 64 && p.d_r == 32) return launch_instance<64, 32, 64, MODE_POPE, false>(p, stream);
+    if (p.d_c == 128 && p.d_r == 64) return launch_instance<128, 64, 128, MODE_POPE, false>(p, stream);
+    if (p.d_c == 128 && p.d_r == 32) return launch_instance<128, 32, 128, MODE_POPE, false>(p, stream);
+    if (p.d_c == 0 && p.d_r == 32) return launch_instance<0, 32, 64, MODE_POPE, false>(p, stream);
+    return launch_instance<0, 64, 128, MODE_POPE, false>(p, stream);
+  }
+  const bool xform = p.variant == PE_ATTN_ROTARY || (p.flags & PE_ATTN_QK_NORM);
+  if (p.d_c == 64) {
+    return xform ? launch_alibi<64, 0, 64, MODE_XFORM>(p, stream) : launch_alibi<64, 0, 64, MODE_PLAIN>(p, stream);
+  }
+  return xform ? launch_alibi<128, 0, 128, MODE_XFORM>(p, stream) : launch_alibi<128, 0, 128, MODE_PLAIN>(p, stream);
+}
+
+}  // namespace pe_attn

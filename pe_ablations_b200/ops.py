@@ -1,0 +1,223 @@
+"""Python entry point of the fused PE-attention forward (calls the C ABI).
+
+``pe_attention`` takes the projected tensors exactly as the reference's
+attention modules hold them before their positional transform -- layout
+[B, S, H, d] (or [B, H, S, d] with ``layout="bhsd"``), any strides with a
+contiguous last dimension -- and returns the attention output in the same
+layout.  It replaces, per variant, the eager code listed in include/pe_attn.h.
+
+There is no CPU or eager fallback: CPU tensors, a mask, or tensors that need
+gradients raise.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from . import _lib
+
+_VARIANTS = {"nope": _lib.NOPE, "rotary": _lib.ROTARY, "alibi": _lib.ALIBI, "pope": _lib.POPE}
+_status_words: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def device_status(device: torch.device) -> torch.Tensor:
+    """The int32 word (one per device and stream) the tensor-core kernel reports expired waits into."""
+    dev = torch.device(device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    key = (idx, torch.cuda.current_stream(idx).cuda_stream)
+    w = _status_words.get(key)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status_words[key] = w
+    return w
+
+
+def check_device_status(device: torch.device | None = None) -> None:
+    """Synchronise and raise if any kernel on ``device`` reported an expired wait."""
+    for (idx, _), w in list(_status_words.items()):
+        if device is not None and torch.device(device).index not in (None, idx):
+            continue
+        code = int(w.item())
+        if code != 0:
+            w.zero_()
+            raise RuntimeError(f"pe_attn tensor-core kernel reported expired waits, code 0x{code:x}; output invalid")
+
+
+def _strides(t: torch.Tensor, layout: str) -> tuple[int, int, int]:
+    if t.stride(-1) != 1:
+        raise ValueError("the last dimension must be contiguous")
+    sb, s1, s2 = t.stride(0), t.stride(1), t.stride(2)
+    return (sb, s2, s1) if layout == "bshd" else (sb, s1, s2)
+
+
+def _dims(t: torch.Tensor, layout: str) -> tuple[int, int, int, int]:
+    B, a, b, d = t.shape
+    return (B, b, a, d) if layout == "bshd" else (B, a, b, d)  # B, H, S, d
+
+
+def _f32(t: torch.Tensor | None, device) -> torch.Tensor | None:
+    if t is None:
+        return None
+    return t.detach().to(device=device, dtype=torch.float32).contiguous()
+
+
+def pe_attention(
+    variant: str,
+    q: torch.Tensor | None,
+    k: torch.Tensor | None,
+    v: torch.Tensor,
+    *,
+    q_r: torch.Tensor | None = None,
+    k_r: torch.Tensor | None = None,
+    layout: str = "bshd",
+    start_pos: int = 0,
+    k_start_pos: int | None = None,
+    scale: float | None = None,
+    qk_norm: bool = False,
+    qk_norm_eps: float = 1e-6,
+    rotary_table: torch.Tensor | None = None,
+    table_pos0: int = 0,
+    mscale: float = 1.0,
+    alibi_slopes: torch.Tensor | None = None,
+    freqs: torch.Tensor | None = None,
+    delta: torch.Tensor | None = None,
+    fourier_coeffs: torch.Tensor | None = None,
+    floor_freq: float = 0.0,
+    normalize_coeffs: bool = True,
+    ceil_freq: float | None = None,
+    out: torch.Tensor | None = None,
+    mask: torch.Tensor | None = None,
+    simt_check: bool = False,
+) -> torch.Tensor:
+    """Fused causal attention forward with the positional transform applied in-kernel.
+
+    variant: ``nope`` | ``rotary`` | ``alibi`` | ``pope``.
+      rotary: ``rotary_table`` is [rows, d/2, 2] fp32 (cos, sin), row i = position
+              ``table_pos0 + i`` (``torch.view_as_real`` of the reference's ``freqs_cis``).
+      alibi:  ``alibi_slopes`` is [H].
+      pope:   ``q``/``k`` are the content halves (or None), ``q_r``/``k_r`` the position
+              halves before softplus; ``freqs`` [d_r] effective frequencies, or base
+              frequencies together with ``fourier_coeffs`` [d_r, D_f] (the FoPE mix and the
+              ``floor_freq`` clip then run inside the kernel); ``delta`` [d_r] raw phase bias.
+    """
+    if mask is not None:
+        raise NotImplementedError("pe_attention is causal-only: an explicit mask is not supported (no fallback)")
+    if variant not in _VARIANTS:
+        raise ValueError(f"unknown variant {variant!r}")
+    if layout not in ("bshd", "bhsd"):
+        raise ValueError("layout must be 'bshd' or 'bhsd'")
+    ref = v
+    if not ref.is_cuda:
+        raise RuntimeError("pe_attention needs CUDA tensors: there is no CPU path")
+    for t in (q, k, v, q_r, k_r):
+        if t is not None and t.requires_grad and torch.is_grad_enabled():
+            raise RuntimeError("pe_attention is forward-only: call it under torch.no_grad()")
+    if ref.dtype == torch.bfloat16:
+        dtype = _lib.BF16
+    elif ref.dtype == torch.float32:
+        dtype = _lib.FP32
+    else:
+        raise TypeError(f"unsupported dtype {ref.dtype}")
+    for t in (q, k, q_r, k_r):
+        if t is not None and (t.dtype != ref.dtype or t.device != ref.device):
+            raise TypeError("all tensors must share dtype and device")
+
+    a = _lib.PeAttnArgs()
+    a.struct_size = C.sizeof(_lib.PeAttnArgs)
+    a.variant = _VARIANTS[variant]
+    a.dtype = dtype
+    flags = 0
+    B, Hkv, Sk, d_v = _dims(v, layout)
+    qq = q if q is not None else q_r
+    if qq is None:
+        raise ValueError("q or q_r is required")
+    _, H, Sq, _ = _dims(qq, layout)
+    a.B, a.H, a.Hkv, a.Sq, a.Sk = B, H, Hkv, Sq, Sk
+    a.d_c = q.shape[-1] if q is not None else 0
+    a.d_r = q_r.shape[-1] if q_r is not None else 0
+    a.d_v = d_v
+    a.q_pos0 = int(start_pos)
+    a.k_pos0 = int(start_pos if k_start_pos is None else k_start_pos)
+    d_qk = a.d_c + 2 * a.d_r
+    a.scale = float(scale) if scale is not None else d_qk ** -0.5
+    a.qk_norm_eps = float(qk_norm_eps)
+    a.mscale = float(mscale)
+    if qk_norm:
+        flags |= _lib.QK_NORM
+
+    if out is None:
+        shape = (B, Sq, H, d_v) if layout == "bshd" else (B, H, Sq, d_v)
+        out = torch.empty(shape, dtype=ref.dtype, device=ref.device)
+    keep = [out]
+
+    def bind(name, sname, t):
+        if t is None:
+            return
+        setattr(a, name, t.data_ptr())
+        getattr(a, sname)[:] = _strides(t, layout)
+
+    bind("q", "q_stride", q)
+    bind("k", "k_stride", k)
+    bind("v", "v_stride", v)
+    bind("out", "out_stride", out)
+    bind("q_r", "qr_stride", q_r)
+    bind("k_r", "kr_stride", k_r)
+
+    dev = ref.device
+    if variant == "rotary":
+        if rotary_table is None:
+            raise ValueError("rotary needs rotary_table")
+        tab = rotary_table
+        if tab.is_complex():
+            tab = torch.view_as_real(tab)
+        tab = _f32(tab, dev)
+        keep.append(tab)
+        a.rotary_table = tab.data_ptr()
+        a.table_pos0 = int(table_pos0)
+        a.table_rows = tab.shape[0]
+    if variant == "alibi":
+        sl = _f32(alibi_slopes.reshape(-1), dev)
+        keep.append(sl)
+        a.alibi_slopes = sl.data_ptr()
+    if variant == "pope":
+        fr = _f32(freqs, dev)
+        keep.append(fr)
+        a.freqs = fr.data_ptr()
+        if delta is not None:
+            dl = _f32(delta, dev)
+            keep.append(dl)
+            a.delta = dl.data_ptr()
+        if fourier_coeffs is not None:
+            co = _f32(fourier_coeffs, dev)
+            keep.append(co)
+            a.fourier_coeffs = co.data_ptr()
+            a.n_fourier = co.shape[1]
+            flags |= _lib.FOURIER_MIX
+            if normalize_coeffs:
+                flags |= _lib.FOURIER_NORMALIZE
+            a.floor_freq = float(floor_freq)
+            if ceil_freq is not None:
+                flags |= _lib.FOURIER_CEILING
+                a.ceil_freq = float(ceil_freq)
+    if simt_check:
+        flags |= _lib.SIMT_CHECK
+    a.flags = flags
+    with torch.cuda.device(dev):
+        if dtype == _lib.BF16 and not simt_check:
+            a.device_status = device_status(dev).data_ptr()
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        rc = _lib.lib.pe_attn_forward(C.byref(a), C.c_void_p(stream))
+    if rc != 0:
+        raise _lib.PeAttnError(rc)
+    # parameter tensors created here stay referenced until the stream has used them
+    for t in keep[1:]:
+        t.record_stream(torch.cuda.current_stream(dev))
+    return out
+
+
+def attention_flops(B: int, H: int, S: int, d_qk: int, d_v: int) -> float:
+    """Algorithmic causal attention FLOPs (the benchmark's convention): B H S^2 (d_qk + d_v)."""
+    return float(B) * H * S * S * (d_qk + d_v)
