@@ -1,0 +1,306 @@
+#!/usr/bin/env python
+"""Benchmark of the fused PE-attention forward on B200.
+
+Workload: the combined FoPE+PoPE causal attention forward of the benchmark
+configuration list -- bf16, batch 2, 16 heads, sequence 16384, content dim 128, position
+dim 64 (d_qk = 256), value dim 128; Q, K, V ~ N(0, 1) seeded, key phase bias ~ U(-pi, pi),
+16 Fourier terms (sigma 0.3), floor 2 pi / 16384.  Heads are sharded over the N GPUs of one
+box (16 / N heads each, both batch items), no collective on the data path.
+
+A step is one forward over the whole workload.  ``value`` is algorithmic TFLOP/s,
+B H S^2 (d_qk + d_v) per step (3.2985 TFLOP), over the slowest rank's device time with the
+inputs resident in HBM; ``e2e`` is the same through ``pe_attention`` with pinned host
+buffers, host-to-device copies of all five inputs and a device-to-host copy of the output
+inside the timed region.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+  python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+
+``--impl reference`` times the reference's eager data flow (CPU port under oracle/) on the
+host cores, on a bounded slice of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+B, H, S, D_C, D_R, D_V = 2, 16, 16384, 128, 64, 128
+N_FOURIER, SIGMA = 16, 0.3
+FLOPS_PER_STEP = float(B) * H * S * S * (D_C + 2 * D_R + D_V)
+METRIC = "fused PE-attention TFLOP/s (FoPE+PoPE causal forward, bf16, B2 H16 S16384 d_qk256 d_v128)"
+WORKLOAD = "config 4: FoPE+PoPE causal attention forward, bf16, B2 H16 S16384 d_c128 d_r64 d_v128"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the tcgen05 kernel on this
+# workload, from the ncu capture summarised under profiles/ (None until captured)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+FALLBACK_BF16_TFLOPS = 1590.0
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured (MEASURED_PEAKS.json bf16_tflops, burst)"
+    except Exception:
+        return FALLBACK_BF16_TFLOPS, "fallback (1.59 PFLOP/s)"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        # the idle samples before and after the kernels would drag the median down
+        busy = [x for x in sm if x >= 0.5 * max(sm)] if sm else []
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_inputs(torch, heads: int, seed: int, pinned: bool):
+    """Seeded N(0,1) inputs for ``heads`` heads of the workload, on the host (bf16)."""
+    g = torch.Generator().manual_seed(seed)
+
+    def mk(d):
+        t = torch.randn(B, S, heads, d, generator=g, dtype=torch.float32).to(torch.bfloat16)
+        return t.pin_memory() if pinned else t
+
+    host = dict(q=mk(D_C), k=mk(D_C), q_r=mk(D_R), k_r=mk(D_R), v=mk(D_V))
+    gp = torch.Generator().manual_seed(12345)  # positional parameters are replicated, not sharded
+    params = dict(
+        delta=(torch.rand(D_R, generator=gp) * 2 - 1) * math.pi,
+        fourier_coeffs=torch.randn(D_R, N_FOURIER, generator=gp) * SIGMA,
+        freqs=10000.0 ** (-(torch.arange(0, D_R, dtype=torch.float32) / D_R)),
+        floor_freq=2 * math.pi / S,
+    )
+    return host, params
+
+
+def run_ours(args) -> dict:
+    import torch
+    import torch.distributed as dist
+
+    import pe_ablations_b200 as P  # fails loudly if the CUDA library is missing
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N > 1")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if H % world != 0:
+        raise SystemExit(f"{H} heads do not shard over {world} GPUs")
+    heads = H // world
+
+    host, params = make_inputs(torch, heads, seed=1000 + rank, pinned=True)
+    dparams = {k: (v.to(dev) if hasattr(v, "to") else v) for k, v in params.items()}
+    dten = {k: v.to(dev) for k, v in host.items()}
+    out = torch.empty(B, S, heads, D_V, dtype=torch.bfloat16, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > 126 MB of L2
+
+    def step(t):
+        P.pe_attention("pope", t["q"], t["k"], t["v"], q_r=t["q_r"], k_r=t["k_r"], out=out, **dparams)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident timing -------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        flush.zero_()
+        step(dten)
+    barrier()
+    P.check_device_status()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    barrier()
+    for e0, e1 in ev:
+        flush.zero_()          # evict the previous step's tensors from L2
+        e0.record()
+        step(dten)
+        e1.record()
+    barrier()
+    P.check_device_status()
+    step_ms = [e0.elapsed_time(e1) for e0, e1 in ev]
+    local_ms = sum(step_ms)
+    total_ms = max_over_ranks(local_ms)
+    # keep the GPU busy a little longer so that nvidia-smi gets samples under load
+    t_end = time.time() + 1.0
+    while time.time() < t_end:
+        step(dten)
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_per_step = total_ms / args.steps
+    value = FLOPS_PER_STEP / (ms_per_step * 1e-3) / 1e12
+    kernel_ms = statistics.mean(step_ms)            # one kernel launch per step on this rank
+    kernel_tflops = (FLOPS_PER_STEP / world) / (kernel_ms * 1e-3) / 1e12
+
+    # ---- end-to-end: host buffers in, host buffer out -----------------------------------
+    stage = {k: torch.empty_like(v, device=dev) for k, v in host.items()}
+    out_host = torch.empty(B, S, heads, D_V, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        for k in stage:
+            stage[k].copy_(host[k], non_blocking=True)
+        step(stage)
+        out_host.copy_(out, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_steps = min(args.steps, 10)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
+    h2d = sum(v.numel() * v.element_size() for v in host.values())
+    d2h = out_host.numel() * out_host.element_size()
+
+    peak, peak_src = measured_peak()
+    line = {
+        "metric": METRIC, "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "parallelism": f"heads sharded over {world} GPU(s), {heads} heads each",
+                   "l2": "flushed between steps by writing a 256 MiB buffer",
+                   "flops_per_step": FLOPS_PER_STEP, "flops_convention": "B*H*S^2*(d_qk+d_v), causal"},
+        "e2e": {"value": round(FLOPS_PER_STEP / (e2e_ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+                "ms_per_step": round(e2e_ms, 3), "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world},
+        "gpu_launches": args.steps,
+        "clocks": clocks,
+        "roofline": {"bound": "tensor", "kernel": "pe_attn_tc_kernel<128,64,128,POPE>",
+                     "achieved": round(kernel_tflops, 2), "peak": peak, "unit": "TFLOP/s",
+                     "frac": round(kernel_tflops / peak, 4), "peak_source": peak_src,
+                     "frac_of_nominal_2250": round(kernel_tflops / 2250.0, 4),
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                     "launch_ms": round(kernel_ms, 4)},
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(budget_s=20.0)
+    if world > 1:
+        dist.destroy_process_group()
+    return line if rank == 0 else None
+
+
+def cpu_baseline(budget_s: float) -> dict:
+    """The reference's eager data flow on the host cores, on a bounded slice of the workload."""
+    from oracle.cpu_baseline import time_cfg4_sample
+
+    probe = time_cfg4_sample(2048, 1)
+    est_16k = probe["seconds"] * 64 * 1.5
+    seq = 16384 if est_16k <= budget_s else (8192 if est_16k / 4 <= budget_s else 4096)
+    r = time_cfg4_sample(seq, 1)
+    return {"value": round(r["flops"] / r["seconds"] / 1e12, 5), "unit": "TFLOP/s", "cores": r["threads"],
+            "kind": "port", "seconds": round(r["seconds"], 3),
+            "sample": f"1 of the {B * H} (batch, head) slices at sequence {seq} (eager fp32 transform + bf16 SDPA on CPU)"}
+
+
+def run_reference(args) -> dict | None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return None
+    from oracle.cpu_baseline import time_cfg4_sample
+
+    probe = time_cfg4_sample(2048, 1)
+    n = args.steps + args.warmup
+    est_16k = probe["seconds"] * 64 * 1.5
+    seq = 16384
+    while seq > 2048 and est_16k * (seq / 16384) ** 2 * n > 150.0:
+        seq //= 2
+    for _ in range(args.warmup):
+        time_cfg4_sample(seq, 1)
+    t = [time_cfg4_sample(seq, 1) for _ in range(args.steps)]
+    sec = sum(x["seconds"] for x in t) / len(t)
+    val = t[0]["flops"] / sec / 1e12
+    sample = f"per step: 1 of the {B * H} (batch, head) slices at sequence {seq}, reference eager data flow on CPU"
+    return {
+        "impl": "reference", "metric": METRIC, "value": round(val, 5), "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 2), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": round(val, 5), "unit": "TFLOP/s", "cores": t[0]["threads"], "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": round(val, 5), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    line = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

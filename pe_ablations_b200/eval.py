@@ -1,0 +1,80 @@
+"""Sharded long-context evaluation: batch-sharded perplexity, head-sharded attention.
+
+The eval batch (independent sequences) and the attention heads (independent (batch, head)
+problems) partition across the GPUs of one box with no activation exchange.  The only
+collective is one all-reduce (SUM) of two scalars per evaluation -- the summed token NLL and
+the token count -- issued on the compute stream through ``torch.distributed`` (NCCL over
+NVLink on GPUs, gloo on CPU for tests).
+
+The reference evaluates one sequence at a time on one GPU
+(scripts/evaluate_ppl_degradation.py:72-111: exp(sum of per-window mean losses weighted by
+their token counts / total tokens)); ``perplexity`` computes the same quantity from NLL sums.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+
+
+def shard_range(n_items: int, world: int, rank: int) -> range:
+    """Contiguous, balanced slice of ``n_items`` for ``rank`` (first ``n % world`` ranks get one more)."""
+    if not (0 <= rank < world):
+        raise ValueError(f"rank {rank} outside world {world}")
+    base, extra = divmod(n_items, world)
+    start = rank * base + min(rank, extra)
+    return range(start, start + base + (1 if rank < extra else 0))
+
+
+def shard_heads(num_heads: int, num_kv_heads: int, world: int, rank: int) -> tuple[range, range]:
+    """(query heads, key/value heads) owned by ``rank``: whole GQA groups, so no K/V is shared."""
+    if num_kv_heads % world != 0:
+        raise ValueError(f"num_kv_heads={num_kv_heads} must be divisible by world={world} to shard by heads")
+    g = num_heads // num_kv_heads
+    kv = shard_range(num_kv_heads, world, rank)
+    return range(kv.start * g, kv.stop * g), kv
+
+
+def reduce_loss_sums(nll_sum: torch.Tensor, count: torch.Tensor, group=None) -> tuple[float, float]:
+    """All-reduce (SUM) of the two scalars over ``group``; identity without a process group."""
+    buf = torch.stack([nll_sum.double().reshape(()), count.double().reshape(())])
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group)
+    nll, cnt = buf.tolist()
+    return nll, cnt
+
+
+def perplexity(nll_sum: float, count: float) -> float:
+    return math.exp(nll_sum / count) if count > 0 else float("inf")
+
+
+@torch.no_grad()
+def evaluate_shard(model, input_ids: torch.Tensor, micro_batch: int = 1, autocast_dtype=torch.bfloat16):
+    """NLL sum and token count of this rank's sequences [n, S] (device tensors)."""
+    dev = input_ids.device
+    nll = torch.zeros((), dtype=torch.float64, device=dev)
+    cnt = torch.zeros((), dtype=torch.float64, device=dev)
+    for i in range(0, input_ids.shape[0], micro_batch):
+        ids = input_ids[i:i + micro_batch]
+        if autocast_dtype is not None and dev.type == "cuda":
+            with torch.autocast("cuda", dtype=autocast_dtype):
+                a, c = model.loss_sums(ids)
+        else:
+            a, c = model.loss_sums(ids)
+        nll += a.double()
+        cnt += c.double()
+    return nll, cnt
+
+
+@torch.no_grad()
+def sharded_perplexity(model, all_input_ids: torch.Tensor, rank: int, world: int, micro_batch: int = 1,
+                       autocast_dtype=torch.bfloat16, group=None) -> dict:
+    """Perplexity of ``all_input_ids`` [N, S] with sequences sharded over ``world`` ranks."""
+    mine = shard_range(all_input_ids.shape[0], world, rank)
+    ids = all_input_ids[mine.start:mine.stop].to(next(model.parameters()).device, non_blocking=True)
+    nll, cnt = evaluate_shard(model, ids, micro_batch, autocast_dtype)
+    tot_nll, tot_cnt = reduce_loss_sums(nll, cnt, group)
+    return {"nll_sum": tot_nll, "count": tot_cnt, "loss": tot_nll / max(tot_cnt, 1.0),
+            "perplexity": perplexity(tot_nll, tot_cnt), "local_sequences": len(mine)}

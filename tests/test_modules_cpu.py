@@ -1,0 +1,118 @@
+"""Host-side mirror of the reference's module interface: names, shapes, constants (CPU only)."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import golden_cases as G
+
+
+@pytest.fixture(scope="module")
+def mods(golden_dir):
+    return np.load(os.path.join(golden_dir, "modules.npz"))
+
+
+@pytest.fixture(scope="module")
+def models(golden_dir):
+    return np.load(os.path.join(golden_dir, "models.npz"))
+
+
+def build_module(spec):
+    from pe_ablations_b200 import modules as M
+    from pe_ablations_b200 import pe as P
+
+    kind = spec["kind"]
+    hd, H, Hkv, hidden, S = spec["head_dim"], spec["H"], spec["Hkv"], spec["hidden"], spec["S"]
+    if kind in ("rope", "yarn", "ntk", "nope"):
+        rope = None
+        if kind == "rope":
+            rope = P.RotaryEmbedding(hd, S, 10000.0)
+        elif kind == "ntk":
+            rope = P.NTKAwareRotaryEmbedding(hd, S, 10000.0, spec["rope_scale"])
+        elif kind == "yarn":
+            rope = P.YaRNRotaryEmbedding(hd, S, 10000.0, spec["rope_scale"], original_max_seq_len=512)
+        return M.GroupedQueryAttention(hidden, H, Hkv, hd, spec["use_qk_norm"], rope)
+    if kind == "alibi":
+        return M.ALiBiAttention(hidden, H, Hkv, hd, spec["use_qk_norm"])
+    if kind == "fpope":
+        pe = P.FoPEPoPEEmbedding(dim=spec["d_rope"], max_seq_len=S, num_fourier_terms=spec["n_fourier"],
+                                 fourier_sigma=spec["sigma"], training_length=spec["training_length"],
+                                 delta_init=spec["delta_init"])
+    else:
+        pe = P.PoPEEmbedding(dim=spec["d_rope"], max_seq_len=S, training_length=spec.get("training_length", 512),
+                             use_floor=(kind == "pope_floor"), delta_init=spec["delta_init"])
+    return M.FPoPEGroupedQueryAttention(hidden, H, Hkv, hd, spec["d_rope"], spec["use_qk_norm"], pe)
+
+
+@pytest.mark.parametrize("spec", G.MODULE_CASES, ids=lambda s: s["name"])
+def test_module_state_dict_keys_and_buffers_match_reference(mods, spec):
+    m = build_module(spec)
+    assert sorted(m.state_dict().keys()) == list(mods[f"{spec['name']}/state_keys"])
+    bufs = dict(m.named_buffers())
+    for key in mods.files:
+        if key.startswith(f"{spec['name']}/buf/"):
+            name = key.split("/buf/")[1]
+            got = bufs[name].float().reshape(-1)
+            want = torch.from_numpy(mods[key]).reshape(-1)
+            assert torch.allclose(got, want, rtol=2e-6, atol=1e-9), name
+
+
+def build_model(spec):
+    from pe_ablations_b200.model import Transformer, TransformerConfig
+
+    kw = dict(G.MODEL_BASE)
+    kw.update({k: v for k, v in spec.items() if k != "name"})
+    return Transformer(TransformerConfig(**kw)).eval()
+
+
+@pytest.mark.parametrize("spec", G.MODEL_CASES, ids=lambda s: s["name"])
+def test_model_state_dict_matches_reference(models, spec):
+    model = build_model(spec)
+    sd = model.state_dict()
+    assert sorted(sd.keys()) == list(models[f"{spec['name']}/state_keys"])
+    shapes = [",".join(map(str, sd[k].shape)) for k in sorted(sd.keys())]
+    assert shapes == list(models[f"{spec['name']}/state_shapes"])
+
+
+def test_yarn_extend_falls_back_to_plain_rope_like_the_reference():
+    from pe_ablations_b200 import pe as P
+
+    y = P.YaRNRotaryEmbedding(64, 128, 10000.0, 4.0)
+    r = P.RotaryEmbedding(64, 256, 10000.0)
+    assert not torch.allclose(y.freqs_cis, r.freqs_cis[:128])
+    y.extend_seq_len(256)
+    assert torch.allclose(torch.view_as_real(y.freqs_cis), torch.view_as_real(r.freqs_cis))
+    assert abs(y.attention_scale - (0.1 * np.log(4.0) + 1.0)) < 1e-6
+
+
+def test_pe_holders_do_not_compute():
+    from pe_ablations_b200 import pe as P
+
+    with pytest.raises(NotImplementedError):
+        P.PoPEEmbedding(8).forward_query(torch.zeros(1, 1, 1, 8))
+    with pytest.raises(NotImplementedError):
+        P.RotaryEmbedding(8, 16)(torch.zeros(1), torch.zeros(1))
+
+
+def test_modules_refuse_masks_and_cpu():
+    from pe_ablations_b200 import modules as M
+
+    m = M.GroupedQueryAttention(64, 2, 2, 32, True, None).eval()
+    with torch.no_grad():
+        with pytest.raises(NotImplementedError):
+            m(torch.zeros(1, 4, 64), mask=torch.ones(1, 1, 4, 4))
+        with pytest.raises(RuntimeError):
+            m(torch.zeros(1, 4, 64))
+
+
+def test_fope_effective_freqs_host_formula_matches_oracle():
+    from oracle import pe_attention_oracle as O
+    from pe_ablations_b200 import pe as P
+
+    torch.manual_seed(3)
+    e = P.FoPEPoPEEmbedding(dim=32, num_fourier_terms=16, fourier_sigma=0.3, training_length=128)
+    want = O.fope_effective_freqs(e.base_freqs, e.fourier_coeffs.detach(), 128)
+    assert torch.allclose(e.effective_freqs(), want, rtol=1e-6, atol=0)
+    assert (want == 0).any()  # the floor clip is active at this size
