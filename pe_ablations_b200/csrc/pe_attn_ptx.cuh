@@ -13,6 +13,18 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// One lane of a converged warp; the predicate is warp-uniform knowledge for the compiler, so
+// operands of the guarded instructions can live in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred = 0;
+  asm volatile(
+      "{\n\t.reg .b32 rx;\n\t.reg .pred px;\n\t"
+      "elect.sync rx|px, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, px;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // ---- mbarrier -------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -131,6 +143,11 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, bool b_mn_m
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
   return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
          ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Same descriptor advanced by ``bytes`` (a multiple of 16 that does not carry out of the
+// 14-bit address field): only the low word changes.
+__device__ __forceinline__ uint64_t advance_smem_desc(uint64_t desc, uint32_t bytes) {
+  return desc + (uint64_t)(bytes >> 4);
 }
 
 // ---- TMEM loads / stores: 32 lanes x 32 bit, 32 consecutive columns per thread ----------

@@ -275,7 +275,7 @@ pe_attn_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tmQ, cons
     }
     for (int i = 0; i < 4; ++i) {
       mbar_init(bar(BAR_SFULL + i), 1);
-      mbar_init(bar(BAR_PREADY + i), BLOCK_M);
+      mbar_init(bar(BAR_PREADY + i), 4);
       mbar_init(bar(BAR_PVDONE + i), 1);
     }
     mbar_init(bar(BAR_MMADONE), 1);
@@ -298,106 +298,158 @@ pe_attn_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tmQ, cons
   const uint32_t tmem_base = *tmem_slot;
   const bool run = *abort_slot == 0;
 
+  // Register budget: the producer / MMA / allocator warpgroup gives registers back, the
+  // softmax and transform warpgroups take them (4 x 128 x 56 + 12 x 128 x 152 = 64 K).
+
   const uint32_t q_smem = smem_base + C::Q_OFF;
   const uint32_t k_smem = smem_base + C::K_OFF;
   const uint32_t v_smem = smem_base + C::V_OFF;
 
+  // The role code sits inside the branch that sets its register budget, so that the
+  // budget is unambiguous along every path.
+  if (warp < 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
   if (!run) {
     // nothing to do
   } else if (warp == 0) {
     // ===================== TMA producer =====================
-    if (lane == 0) {
+    // The whole warp runs the loop (waits included); one elected lane issues the copies.
+    if (elect_one()) {
       tma_prefetch_desc(&tmV);
       if constexpr (HAS_TMA_QK) {
         tma_prefetch_desc(&tmQ);
         tma_prefetch_desc(&tmK);
-        for (int i = 0; i < Q_TILES; ++i) {
-          if (nt[i] == 0) continue;
+      }
+    }
+    if constexpr (HAS_TMA_QK) {
+      for (int i = 0; i < Q_TILES; ++i) {
+        if (nt[i] == 0) continue;
+        if (elect_one()) {
           mbar_arrive_expect_tx(bar(BAR_QFULL + i), C::NCC * C::Q_CHUNK_BYTES);
+#pragma unroll
           for (int c = 0; c < C::NCC; ++c)
             tma_load_4d(q_smem + i * C::Q_TILE_BYTES + c * C::Q_CHUNK_BYTES, &tmQ, bar(BAR_QFULL + i), c * 64,
                         m0 + i * BLOCK_M, h, b);
         }
+        __syncwarp();
       }
-      for (int j = 0; j < n_tiles; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (uint32_t)((j >> 1) & 1);
-        if constexpr (HAS_TMA_QK) {
-          if (!mbar_wait(bar(BAR_KEMPTY + s), ph ^ 1u)) { fail(ST_WAIT_KEMPTY); break; }
+    }
+#pragma unroll 1
+    for (int j = 0; j < n_tiles; ++j) {
+      const int s = j & 1;
+      const uint32_t ph = (uint32_t)((j >> 1) & 1);
+      if constexpr (HAS_TMA_QK) {
+        if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_KEMPTY + s), ph ^ 1u))) { fail(ST_WAIT_KEMPTY); break; }
+        if (elect_one()) {
           mbar_arrive_expect_tx(bar(BAR_KFULL + s), C::NCC * C::K_CHUNK_BYTES);
+#pragma unroll
           for (int c = 0; c < C::NCC; ++c)
             tma_load_4d(k_smem + s * C::K_STAGE_BYTES + c * C::K_CHUNK_BYTES, &tmK, bar(BAR_KFULL + s), c * 64,
                         j * BLOCK_N, hk, b);
         }
-        if (!mbar_wait(bar(BAR_VEMPTY + s), ph ^ 1u)) { fail(ST_WAIT_VEMPTY); break; }
+        __syncwarp();
+      }
+      if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_VEMPTY + s), ph ^ 1u))) { fail(ST_WAIT_VEMPTY); break; }
+      if (elect_one()) {
         mbar_arrive_expect_tx(bar(BAR_VFULL + s), C::V_STAGE_BYTES);
+#pragma unroll
         for (int c = 0; c < C::VCH; ++c)
           tma_load_4d(v_smem + s * C::V_STAGE_BYTES + c * C::V_CHUNK_BYTES, &tmV, bar(BAR_VFULL + s), c * 64,
                       j * BLOCK_N, hk, b);
       }
+      __syncwarp();
     }
-    __syncwarp();
   } else if (warp == 1) {
     // ===================== MMA issuer =====================
-    if (lane == 0) {
-      constexpr uint32_t IDESC_QK = make_idesc_bf16(BLOCK_M, BLOCK_N, false);
-      constexpr uint32_t IDESC_PV = make_idesc_bf16(BLOCK_M, DV, true);
-      bool ok = true;
-      for (int i = 0; i < Q_TILES && ok; ++i)
-        if (nt[i] > 0 && !mbar_wait(bar(BAR_QFULL + i), 0)) { fail(ST_WAIT_QFULL); ok = false; }
+    // The whole warp runs the loop; descriptors are warp-uniform values and one elected lane
+    // issues the tcgen05 instructions.
+    constexpr uint32_t IDESC_QK = make_idesc_bf16(BLOCK_M, BLOCK_N, false);
+    constexpr uint32_t IDESC_PV = make_idesc_bf16(BLOCK_M, DV, true);
+    const uint64_t qdesc0 = make_smem_desc(q_smem, 16, 1024);
+    const uint64_t kdesc0 = make_smem_desc(k_smem, 16, 1024);
+    const uint64_t vdesc0 = make_smem_desc(v_smem, C::V_CHUNK_BYTES, 1024);
+    bool ok = true;
+    for (int i = 0; i < Q_TILES && ok; ++i)
+      if (nt[i] > 0 && !__all_sync(0xffffffffu, mbar_wait(bar(BAR_QFULL + i), 0))) { fail(ST_WAIT_QFULL); ok = false; }
 
-      auto issue_qk = [&](int j) -> bool {
-        const int s = j & 1;
-        if (!mbar_wait(bar(BAR_KFULL + s), (uint32_t)((j >> 1) & 1))) { fail(ST_WAIT_KFULL); return false; }
-        tc_fence_after_sync();
-        for (int i = 0; i < Q_TILES; ++i) {
-          if (j >= nt[i]) continue;
-          const uint32_t d = tmem_base + (uint32_t)((2 * i + (j & 1)) * BLOCK_N);
+    auto issue_qk = [&](int j) -> bool {
+      const int s = j & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_KFULL + s), (uint32_t)((j >> 1) & 1)))) {
+        fail(ST_WAIT_KFULL);
+        return false;
+      }
+      tc_fence_after_sync();
+      if (elect_one()) {
+        const uint64_t kd = advance_smem_desc(kdesc0, (uint32_t)(s * C::K_STAGE_BYTES));
 #pragma unroll
-          for (int kk = 0; kk < C::DQK / 16; ++kk) {
-            const uint64_t ad = make_smem_desc(
-                q_smem + i * C::Q_TILE_BYTES + (kk >> 2) * C::Q_CHUNK_BYTES + (kk & 3) * 32, 16, 1024);
-            const uint64_t bd = make_smem_desc(
-                k_smem + s * C::K_STAGE_BYTES + (kk >> 2) * C::K_CHUNK_BYTES + (kk & 3) * 32, 16, 1024);
-            mma_ss(d, ad, bd, IDESC_QK, kk > 0 ? 1u : 0u);
+        for (int i = 0; i < Q_TILES; ++i) {
+          if (j < nt[i]) {
+            const uint32_t d = tmem_base + (uint32_t)((2 * i + (j & 1)) * BLOCK_N);
+            uint64_t qd = advance_smem_desc(qdesc0, (uint32_t)(i * C::Q_TILE_BYTES));
+            uint64_t kc = kd;
+#pragma unroll 1
+            for (int c = 0; c < C::NCHUNK; ++c) {
+#pragma unroll
+              for (int k4 = 0; k4 < 4; ++k4)
+                mma_ss(d, advance_smem_desc(qd, (uint32_t)(k4 * 32)), advance_smem_desc(kc, (uint32_t)(k4 * 32)),
+                       IDESC_QK, (c > 0 || k4 > 0) ? 1u : 0u);
+              qd = advance_smem_desc(qd, C::Q_CHUNK_BYTES);
+              kc = advance_smem_desc(kc, C::K_CHUNK_BYTES);
+            }
+            tc_commit(bar(BAR_SFULL + 2 * i + (j & 1)));
           }
-          tc_commit(bar(BAR_SFULL + 2 * i + (j & 1)));
         }
         tc_commit(bar(BAR_KEMPTY + s));
-        return true;
-      };
-      auto issue_pv = [&](int j) -> bool {
-        const int s = j & 1;
-        const uint32_t ph = (uint32_t)((j >> 1) & 1);
-        if (!mbar_wait(bar(BAR_VFULL + s), ph)) { fail(ST_WAIT_VFULL); return false; }
-        for (int i = 0; i < Q_TILES; ++i) {
-          if (j >= nt[i]) continue;
-          if (!mbar_wait(bar(BAR_PREADY + 2 * i + (j & 1)), ph)) { fail(ST_WAIT_PREADY); return false; }
-          tc_fence_after_sync();
-          const uint32_t d = tmem_base + 256u + (uint32_t)(i * DV);
-          const uint32_t a = tmem_base + (uint32_t)((2 * i + (j & 1)) * BLOCK_N);
-#pragma unroll
-          for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
-            const uint64_t bd = make_smem_desc(v_smem + s * C::V_STAGE_BYTES + kk * 16 * 128, C::V_CHUNK_BYTES, 1024);
-            mma_ts(d, a + (uint32_t)(kk * 8), bd, IDESC_PV, (j > 0 || kk > 0) ? 1u : 0u);
-          }
-          tc_commit(bar(BAR_PVDONE + 2 * i + (j & 1)));
-        }
-        tc_commit(bar(BAR_VEMPTY + s));
-        return true;
-      };
-
-      if (ok && n_tiles > 0) ok = issue_qk(0);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        if (j + 1 < n_tiles) ok = issue_qk(j + 1);
-        if (ok) ok = issue_pv(j);
       }
-      // every MMA, and with it every barrier arrival they trigger, has landed before the CTA exits
-      tc_commit(bar(BAR_MMADONE));
-      if (!mbar_wait(bar(BAR_MMADONE), 0)) fail(ST_WAIT_MMADONE);
+      __syncwarp();
+      return true;
+    };
+    auto issue_pv = [&](int j) -> bool {
+      const int s = j & 1;
+      const uint32_t ph = (uint32_t)((j >> 1) & 1);
+      if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_VFULL + s), ph))) { fail(ST_WAIT_VFULL); return false; }
+      const uint64_t vd = advance_smem_desc(vdesc0, (uint32_t)(s * C::V_STAGE_BYTES));
+#pragma unroll
+      for (int i = 0; i < Q_TILES; ++i) {
+        if (j < nt[i]) {
+          if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_PREADY + 2 * i + (j & 1)), ph))) {
+            fail(ST_WAIT_PREADY);
+            return false;
+          }
+          tc_fence_after_sync();
+          if (elect_one()) {
+            const uint32_t d = tmem_base + 256u + (uint32_t)(i * DV);
+            const uint32_t a = tmem_base + (uint32_t)((2 * i + (j & 1)) * BLOCK_N);
+#pragma unroll
+            for (int kk = 0; kk < BLOCK_N / 16; ++kk)
+              mma_ts(d, a + (uint32_t)(kk * 8), advance_smem_desc(vd, (uint32_t)(kk * 16 * 128)), IDESC_PV,
+                     (j > 0 || kk > 0) ? 1u : 0u);
+            tc_commit(bar(BAR_PVDONE + 2 * i + (j & 1)));
+          }
+          __syncwarp();
+        }
+      }
+      if (elect_one()) tc_commit(bar(BAR_VEMPTY + s));
+      __syncwarp();
+      return true;
+    };
+
+    if (ok && n_tiles > 0) ok = issue_qk(0);
+#pragma unroll 1
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      if (j + 1 < n_tiles) ok = issue_qk(j + 1);
+      if (ok) ok = issue_pv(j);
     }
+    // every MMA, and with it every barrier arrival they trigger, has landed before the CTA exits
+    if (elect_one()) tc_commit(bar(BAR_MMADONE));
     __syncwarp();
-  } else if (warp >= 4 && warp < 12) {
+    if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_MMADONE), 0))) fail(ST_WAIT_MMADONE);
+  }
+  } else {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
+  if (!run) {
+    // nothing to do
+  } else if (warp < 12) {
     // ===================== softmax warpgroups =====================
     const int i = (warp - 4) >> 2;
     const int tg = tid - 128 - i * BLOCK_M;
@@ -503,7 +555,8 @@ pe_attn_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tmQ, cons
         tmem_st32(s_addr, pk);  // P over the first 32 columns of this S buffer
         tmem_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(bar(BAR_PREADY + bsel));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(BAR_PREADY + bsel));
       }
 
       if (ok) {
@@ -536,10 +589,80 @@ pe_attn_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tmQ, cons
         }
       }
     }
-  } else if (warp >= 12) {
+  } else {
     // ===================== K-tile positional transform =====================
-    if constexpr (HAS_XFORM) {
-      const int tg = tid - 384;
+    const int tg = tid - 384;
+    if constexpr (MODE == MODE_POPE) {
+      // Thread (r_in, cv) owns columns [8 cv, 8 cv + 8) of rows r_in + k * RPP of every key tile.
+      // cos / sin of (row-in-tile * freq + delta) for those cells are computed once and kept in
+      // registers; per tile only the tile's base angle pos0 * freq needs the special-function
+      // unit, and each cell is rotated by it with four FMAs:
+      //   cos(pos0 w + (r w + d)) = cb Tc - sb Ts,  sin(...) = sb Tc + cb Ts.
+      constexpr int VPR = DR / 8, RPP = 128 / VPR, PASSES = BLOCK_N / RPP;
+      const int cv = tg % VPR, r_in = tg / VPR;
+      float th[8], tcs[PASSES][8], tsn[PASSES][8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        th[e] = freq_s[cv * 8 + e];
+        const float dl = delta_s[cv * 8 + e];
+#pragma unroll
+        for (int k = 0; k < PASSES; ++k)
+          sincos_reduced(__fadd_rn(__fmul_rn((float)(r_in + k * RPP), th[e]), dl), &tsn[k][e], &tcs[k][e]);
+      }
+      const char* src = reinterpret_cast<const char*>(p.kr.ptr) +
+                        2 * ((long long)b * p.kr.sb + (long long)hk * p.kr.sh + (long long)cv * 8);
+      const int col_c = DC + cv * 8, col_s = DC + DR + cv * 8;
+      const uint32_t off_c = (uint32_t)((col_c / 64) * C::K_CHUNK_BYTES), off_s = (uint32_t)((col_s / 64) * C::K_CHUNK_BYTES);
+      const int slot_c = (col_c % 64) / 8, slot_s = (col_s % 64) / 8;
+      uint4 nxt[PASSES];
+#pragma unroll
+      for (int k = 0; k < PASSES; ++k) {
+        const int grow = r_in + k * RPP;
+        nxt[k] = grow < p.Sk ? ldg_nc_v4(src + 2 * (long long)grow * p.kr.ss) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll 1
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j & 1;
+        uint4 cur[PASSES];
+#pragma unroll
+        for (int k = 0; k < PASSES; ++k) cur[k] = nxt[k];
+        if (j + 1 < n_tiles) {
+#pragma unroll
+          for (int k = 0; k < PASSES; ++k) {
+            const int grow = (j + 1) * BLOCK_N + r_in + k * RPP;
+            nxt[k] = grow < p.Sk ? ldg_nc_v4(src + 2 * (long long)grow * p.kr.ss) : make_uint4(0, 0, 0, 0);
+          }
+        }
+        float cb[8], sb[8];
+        const float pos0 = (float)(p.k_pos0 + j * BLOCK_N);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sincos_reduced(__fmul_rn(pos0, th[e]), &sb[e], &cb[e]);
+        const bool ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_KEMPTY + s), (uint32_t)(((j >> 1) & 1) ^ 1)));
+        if (!ok) { fail(ST_WAIT_KEMPTY); break; }
+        const uint32_t kb = k_smem + s * C::K_STAGE_BYTES;
+#pragma unroll
+        for (int k = 0; k < PASSES; ++k) {
+          const int r = r_in + k * RPP;
+          const uint32_t w[4] = {cur[k].x, cur[k].y, cur[k].z, cur[k].w};
+          float oc[8], os[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float x = (e & 1) ? bf16_hi(w[e >> 1]) : bf16_lo(w[e >> 1]);
+            const float mu = softplus_fast(x);
+            const float mc = mu * cb[e], ms = mu * sb[e];
+            oc[e] = mc * tcs[k][e] - ms * tsn[k][e];
+            os[e] = ms * tcs[k][e] + mc * tsn[k][e];
+          }
+          sts_v4(kb + off_c + swz(r, slot_c), make_uint4(pack_bf16x2(oc[0], oc[1]), pack_bf16x2(oc[2], oc[3]),
+                                                         pack_bf16x2(oc[4], oc[5]), pack_bf16x2(oc[6], oc[7])));
+          sts_v4(kb + off_s + swz(r, slot_s), make_uint4(pack_bf16x2(os[0], os[1]), pack_bf16x2(os[2], os[3]),
+                                                         pack_bf16x2(os[4], os[5]), pack_bf16x2(os[6], os[7])));
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(BAR_KFULL + s));
+      }
+    } else if constexpr (MODE == MODE_XFORM) {
 #pragma unroll 1
       for (int j = 0; j < n_tiles; ++j) {
         const int s = j & 1;
@@ -553,6 +676,8 @@ pe_attn_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tmQ, cons
       }
     }
   }
+
+  }  // register-budget branch
 
   // common exit: after a failed wait give copies in flight time to land before the
   // shared memory and TMEM are released
