@@ -126,7 +126,8 @@ def run_ours(args) -> dict:
     import torch
     import torch.distributed as dist
 
-    import pe_ablations_b200 as P  # fails loudly if the CUDA library is missing
+    import pe_ablations_b200 as P
+    from pe_ablations_b200 import _lib  # noqa: F401  fails loudly here if the CUDA library is missing
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

@@ -42,6 +42,7 @@
 #ifndef PE_ATTN_H_
 #define PE_ATTN_H_
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -151,6 +152,27 @@ const char* pe_attn_status_string(int status);
 
 /* Algorithmic FLOPs of one call: B * H * (causal pairs) * 2 * (d_c + 2 d_r + d_v). */
 double pe_attn_flops(const pe_attn_args* args);
+
+/* ---- perplexity evaluation: next-token cross-entropy as loss sums ------------------------
+ *
+ * Replaces, for the evaluation path, F.cross_entropy on the shifted logits
+ * (src/model/transformer.py:362-370) together with the per-window weighting
+ * total_loss += loss * n_tokens of scripts/evaluate_ppl_degradation.py:96-108: instead of a
+ * mean per call it accumulates the two sums a sharded evaluation reduces.
+ *
+ *   out[0] += sum over rows with target != ignore_index of
+ *             logsumexp(logits[r, 0:vocab]) - logits[r, target[r]]
+ *   out[1] += number of such rows
+ *
+ * logits: device [n_rows, vocab] of ``dtype`` (pe_attn_dtype), rows ``row_stride`` elements
+ * apart (16-byte aligned rows are read fastest; any element-aligned pitch works).  targets: device int64 [n_rows].  out: device
+ * double[2], accumulated (zero it before the first chunk).  scratch: device buffer of
+ * pe_ce_scratch_bytes(n_rows) bytes, 256-byte aligned, whose first 256 bytes are zero on
+ * entry (the kernel leaves them zero, so one cudaMemset after allocation is enough).
+ * Calls that share a scratch buffer must be ordered on one stream. */
+size_t pe_ce_scratch_bytes(int n_rows);
+int pe_ce_loss_sums(const void* logits, int dtype, int64_t row_stride, const int64_t* targets, int n_rows, int vocab,
+                    int ignore_index, void* scratch, double* out, void* stream);
 
 #ifdef __cplusplus
 }

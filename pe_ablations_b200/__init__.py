@@ -1,12 +1,20 @@
 """B200-native fused positional-encoding attention (sm_100a) behind the reference's module API.
 
-``ops.pe_attention`` is the functional entry point over the C ABI in
-``include/pe_attn.h``; ``modules`` holds drop-in replacements for the
-reference's three attention classes.  Importing the package loads the in-tree
-CUDA library and fails loudly if it has not been built.
+``pe_attention`` / ``ce_loss_sums`` are the functional entry points over the C ABI in
+``include/pe_attn.h``; ``modules`` holds drop-in replacements for the reference's three
+attention classes, ``model`` the Transformer host, ``eval`` the sharded evaluation.
+
+The CUDA library is loaded on first use of any of them and there is no fallback: if
+``libpe_attn.so`` has not been built (``python -m pe_ablations_b200.build_ext``) or lacks a
+symbol, that first use raises ImportError.  Only ``build_ext`` can be imported without it.
 """
 
-from . import _lib  # noqa: F401  (raises if the CUDA library is missing)
-from .ops import attention_flops, check_device_status, pe_attention  # noqa: F401
+__all__ = ["pe_attention", "ce_loss_sums", "check_device_status", "attention_flops"]
 
-__all__ = ["pe_attention", "check_device_status", "attention_flops"]
+
+def __getattr__(name):
+    if name in __all__:
+        from . import ops
+
+        return getattr(ops, name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

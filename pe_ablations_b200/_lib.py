@@ -25,6 +25,7 @@ SIMT_CHECK = 1 << 8
 EXPORTS = (
     "pe_attn_version", "pe_attn_forward", "pe_attn_validate", "pe_attn_kernel_name",
     "pe_attn_last_error", "pe_attn_status_string", "pe_attn_flops",
+    "pe_ce_scratch_bytes", "pe_ce_loss_sums",
 )
 
 
@@ -68,6 +69,11 @@ def _load() -> C.CDLL:
     lib.pe_attn_status_string.argtypes = [C.c_int]
     lib.pe_attn_flops.restype = C.c_double
     lib.pe_attn_flops.argtypes = [C.POINTER(PeAttnArgs)]
+    lib.pe_ce_scratch_bytes.restype = C.c_size_t
+    lib.pe_ce_scratch_bytes.argtypes = [C.c_int]
+    lib.pe_ce_loss_sums.restype = C.c_int
+    lib.pe_ce_loss_sums.argtypes = [C.c_void_p, C.c_int, C.c_int64, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                                    C.c_void_p, C.c_void_p, C.c_void_p]
     return lib
 
 

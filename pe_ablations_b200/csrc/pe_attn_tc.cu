@@ -240,9 +240,14 @@ pe_attn_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tmQ, cons
   auto bar = [&](int idx) -> uint32_t { return bars + 8u * (uint32_t)idx; };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // 1-D grid in longest-first order over the whole launch: block ids are handed out in
+  // increasing order, so all (batch, head) problems get their last (longest) query block
+  // first, then the second to last, and so on.
   const int n_qblk = (p.Sq + Q_TILES * BLOCK_M - 1) / (Q_TILES * BLOCK_M);
-  const int qblk = n_qblk - 1 - (int)blockIdx.x;  // longest (last) query blocks are scheduled first
-  const int h = blockIdx.y, b = blockIdx.z;
+  const int n_bh = p.B * p.H;
+  const int qblk = n_qblk - 1 - (int)(blockIdx.x / n_bh);
+  const int bh = (int)(blockIdx.x % n_bh);
+  const int h = bh % p.H, b = bh / p.H;
   const int hk = h / p.groups;
   const int m0 = qblk * Q_TILES * BLOCK_M;
 
@@ -759,7 +764,7 @@ int launch_instance(const KParams& p, cudaStream_t stream) {
     }
   }
   const int n_qblk = (p.Sq + Q_TILES * BLOCK_M - 1) / (Q_TILES * BLOCK_M);
-  dim3 grid(n_qblk, p.H, p.B), block(NTHREADS);
+  dim3 grid((unsigned)((long long)n_qblk * p.H * p.B)), block(NTHREADS);
   kern<<<grid, block, C::SMEM_BYTES, stream>>>(p, tmQ, tmK, tmV);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {

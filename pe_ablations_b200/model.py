@@ -188,23 +188,23 @@ class Transformer(nn.Module):
     @torch.no_grad()
     def loss_sums(self, input_ids: torch.Tensor, labels: torch.Tensor | None = None, start_pos: int = 0,
                   chunk_tokens: int = 8192) -> tuple[torch.Tensor, torch.Tensor]:
-        """(sum of next-token NLLs in fp32, number of scored tokens) for a batch, both on device.
+        """(sum of next-token NLLs, number of scored tokens) for a batch, both fp64 scalars on device.
 
         The language-model head and the cross-entropy run over ``chunk_tokens`` positions at a
         time, so the [tokens, vocab] logits never exist in full (1 GB per 16k sequence at the
         1B shape otherwise).  mean loss = nll_sum / count, perplexity = exp of it.
         """
+        from .ops import ce_loss_sums
+
         labels = input_ids if labels is None else labels
         h = self.hidden_states(input_ids, start_pos)[:, :-1].reshape(-1, self.config.hidden_dim)
         tgt = labels[:, 1:].reshape(-1)
-        nll = torch.zeros((), dtype=torch.float32, device=h.device)
-        cnt = torch.zeros((), dtype=torch.float32, device=h.device)
+        sums = torch.zeros(2, dtype=torch.float64, device=h.device)
         for i in range(0, h.shape[0], chunk_tokens):
-            logits = self.output(h[i:i + chunk_tokens]).float()
-            t = tgt[i:i + chunk_tokens]
-            nll += F.cross_entropy(logits, t, ignore_index=-100, reduction="sum")
-            cnt += (t != -100).sum()
-        return nll, cnt
+            # logits stay in the head's output dtype (bf16 under autocast); the loss kernel
+            # reads them once and accumulates in fp32 / fp64
+            ce_loss_sums(self.output(h[i:i + chunk_tokens]), tgt[i:i + chunk_tokens], out=sums)
+        return sums[0], sums[1]
 
     def extend_context_length(self, new_max_seq_len: int) -> None:
         for pe in (self.rope, self.fpope, self.pope):

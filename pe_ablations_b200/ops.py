@@ -218,6 +218,51 @@ def pe_attention(
     return out
 
 
+_ce_scratch: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def ce_loss_sums(logits: torch.Tensor, targets: torch.Tensor, out: torch.Tensor | None = None,
+                 ignore_index: int = -100) -> torch.Tensor:
+    """Accumulate (sum of next-token NLLs, scored-token count) of one logits chunk into ``out``.
+
+    logits: CUDA [n, vocab] bf16 or fp32 (last dim contiguous); targets: CUDA int64 [n];
+    out: CUDA float64 [2], created zeroed if None.  Reads every logit once in its stored type.
+    """
+    if not logits.is_cuda:
+        raise RuntimeError("ce_loss_sums needs CUDA tensors: there is no CPU path")
+    if logits.dim() != 2 or logits.stride(1) != 1:
+        raise ValueError("logits must be [n, vocab] with a contiguous last dimension")
+    if logits.dtype == torch.bfloat16:
+        dtype = _lib.BF16
+    elif logits.dtype == torch.float32:
+        dtype = _lib.FP32
+    else:
+        raise TypeError(f"unsupported dtype {logits.dtype}")
+    n, vocab = logits.shape
+    targets = targets.reshape(-1).to(torch.int64).contiguous()
+    if targets.numel() != n:
+        raise ValueError("targets must have one entry per row of logits")
+    dev = logits.device
+    if out is None:
+        out = torch.zeros(2, dtype=torch.float64, device=dev)
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev)
+        need = _lib.lib.pe_ce_scratch_bytes(n)
+        key = (dev.index if dev.index is not None else torch.cuda.current_device(), stream.cuda_stream)
+        scratch = _ce_scratch.get(key)
+        if scratch is None or scratch.numel() < need:
+            # zeroed once: the kernel leaves the counter word at zero after every call
+            scratch = torch.zeros(max(need, 1 << 16), dtype=torch.uint8, device=dev)
+            _ce_scratch[key] = scratch
+        rc = _lib.lib.pe_ce_loss_sums(logits.data_ptr(), dtype, logits.stride(0), targets.data_ptr(), n, vocab,
+                                      int(ignore_index), scratch.data_ptr(), out.data_ptr(),
+                                      C.c_void_p(stream.cuda_stream))
+    if rc != 0:
+        raise _lib.PeAttnError(rc)
+    targets.record_stream(stream)
+    return out
+
+
 def attention_flops(B: int, H: int, S: int, d_qk: int, d_v: int) -> float:
     """Algorithmic causal attention FLOPs (the benchmark's convention): B H S^2 (d_qk + d_v)."""
     return float(B) * H * S * S * (d_qk + d_v)

@@ -83,3 +83,25 @@ def test_bf16_autocast_model_close_to_fp32():
     la, lb = (a / c).item(), (b / c).item()
     # a sanity bound: the bf16 linears around the kernel contribute most of this difference
     assert abs(la - lb) <= 5e-3, (la, lb)
+
+
+@pytest.mark.parametrize("dtype,n,vocab", [(torch.float32, 300, 1000), (torch.bfloat16, 700, 32000),
+                                           (torch.bfloat16, 64, 50257), (torch.float32, 5, 7)])
+def test_ce_loss_sums_matches_torch(dtype, n, vocab):
+    from pe_ablations_b200 import ce_loss_sums
+
+    g = torch.Generator().manual_seed(n)
+    logits = (torch.randn(n, vocab, generator=g) * 3).to(dtype).cuda()
+    tgt = torch.randint(0, vocab, (n,), generator=g).cuda()
+    tgt[::7] = -100
+    out = ce_loss_sums(logits, tgt)
+    out = ce_loss_sums(logits, tgt, out=out)          # accumulates
+    want = torch.nn.functional.cross_entropy(logits.double(), tgt, ignore_index=-100, reduction="sum").item() * 2
+    cnt = int((tgt != -100).sum().item()) * 2
+    assert int(out[1].item()) == cnt
+    assert abs(out[0].item() - want) <= 2e-6 * abs(want)
+    # a strided view (the head's output sliced along vocab) works too
+    out2 = ce_loss_sums(logits[:, : vocab - 1], tgt.clamp(max=vocab - 2))
+    want2 = torch.nn.functional.cross_entropy(logits[:, : vocab - 1].double(), tgt.clamp(max=vocab - 2),
+                                              ignore_index=-100, reduction="sum").item()
+    assert abs(out2[0].item() - want2) <= 2e-6 * abs(want2)
