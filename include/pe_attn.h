@@ -174,6 +174,30 @@ size_t pe_ce_scratch_bytes(int n_rows);
 int pe_ce_loss_sums(const void* logits, int dtype, int64_t row_stride, const int64_t* targets, int n_rows, int vocab,
                     int ignore_index, void* scratch, double* out, void* stream);
 
+/* Same computation as pe_ce_loss_sums for callers that must not allocate.  No counterpart
+ * in the reference.
+ *
+ * Who needs it: an evaluation loop embedded in a process that handed all of its device
+ * memory to a pool at start-up, or one that runs where cudaMalloc is off limits because it
+ * synchronises the whole device (a serving thread sharing the GPU with latency-bound work).
+ * Such a caller has nowhere to get the scratch buffer from, so this entry point keeps one
+ * inside the library: a fixed device array of 256 + 4 * pe_ce_static_max_rows() bytes
+ * (64.25 KiB) that every GPU loading the library carries until the process ends.  The call
+ * itself allocates and frees nothing, on the device or through any library.
+ *
+ *   - n_rows above pe_ce_static_max_rows() (16384) is refused with PE_ATTN_ERR_TOO_LARGE:
+ *     feed the logits in smaller chunks, ``out`` accumulates across calls.
+ *   - The first call on each device looks up the array's device address (a one-time host
+ *     step); make that first call during set-up, before any stream capture starts.
+ *   - All calls on a device share the one array.  Each call clears the part that has to
+ *     start at zero and the rest is overwritten before it is read, so consecutive calls
+ *     on one stream are safe; calls that can overlap on the GPU (different streams, or
+ *     several host threads) would race on it and must be serialised by the caller.
+ *   - logits / targets / out as for pe_ce_loss_sums; the caller still owns all three. */
+int pe_ce_static_max_rows(void);
+int pe_ce_loss_sums_static(const void* logits, int dtype, int64_t row_stride, const int64_t* targets, int n_rows,
+                           int vocab, int ignore_index, double* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

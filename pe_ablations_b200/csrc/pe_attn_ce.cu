@@ -12,6 +12,8 @@
 // losses go to a scratch array; the last CTA to finish adds them up in a fixed order, so
 // the result does not depend on the order in which CTAs run.  The scratch is
 // [n_rows] floats plus one counter word that must be zero on entry and is left zero.
+#include <mutex>
+
 #include "pe_attn_common.cuh"
 #include "pe_attn_ptx.cuh"
 
@@ -19,6 +21,12 @@ namespace pe_attn {
 namespace {
 
 constexpr int CE_THREADS = 256;
+
+// Scratch of the allocation-free entry point: a counter block followed by one float per
+// row.  It is part of the library image, so every GPU that loads the library holds these
+// 64.25 KiB until the process exits.
+constexpr int CE_STATIC_MAX_ROWS = 16384;
+static __device__ __align__(256) unsigned char g_ce_static_scratch[256 + CE_STATIC_MAX_ROWS * sizeof(float)];
 
 struct CeParams {
   const void* logits;
@@ -200,6 +208,57 @@ int pe_ce_loss_sums(const void* logits, int dtype, int64_t row_stride, const int
   float* row_loss = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + 256);
   return pe_attn::launch_ce(logits, dtype, row_stride, reinterpret_cast<const long long*>(targets), n_rows, vocab,
                             ignore_index, row_loss, counter, out, static_cast<cudaStream_t>(stream));
+}
+
+// Device address of g_ce_static_scratch on the current device.  In host code the array's
+// name is only a handle for the runtime, never a device pointer, so the address is asked
+// for once per device (with that device current) and remembered.
+static int static_scratch_address(void** ptr) {
+  static std::mutex mu;
+  static void* cached[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    pe_attn::set_error("no usable CUDA device is current (%s)", cudaGetErrorString(e));
+    return PE_ATTN_ERR_DEVICE;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, pe_attn::g_ce_static_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      pe_attn::set_error("cudaGetSymbolAddress failed for the static scratch: %s", cudaGetErrorString(e));
+      return PE_ATTN_ERR_LAUNCH;
+    }
+    cached[dev] = p;
+  }
+  *ptr = cached[dev];
+  return PE_ATTN_OK;
+}
+
+int pe_ce_static_max_rows(void) { return pe_attn::CE_STATIC_MAX_ROWS; }
+
+int pe_ce_loss_sums_static(const void* logits, int dtype, int64_t row_stride, const int64_t* targets, int n_rows,
+                           int vocab, int ignore_index, double* out, void* stream) {
+  if (n_rows > pe_attn::CE_STATIC_MAX_ROWS) {
+    pe_attn::set_error("n_rows=%d exceeds the %d rows the built-in scratch holds; split the chunk or use "
+                       "pe_ce_loss_sums with your own scratch", n_rows, pe_attn::CE_STATIC_MAX_ROWS);
+    return PE_ATTN_ERR_TOO_LARGE;
+  }
+  void* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc != PE_ATTN_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // the array keeps whatever the previous call left: the counter block must start at zero
+  const cudaError_t e = cudaMemsetAsync(scratch, 0, 256, s);
+  if (e != cudaSuccess) {
+    pe_attn::set_error("clearing the static scratch failed: %s", cudaGetErrorString(e));
+    return PE_ATTN_ERR_LAUNCH;
+  }
+  unsigned int* counter = reinterpret_cast<unsigned int*>(scratch);
+  float* row_loss = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + 256);
+  return pe_attn::launch_ce(logits, dtype, row_stride, reinterpret_cast<const long long*>(targets), n_rows, vocab,
+                            ignore_index, row_loss, counter, out, s);
 }
 
 }  // extern "C"
