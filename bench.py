@@ -241,11 +241,57 @@ def run_ours(args) -> dict:
                      "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
                      "launch_ms": round(kernel_ms, 4)},
     }
+    if not args.no_eval:
+        ev_line = run_eval(torch, dist, dev, rank, world, args.eval_sequences)
+        if ev_line is not None:
+            line["eval_1b_16k"] = ev_line
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(budget_s=20.0)
     if world > 1:
         dist.destroy_process_group()
     return line if rank == 0 else None
+
+
+def run_eval(torch, dist, dev, rank: int, world: int, n_sequences: int):
+    """Second headline: 1B-shape forward + perplexity, 16k context, sequences sharded over ranks.
+
+    Random-init bf16 weights (seeded), ``n_sequences`` x 16384 uniform-random token ids; each
+    rank runs its shard through the fused attention and the loss-sum kernel, one NCCL
+    all-reduce of (sum NLL, count).  Timed once over the whole evaluation after one warm-up
+    sequence, device time, max over ranks.
+    """
+    from pe_ablations_b200 import eval as E
+
+    seq = E.MODEL_1B["max_seq_len"]
+    model = E.build_1b_model(dev, seed=0)
+    g = torch.Generator().manual_seed(4242)
+    ids = torch.randint(0, E.MODEL_1B["vocab_size"], (n_sequences, seq), generator=g)
+    mine = E.shard_range(n_sequences, world, rank)
+    my_ids = ids[mine.start:mine.stop].to(dev)
+    E.evaluate_shard(model, my_ids[:1])          # warm-up: cuBLAS heuristics, allocator
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    nll, cnt = E.evaluate_shard(model, my_ids)
+    tot_nll, tot_cnt = E.reduce_loss_sums(nll, cnt)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    del model
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return None
+    return {"metric": "1B-shape forward+perplexity tokens/s at 16k context", "value": round(n_sequences * seq / (ms * 1e-3), 1),
+            "unit": "tokens/s", "sequences": n_sequences, "seq_len": seq, "ms_total": round(ms, 2),
+            "perplexity": round(E.perplexity(tot_nll, tot_cnt), 3), "scaling": "strong",
+            "parallelism": f"sequences sharded over {world} GPU(s); one all-reduce of 2 scalars",
+            "flops_per_token": 3.52e9}
 
 
 def cpu_baseline(budget_s: float) -> dict:
@@ -297,6 +343,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-eval", action="store_true", help="skip the 1B-shape 16k perplexity evaluation")
+    ap.add_argument("--eval-sequences", type=int, default=64)
     args = ap.parse_args()
     line = run_reference(args) if args.impl == "reference" else run_ours(args)
     if line is not None:

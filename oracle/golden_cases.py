@@ -80,7 +80,15 @@ MODEL_BASE = dict(vocab_size=256, hidden_dim=128, num_layers=2, num_heads=4, num
 MODEL_BATCH, MODEL_SEQ = 2, 64
 
 
-def fill_parameters(module: torch.nn.Module, seed: int, std: float = 0.02) -> None:
+# the 1B-shape FoPE+PoPE decoder of the benchmark configuration list (d_model 2048, 16 layers,
+# 16 heads x head_dim 128, SwiGLU 5632, vocab 32000); MHA and d_rope 64 (d_qk 256)
+MODEL_1B = dict(vocab_size=32000, hidden_dim=2048, num_layers=16, num_heads=16, num_kv_heads=16, head_dim=128,
+                ffn_dim=5632, max_seq_len=16384, pe_mode="fpope", fpope_d_rope=64, fpope_num_fourier_terms=16,
+                fpope_sigma=0.3, fpope_training_length=16384, fpope_delta_init="uniform")
+MODEL_1B_SEQ, MODEL_1B_SEED, MODEL_1B_IDS_SEED = 16384, 7000, 7001
+
+
+def fill_parameters(module: torch.nn.Module, seed: int, std: float = 0.02, linear_gain: float = 4.0) -> None:
     """Overwrite every parameter from one seeded generator, in sorted-name order.
 
     Independent of construction order, so the reference's modules and the
@@ -104,4 +112,4 @@ def fill_parameters(module: torch.nn.Module, seed: int, std: float = 0.02) -> No
             elif "norm" in name and p.dim() == 1:
                 p.copy_(1.0 + 0.1 * torch.randn(p.shape, generator=g))
             else:
-                p.copy_(torch.randn(p.shape, generator=g) * std * (4.0 if p.dim() == 2 and "norm" not in name else 1.0))
+                p.copy_(torch.randn(p.shape, generator=g) * std * (linear_gain if p.dim() == 2 and "norm" not in name else 1.0))

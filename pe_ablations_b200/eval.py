@@ -78,3 +78,32 @@ def sharded_perplexity(model, all_input_ids: torch.Tensor, rank: int, world: int
     tot_nll, tot_cnt = reduce_loss_sums(nll, cnt, group)
     return {"nll_sum": tot_nll, "count": tot_cnt, "loss": tot_nll / max(tot_cnt, 1.0),
             "perplexity": perplexity(tot_nll, tot_cnt), "local_sequences": len(mine)}
+
+
+# ---- the 1B-shape 16k-context evaluation of the benchmark configuration list -----------------
+MODEL_1B = dict(vocab_size=32000, hidden_dim=2048, num_layers=16, num_heads=16, num_kv_heads=16, head_dim=128,
+                ffn_dim=5632, max_seq_len=16384, pe_mode="fpope", fpope_d_rope=64, fpope_num_fourier_terms=16,
+                fpope_sigma=0.3, fpope_training_length=16384, fpope_delta_init="uniform")
+
+
+def cast_matmul_weights(model, dtype=torch.bfloat16):
+    """Store the weights of every Linear / Embedding in ``dtype`` (norm weights and positional
+    parameters stay fp32), so that a bf16-autocast forward does not re-cast them per call."""
+    import torch.nn as nn
+
+    seen = set()
+    for m in model.modules():
+        if isinstance(m, (nn.Linear, nn.Embedding)) and id(m.weight) not in seen:
+            seen.add(id(m.weight))
+            m.weight.data = m.weight.data.to(dtype)
+    return model
+
+
+def build_1b_model(device, seed: int = 0, dtype=torch.bfloat16):
+    """Random-init (N(0, 0.02^2), seeded) 1B-shape FoPE+PoPE decoder on ``device``."""
+    from .model import Transformer, TransformerConfig
+
+    torch.manual_seed(seed)
+    with torch.device(device):
+        model = Transformer(TransformerConfig(**MODEL_1B)).eval()
+    return cast_matmul_weights(model, dtype) if dtype is not None else model

@@ -105,3 +105,39 @@ def test_ce_loss_sums_matches_torch(dtype, n, vocab):
     want2 = torch.nn.functional.cross_entropy(logits[:, : vocab - 1].double(), tgt.clamp(max=vocab - 2),
                                               ignore_index=-100, reduction="sum").item()
     assert abs(out2[0].item() - want2) <= 2e-6 * abs(want2)
+
+
+def test_1b_shape_16k_loss_matches_reference(golden_dir):
+    """The 1B-shape FoPE+PoPE decoder on one 16k sequence against the loss the reference itself
+    produced (fp32, CPU, eager) on the same weights and ids.
+
+    fp32 fused path: same loss to fp32 noise.  bf16 fused path (bf16 weights + autocast, the
+    benchmark's protocol): perplexity within 0.1 % relative, i.e. |delta loss| <= 1e-3.
+    """
+    path = os.path.join(golden_dir, "model_1b.npz")
+    if not os.path.exists(path):
+        pytest.skip("model_1b.npz has not been generated")
+    from pe_ablations_b200 import eval as E
+    from pe_ablations_b200.model import Transformer, TransformerConfig
+
+    gold = np.load(path)
+    want, seq = float(gold["loss"]), int(gold["seq_len"])
+    assert G.MODEL_1B == E.MODEL_1B
+    torch.manual_seed(0)
+    with torch.device("cuda"):
+        model = Transformer(TransformerConfig(**G.MODEL_1B)).eval()
+    G.fill_parameters(model, G.MODEL_1B_SEED, std=0.02, linear_gain=1.0)
+    ids = torch.randint(0, G.MODEL_1B["vocab_size"], (1, seq),
+                        generator=torch.Generator().manual_seed(G.MODEL_1B_IDS_SEED)).cuda()
+    with torch.no_grad():
+        nll, cnt = model.loss_sums(ids)
+        h = model.hidden_states(ids)
+        sample = model.output(h[0, ::1024])[:, ::4000].float().cpu()
+    got32 = (nll / cnt).item()
+    assert abs(got32 - want) <= 2e-5 * want, (got32, want)
+    assert (sample - torch.from_numpy(gold["logits_sample"])).abs().max().item() <= 2e-4
+    E.cast_matmul_weights(model)
+    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+        nll, cnt = model.loss_sums(ids)
+    got16 = (nll / cnt).item()
+    assert abs(got16 - want) <= 1e-3, (got16, want)
