@@ -41,8 +41,8 @@ FLOPS_PER_STEP = float(B) * H * S * S * (D_C + 2 * D_R + D_V)
 METRIC = "fused PE-attention TFLOP/s (FoPE+PoPE causal forward, bf16, B2 H16 S16384 d_qk256 d_v128)"
 WORKLOAD = "config 4: FoPE+PoPE causal attention forward, bf16, B2 H16 S16384 d_c128 d_r64 d_v128"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the tcgen05 kernel on this
-# workload, from the ncu capture summarised under profiles/ (None until captured)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# workload, from the ncu capture summarised in profiles/pe_attn_tc_kernel_config4_fopepope.md
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 669_989_888
 FALLBACK_BF16_TFLOPS = 1590.0
 
 

@@ -3,7 +3,8 @@
 // One CTA (512 threads, 1 per SM) owns 256 query rows of one (batch, head) as two
 // 128-row tiles and streams 64-key tiles through a 2-stage shared-memory ring:
 //
-//   warp 0        TMA producer: content halves of Q and K, and V, as 128B-swizzled tiles
+//   warp 0        TMA producer: content halves of Q and K as 128B-swizzled tiles
+//   warp 3        TMA producer: V tiles
 //   warp 1        MMA issuer:   S_i = Q_i K^T  (SS, M128 N64 K16 x d_qk/16) into TMEM,
 //                               O_i += P_i V   (TS: P read from TMEM, V from smem, N = d_v)
 //   warp 2        TMEM allocation / release (512 columns)
@@ -53,7 +54,7 @@ enum : int {
 
 enum : int {
   BAR_QFULL = 0, BAR_KFULL = 2, BAR_KEMPTY = 4, BAR_VFULL = 6, BAR_VEMPTY = 8, BAR_SFULL = 10, BAR_PREADY = 14,
-  BAR_PVDONE = 18, BAR_MMADONE = 22, NUM_BARS = 23
+  BAR_PVDONE = 18 /* one per query tile, completes once */, BAR_MMADONE = 22, NUM_BARS = 23
 };
 
 template <int DC, int DR, int DV>
@@ -223,8 +224,8 @@ __device__ __forceinline__ void build_slab(const KParams& p, uint32_t base, uint
 
 template <int DC, int DR, int DV, int MODE, bool ALIBI>
 __global__ void __launch_bounds__(NTHREADS, 1)
-pe_attn_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                  const __grid_constant__ CUtensorMap tmV) {
+pe_attn_tc_kernel(const KParams p, const int bh_group, const __grid_constant__ CUtensorMap tmQ,
+                  const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV) {
   using C = Cfg<DC, DR, DV>;
   constexpr bool HAS_TMA_QK = (MODE == MODE_PLAIN) || (MODE == MODE_POPE && DC > 0);
   constexpr bool HAS_XFORM = MODE != MODE_PLAIN;
@@ -240,13 +241,17 @@ pe_attn_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tmQ, cons
   auto bar = [&](int idx) -> uint32_t { return bars + 8u * (uint32_t)idx; };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // 1-D grid in longest-first order over the whole launch: block ids are handed out in
-  // increasing order, so all (batch, head) problems get their last (longest) query block
-  // first, then the second to last, and so on.
+  // 1-D grid, longest query blocks first within groups of ``bh_group`` (batch, head) problems.
+  // Block ids are handed out in increasing order, so a group's last (longest) query blocks
+  // start first; the group is sized so that the K/V of the heads in flight stay in L2.
   const int n_qblk = (p.Sq + Q_TILES * BLOCK_M - 1) / (Q_TILES * BLOCK_M);
   const int n_bh = p.B * p.H;
-  const int qblk = n_qblk - 1 - (int)(blockIdx.x / n_bh);
-  const int bh = (int)(blockIdx.x % n_bh);
+  const int per_group = bh_group * n_qblk;
+  const int grp = (int)(blockIdx.x / per_group), in_grp = (int)(blockIdx.x % per_group);
+  const int g_first = grp * bh_group;
+  const int g_size = (n_bh - g_first) < bh_group ? (n_bh - g_first) : bh_group;
+  const int qblk = n_qblk - 1 - in_grp / g_size;
+  const int bh = g_first + in_grp % g_size;
   const int h = bh % p.H, b = bh / p.H;
   const int hk = h / p.groups;
   const int m0 = qblk * Q_TILES * BLOCK_M;
@@ -319,9 +324,8 @@ pe_attn_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tmQ, cons
   } else if (warp == 0) {
     // ===================== TMA producer =====================
     // The whole warp runs the loop (waits included); one elected lane issues the copies.
-    if (elect_one()) {
-      tma_prefetch_desc(&tmV);
-      if constexpr (HAS_TMA_QK) {
+    if constexpr (HAS_TMA_QK) {
+      if (elect_one()) {
         tma_prefetch_desc(&tmQ);
         tma_prefetch_desc(&tmK);
       }
@@ -339,11 +343,11 @@ pe_attn_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tmQ, cons
         __syncwarp();
       }
     }
+    if constexpr (HAS_TMA_QK) {
 #pragma unroll 1
-    for (int j = 0; j < n_tiles; ++j) {
-      const int s = j & 1;
-      const uint32_t ph = (uint32_t)((j >> 1) & 1);
-      if constexpr (HAS_TMA_QK) {
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (uint32_t)((j >> 1) & 1);
         if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_KEMPTY + s), ph ^ 1u))) { fail(ST_WAIT_KEMPTY); break; }
         if (elect_one()) {
           mbar_arrive_expect_tx(bar(BAR_KFULL + s), C::NCC * C::K_CHUNK_BYTES);
@@ -354,6 +358,15 @@ pe_attn_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tmQ, cons
         }
         __syncwarp();
       }
+    }
+  } else if (warp == 3) {
+    // ===================== TMA producer for V (its own warp: K and V stages are released at
+    // different times, and one warp waiting on both in turn would issue each copy late)
+    if (elect_one()) tma_prefetch_desc(&tmV);
+#pragma unroll 1
+    for (int j = 0; j < n_tiles; ++j) {
+      const int s = j & 1;
+      const uint32_t ph = (uint32_t)((j >> 1) & 1);
       if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_VEMPTY + s), ph ^ 1u))) { fail(ST_WAIT_VEMPTY); break; }
       if (elect_one()) {
         mbar_arrive_expect_tx(bar(BAR_VFULL + s), C::V_STAGE_BYTES);
@@ -429,7 +442,7 @@ pe_attn_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tmQ, cons
             for (int kk = 0; kk < BLOCK_N / 16; ++kk)
               mma_ts(d, a + (uint32_t)(kk * 8), advance_smem_desc(vd, (uint32_t)(kk * 16 * 128)), IDESC_PV,
                      (j > 0 || kk > 0) ? 1u : 0u);
-            tc_commit(bar(BAR_PVDONE + 2 * i + (j & 1)));
+            if (j == nt[i] - 1) tc_commit(bar(BAR_PVDONE + i));  // this tile's output is final
           }
           __syncwarp();
         }
@@ -524,8 +537,8 @@ pe_attn_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tmQ, cons
         if (__any_sync(0xffffffffu, need)) {
           const float alpha = need ? ex2_approx((m_used - mx) * kf) : 1.0f;
           if (j > 0) {
-            const int pb = 2 * i + ((j - 1) & 1);
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_PVDONE + pb), (uint32_t)(((j - 1) >> 1) & 1)));
+            // PV(j-1) of both query tiles is complete once its V stage has been released
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_VEMPTY + ((j - 1) & 1)), (uint32_t)(((j - 1) >> 1) & 1)));
             if (!ok) { fail(ST_WAIT_PVDONE); break; }
             tc_fence_after_sync();
             const uint32_t o_addr = tmem_base + lane_sel + 256u + (uint32_t)(i * DV);
@@ -565,8 +578,7 @@ pe_attn_tc_kernel(const KParams p, const __grid_constant__ CUtensorMap tmQ, cons
       }
 
       if (ok) {
-        const int lb = 2 * i + ((ntile - 1) & 1);
-        ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_PVDONE + lb), (uint32_t)(((ntile - 1) >> 1) & 1)));
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_PVDONE + i), 0));
         if (!ok) fail(ST_WAIT_PVDONE);
       }
       if (ok) {
@@ -764,8 +776,18 @@ int launch_instance(const KParams& p, cudaStream_t stream) {
     }
   }
   const int n_qblk = (p.Sq + Q_TILES * BLOCK_M - 1) / (Q_TILES * BLOCK_M);
+  // (batch, head) problems per scheduling group: enough blocks to fill the GPU twice over, but
+  // no more heads than keep their K/V (about 48 MB) resident in the 126 MB L2
+  const long long kv_bytes_per_head = 2ll * p.Sk * (DC + DR + DV);
+  long long by_l2 = (48ll << 20) / (kv_bytes_per_head > 0 ? kv_bytes_per_head : 1);
+  long long by_fill = (2 * 148 + n_qblk - 1) / n_qblk;
+  long long bh_group = by_fill < by_l2 ? by_fill : by_l2;
+  // a group that is not a multiple of the GQA ratio would split K/V-sharing heads across groups
+  if (bh_group < p.groups) bh_group = p.groups;
+  if (bh_group > (long long)p.B * p.H) bh_group = (long long)p.B * p.H;
+  if (bh_group < 1) bh_group = 1;
   dim3 grid((unsigned)((long long)n_qblk * p.H * p.B)), block(NTHREADS);
-  kern<<<grid, block, C::SMEM_BYTES, stream>>>(p, tmQ, tmK, tmV);
+  kern<<<grid, block, C::SMEM_BYTES, stream>>>(p, (int)bh_group, tmQ, tmK, tmV);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("tcgen05 kernel launch failed: %s", cudaGetErrorString(e));
