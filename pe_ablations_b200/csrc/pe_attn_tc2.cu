@@ -1,0 +1,637 @@
+// CTA-pair variant of the tcgen05 fused PE-attention forward (bf16, d_v = 128).
+//
+// Two CTAs on neighbouring SMs (a cluster of 2) own 512 query rows of one (batch, head) and
+// share every K/V tile: each CTA loads and transforms only HALF of a 128-key tile (64 keys of
+// K, 64 value columns of V), and the leader CTA issues `tcgen05.mma.cta_group::2` instructions
+// that span both SMs (M = 256: 128 rows in each CTA's TMEM; N = 128 taken half from each CTA's
+// shared memory).  Compared with the single-CTA kernel this halves the shared-memory operand
+// traffic per MMA (the QK product is no longer port-bound), the L2 -> SM traffic, and the
+// positional transform work per FLOP, and doubles the keys per synchronisation step.
+//
+// Per CTA: two 128-row query tiles.  "Pair tile" i is the 256 rows made of tile i of both CTAs
+// (CTA rank r holds rows m0 + (2 i + r) * 128 ...).  TMEM per CTA: S_i / P_i at columns
+// i * 128 (P, packed bf16, overwrites its own S tile chunk by chunk), O_i at 256 + i * 128.
+//
+// Warp roles per CTA as in the single-CTA kernel (0: Q/K TMA, 1: MMA issue -- leader only,
+// 2: TMEM, 3: V TMA, 4-7 / 8-11: softmax of tile 0 / 1, 12-15: K transform).  Barriers that
+// gate MMA issue (q_full, k_full, v_full, p_ready) live in the leader's shared memory and
+// collect arrivals from both CTAs; barriers signalled by MMA completion (s_full, k_empty,
+// v_empty, o_done) exist in both CTAs and are signalled together by one multicast commit.
+// Issue order of the leader, per key tile j:  PV_0(j)  QK_0(j+1)  PV_1(j)  QK_1(j+1), so the
+// tensor pipe works on one pair tile while the softmax warps work on the other.
+//
+// Every wait is bounded; a CTA that gives up reports through the status word and both CTAs
+// still meet at the final cluster barrier before releasing TMEM.
+#include <cuda.h>
+
+#include "pe_attn_tc_common.cuh"
+
+namespace pe_attn {
+namespace {
+
+using namespace ptx;
+using namespace tc;
+
+constexpr int BLOCK_M = 128;     // query rows per tile per CTA (TMEM lanes)
+constexpr int Q_TILES = 2;       // query tiles per CTA
+constexpr int PAIR_ROWS = 512;   // query rows per CTA pair
+constexpr int BLOCK_N = 128;     // keys per tile (64 held by each CTA)
+constexpr int HALF_N = 64;
+constexpr int DV = 128;
+constexpr int KV_STAGES = 2;
+constexpr int NTHREADS = 512;
+constexpr int TMEM_COLS = 512;
+constexpr int TAIL_BYTES = 1024;
+
+enum : int {
+  BAR_QFULL = 0, BAR_KFULL = 2, BAR_KEMPTY = 4, BAR_VFULL = 6, BAR_VEMPTY = 8, BAR_SFULL = 10, BAR_PREADY = 12,
+  BAR_ODONE = 14, BAR_MMADONE = 16, NUM_BARS = 17
+};
+
+template <int DC, int DR>
+struct Cfg2 {
+  static constexpr int DQK = DC + 2 * DR;
+  static constexpr int NCHUNK = DQK / 64;
+  static constexpr int NCC = DC / 64;
+  static constexpr int Q_CHUNK_BYTES = BLOCK_M * 128;
+  static constexpr int K_CHUNK_BYTES = HALF_N * 128;
+  static constexpr int Q_TILE_BYTES = NCHUNK * Q_CHUNK_BYTES;
+  static constexpr int K_STAGE_BYTES = NCHUNK * K_CHUNK_BYTES;   // this CTA's 64 keys
+  static constexpr int V_STAGE_BYTES = BLOCK_N * 128;            // 128 keys x this CTA's 64 value columns
+  static constexpr int Q_OFF = TAIL_BYTES;
+  static constexpr int K_OFF = Q_OFF + Q_TILES * Q_TILE_BYTES;
+  static constexpr int V_OFF = K_OFF + KV_STAGES * K_STAGE_BYTES;
+  static constexpr int SMEM_USED = V_OFF + KV_STAGES * V_STAGE_BYTES;
+  static constexpr int SMEM_BYTES = SMEM_USED + 1024;
+  static_assert(DQK % 64 == 0 && DQK >= 64 && DQK <= 256, "d_qk must be 64..256 in steps of 64");
+  static_assert(SMEM_BYTES <= 232448, "shared memory budget exceeded");
+};
+
+template <int DC, int DR, int MODE, bool ALIBI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NTHREADS, 1)
+pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ CUtensorMap tmQ,
+                   const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV) {
+  using C = Cfg2<DC, DR>;
+  constexpr bool HAS_TMA_QK = (MODE == MODE_PLAIN) || (MODE == MODE_POPE && DC > 0);
+  constexpr bool HAS_XFORM = MODE != MODE_PLAIN;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + 256);
+  volatile uint32_t* abort_slot = reinterpret_cast<volatile uint32_t*>(smem + 260);
+  float* freq_s = reinterpret_cast<float*>(smem + 512);
+  float* delta_s = reinterpret_cast<float*>(smem + 768);
+  auto bar = [&](int idx) -> uint32_t { return smem_base + 8u * (uint32_t)idx; };
+
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
+  const uint32_t rank = cluster_ctarank();          // 0 = leader
+  auto lbar = [&](int idx) -> uint32_t { return mapa(bar(idx), 0); };  // the leader's copy of a barrier
+
+  // pair (cluster) index -> (query super-block, batch, head), longest first within head groups
+  const int n_sblk = (p.Sq + PAIR_ROWS - 1) / PAIR_ROWS;
+  const int n_bh = p.B * p.H;
+  const int pair = (int)(blockIdx.x >> 1);
+  const int per_group = bh_group * n_sblk;
+  const int grp = pair / per_group, in_grp = pair % per_group;
+  const int g_first = grp * bh_group;
+  const int g_size = (n_bh - g_first) < bh_group ? (n_bh - g_first) : bh_group;
+  const int sblk = n_sblk - 1 - in_grp / g_size;
+  const int bh = g_first + in_grp % g_size;
+  const int h = bh % p.H, b = bh / p.H;
+  const int hk = h / p.groups;
+  const int m0 = sblk * PAIR_ROWS;
+
+  // key tiles pair tile i needs: keys [0, min(Sk, last row of the pair tile + 1 + off))
+  int nt[Q_TILES];
+#pragma unroll
+  for (int i = 0; i < Q_TILES; ++i) {
+    const int first = m0 + i * 2 * BLOCK_M;
+    int kend = first + 2 * BLOCK_M + p.causal_off;
+    if (kend > p.Sk) kend = p.Sk;
+    nt[i] = first < p.Sq ? (kend + BLOCK_N - 1) / BLOCK_N : 0;
+  }
+  const int n_tiles = nt[1] > nt[0] ? nt[1] : nt[0];
+
+  auto fail = [&](int code) {
+    if (p.status != nullptr) atomicOr(p.status, code);
+  };
+
+  if (tid == 0) {
+    *abort_slot = (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1u : 0u;
+    const uint32_t n_xf = HAS_XFORM ? 4u : 0u;
+    const uint32_t n_tma = HAS_TMA_QK ? 1u : 0u;
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(BAR_QFULL + i), 2 * (n_tma + n_xf));   // both CTAs report to the leader's copy
+      mbar_init(bar(BAR_KFULL + i), 2 * (n_tma + n_xf));
+      mbar_init(bar(BAR_VFULL + i), 2);
+      mbar_init(bar(BAR_PREADY + i), 8);                   // 4 softmax warps x 2 CTAs
+      mbar_init(bar(BAR_KEMPTY + i), 1);
+      mbar_init(bar(BAR_VEMPTY + i), 1);
+      mbar_init(bar(BAR_SFULL + i), 1);
+      mbar_init(bar(BAR_ODONE + i), 1);
+    }
+    mbar_init(bar(BAR_MMADONE), 1);
+    mbar_fence_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 2) {
+    tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  if constexpr (MODE == MODE_POPE) {
+    if (tid >= 128 && tid < 128 + DR) {
+      freq_s[tid - 128] = effective_freq(p, tid - 128);
+      delta_s[tid - 128] = clamped_delta(p, tid - 128);
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync();  // both CTAs' barriers are initialised before anyone signals across the pair
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const bool run = *abort_slot == 0;
+
+  const uint32_t q_smem = smem_base + C::Q_OFF;
+  const uint32_t k_smem = smem_base + C::K_OFF;
+  const uint32_t v_smem = smem_base + C::V_OFF;
+
+  // Register budget per warpgroup (40 / 160 / 160 / 152 x 128 threads = 64 K registers); each
+  // role sits inside the branch that sets its budget.
+  if (warp < 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+  if (!run) {
+    // nothing to do
+  } else if (warp == 0) {
+    // ===================== TMA producer: content halves of this CTA's Q tiles and K half-tiles
+    if constexpr (HAS_TMA_QK) {
+      if (elect_one()) {
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+      }
+      for (int i = 0; i < Q_TILES; ++i) {
+        if (nt[i] == 0) continue;
+        if (elect_one()) {
+          const uint32_t qb = lbar(BAR_QFULL + i);
+          mbar_arrive_expect_tx_cluster(qb, C::NCC * C::Q_CHUNK_BYTES);
+#pragma unroll
+          for (int c = 0; c < C::NCC; ++c)
+            tma_load_4d_pair(q_smem + i * C::Q_TILE_BYTES + c * C::Q_CHUNK_BYTES, &tmQ, qb, c * 64,
+                             m0 + (2 * i + (int)rank) * BLOCK_M, h, b);
+        }
+        __syncwarp();
+      }
+#pragma unroll 1
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (uint32_t)((j >> 1) & 1);
+        if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_KEMPTY + s), ph ^ 1u))) { fail(ST_WAIT_KEMPTY); break; }
+        if (elect_one()) {
+          const uint32_t kb = lbar(BAR_KFULL + s);
+          mbar_arrive_expect_tx_cluster(kb, C::NCC * C::K_CHUNK_BYTES);
+#pragma unroll
+          for (int c = 0; c < C::NCC; ++c)
+            tma_load_4d_pair(k_smem + s * C::K_STAGE_BYTES + c * C::K_CHUNK_BYTES, &tmK, kb, c * 64,
+                             j * BLOCK_N + (int)rank * HALF_N, hk, b);
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp == 3) {
+    // ===================== TMA producer: this CTA's 64 value columns of every V tile
+    if (elect_one()) tma_prefetch_desc(&tmV);
+#pragma unroll 1
+    for (int j = 0; j < n_tiles; ++j) {
+      const int s = j & 1;
+      const uint32_t ph = (uint32_t)((j >> 1) & 1);
+      if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_VEMPTY + s), ph ^ 1u))) { fail(ST_WAIT_VEMPTY); break; }
+      if (elect_one()) {
+        const uint32_t vb = lbar(BAR_VFULL + s);
+        mbar_arrive_expect_tx_cluster(vb, C::V_STAGE_BYTES);
+        tma_load_4d_pair(v_smem + s * C::V_STAGE_BYTES, &tmV, vb, (int)rank * 64, j * BLOCK_N, hk, b);
+      }
+      __syncwarp();
+    }
+  } else if (warp == 1 && rank == 0) {
+    // ===================== MMA issuer (leader CTA only) =====================
+    constexpr uint32_t IDESC_QK = make_idesc_bf16(2 * BLOCK_M, BLOCK_N, false);
+    constexpr uint32_t IDESC_PV = make_idesc_bf16(2 * BLOCK_M, DV, true);
+    constexpr uint16_t BOTH = 3;
+    const uint64_t qdesc0 = make_smem_desc(q_smem, 16, 1024);
+    const uint64_t kdesc0 = make_smem_desc(k_smem, 16, 1024);
+    const uint64_t vdesc0 = make_smem_desc(v_smem, 16, 1024);
+    bool ok = true;
+    for (int i = 0; i < Q_TILES && ok; ++i)
+      if (nt[i] > 0 && !__all_sync(0xffffffffu, mbar_wait(bar(BAR_QFULL + i), 0))) { fail(ST_WAIT_QFULL); ok = false; }
+
+    // S_i = Q_i K(j)^T for pair tile i, then tell both CTAs' softmax warps
+    auto issue_qk = [&](int i, int j) {
+      if (elect_one()) {
+        const uint32_t d = tmem_base + (uint32_t)(i * BLOCK_N);
+        uint64_t qd = advance_smem_desc(qdesc0, (uint32_t)(i * C::Q_TILE_BYTES));
+        uint64_t kd = advance_smem_desc(kdesc0, (uint32_t)((j & 1) * C::K_STAGE_BYTES));
+#pragma unroll 1
+        for (int c = 0; c < C::NCHUNK; ++c) {
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4)
+            mma_ss_pair(d, advance_smem_desc(qd, (uint32_t)(k4 * 32)), advance_smem_desc(kd, (uint32_t)(k4 * 32)),
+                        IDESC_QK, (c > 0 || k4 > 0) ? 1u : 0u);
+          qd = advance_smem_desc(qd, C::Q_CHUNK_BYTES);
+          kd = advance_smem_desc(kd, C::K_CHUNK_BYTES);
+        }
+        tc_commit_pair(bar(BAR_SFULL + i), BOTH);
+      }
+      __syncwarp();
+    };
+    auto wait_k = [&](int j) -> bool {
+      if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_KFULL + (j & 1)), (uint32_t)((j >> 1) & 1)))) {
+        fail(ST_WAIT_KFULL);
+        return false;
+      }
+      tc_fence_after_sync();
+      return true;
+    };
+
+    if (ok && n_tiles > 0) {
+      ok = wait_k(0);
+      if (ok) {
+        for (int i = 0; i < Q_TILES; ++i)
+          if (nt[i] > 0) issue_qk(i, 0);
+        if (elect_one()) tc_commit_pair(bar(BAR_KEMPTY + 0), BOTH);
+        __syncwarp();
+      }
+    }
+#pragma unroll 1
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int s = j & 1;
+      const uint32_t ph = (uint32_t)((j >> 1) & 1);
+      if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_VFULL + s), ph))) { fail(ST_WAIT_VFULL); ok = false; break; }
+      bool have_k = false;
+      const uint64_t vd = advance_smem_desc(vdesc0, (uint32_t)(s * C::V_STAGE_BYTES));
+#pragma unroll
+      for (int i = 0; i < Q_TILES; ++i) {
+        if (j < nt[i]) {
+          if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_PREADY + i), (uint32_t)(j & 1)))) {
+            fail(ST_WAIT_PREADY);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          if (elect_one()) {
+            const uint32_t d = tmem_base + 256u + (uint32_t)(i * DV);
+            const uint32_t a = tmem_base + (uint32_t)(i * BLOCK_N);
+#pragma unroll
+            for (int kk = 0; kk < BLOCK_N / 16; ++kk)
+              mma_ts_pair(d, a + (uint32_t)(kk * 8), advance_smem_desc(vd, (uint32_t)(kk * 16 * 128)), IDESC_PV,
+                          (j > 0 || kk > 0) ? 1u : 0u);
+            tc_commit_pair(bar(BAR_ODONE + i), BOTH);
+          }
+          __syncwarp();
+        }
+        if (j + 1 < nt[i]) {
+          if (!have_k) {
+            if (!wait_k(j + 1)) { ok = false; break; }
+            have_k = true;
+          }
+          issue_qk(i, j + 1);   // overwrites S_i / P_i: ordered after PV_i(j) by the in-order tensor pipe
+        }
+      }
+      if (!ok) break;
+      if (elect_one()) {
+        tc_commit_pair(bar(BAR_VEMPTY + s), BOTH);
+        if (j + 1 < n_tiles) tc_commit_pair(bar(BAR_KEMPTY + ((j + 1) & 1)), BOTH);
+      }
+      __syncwarp();
+    }
+    if (elect_one()) tc_commit_pair(bar(BAR_MMADONE), 1);
+    __syncwarp();
+    if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_MMADONE), 0))) fail(ST_WAIT_MMADONE);
+  }
+  } else if (warp < 12) {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 160;");
+  if (run) {
+    // ===================== softmax warpgroups =====================
+    const int i = (warp - 4) >> 2;
+    const int tg = tid - 128 - i * BLOCK_M;
+    const int ntile = nt[i];
+    const int row0 = m0 + (2 * i + (int)rank) * BLOCK_M;   // first query row of this CTA's tile i
+    if (ntile > 0) {
+      if constexpr (HAS_XFORM) {
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+          const int r0 = row0 + half * 64;
+          build_slab<DC, DR, MODE>(p, q_smem + i * C::Q_TILE_BYTES + half * 64 * 128, C::Q_CHUNK_BYTES, p.q, p.qr, b,
+                                   h, r0, p.Sq, p.q_pos0 + r0, false, freq_s, delta_s, tg);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(lbar(BAR_QFULL + i));
+      }
+      const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+      const int row = row0 + tg;
+      const int row_lim = row + p.causal_off;
+      const float c2 = p.scale * 1.4426950408889634f;
+      float slope2 = 0.f;
+      if constexpr (ALIBI) slope2 = p.slopes[h] * 1.4426950408889634f;
+      const float kf = ALIBI ? 1.0f : c2;
+      float m_used = -INFINITY, l_sum = 0.f;
+      bool ok = true;
+      const uint32_t s_addr = tmem_base + lane_sel + (uint32_t)(i * BLOCK_N);
+      const uint32_t o_addr = tmem_base + lane_sel + 256u + (uint32_t)(i * DV);
+      const uint32_t pready = lbar(BAR_PREADY + i);
+
+#pragma unroll 1
+      for (int j = 0; j < ntile; ++j) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_SFULL + i), (uint32_t)(j & 1)));
+        if (!ok) { fail(ST_WAIT_SFULL); break; }
+        tc_fence_after_sync();
+        const int key0 = j * BLOCK_N;
+        const bool need_mask = (key0 + BLOCK_N - 1 > row0 + p.causal_off) || (key0 + BLOCK_N > p.Sk);
+        float base_bias = 0.f;
+        if constexpr (ALIBI) base_bias = slope2 * (float)(key0 - row_lim);
+
+        // ---- the whole S row (128 fp32) into registers with one wait, bias / mask in place
+        uint32_t sr[4][32];
+        tmem_ld32(s_addr, sr[0]);
+        tmem_ld32(s_addr + 32, sr[1]);
+        tmem_ld32(s_addr + 64, sr[2]);
+        tmem_ld32(s_addr + 96, sr[3]);
+        tmem_wait_ld();
+        float t[BLOCK_N];
+#pragma unroll
+        for (int c = 0; c < BLOCK_N; ++c) t[c] = __uint_as_float(sr[c >> 5][c & 31]);
+        if constexpr (ALIBI) {
+#pragma unroll
+          for (int c = 0; c < BLOCK_N; ++c) t[c] = fmaf(t[c], c2, fmaf((float)c, slope2, base_bias));
+        }
+        if (need_mask) {
+#pragma unroll
+          for (int c = 0; c < BLOCK_N; ++c)
+            if (key0 + c > row_lim || key0 + c >= p.Sk) t[c] = -INFINITY;
+        }
+        float mx0 = t[0], mx1 = t[1], mx2 = t[2], mx3 = t[3];
+#pragma unroll
+        for (int c = 4; c < BLOCK_N; c += 4) {
+          mx0 = fmaxf(mx0, t[c]);
+          mx1 = fmaxf(mx1, t[c + 1]);
+          mx2 = fmaxf(mx2, t[c + 2]);
+          mx3 = fmaxf(mx3, t[c + 3]);
+        }
+        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+
+        // ---- lazy rescale of the running output
+        const bool need = (mx - m_used) * kf > 8.0f;
+        if (__any_sync(0xffffffffu, need)) {
+          const float alpha = need ? ex2_approx((m_used - mx) * kf) : 1.0f;
+          if (j > 0) {
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_ODONE + i), (uint32_t)((j - 1) & 1)));
+            if (!ok) { fail(ST_WAIT_PVDONE); break; }
+            tc_fence_after_sync();
+            // rare path, and the whole S row is live in registers: 16 columns at a time
+#pragma unroll 1
+            for (int cb = 0; cb < DV / 16; ++cb) {
+              uint32_t orow[16];
+              tmem_ld16(o_addr + cb * 16, orow);
+              tmem_wait_ld();
+#pragma unroll
+              for (int c = 0; c < 16; ++c) orow[c] = __float_as_uint(__uint_as_float(orow[c]) * alpha);
+              tmem_st16(o_addr + cb * 16, orow);
+            }
+            tmem_wait_st();
+          }
+          l_sum *= alpha;
+          if (need) m_used = mx;
+        }
+
+        // ---- exponentials, row sum, P as bf16 pairs over the first 64 columns of this S tile
+        // (every S value of the row is already in registers)
+        const float neg_m = -m_used * kf;
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+        for (int cb = 0; cb < BLOCK_N / 32; ++cb) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int c = 0; c < 32; c += 4) {
+            const float p0 = ex2_approx(fmaf(t[cb * 32 + c], kf, neg_m));
+            const float p1 = ex2_approx(fmaf(t[cb * 32 + c + 1], kf, neg_m));
+            const float p2 = ex2_approx(fmaf(t[cb * 32 + c + 2], kf, neg_m));
+            const float p3 = ex2_approx(fmaf(t[cb * 32 + c + 3], kf, neg_m));
+            a0 += p0; a1 += p1; a2 += p2; a3 += p3;
+            pk[c >> 1] = pack_bf16x2(p0, p1);
+            pk[(c >> 1) + 1] = pack_bf16x2(p2, p3);
+          }
+          tmem_st16(s_addr + cb * 16, pk);
+        }
+        l_sum += (a0 + a1) + (a2 + a3);
+        tmem_wait_st();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(pready);
+      }
+
+      if (ok) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_ODONE + i), (uint32_t)((ntile - 1) & 1)));
+        if (!ok) fail(ST_WAIT_PVDONE);
+      }
+      if (ok) {
+        tc_fence_after_sync();
+        const float inv_l = 1.0f / l_sum;
+        char* dst = reinterpret_cast<char*>(const_cast<void*>(p.out.ptr)) +
+                    2 * ((long long)b * p.out.sb + (long long)h * p.out.sh + (long long)row * p.out.ss);
+#pragma unroll 1
+        for (int cb = 0; cb < DV / 32; ++cb) {
+          uint32_t orow[32];
+          tmem_ld32(o_addr + cb * 32, orow);
+          tmem_wait_ld();
+          if (row < p.Sq) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(orow[v * 8 + 0]) * inv_l, __uint_as_float(orow[v * 8 + 1]) * inv_l);
+              o.y = pack_bf16x2(__uint_as_float(orow[v * 8 + 2]) * inv_l, __uint_as_float(orow[v * 8 + 3]) * inv_l);
+              o.z = pack_bf16x2(__uint_as_float(orow[v * 8 + 4]) * inv_l, __uint_as_float(orow[v * 8 + 5]) * inv_l);
+              o.w = pack_bf16x2(__uint_as_float(orow[v * 8 + 6]) * inv_l, __uint_as_float(orow[v * 8 + 7]) * inv_l);
+              *reinterpret_cast<uint4*>(dst + (cb * 32 + v * 8) * 2) = o;
+            }
+          }
+        }
+      }
+    }
+  }
+  } else {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
+  if (run) {
+    // ===================== positional transform of this CTA's 64 keys of every K tile ===========
+    const int tg = tid - 384;
+    if constexpr (MODE == MODE_POPE) {
+      constexpr int VPR = DR / 8, RPP = 128 / VPR, PASSES = HALF_N / RPP;
+      const int cv = tg % VPR, r_in = tg / VPR;
+      float th[8], tcs[PASSES][8], tsn[PASSES][8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        th[e] = freq_s[cv * 8 + e];
+        const float dl = delta_s[cv * 8 + e];
+#pragma unroll
+        for (int k = 0; k < PASSES; ++k)
+          sincos_reduced(__fadd_rn(__fmul_rn((float)(r_in + k * RPP), th[e]), dl), &tsn[k][e], &tcs[k][e]);
+      }
+      const char* src = reinterpret_cast<const char*>(p.kr.ptr) +
+                        2 * ((long long)b * p.kr.sb + (long long)hk * p.kr.sh + (long long)cv * 8);
+      const int col_c = DC + cv * 8, col_s = DC + DR + cv * 8;
+      const uint32_t off_c = (uint32_t)((col_c / 64) * C::K_CHUNK_BYTES), off_s = (uint32_t)((col_s / 64) * C::K_CHUNK_BYTES);
+      const int slot_c = (col_c % 64) / 8, slot_s = (col_s % 64) / 8;
+      const int rbase = (int)rank * HALF_N;   // this CTA's keys inside a tile
+      uint4 nxt[PASSES];
+#pragma unroll
+      for (int k = 0; k < PASSES; ++k) {
+        const int grow = rbase + r_in + k * RPP;
+        nxt[k] = grow < p.Sk ? ldg_nc_v4(src + 2 * (long long)grow * p.kr.ss) : make_uint4(0, 0, 0, 0);
+      }
+      const uint32_t kfull = lbar(BAR_KFULL + 0), kfull1 = lbar(BAR_KFULL + 1);
+#pragma unroll 1
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j & 1;
+        uint4 cur[PASSES];
+#pragma unroll
+        for (int k = 0; k < PASSES; ++k) cur[k] = nxt[k];
+        if (j + 1 < n_tiles) {
+#pragma unroll
+          for (int k = 0; k < PASSES; ++k) {
+            const int grow = (j + 1) * BLOCK_N + rbase + r_in + k * RPP;
+            nxt[k] = grow < p.Sk ? ldg_nc_v4(src + 2 * (long long)grow * p.kr.ss) : make_uint4(0, 0, 0, 0);
+          }
+        }
+        float cb[8], sb[8];
+        const float pos0 = (float)(p.k_pos0 + j * BLOCK_N + rbase);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sincos_reduced(__fmul_rn(pos0, th[e]), &sb[e], &cb[e]);
+        const bool ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_KEMPTY + s), (uint32_t)(((j >> 1) & 1) ^ 1)));
+        if (!ok) { fail(ST_WAIT_KEMPTY); break; }
+        const uint32_t kb = k_smem + s * C::K_STAGE_BYTES;
+#pragma unroll
+        for (int k = 0; k < PASSES; ++k) {
+          const int r = r_in + k * RPP;
+          const uint32_t w[4] = {cur[k].x, cur[k].y, cur[k].z, cur[k].w};
+          float oc[8], os[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float x = (e & 1) ? bf16_hi(w[e >> 1]) : bf16_lo(w[e >> 1]);
+            const float mu = softplus_fast(x);
+            const float mc = mu * cb[e], ms = mu * sb[e];
+            oc[e] = mc * tcs[k][e] - ms * tsn[k][e];
+            os[e] = ms * tcs[k][e] + mc * tsn[k][e];
+          }
+          sts_v4(kb + off_c + swz(r, slot_c), make_uint4(pack_bf16x2(oc[0], oc[1]), pack_bf16x2(oc[2], oc[3]),
+                                                         pack_bf16x2(oc[4], oc[5]), pack_bf16x2(oc[6], oc[7])));
+          sts_v4(kb + off_s + swz(r, slot_s), make_uint4(pack_bf16x2(os[0], os[1]), pack_bf16x2(os[2], os[3]),
+                                                         pack_bf16x2(os[4], os[5]), pack_bf16x2(os[6], os[7])));
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(s ? kfull1 : kfull);
+      }
+    } else if constexpr (MODE == MODE_XFORM) {
+#pragma unroll 1
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j & 1;
+        const bool ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_KEMPTY + s), (uint32_t)(((j >> 1) & 1) ^ 1)));
+        if (!ok) { fail(ST_WAIT_KEMPTY); break; }
+        const int r0 = j * BLOCK_N + (int)rank * HALF_N;
+        build_slab<DC, DR, MODE>(p, k_smem + s * C::K_STAGE_BYTES, C::K_CHUNK_BYTES, p.k, p.kr, b, hk, r0, p.Sk,
+                                 p.k_pos0 + r0, true, freq_s, delta_s, tg);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(lbar(BAR_KFULL + s));
+      }
+    }
+  }
+  }  // register-budget branch
+
+  if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 200000) {
+    }
+  }
+  // neither CTA may release shared memory or TMEM while the other one's MMAs, copies or
+  // barrier arrivals can still touch them
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync();
+  if (warp == 2) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int DC, int DR, int MODE, bool ALIBI>
+int launch_instance2(const KParams& p, cudaStream_t stream) {
+  using C = Cfg2<DC, DR>;
+  auto kern = pe_attn_tc2_kernel<DC, DR, MODE, ALIBI>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (e != cudaSuccess) {
+      set_error("cudaFuncSetAttribute(%d bytes) failed: %s", C::SMEM_BYTES, cudaGetErrorString(e));
+      return PE_ATTN_ERR_LAUNCH;
+    }
+    configured = true;
+  }
+  CUtensorMap tmQ, tmK, tmV;
+  memset(&tmQ, 0, sizeof(tmQ));
+  memset(&tmK, 0, sizeof(tmK));
+  if (!encode_map(&tmV, p.v, DV, p.Sk, p.Hkv, p.B, BLOCK_N)) {
+    set_error("cuTensorMapEncodeTiled failed for v");
+    return PE_ATTN_ERR_LAUNCH;
+  }
+  if constexpr (MODE == MODE_PLAIN || (MODE == MODE_POPE && DC > 0)) {
+    if (!encode_map(&tmQ, p.q, DC, p.Sq, p.H, p.B, BLOCK_M) || !encode_map(&tmK, p.k, DC, p.Sk, p.Hkv, p.B, HALF_N)) {
+      set_error("cuTensorMapEncodeTiled failed for q / k");
+      return PE_ATTN_ERR_LAUNCH;
+    }
+  }
+  const int n_sblk = (p.Sq + PAIR_ROWS - 1) / PAIR_ROWS;
+  const long long kv_bytes_per_head = 2ll * p.Sk * (DC + DR + DV);
+  long long by_l2 = (48ll << 20) / (kv_bytes_per_head > 0 ? kv_bytes_per_head : 1);
+  long long by_fill = (2 * 74 + n_sblk - 1) / n_sblk;   // 74 CTA pairs fit the GPU at a time
+  long long bh_group = by_fill < by_l2 ? by_fill : by_l2;
+  if (bh_group < p.groups) bh_group = p.groups;
+  if (bh_group > (long long)p.B * p.H) bh_group = (long long)p.B * p.H;
+  if (bh_group < 1) bh_group = 1;
+  dim3 grid((unsigned)(2ll * n_sblk * p.H * p.B)), block(NTHREADS);
+  kern<<<grid, block, C::SMEM_BYTES, stream>>>(p, (int)bh_group, tmQ, tmK, tmV);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("tcgen05 CTA-pair kernel launch failed: %s", cudaGetErrorString(e));
+    return PE_ATTN_ERR_LAUNCH;
+  }
+  return PE_ATTN_OK;
+}
+
+template <int DC, int DR, int MODE>
+int launch_alibi2(const KParams& p, cudaStream_t stream) {
+  if (p.variant == PE_ATTN_ALIBI) return launch_instance2<DC, DR, MODE, true>(p, stream);
+  return launch_instance2<DC, DR, MODE, false>(p, stream);
+}
+
+}  // namespace
+
+// The CTA-pair kernel covers d_v = 128 (each CTA then owns one 64-column, 128-byte chunk of V).
+bool tc2_supports(const KParams& p) {
+  if (p.d_v != 128) return false;
+  if (p.variant == PE_ATTN_POPE)
+    return (p.d_c == 128 && (p.d_r == 64 || p.d_r == 32)) || (p.d_c == 0 && p.d_r == 64);
+  return p.d_c == 128;
+}
+
+int launch_tc2(const KParams& p, cudaStream_t stream) {
+  if (p.variant == PE_ATTN_POPE) {
+    if (p.d_c == 128 && p.d_r == 64) return launch_instance2<128, 64, MODE_POPE, false>(p, stream);
+    if (p.d_c == 128 && p.d_r == 32) return launch_instance2<128, 32, MODE_POPE, false>(p, stream);
+    return launch_instance2<0, 64, MODE_POPE, false>(p, stream);
+  }
+  const bool xform = p.variant == PE_ATTN_ROTARY || (p.flags & PE_ATTN_QK_NORM);
+  return xform ? launch_alibi2<128, 0, MODE_XFORM>(p, stream) : launch_alibi2<128, 0, MODE_PLAIN>(p, stream);
+}
+
+}  // namespace pe_attn

@@ -1,0 +1,209 @@
+// Pieces shared by the tcgen05 attention kernels (single-CTA and CTA-pair variants): the
+// positional transforms that build MMA operands in shared memory, and the host-side TMA
+// descriptor encoding.
+#pragma once
+
+#include <cuda.h>
+
+#include "pe_attn_common.cuh"
+#include "pe_attn_ptx.cuh"
+
+namespace pe_attn {
+namespace tc {
+
+using namespace ptx;
+
+constexpr int SLAB_ROWS = 64;  // rows one build_slab call produces
+
+enum Mode { MODE_PLAIN = 0, MODE_XFORM = 1, MODE_POPE = 2 };
+
+// status codes ORed into the caller's device status word
+enum : int {
+  ST_WAIT_QFULL = 1 << 0, ST_WAIT_KFULL = 1 << 1, ST_WAIT_VFULL = 1 << 2, ST_WAIT_KEMPTY = 1 << 3,
+  ST_WAIT_VEMPTY = 1 << 4, ST_WAIT_SFULL = 1 << 5, ST_WAIT_PREADY = 1 << 6, ST_WAIT_PVDONE = 1 << 7,
+  ST_WAIT_MMADONE = 1 << 8
+};
+
+// softplus with the special-function unit: max(x, 0) + log1p(exp(-|x|))
+__device__ __forceinline__ float softplus_fast(float x) {
+  const float e = ex2_approx(-fabsf(x) * 1.4426950408889634f);
+  return fmaxf(x, 0.f) + lg2_approx(1.0f + e) * 0.6931471805599453f;
+}
+
+// sin / cos of a large fp32 angle: two-term Cody-Waite reduction by 2 pi, then MUFU
+__device__ __forceinline__ void sincos_reduced(float x, float* s, float* c) {
+  const float k = rintf(x * 0.15915494309189535f);
+  float r = fmaf(k, -6.2831854820251465f, x);
+  r = fmaf(k, 1.7484556000744883e-7f, r);
+  *s = __sinf(r);
+  *c = __cosf(r);
+}
+
+// byte offset of the 16-byte slot ``slot`` (0..7) of row ``r`` inside a 128B-swizzled chunk
+__device__ __forceinline__ uint32_t swz(int r, int slot) { return (uint32_t)(r * 128 + ((slot ^ (r & 7)) << 4)); }
+
+// Build 64 operand rows (positional / transformed columns only) in shared memory with a
+// group of 128 threads (tg = 0..127).  ``base`` is the shared address of chunk 0 at the
+// slab's first row (1024-byte aligned), chunks are ``chunk_stride`` bytes apart.
+//   MODE_POPE : columns [DC, DC + 2 DR): softplus magnitude x (cos, sin) of the phase
+//   MODE_XFORM: columns [0, DC): optional pair rotation, mscale, optional L2 normalisation
+template <int DC, int DR, int MODE>
+__device__ __forceinline__ void build_slab(const KParams& p, uint32_t base, uint32_t chunk_stride,
+                                           const TensorRef& content, const TensorRef& posi, int b, int head,
+                                           int row0, int n_rows, int pos_row0, bool is_key, const float* freq_s,
+                                           const float* delta_s, int tg) {
+  if constexpr (MODE == MODE_POPE) {
+    constexpr int VPR = DR / 8;            // 16-byte vectors per row
+    constexpr int RPP = 128 / VPR;         // rows per pass
+    constexpr int PASSES = SLAB_ROWS / RPP;
+    const int cv = tg % VPR, r_in = tg / VPR;
+    float f[8], dl[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      f[e] = freq_s[cv * 8 + e];
+      dl[e] = is_key ? delta_s[cv * 8 + e] : 0.f;
+    }
+    const char* src = reinterpret_cast<const char*>(posi.ptr) +
+                      2 * ((long long)b * posi.sb + (long long)head * posi.sh + (long long)cv * 8);
+    uint4 raw[PASSES];
+#pragma unroll
+    for (int k = 0; k < PASSES; ++k) {
+      const int grow = row0 + r_in + k * RPP;
+      raw[k] = make_uint4(0, 0, 0, 0);
+      if (grow < n_rows) raw[k] = ldg_nc_v4(src + 2 * (long long)grow * posi.ss);
+    }
+#pragma unroll
+    for (int k = 0; k < PASSES; ++k) {
+      const int r = r_in + k * RPP;
+      const bool live = (row0 + r) < n_rows;
+      const float pos = (float)(pos_row0 + r);
+      const uint32_t w[4] = {raw[k].x, raw[k].y, raw[k].z, raw[k].w};
+      float oc[8], os[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float x = (e & 1) ? bf16_hi(w[e >> 1]) : bf16_lo(w[e >> 1]);
+        const float mu = live ? softplus_fast(x) : 0.f;
+        // phase = fl(fl(pos * freq) + delta), the reference's rounding order
+        const float ph = __fadd_rn(__fmul_rn(pos, f[e]), dl[e]);
+        float sn, cs;
+        sincos_reduced(ph, &sn, &cs);
+        oc[e] = mu * cs;
+        os[e] = mu * sn;
+      }
+      const uint4 vc = make_uint4(pack_bf16x2(oc[0], oc[1]), pack_bf16x2(oc[2], oc[3]), pack_bf16x2(oc[4], oc[5]),
+                                  pack_bf16x2(oc[6], oc[7]));
+      const uint4 vs = make_uint4(pack_bf16x2(os[0], os[1]), pack_bf16x2(os[2], os[3]), pack_bf16x2(os[4], os[5]),
+                                  pack_bf16x2(os[6], os[7]));
+      const int col_c = DC + cv * 8, col_s = DC + DR + cv * 8;
+      sts_v4(base + (col_c / 64) * chunk_stride + swz(r, (col_c % 64) / 8), vc);
+      sts_v4(base + (col_s / 64) * chunk_stride + swz(r, (col_s % 64) / 8), vs);
+    }
+  } else if constexpr (MODE == MODE_XFORM) {
+    constexpr int VPR = DC / 8;
+    constexpr int RPP = 128 / VPR;
+    constexpr int PASSES = SLAB_ROWS / RPP;
+    const int cv = tg % VPR, r_in = tg / VPR;
+    const bool rotary = p.variant == PE_ATTN_ROTARY;
+    const bool norm = (p.flags & PE_ATTN_QK_NORM) != 0;
+    const char* src = reinterpret_cast<const char*>(content.ptr) +
+                      2 * ((long long)b * content.sb + (long long)head * content.sh + (long long)cv * 8);
+    uint4 pk[PASSES];
+    float ss[PASSES];
+#pragma unroll
+    for (int k = 0; k < PASSES; ++k) {
+      const int grow = row0 + r_in + k * RPP;
+      pk[k] = make_uint4(0, 0, 0, 0);
+      if (grow < n_rows) pk[k] = ldg_nc_v4(src + 2 * (long long)grow * content.ss);
+    }
+#pragma unroll
+    for (int k = 0; k < PASSES; ++k) {
+      const int r = r_in + k * RPP;
+      const bool live = (row0 + r) < n_rows;
+      uint32_t w[4] = {pk[k].x, pk[k].y, pk[k].z, pk[k].w};
+      if (rotary && live) {
+        const int trow = pos_row0 + r - p.table_pos0;
+        const float4* tp = reinterpret_cast<const float4*>(p.table + ((size_t)trow * (DC / 2) + cv * 4) * 2);
+        const float4 t0 = __ldg(tp), t1 = __ldg(tp + 1);
+        const float cs[4] = {t0.x, t0.z, t1.x, t1.z}, sn[4] = {t0.y, t0.w, t1.y, t1.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float x0 = bf16_lo(w[e]), x1 = bf16_hi(w[e]);
+          const float o0 = x0 * cs[e] - x1 * sn[e];
+          const float o1 = x0 * sn[e] + x1 * cs[e];
+          w[e] = pack_bf16x2(o0, o1);
+          if (p.mscale != 1.0f) w[e] = pack_bf16x2(bf16_lo(w[e]) * p.mscale, bf16_hi(w[e]) * p.mscale);
+        }
+      }
+      float acc = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float x0 = bf16_lo(w[e]), x1 = bf16_hi(w[e]);
+        acc = fmaf(x0, x0, acc);
+        acc = fmaf(x1, x1, acc);
+      }
+      ss[k] = acc;
+      pk[k] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    if (norm) {
+      // row sum of squares across the VPR lanes that share a row (warp-level reduction)
+#pragma unroll
+      for (int k = 0; k < PASSES; ++k) {
+#pragma unroll
+        for (int d = 1; d < VPR; d <<= 1) ss[k] += __shfl_xor_sync(0xffffffffu, ss[k], d);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < PASSES; ++k) {
+      const int r = r_in + k * RPP;
+      uint32_t w[4] = {pk[k].x, pk[k].y, pk[k].z, pk[k].w};
+      if (norm) {
+        const float inv = 1.0f / (sqrtf(ss[k]) + p.eps);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) w[e] = pack_bf16x2(bf16_lo(w[e]) * inv, bf16_hi(w[e]) * inv);
+      }
+      const int col = cv * 8;
+      sts_v4(base + (col / 64) * chunk_stride + swz(r, (col % 64) / 8), make_uint4(w[0], w[1], w[2], w[3]));
+    }
+  }
+}
+
+// ---- host side --------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// [B, H, S, d] bf16 tensor viewed as a 4-D TMA tensor (d, S, H, B) with a (64 x rows) box,
+// 128-byte swizzle, zero fill outside the tensor.
+inline bool encode_map(CUtensorMap* map, const TensorRef& t, int d, int S, int H, int B, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)t.ss * 2, (cuuint64_t)t.sh * 2, (cuuint64_t)t.sb * 2};
+  // a size-1 dimension may carry any stride; TMA still wants a multiple of 16 bytes
+  for (int i = 0; i < 3; ++i)
+    if (strides[i] == 0 || strides[i] % 16 != 0) strides[i] = (cuuint64_t)d * 2;
+  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(t.ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+}  // namespace tc
+}  // namespace pe_attn
