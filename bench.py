@@ -234,11 +234,11 @@ def run_ours(args) -> dict:
                 "ms_per_step": round(e2e_ms, 3), "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world},
         "gpu_launches": args.steps,
         "clocks": clocks,
-        "roofline": {"bound": "tensor", "kernel": "pe_attn_tc_kernel<128,64,128,POPE>",
+        "roofline": {"bound": "tensor", "kernel": "pe_attn_tc2_kernel<128,64,POPE> (CTA pair, cta_group::2)",
                      "achieved": round(kernel_tflops, 2), "peak": peak, "unit": "TFLOP/s",
                      "frac": round(kernel_tflops / peak, 4), "peak_source": peak_src,
                      "frac_of_nominal_2250": round(kernel_tflops / 2250.0, 4),
-                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH // world,   # compulsory-traffic kernel: scales with the heads per rank
                      "launch_ms": round(kernel_ms, 4)},
     }
     if not args.no_eval:

@@ -71,8 +71,10 @@ enum pe_attn_flags {
                                       /* fourier_coeffs[] inside the kernel (fpope.py:107-146)     */
   PE_ATTN_FOURIER_NORMALIZE = 1 << 2, /* L1-normalise each row of coefficients first               */
   PE_ATTN_FOURIER_CEILING = 1 << 3,   /* clamp effective frequencies to +-ceil_freq                */
-  PE_ATTN_SIMT_CHECK = 1 << 8         /* bf16 only: run the FFMA kernel on the bf16 tensors (an    */
-                                      /* on-device cross-check for the tensor-core kernel)         */
+  PE_ATTN_SIMT_CHECK = 1 << 8,        /* bf16 only: run the FFMA kernel on the bf16 tensors (an    */
+                                      /* on-device cross-check for the tensor-core kernels)        */
+  PE_ATTN_SINGLE_CTA = 1 << 9         /* bf16 only: keep the single-CTA tcgen05 kernel where the   */
+                                      /* CTA-pair kernel (d_v = 128, Sq > 256) would be chosen     */
 };
 
 typedef enum pe_attn_status {
@@ -140,7 +142,8 @@ int pe_attn_forward(const pe_attn_args* args, void* stream);
 /* Validate only: same checks and return codes as pe_attn_forward, touches no GPU. */
 int pe_attn_validate(const pe_attn_args* args);
 
-/* Name of the kernel family pe_attn_forward would pick for ``args``: "tcgen05" or "ffma";
+/* Name of the kernel family pe_attn_forward would pick for ``args``: "tcgen05" (single CTA),
+ * "tcgen05-pair" (two CTAs share every K/V tile through cta_group::2 MMAs) or "ffma";
  * null if ``args`` does not validate. */
 const char* pe_attn_kernel_name(const pe_attn_args* args);
 

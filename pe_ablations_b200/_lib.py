@@ -22,6 +22,7 @@ FOURIER_MIX = 1 << 1
 FOURIER_NORMALIZE = 1 << 2
 FOURIER_CEILING = 1 << 3
 SIMT_CHECK = 1 << 8
+SINGLE_CTA = 1 << 9
 
 EXPORTS = (
     "pe_attn_version", "pe_attn_forward", "pe_attn_validate", "pe_attn_kernel_name",

@@ -152,7 +152,10 @@ int pe_attn_validate(const pe_attn_args* args) { return validate(args, nullptr);
 
 const char* pe_attn_kernel_name(const pe_attn_args* args) {
   if (validate(args, nullptr) != PE_ATTN_OK) return nullptr;
-  return (args->dtype == PE_ATTN_BF16 && !(args->flags & PE_ATTN_SIMT_CHECK)) ? "tcgen05" : "ffma";
+  if (args->dtype != PE_ATTN_BF16 || (args->flags & PE_ATTN_SIMT_CHECK)) return "ffma";
+  KParams k;
+  validate(args, &k);
+  return (tc2_supports(k) && k.Sq > 256 && !(k.flags & PE_ATTN_SINGLE_CTA)) ? "tcgen05-pair" : "tcgen05";
 }
 
 double pe_attn_flops(const pe_attn_args* a) {

@@ -64,6 +64,30 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   }
 }
 
+// Latency-critical variant: polls with the non-blocking test instead of the suspending
+// try_wait (whose wake-up was measured at 0.6-0.8 us after the arrival), same bound.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity) {
+  if (mbar_test_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+      if (mbar_test_wait(bar, parity)) return true;
+    if (clock64() - t0 > kWaitLimitCycles) return false;
+  }
+}
+
 // ---- proxies / fences --------------------------------------------------------
 // Make generic-proxy shared-memory writes visible to the async proxy (TMA, tcgen05.mma).
 __device__ __forceinline__ void fence_proxy_async_smem() {
@@ -195,6 +219,11 @@ __device__ __forceinline__ void cluster_sync() {
 // arrivals on a barrier that may live in the other CTA of the pair (shared::cluster address)
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cbar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cbar) : "memory");
+}
+// Same without release semantics: for hand-offs whose payload is not in memory (P lives in
+// TMEM and is ordered by the tcgen05 fences), so no cluster-wide release is needed.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cbar) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cbar) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cbar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cbar), "r"(bytes)

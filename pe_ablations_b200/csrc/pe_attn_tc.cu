@@ -237,11 +237,11 @@ pe_attn_tc_kernel(const KParams p, const int bh_group, const __grid_constant__ C
     const uint64_t vdesc0 = make_smem_desc(v_smem, C::V_CHUNK_BYTES, 1024);
     bool ok = true;
     for (int i = 0; i < Q_TILES && ok; ++i)
-      if (nt[i] > 0 && !__all_sync(0xffffffffu, mbar_wait(bar(BAR_QFULL + i), 0))) { fail(ST_WAIT_QFULL); ok = false; }
+      if (nt[i] > 0 && !__all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_QFULL + i), 0))) { fail(ST_WAIT_QFULL); ok = false; }
 
     auto issue_qk = [&](int j) -> bool {
       const int s = j & 1;
-      if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_KFULL + s), (uint32_t)((j >> 1) & 1)))) {
+      if (!__all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_KFULL + s), (uint32_t)((j >> 1) & 1)))) {
         fail(ST_WAIT_KFULL);
         return false;
       }
@@ -274,12 +274,12 @@ pe_attn_tc_kernel(const KParams p, const int bh_group, const __grid_constant__ C
     auto issue_pv = [&](int j) -> bool {
       const int s = j & 1;
       const uint32_t ph = (uint32_t)((j >> 1) & 1);
-      if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_VFULL + s), ph))) { fail(ST_WAIT_VFULL); return false; }
+      if (!__all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_VFULL + s), ph))) { fail(ST_WAIT_VFULL); return false; }
       const uint64_t vd = advance_smem_desc(vdesc0, (uint32_t)(s * C::V_STAGE_BYTES));
 #pragma unroll
       for (int i = 0; i < Q_TILES; ++i) {
         if (j < nt[i]) {
-          if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_PREADY + 2 * i + (j & 1)), ph))) {
+          if (!__all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_PREADY + 2 * i + (j & 1)), ph))) {
             fail(ST_WAIT_PREADY);
             return false;
           }
@@ -310,7 +310,7 @@ pe_attn_tc_kernel(const KParams p, const int bh_group, const __grid_constant__ C
     // every MMA, and with it every barrier arrival they trigger, has landed before the CTA exits
     if (elect_one()) tc_commit(bar(BAR_MMADONE));
     __syncwarp();
-    if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_MMADONE), 0))) fail(ST_WAIT_MMADONE);
+    if (!__all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_MMADONE), 0))) fail(ST_WAIT_MMADONE);
   }
   } else {
   asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
@@ -346,7 +346,7 @@ pe_attn_tc_kernel(const KParams p, const int bh_group, const __grid_constant__ C
       for (int j = 0; j < ntile; ++j) {
         const int bsel = 2 * i + (j & 1);
         const uint32_t ph = (uint32_t)((j >> 1) & 1);
-        ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_SFULL + bsel), ph));
+        ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_SFULL + bsel), ph));
         if (!ok) { fail(ST_WAIT_SFULL); break; }
         tc_fence_after_sync();
         const uint32_t s_addr = tmem_base + lane_sel + (uint32_t)(bsel * BLOCK_N);
@@ -387,7 +387,7 @@ pe_attn_tc_kernel(const KParams p, const int bh_group, const __grid_constant__ C
           const float alpha = need ? ex2_approx((m_used - mx) * kf) : 1.0f;
           if (j > 0) {
             // PV(j-1) of both query tiles is complete once its V stage has been released
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_VEMPTY + ((j - 1) & 1)), (uint32_t)(((j - 1) >> 1) & 1)));
+            ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_VEMPTY + ((j - 1) & 1)), (uint32_t)(((j - 1) >> 1) & 1)));
             if (!ok) { fail(ST_WAIT_PVDONE); break; }
             tc_fence_after_sync();
             const uint32_t o_addr = tmem_base + lane_sel + 256u + (uint32_t)(i * DV);
@@ -427,7 +427,7 @@ pe_attn_tc_kernel(const KParams p, const int bh_group, const __grid_constant__ C
       }
 
       if (ok) {
-        ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_PVDONE + i), 0));
+        ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_PVDONE + i), 0));
         if (!ok) fail(ST_WAIT_PVDONE);
       }
       if (ok) {
@@ -627,7 +627,7 @@ bool tc_supports(const KParams& p) {
 
 int launch_tc(const KParams& p, cudaStream_t stream) {
   // long sequences at d_v = 128 go to the CTA-pair kernel (two CTAs share every K/V tile)
-  if (tc2_supports(p) && p.Sq > 256) return launch_tc2(p, stream);
+  if (tc2_supports(p) && p.Sq > 256 && !(p.flags & PE_ATTN_SINGLE_CTA)) return launch_tc2(p, stream);
   if (p.variant == PE_ATTN_POPE) {
     if (p.d_c == 64 && p.d_r == 32) return launch_instance<64, 32, 64, MODE_POPE, false>(p, stream);
     if (p.d_c == 128 && p.d_r == 64) return launch_instance<128, 64, 128, MODE_POPE, false>(p, stream);

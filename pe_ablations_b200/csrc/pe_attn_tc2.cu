@@ -223,7 +223,7 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
     const uint64_t vdesc0 = make_smem_desc(v_smem, 16, 1024);
     bool ok = true;
     for (int i = 0; i < Q_TILES && ok; ++i)
-      if (nt[i] > 0 && !__all_sync(0xffffffffu, mbar_wait(bar(BAR_QFULL + i), 0))) { fail(ST_WAIT_QFULL); ok = false; }
+      if (nt[i] > 0 && !__all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_QFULL + i), 0))) { fail(ST_WAIT_QFULL); ok = false; }
 
     // S_i = Q_i K(j)^T for pair tile i, then tell both CTAs' softmax warps
     auto issue_qk = [&](int i, int j) {
@@ -245,7 +245,7 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
       __syncwarp();
     };
     auto wait_k = [&](int j) -> bool {
-      if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_KFULL + (j & 1)), (uint32_t)((j >> 1) & 1)))) {
+      if (!__all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_KFULL + (j & 1)), (uint32_t)((j >> 1) & 1)))) {
         fail(ST_WAIT_KFULL);
         return false;
       }
@@ -266,13 +266,13 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int s = j & 1;
       const uint32_t ph = (uint32_t)((j >> 1) & 1);
-      if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_VFULL + s), ph))) { fail(ST_WAIT_VFULL); ok = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_VFULL + s), ph))) { fail(ST_WAIT_VFULL); ok = false; break; }
       bool have_k = false;
       const uint64_t vd = advance_smem_desc(vdesc0, (uint32_t)(s * C::V_STAGE_BYTES));
 #pragma unroll
       for (int i = 0; i < Q_TILES; ++i) {
         if (j < nt[i]) {
-          if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_PREADY + i), (uint32_t)(j & 1)))) {
+          if (!__all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_PREADY + i), (uint32_t)(j & 1)))) {
             fail(ST_WAIT_PREADY);
             ok = false;
             break;
@@ -306,7 +306,7 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
     }
     if (elect_one()) tc_commit_pair(bar(BAR_MMADONE), 1);
     __syncwarp();
-    if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_MMADONE), 0))) fail(ST_WAIT_MMADONE);
+    if (!__all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_MMADONE), 0))) fail(ST_WAIT_MMADONE);
   }
   } else if (warp < 12) {
   asm volatile("setmaxnreg.inc.sync.aligned.u32 160;");
@@ -343,7 +343,7 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
 
 #pragma unroll 1
       for (int j = 0; j < ntile; ++j) {
-        ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_SFULL + i), (uint32_t)(j & 1)));
+        ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_SFULL + i), (uint32_t)(j & 1)));
         if (!ok) { fail(ST_WAIT_SFULL); break; }
         tc_fence_after_sync();
         const int key0 = j * BLOCK_N;
@@ -385,7 +385,7 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
         if (__any_sync(0xffffffffu, need)) {
           const float alpha = need ? ex2_approx((m_used - mx) * kf) : 1.0f;
           if (j > 0) {
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_ODONE + i), (uint32_t)((j - 1) & 1)));
+            ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_ODONE + i), (uint32_t)((j - 1) & 1)));
             if (!ok) { fail(ST_WAIT_PVDONE); break; }
             tc_fence_after_sync();
             // rare path, and the whole S row is live in registers: 16 columns at a time
@@ -427,11 +427,11 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
         tmem_wait_st();
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(pready);
+        if (lane == 0) mbar_arrive_cluster_relaxed(pready);
       }
 
       if (ok) {
-        ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_ODONE + i), (uint32_t)((ntile - 1) & 1)));
+        ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_ODONE + i), (uint32_t)((ntile - 1) & 1)));
         if (!ok) fail(ST_WAIT_PVDONE);
       }
       if (ok) {

@@ -91,6 +91,7 @@ def pe_attention(
     out: torch.Tensor | None = None,
     mask: torch.Tensor | None = None,
     simt_check: bool = False,
+    single_cta: bool = False,
 ) -> torch.Tensor:
     """Fused causal attention forward with the positional transform applied in-kernel.
 
@@ -204,6 +205,8 @@ def pe_attention(
                 a.ceil_freq = float(ceil_freq)
     if simt_check:
         flags |= _lib.SIMT_CHECK
+    if single_cta:
+        flags |= _lib.SINGLE_CTA
     a.flags = flags
     with torch.cuda.device(dev):
         if dtype == _lib.BF16 and not simt_check:

@@ -5,7 +5,8 @@ import torch
 from oracle.inputs import Case, make_inputs, oracle_output
 
 
-def run_case_on_gpu(case: Case, inp: dict, simt_check: bool = False, fused_fourier: bool = True) -> torch.Tensor:
+def run_case_on_gpu(case: Case, inp: dict, simt_check: bool = False, fused_fourier: bool = True,
+                    single_cta: bool = False) -> torch.Tensor:
     from pe_ablations_b200 import check_device_status, pe_attention
 
     dev = torch.device("cuda", 0)
@@ -27,7 +28,7 @@ def run_case_on_gpu(case: Case, inp: dict, simt_check: bool = False, fused_fouri
     elif case.variant == "alibi":
         kw["alibi_slopes"] = inp["slopes"]
     out = pe_attention(case.variant, cast(inp["q"]), cast(inp["k"]), cast(inp["v"]), start_pos=case.pos0,
-                       qk_norm=case.qk_norm, simt_check=simt_check, **kw)
+                       qk_norm=case.qk_norm, simt_check=simt_check, single_cta=single_cta, **kw)
     torch.cuda.synchronize()
     check_device_status()
     return out.float().cpu()

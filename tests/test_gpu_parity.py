@@ -105,6 +105,27 @@ def test_ffma_kernel_cross_checks_tensor_core_kernel():
     assert (a - b).abs().max().item() <= 2e-2
 
 
+@pytest.mark.parametrize("case", [
+    Case("x_pair_fpope", "pope", BF16, 1, 4, 2, 1500, 128, 64, 128, seed=81, pope_kind="fpope", training_length=1024),
+    Case("x_pair_rope_qkn", "rotary", BF16, 2, 2, 2, 1100, 128, 0, 128, seed=82, qk_norm=True),
+    Case("x_pair_alibi", "alibi", BF16, 1, 4, 4, 777, 128, 0, 128, seed=83),
+    Case("x_pair_nope_gqa", "nope", BF16, 1, 8, 2, 1030, 128, 0, 128, seed=84),
+    Case("x_pair_pope_dr32", "pope", BF16, 1, 2, 2, 900, 128, 32, 128, seed=85, pos0=300),
+    Case("x_pair_posonly", "pope", BF16, 1, 2, 1, 700, 0, 64, 128, seed=86),
+], ids=lambda c: c.name)
+def test_cta_pair_and_single_cta_kernels_agree(case):
+    """Both tcgen05 kernels on the same tensors, each against the oracle and against each other."""
+    from tests.gpu_util import run_case_on_gpu
+
+    inp = make_inputs(case)
+    want = oracle_output(case, inp).float()
+    pair = run_case_on_gpu(case, inp)
+    single = run_case_on_gpu(case, inp, single_cta=True)
+    assert (pair - want).abs().max().item() <= 2e-2
+    assert (single - want).abs().max().item() <= 2e-2
+    assert (pair - single).abs().max().item() <= 2e-2
+
+
 def test_fused_fourier_mix_equals_host_mix():
     from tests.gpu_util import run_case_on_gpu
 
