@@ -177,6 +177,20 @@ size_t pe_ce_scratch_bytes(int n_rows);
 int pe_ce_loss_sums(const void* logits, int dtype, int64_t row_stride, const int64_t* targets, int n_rows, int vocab,
                     int ignore_index, void* scratch, double* out, void* stream);
 
+/* ---- the memory-bound neighbours of attention on the evaluation path -------------------------
+ *
+ * pe_rmsnorm_forward replaces RMSNorm.forward (src/model/normalization.py:22-27) followed by
+ * the cast the next linear layer's autocast applies: y = cast(cast(x * rsqrt(mean(x^2) + eps))
+ * * weight), one read and one write of the activation.  x, y: device [rows, dim] of ``dtype``
+ * (bf16: 16-byte aligned rows; fp32: 32-byte), rows ``x_stride`` / ``y_stride`` elements
+ * apart, dim a multiple of 8; weight: device fp32 [dim].
+ *
+ * pe_swiglu_forward replaces SwiGLU.forward (src/model/ffn.py:8-27, called at ffn.py:68):
+ * y = cast(cast(silu(gate)) * up) over ``n`` contiguous elements (a multiple of 8). */
+int pe_rmsnorm_forward(const void* x, const float* weight, void* y, int dtype, int rows, int dim, int64_t x_stride,
+                       int64_t y_stride, float eps, void* stream);
+int pe_swiglu_forward(const void* gate, const void* up, void* y, int dtype, int64_t n, void* stream);
+
 /* Same computation as pe_ce_loss_sums for callers that must not allocate.  No counterpart
  * in the reference.
  *

@@ -97,7 +97,13 @@ class FeedForward(nn.Module):
         self.w3 = nn.Linear(hidden_dim, ffn_dim, bias=False)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.w2(F.silu(self.w3(x)) * self.w1(x))
+        gate, up = self.w3(x), self.w1(x)
+        if gate.is_cuda and not (torch.is_grad_enabled() and gate.requires_grad) and gate.numel() % 8 == 0 \
+                and gate.dtype in (torch.bfloat16, torch.float32):
+            from .ops import swiglu
+
+            return self.w2(swiglu(gate, up))
+        return self.w2(F.silu(gate) * up)
 
 
 def _build_pe(cfg: TransformerConfig):

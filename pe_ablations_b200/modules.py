@@ -33,6 +33,15 @@ class RMSNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(dim))
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.is_cuda and not (torch.is_grad_enabled() and (x.requires_grad or self.weight.requires_grad)):
+            fused_bf16 = x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and (
+                self.weight.dtype == torch.bfloat16
+                or (torch.is_autocast_enabled() and torch.get_autocast_dtype("cuda") == torch.bfloat16))
+            if fused_bf16 or (x.dtype == torch.float32 and self.weight.dtype == torch.float32 and x.shape[-1] % 8 == 0):
+                # one pass; for bf16 the result already carries the cast the next linear applies
+                from .ops import rmsnorm
+
+                return rmsnorm(x, self.weight, self.eps)
         xf = x.float()
         y = xf * torch.rsqrt(xf.square().mean(dim=-1, keepdim=True) + self.eps)
         return y.type_as(x) * self.weight

@@ -266,6 +266,55 @@ def ce_loss_sums(logits: torch.Tensor, targets: torch.Tensor, out: torch.Tensor 
     return out
 
 
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return _lib.BF16
+    if t.dtype == torch.float32:
+        return _lib.FP32
+    raise TypeError(f"unsupported dtype {t.dtype}")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """cast(cast(x * rsqrt(mean(x^2) + eps)) * weight) over the last dim, in one pass; dtype of ``x``.
+
+    For fp32 ``x`` this is the reference's RMSNorm; for bf16 ``x`` it is RMSNorm followed by the
+    bf16 cast the next linear layer applies under autocast.
+    """
+    if not x.is_cuda:
+        raise RuntimeError("rmsnorm needs CUDA tensors: there is no CPU path")
+    dim = x.shape[-1]
+    x2 = x.reshape(-1, dim)
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    y = torch.empty_like(x2)
+    w = weight.detach()
+    if w.dtype != torch.float32 or not w.is_contiguous():
+        w = w.float().contiguous()
+    with torch.cuda.device(x.device):
+        rc = _lib.lib.pe_rmsnorm_forward(x2.data_ptr(), w.data_ptr(), y.data_ptr(), _dtype_code(x2), x2.shape[0], dim,
+                                         x2.stride(0), y.stride(0), float(eps),
+                                         C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream))
+    if rc != 0:
+        raise _lib.PeAttnError(rc)
+    return y.view(x.shape)
+
+
+def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """cast(cast(silu(gate)) * up), elementwise, one pass."""
+    if not gate.is_cuda:
+        raise RuntimeError("swiglu needs CUDA tensors: there is no CPU path")
+    if gate.shape != up.shape or gate.dtype != up.dtype:
+        raise ValueError("gate and up must have the same shape and dtype")
+    g, u = gate.contiguous(), up.contiguous()
+    y = torch.empty_like(g)
+    with torch.cuda.device(g.device):
+        rc = _lib.lib.pe_swiglu_forward(g.data_ptr(), u.data_ptr(), y.data_ptr(), _dtype_code(g), g.numel(),
+                                        C.c_void_p(torch.cuda.current_stream(g.device).cuda_stream))
+    if rc != 0:
+        raise _lib.PeAttnError(rc)
+    return y
+
+
 def attention_flops(B: int, H: int, S: int, d_qk: int, d_v: int) -> float:
     """Algorithmic causal attention FLOPs (the benchmark's convention): B H S^2 (d_qk + d_v)."""
     return float(B) * H * S * S * (d_qk + d_v)

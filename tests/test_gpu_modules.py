@@ -143,3 +143,45 @@ def test_1b_shape_16k_loss_matches_reference(golden_dir):
         nll, cnt = model.loss_sums(ids)
     got16 = (nll / cnt).item()
     assert abs(got16 - want) <= 1e-3, (got16, want)
+
+
+@pytest.mark.parametrize("dtype,rows,dim", [(torch.float32, 37, 2048), (torch.bfloat16, 1000, 2048),
+                                            (torch.bfloat16, 5, 1024), (torch.float32, 3, 64)])
+def test_fused_rmsnorm_matches_reference_formula(dtype, rows, dim):
+    from pe_ablations_b200.ops import rmsnorm
+
+    g = torch.Generator().manual_seed(rows)
+    x = (torch.randn(rows, dim, generator=g) * 2).to(dtype).cuda()
+    w = (1 + 0.1 * torch.randn(dim, generator=g)).cuda()
+    got = rmsnorm(x, w, 1e-6)
+    xf = x.float()
+    ref = (xf * torch.rsqrt(xf.square().mean(-1, keepdim=True) + 1e-6)).type_as(x) * w   # normalization.py:22-27
+    ref = ref.to(dtype)                                                                   # the next linear's autocast
+    assert got.dtype == dtype and got.shape == x.shape
+    if dtype == torch.float32:
+        assert torch.allclose(got, ref, rtol=2e-6, atol=1e-7)
+    else:
+        d = (got.float() - ref.float()).abs()
+        assert (d > 0).float().mean().item() < 0.02           # a different summation order flips few roundings
+        assert (d <= ref.float().abs() * 2 ** -7 + 1e-6).all()  # and never by more than one bf16 ulp
+    # a strided view (rows of a wider tensor) is read in place
+    wide = torch.zeros(rows, dim + 64, dtype=dtype, device="cuda")
+    wide[:, :dim] = x
+    assert torch.equal(rmsnorm(wide[:, :dim], w, 1e-6), got)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_fused_swiglu_matches_reference_formula(dtype):
+    from pe_ablations_b200.ops import swiglu
+
+    g = torch.Generator().manual_seed(3)
+    a = (torch.randn(257, 5632, generator=g) * 3).to(dtype).cuda()
+    b = torch.randn(257, 5632, generator=g).to(dtype).cuda()
+    got = swiglu(a, b)
+    ref = torch.nn.functional.silu(a) * b            # ffn.py:27,68
+    if dtype == torch.float32:
+        assert torch.allclose(got, ref, rtol=2e-6, atol=1e-7)
+    else:
+        d = (got.float() - ref.float()).abs()
+        assert (d > 0).float().mean().item() < 0.01
+        assert (d <= ref.float().abs() * 2 ** -7 + 1e-6).all()
