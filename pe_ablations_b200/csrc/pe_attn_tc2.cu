@@ -370,14 +370,18 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
           for (int c = 0; c < BLOCK_N; ++c)
             if (key0 + c > row_lim || key0 + c >= p.Sk) t[c] = -INFINITY;
         }
-        float mx0 = t[0], mx1 = t[1], mx2 = t[2], mx3 = t[3];
+        float mx0 = fmax3(t[0], t[1], t[2]), mx1 = fmax3(t[3], t[4], t[5]), mx2 = fmax3(t[6], t[7], t[8]),
+              mx3 = fmax3(t[9], t[10], t[11]);
 #pragma unroll
-        for (int c = 4; c < BLOCK_N; c += 4) {
-          mx0 = fmaxf(mx0, t[c]);
-          mx1 = fmaxf(mx1, t[c + 1]);
-          mx2 = fmaxf(mx2, t[c + 2]);
-          mx3 = fmaxf(mx3, t[c + 3]);
+        for (int c = 12; c + 8 <= BLOCK_N; c += 8) {
+          mx0 = fmax3(mx0, t[c], t[c + 1]);
+          mx1 = fmax3(mx1, t[c + 2], t[c + 3]);
+          mx2 = fmax3(mx2, t[c + 4], t[c + 5]);
+          mx3 = fmax3(mx3, t[c + 6], t[c + 7]);
         }
+        // 12 + 14 * 8 = 124: the last four columns
+        mx0 = fmax3(mx0, t[BLOCK_N - 4], t[BLOCK_N - 3]);
+        mx1 = fmax3(mx1, t[BLOCK_N - 2], t[BLOCK_N - 1]);
         const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
 
         // ---- lazy rescale of the running output
@@ -406,23 +410,27 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
 
         // ---- exponentials, row sum, P as bf16 pairs over the first 64 columns of this S tile
         // (every S value of the row is already in registers)
-        const float neg_m = -m_used * kf;
-        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        // scale-and-shift and the row sum use the packed fp32x2 FMA / ADD of sm_100 (half the
+        // issue slots of scalar code); the exponentials stay on the special-function unit
+        const float2 kf2 = make_float2(kf, kf), nm2 = make_float2(-m_used * kf, -m_used * kf);
+        float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
 #pragma unroll
         for (int cb = 0; cb < BLOCK_N / 32; ++cb) {
           uint32_t pk[16];
 #pragma unroll
           for (int c = 0; c < 32; c += 4) {
-            const float p0 = ex2_approx(fmaf(t[cb * 32 + c], kf, neg_m));
-            const float p1 = ex2_approx(fmaf(t[cb * 32 + c + 1], kf, neg_m));
-            const float p2 = ex2_approx(fmaf(t[cb * 32 + c + 2], kf, neg_m));
-            const float p3 = ex2_approx(fmaf(t[cb * 32 + c + 3], kf, neg_m));
-            a0 += p0; a1 += p1; a2 += p2; a3 += p3;
-            pk[c >> 1] = pack_bf16x2(p0, p1);
-            pk[(c >> 1) + 1] = pack_bf16x2(p2, p3);
+            const float2 x01 = __ffma2_rn(make_float2(t[cb * 32 + c], t[cb * 32 + c + 1]), kf2, nm2);
+            const float2 x23 = __ffma2_rn(make_float2(t[cb * 32 + c + 2], t[cb * 32 + c + 3]), kf2, nm2);
+            const float2 p01 = make_float2(ex2_approx(x01.x), ex2_approx(x01.y));
+            const float2 p23 = make_float2(ex2_approx(x23.x), ex2_approx(x23.y));
+            acc0 = __fadd2_rn(acc0, p01);
+            acc1 = __fadd2_rn(acc1, p23);
+            pk[c >> 1] = pack_bf16x2(p01.x, p01.y);
+            pk[(c >> 1) + 1] = pack_bf16x2(p23.x, p23.y);
           }
           tmem_st16(s_addr + cb * 16, pk);
         }
+        const float a0 = acc0.x, a1 = acc0.y, a2 = acc1.x, a3 = acc1.y;
         l_sum += (a0 + a1) + (a2 + a3);
         tmem_wait_st();
         tc_fence_before_sync();
@@ -515,12 +523,22 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
           const uint32_t w[4] = {cur[k].x, cur[k].y, cur[k].z, cur[k].w};
           float oc[8], os[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const float x = (e & 1) ? bf16_hi(w[e >> 1]) : bf16_lo(w[e >> 1]);
-            const float mu = softplus_fast(x);
-            const float mc = mu * cb[e], ms = mu * sb[e];
-            oc[e] = mc * tcs[k][e] - ms * tsn[k][e];
-            os[e] = ms * tcs[k][e] + mc * tsn[k][e];
+          for (int e = 0; e < 8; e += 2) {
+            // two columns at a time with the packed fp32x2 FMA / MUL / ADD
+            const float2 x = make_float2(bf16_lo(w[e >> 1]), bf16_hi(w[e >> 1]));
+            const float2 ex = __fmul2_rn(make_float2(-fabsf(x.x), -fabsf(x.y)), make_float2(1.4426950408889634f, 1.4426950408889634f));
+            const float2 on = __fadd2_rn(make_float2(ex2_approx(ex.x), ex2_approx(ex.y)), make_float2(1.0f, 1.0f));
+            const float2 mu = __ffma2_rn(make_float2(lg2_approx(on.x), lg2_approx(on.y)),
+                                         make_float2(0.6931471805599453f, 0.6931471805599453f),
+                                         make_float2(fmaxf(x.x, 0.f), fmaxf(x.y, 0.f)));
+            const float2 mc = __fmul2_rn(mu, make_float2(cb[e], cb[e + 1]));
+            const float2 ms = __fmul2_rn(mu, make_float2(sb[e], sb[e + 1]));
+            const float2 tc2 = make_float2(tcs[k][e], tcs[k][e + 1]), ts2 = make_float2(tsn[k][e], tsn[k][e + 1]);
+            // cos(a + b) = ca cb - sa sb ; sin(a + b) = sa cb + ca sb
+            const float2 c2v = __ffma2_rn(mc, tc2, __fmul2_rn(make_float2(-ms.x, -ms.y), ts2));
+            const float2 s2v = __ffma2_rn(ms, tc2, __fmul2_rn(mc, ts2));
+            oc[e] = c2v.x; oc[e + 1] = c2v.y;
+            os[e] = s2v.x; os[e + 1] = s2v.y;
           }
           sts_v4(kb + off_c + swz(r, slot_c), make_uint4(pack_bf16x2(oc[0], oc[1]), pack_bf16x2(oc[2], oc[3]),
                                                          pack_bf16x2(oc[4], oc[5]), pack_bf16x2(oc[6], oc[7])));
