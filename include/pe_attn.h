@@ -156,6 +156,14 @@ const char* pe_attn_status_string(int status);
 /* Algorithmic FLOPs of one call: B * H * (causal pairs) * 2 * (d_c + 2 d_r + d_v). */
 double pe_attn_flops(const pe_attn_args* args);
 
+/* Failure-reporting self-test (no counterpart in the reference).  Launches one warp that
+ * waits, with the same bounded wait the attention kernels use, on a barrier nothing ever
+ * signals.  After ``limit_cycles`` SM clocks the wait gives up, the kernel ORs
+ * PE_ATTN_SELFTEST_WAIT_EXPIRED into *device_status and returns normally; the context stays
+ * usable.  Shows on a live GPU that an expired wait is reported, not hung on. */
+#define PE_ATTN_SELFTEST_WAIT_EXPIRED 0x40000000
+int pe_attn_selftest_wait_expiry(int32_t* device_status, int64_t limit_cycles, void* stream);
+
 /* ---- perplexity evaluation: next-token cross-entropy as loss sums ------------------------
  *
  * Replaces, for the evaluation path, F.cross_entropy on the shifted logits

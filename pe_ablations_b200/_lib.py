@@ -28,7 +28,7 @@ EXPORTS = (
     "pe_attn_version", "pe_attn_forward", "pe_attn_validate", "pe_attn_kernel_name",
     "pe_attn_last_error", "pe_attn_status_string", "pe_attn_flops",
     "pe_ce_scratch_bytes", "pe_ce_loss_sums", "pe_ce_static_max_rows", "pe_ce_loss_sums_static",
-    "pe_rmsnorm_forward", "pe_swiglu_forward",
+    "pe_rmsnorm_forward", "pe_swiglu_forward", "pe_attn_selftest_wait_expiry",
 )
 
 
@@ -82,6 +82,8 @@ def _load() -> C.CDLL:
                                        C.c_int64, C.c_float, C.c_void_p]
     lib.pe_swiglu_forward.restype = C.c_int
     lib.pe_swiglu_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_void_p]
+    lib.pe_attn_selftest_wait_expiry.restype = C.c_int
+    lib.pe_attn_selftest_wait_expiry.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]
     lib.pe_ce_static_max_rows.restype = C.c_int
     lib.pe_ce_loss_sums_static.restype = C.c_int
     lib.pe_ce_loss_sums_static.argtypes = [C.c_void_p, C.c_int, C.c_int64, C.c_void_p, C.c_int, C.c_int, C.c_int,

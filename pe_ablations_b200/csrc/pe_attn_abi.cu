@@ -5,6 +5,7 @@
 #include <cstring>
 
 #include "pe_attn_common.cuh"
+#include "pe_attn_ptx.cuh"
 
 namespace pe_attn {
 
@@ -128,7 +129,30 @@ static int validate(const pe_attn_args* a, KParams* out) {
 
 using namespace pe_attn;
 
+// One warp waits, with the kernels' bounded wait, on a barrier that nothing ever signals.
+__global__ void wait_expiry_selftest_kernel(int* status, long long limit_cycles) {
+  __shared__ uint64_t bar;
+  const uint32_t b = ptx::smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(b, 1);
+    ptx::mbar_fence_init();
+  }
+  __syncthreads();
+  const bool ok = ptx::mbar_wait_for(b, 0, limit_cycles);
+  if (!ok && threadIdx.x == 0) atomicOr(status, PE_ATTN_SELFTEST_WAIT_EXPIRED);
+}
+
 extern "C" {
+
+int pe_attn_selftest_wait_expiry(int32_t* device_status, int64_t limit_cycles, void* stream) {
+  if (device_status == nullptr) return fail(PE_ATTN_ERR_NULL, "device_status is null");
+  if (limit_cycles < 1000 || limit_cycles > 2000000000ll)
+    return fail(PE_ATTN_ERR_SHAPE, "limit_cycles must be in [1e3, 2e9] (got %lld)", (long long)limit_cycles);
+  wait_expiry_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(device_status, limit_cycles);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(PE_ATTN_ERR_LAUNCH, "self-test launch failed: %s", cudaGetErrorString(e));
+  return PE_ATTN_OK;
+}
 
 int pe_attn_version(void) { return PE_ATTN_ABI_VERSION; }
 

@@ -53,15 +53,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait.  Returns false when the limit (about half a second of SM clocks) runs
 // out; the caller then records an error code and leaves through the common exit.
 constexpr long long kWaitLimitCycles = 1000000000ll;
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_for(uint32_t bar, uint32_t parity, long long limit_cycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    if (clock64() - t0 > kWaitLimitCycles) return false;
+    if (clock64() - t0 > limit_cycles) return false;
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  return mbar_wait_for(bar, parity, kWaitLimitCycles);
 }
 
 // Latency-critical variant: polls with the non-blocking test instead of the suspending

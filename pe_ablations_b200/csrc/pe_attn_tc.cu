@@ -371,14 +371,17 @@ pe_attn_tc_kernel(const KParams p, const int bh_group, const __grid_constant__ C
           for (int c = 0; c < 64; ++c)
             if (key0 + c > row_lim || key0 + c >= p.Sk) t[c] = -INFINITY;
         }
-        float mx0 = t[0], mx1 = t[1], mx2 = t[2], mx3 = t[3];
+        float mx0 = fmax3(t[0], t[1], t[2]), mx1 = fmax3(t[3], t[4], t[5]), mx2 = fmax3(t[6], t[7], t[8]),
+              mx3 = fmax3(t[9], t[10], t[11]);
 #pragma unroll
-        for (int c = 4; c < 64; c += 4) {
-          mx0 = fmaxf(mx0, t[c]);
-          mx1 = fmaxf(mx1, t[c + 1]);
-          mx2 = fmaxf(mx2, t[c + 2]);
-          mx3 = fmaxf(mx3, t[c + 3]);
+        for (int c = 12; c + 8 <= 64; c += 8) {
+          mx0 = fmax3(mx0, t[c], t[c + 1]);
+          mx1 = fmax3(mx1, t[c + 2], t[c + 3]);
+          mx2 = fmax3(mx2, t[c + 4], t[c + 5]);
+          mx3 = fmax3(mx3, t[c + 6], t[c + 7]);
         }
+        mx0 = fmax3(mx0, t[60], t[61]);   // 12 + 6 * 8 = 60: the last four columns
+        mx1 = fmax3(mx1, t[62], t[63]);
         const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
         const float kf = ALIBI ? 1.0f : c2;  // t is already in log2 units with ALiBi
         // lazy rescale: move the reference maximum only when it grows by more than 2^8
@@ -405,19 +408,22 @@ pe_attn_tc_kernel(const KParams p, const int bh_group, const __grid_constant__ C
           l_sum *= alpha;
           if (need) m_used = mx;
         }
-        const float neg_m = -m_used * kf;
-        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        // packed fp32x2 FMA / ADD for scale-and-shift and the row sum; exponentials on the SFU
+        const float2 kf2 = make_float2(kf, kf), nm2 = make_float2(-m_used * kf, -m_used * kf);
+        float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
         uint32_t pk[32];
 #pragma unroll
         for (int c = 0; c < 64; c += 4) {
-          const float p0 = ex2_approx(fmaf(t[c], kf, neg_m));
-          const float p1 = ex2_approx(fmaf(t[c + 1], kf, neg_m));
-          const float p2 = ex2_approx(fmaf(t[c + 2], kf, neg_m));
-          const float p3 = ex2_approx(fmaf(t[c + 3], kf, neg_m));
-          a0 += p0; a1 += p1; a2 += p2; a3 += p3;
-          pk[c >> 1] = pack_bf16x2(p0, p1);
-          pk[(c >> 1) + 1] = pack_bf16x2(p2, p3);
+          const float2 x01 = __ffma2_rn(make_float2(t[c], t[c + 1]), kf2, nm2);
+          const float2 x23 = __ffma2_rn(make_float2(t[c + 2], t[c + 3]), kf2, nm2);
+          const float2 p01 = make_float2(ex2_approx(x01.x), ex2_approx(x01.y));
+          const float2 p23 = make_float2(ex2_approx(x23.x), ex2_approx(x23.y));
+          acc0 = __fadd2_rn(acc0, p01);
+          acc1 = __fadd2_rn(acc1, p23);
+          pk[c >> 1] = pack_bf16x2(p01.x, p01.y);
+          pk[(c >> 1) + 1] = pack_bf16x2(p23.x, p23.y);
         }
+        const float a0 = acc0.x, a1 = acc0.y, a2 = acc1.x, a3 = acc1.y;
         l_sum += (a0 + a1) + (a2 + a3);
         tmem_st32(s_addr, pk);  // P over the first 32 columns of this S buffer
         tmem_wait_st();
@@ -512,12 +518,21 @@ pe_attn_tc_kernel(const KParams p, const int bh_group, const __grid_constant__ C
           const uint32_t w[4] = {cur[k].x, cur[k].y, cur[k].z, cur[k].w};
           float oc[8], os[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const float x = (e & 1) ? bf16_hi(w[e >> 1]) : bf16_lo(w[e >> 1]);
-            const float mu = softplus_fast(x);
-            const float mc = mu * cb[e], ms = mu * sb[e];
-            oc[e] = mc * tcs[k][e] - ms * tsn[k][e];
-            os[e] = ms * tcs[k][e] + mc * tsn[k][e];
+          for (int e = 0; e < 8; e += 2) {
+            // two columns at a time with the packed fp32x2 FMA / MUL / ADD
+            const float2 x = make_float2(bf16_lo(w[e >> 1]), bf16_hi(w[e >> 1]));
+            const float2 ex = __fmul2_rn(make_float2(-fabsf(x.x), -fabsf(x.y)), make_float2(1.4426950408889634f, 1.4426950408889634f));
+            const float2 on = __fadd2_rn(make_float2(ex2_approx(ex.x), ex2_approx(ex.y)), make_float2(1.0f, 1.0f));
+            const float2 mu = __ffma2_rn(make_float2(lg2_approx(on.x), lg2_approx(on.y)),
+                                         make_float2(0.6931471805599453f, 0.6931471805599453f),
+                                         make_float2(fmaxf(x.x, 0.f), fmaxf(x.y, 0.f)));
+            const float2 mc = __fmul2_rn(mu, make_float2(cb[e], cb[e + 1]));
+            const float2 ms = __fmul2_rn(mu, make_float2(sb[e], sb[e + 1]));
+            const float2 tc2 = make_float2(tcs[k][e], tcs[k][e + 1]), ts2 = make_float2(tsn[k][e], tsn[k][e + 1]);
+            const float2 c2v = __ffma2_rn(mc, tc2, __fmul2_rn(make_float2(-ms.x, -ms.y), ts2));
+            const float2 s2v = __ffma2_rn(ms, tc2, __fmul2_rn(mc, ts2));
+            oc[e] = c2v.x; oc[e + 1] = c2v.y;
+            os[e] = s2v.x; os[e + 1] = s2v.y;
           }
           sts_v4(kb + off_c + swz(r, slot_c), make_uint4(pack_bf16x2(oc[0], oc[1]), pack_bf16x2(oc[2], oc[3]),
                                                          pack_bf16x2(oc[4], oc[5]), pack_bf16x2(oc[6], oc[7])));

@@ -207,3 +207,29 @@ def test_abi_rejects_bad_arguments_on_gpu():
         pe_attention("nope", q, q, q, mask=torch.ones(1))
     with pytest.raises(RuntimeError):
         pe_attention("nope", q.cpu(), q.cpu(), q.cpu())
+
+
+def test_expired_wait_is_reported_and_context_survives():
+    """A bounded wait that runs out sets the status word; nothing hangs, the next launch works."""
+    import ctypes as C
+
+    from pe_ablations_b200 import _lib as L
+    from pe_ablations_b200 import check_device_status
+    from pe_ablations_b200.ops import device_status
+    from tests.gpu_util import case_error
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    word = device_status(dev)
+    word.zero_()
+    stream = torch.cuda.current_stream().cuda_stream
+    assert L.lib.pe_attn_selftest_wait_expiry(word.data_ptr(), 2_000_000, C.c_void_p(stream)) == 0  # ~1 ms
+    torch.cuda.synchronize()
+    assert int(word.item()) == 0x40000000
+    with pytest.raises(RuntimeError, match="expired waits"):
+        check_device_status()
+    assert int(word.item()) == 0          # the wrapper clears the word after reporting
+    err, _, _ = case_error(Case("after_expiry", "pope", BF16, 1, 2, 2, 300, 128, 64, 128, seed=91))
+    assert err <= 2e-2
+    assert L.lib.pe_attn_selftest_wait_expiry(None, 2_000_000, None) == 1
+    assert L.lib.pe_attn_selftest_wait_expiry(word.data_ptr(), 10, None) == 3
