@@ -544,20 +544,23 @@ pe_attn_tc_kernel(const KParams p, const int bh_group, const __grid_constant__ C
         if (lane == 0) mbar_arrive(bar(BAR_KFULL + s));
       }
     } else if constexpr (MODE == MODE_XFORM) {
+      // raw rows and table entries of the next tile are requested before the wait for its stage
+      XformRegs<DC> xr;
+      if (n_tiles > 0) xform_load<DC>(p, xr, p.k, b, hk, 0, p.Sk, p.k_pos0, tg);
 #pragma unroll 1
       for (int j = 0; j < n_tiles; ++j) {
         const int s = j & 1;
         const bool ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_KEMPTY + s), (uint32_t)(((j >> 1) & 1) ^ 1)));
         if (!ok) { fail(ST_WAIT_KEMPTY); break; }
-        build_slab<DC, DR, MODE>(p, k_smem + s * C::K_STAGE_BYTES, C::K_CHUNK_BYTES, p.k, p.kr, b, hk, j * BLOCK_N,
-                                 p.Sk, p.k_pos0 + j * BLOCK_N, true, freq_s, delta_s, tg);
+        xform_finish<DC>(p, xr, k_smem + s * C::K_STAGE_BYTES, C::K_CHUNK_BYTES, j * BLOCK_N, p.Sk, tg);
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(BAR_KFULL + s));
+        if (j + 1 < n_tiles)
+          xform_load<DC>(p, xr, p.k, b, hk, (j + 1) * BLOCK_N, p.Sk, p.k_pos0 + (j + 1) * BLOCK_N, tg);
       }
     }
   }
-
   }  // register-budget branch
 
   // common exit: after a failed wait give copies in flight time to land before the

@@ -550,17 +550,23 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
         if (lane == 0) mbar_arrive_cluster(s ? kfull1 : kfull);
       }
     } else if constexpr (MODE == MODE_XFORM) {
+      // raw rows and table entries of the next tile are requested before the wait for its stage
+      XformRegs<DC> xr;
+      const int rbase = (int)rank * HALF_N;
+      if (n_tiles > 0) xform_load<DC>(p, xr, p.k, b, hk, rbase, p.Sk, p.k_pos0 + rbase, tg);
 #pragma unroll 1
       for (int j = 0; j < n_tiles; ++j) {
         const int s = j & 1;
         const bool ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_KEMPTY + s), (uint32_t)(((j >> 1) & 1) ^ 1)));
         if (!ok) { fail(ST_WAIT_KEMPTY); break; }
-        const int r0 = j * BLOCK_N + (int)rank * HALF_N;
-        build_slab<DC, DR, MODE>(p, k_smem + s * C::K_STAGE_BYTES, C::K_CHUNK_BYTES, p.k, p.kr, b, hk, r0, p.Sk,
-                                 p.k_pos0 + r0, true, freq_s, delta_s, tg);
+        xform_finish<DC>(p, xr, k_smem + s * C::K_STAGE_BYTES, C::K_CHUNK_BYTES, j * BLOCK_N + rbase, p.Sk, tg);
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(lbar(BAR_KFULL + s));
+        if (j + 1 < n_tiles) {
+          const int r0 = (j + 1) * BLOCK_N + rbase;
+          xform_load<DC>(p, xr, p.k, b, hk, r0, p.Sk, p.k_pos0 + r0, tg);
+        }
       }
     }
   }

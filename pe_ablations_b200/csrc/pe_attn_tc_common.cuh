@@ -42,6 +42,95 @@ __device__ __forceinline__ void sincos_reduced(float x, float* s, float* c) {
 // byte offset of the 16-byte slot ``slot`` (0..7) of row ``r`` inside a 128B-swizzled chunk
 __device__ __forceinline__ uint32_t swz(int r, int slot) { return (uint32_t)(r * 128 + ((slot ^ (r & 7)) << 4)); }
 
+// Rotary family / QKNorm operand rows in two steps, so that a K-tile loop can issue the loads
+// of the next tile before it waits for the stage to become free: the raw rows and their
+// (cos, sin) table entries for the 64-row slab, then rotation, mscale, L2 normalisation and the
+// swizzled stores.  Thread (r_in, cv) owns columns [8 cv, 8 cv + 8) of rows r_in + k * RPP.
+template <int DC>
+struct XformRegs {
+  static constexpr int VPR = DC / 8, RPP = 128 / VPR, PASSES = SLAB_ROWS / RPP;
+  uint4 raw[PASSES];
+  float4 t0[PASSES], t1[PASSES];
+};
+
+template <int DC>
+__device__ __forceinline__ void xform_load(const KParams& p, XformRegs<DC>& x, const TensorRef& content, int b,
+                                           int head, int row0, int n_rows, int pos_row0, int tg) {
+  using X = XformRegs<DC>;
+  const int cv = tg % X::VPR, r_in = tg / X::VPR;
+  const bool rotary = p.variant == PE_ATTN_ROTARY;
+  const char* src = reinterpret_cast<const char*>(content.ptr) +
+                    2 * ((long long)b * content.sb + (long long)head * content.sh + (long long)cv * 8);
+#pragma unroll
+  for (int k = 0; k < X::PASSES; ++k) {
+    const int r = r_in + k * X::RPP;
+    const bool live = (row0 + r) < n_rows;
+    x.raw[k] = live ? ldg_nc_v4(src + 2 * (long long)(row0 + r) * content.ss) : make_uint4(0, 0, 0, 0);
+    x.t0[k] = x.t1[k] = make_float4(1.f, 0.f, 1.f, 0.f);
+    if (rotary && live) {
+      const int trow = pos_row0 + r - p.table_pos0;
+      const float4* tp = reinterpret_cast<const float4*>(p.table + ((size_t)trow * (DC / 2) + cv * 4) * 2);
+      x.t0[k] = __ldg(tp);
+      x.t1[k] = __ldg(tp + 1);
+    }
+  }
+}
+
+template <int DC>
+__device__ __forceinline__ void xform_finish(const KParams& p, XformRegs<DC>& x, uint32_t base, uint32_t chunk_stride,
+                                             int row0, int n_rows, int tg) {
+  using X = XformRegs<DC>;
+  const int cv = tg % X::VPR, r_in = tg / X::VPR;
+  const bool rotary = p.variant == PE_ATTN_ROTARY;
+  const bool norm = (p.flags & PE_ATTN_QK_NORM) != 0;
+  float ss[X::PASSES];
+#pragma unroll
+  for (int k = 0; k < X::PASSES; ++k) {
+    uint32_t w[4] = {x.raw[k].x, x.raw[k].y, x.raw[k].z, x.raw[k].w};
+    if (rotary) {
+      const float cs[4] = {x.t0[k].x, x.t0[k].z, x.t1[k].x, x.t1[k].z};
+      const float sn[4] = {x.t0[k].y, x.t0[k].w, x.t1[k].y, x.t1[k].w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float x0 = bf16_lo(w[e]), x1 = bf16_hi(w[e]);
+        const float o0 = x0 * cs[e] - x1 * sn[e];
+        const float o1 = x0 * sn[e] + x1 * cs[e];
+        w[e] = pack_bf16x2(o0, o1);
+        if (p.mscale != 1.0f) w[e] = pack_bf16x2(bf16_lo(w[e]) * p.mscale, bf16_hi(w[e]) * p.mscale);
+      }
+    }
+    float acc = 0.f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float x0 = bf16_lo(w[e]), x1 = bf16_hi(w[e]);
+      acc = fmaf(x0, x0, acc);
+      acc = fmaf(x1, x1, acc);
+    }
+    ss[k] = acc;
+    x.raw[k] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  if (norm) {
+    // row sum of squares across the VPR lanes that share a row (warp-level reduction)
+#pragma unroll
+    for (int k = 0; k < X::PASSES; ++k) {
+#pragma unroll
+      for (int d = 1; d < X::VPR; d <<= 1) ss[k] += __shfl_xor_sync(0xffffffffu, ss[k], d);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < X::PASSES; ++k) {
+    const int r = r_in + k * X::RPP;
+    uint32_t w[4] = {x.raw[k].x, x.raw[k].y, x.raw[k].z, x.raw[k].w};
+    if (norm) {
+      const float inv = 1.0f / (sqrtf(ss[k]) + p.eps);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) w[e] = pack_bf16x2(bf16_lo(w[e]) * inv, bf16_hi(w[e]) * inv);
+    }
+    const int col = cv * 8;
+    sts_v4(base + (col / 64) * chunk_stride + swz(r, (col % 64) / 8), make_uint4(w[0], w[1], w[2], w[3]));
+  }
+}
+
 // Build 64 operand rows (positional / transformed columns only) in shared memory with a
 // group of 128 threads (tg = 0..127).  ``base`` is the shared address of chunk 0 at the
 // slab's first row (1024-byte aligned), chunks are ``chunk_stride`` bytes apart.
@@ -99,71 +188,9 @@ __device__ __forceinline__ void build_slab(const KParams& p, uint32_t base, uint
       sts_v4(base + (col_s / 64) * chunk_stride + swz(r, (col_s % 64) / 8), vs);
     }
   } else if constexpr (MODE == MODE_XFORM) {
-    constexpr int VPR = DC / 8;
-    constexpr int RPP = 128 / VPR;
-    constexpr int PASSES = SLAB_ROWS / RPP;
-    const int cv = tg % VPR, r_in = tg / VPR;
-    const bool rotary = p.variant == PE_ATTN_ROTARY;
-    const bool norm = (p.flags & PE_ATTN_QK_NORM) != 0;
-    const char* src = reinterpret_cast<const char*>(content.ptr) +
-                      2 * ((long long)b * content.sb + (long long)head * content.sh + (long long)cv * 8);
-    uint4 pk[PASSES];
-    float ss[PASSES];
-#pragma unroll
-    for (int k = 0; k < PASSES; ++k) {
-      const int grow = row0 + r_in + k * RPP;
-      pk[k] = make_uint4(0, 0, 0, 0);
-      if (grow < n_rows) pk[k] = ldg_nc_v4(src + 2 * (long long)grow * content.ss);
-    }
-#pragma unroll
-    for (int k = 0; k < PASSES; ++k) {
-      const int r = r_in + k * RPP;
-      const bool live = (row0 + r) < n_rows;
-      uint32_t w[4] = {pk[k].x, pk[k].y, pk[k].z, pk[k].w};
-      if (rotary && live) {
-        const int trow = pos_row0 + r - p.table_pos0;
-        const float4* tp = reinterpret_cast<const float4*>(p.table + ((size_t)trow * (DC / 2) + cv * 4) * 2);
-        const float4 t0 = __ldg(tp), t1 = __ldg(tp + 1);
-        const float cs[4] = {t0.x, t0.z, t1.x, t1.z}, sn[4] = {t0.y, t0.w, t1.y, t1.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float x0 = bf16_lo(w[e]), x1 = bf16_hi(w[e]);
-          const float o0 = x0 * cs[e] - x1 * sn[e];
-          const float o1 = x0 * sn[e] + x1 * cs[e];
-          w[e] = pack_bf16x2(o0, o1);
-          if (p.mscale != 1.0f) w[e] = pack_bf16x2(bf16_lo(w[e]) * p.mscale, bf16_hi(w[e]) * p.mscale);
-        }
-      }
-      float acc = 0.f;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float x0 = bf16_lo(w[e]), x1 = bf16_hi(w[e]);
-        acc = fmaf(x0, x0, acc);
-        acc = fmaf(x1, x1, acc);
-      }
-      ss[k] = acc;
-      pk[k] = make_uint4(w[0], w[1], w[2], w[3]);
-    }
-    if (norm) {
-      // row sum of squares across the VPR lanes that share a row (warp-level reduction)
-#pragma unroll
-      for (int k = 0; k < PASSES; ++k) {
-#pragma unroll
-        for (int d = 1; d < VPR; d <<= 1) ss[k] += __shfl_xor_sync(0xffffffffu, ss[k], d);
-      }
-    }
-#pragma unroll
-    for (int k = 0; k < PASSES; ++k) {
-      const int r = r_in + k * RPP;
-      uint32_t w[4] = {pk[k].x, pk[k].y, pk[k].z, pk[k].w};
-      if (norm) {
-        const float inv = 1.0f / (sqrtf(ss[k]) + p.eps);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) w[e] = pack_bf16x2(bf16_lo(w[e]) * inv, bf16_hi(w[e]) * inv);
-      }
-      const int col = cv * 8;
-      sts_v4(base + (col / 64) * chunk_stride + swz(r, (col % 64) / 8), make_uint4(w[0], w[1], w[2], w[3]));
-    }
+    XformRegs<DC> x;
+    xform_load<DC>(p, x, content, b, head, row0, n_rows, pos_row0, tg);
+    xform_finish<DC>(p, x, base, chunk_stride, row0, n_rows, tg);
   }
 }
 
