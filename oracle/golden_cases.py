@@ -63,6 +63,12 @@ MODULE_CASES = [
          use_qk_norm=True, delta_init="uniform", n_fourier=8, sigma=0.4, training_length=32),
 ]
 
+# cached decoding through the reference's FPoPEGroupedQueryAttentionWithCache: a prefill of
+# CACHE_PREFILL tokens, then steps of the listed lengths, all with use_cache=True
+CACHE_CASE = dict(name="m_fpope_cache", hidden=128, H=4, Hkv=2, head_dim=32, d_rope=16, B=2, use_qk_norm=True,
+                  n_fourier=8, sigma=0.4, training_length=32, delta_init="uniform", max_cache_len=64)
+CACHE_PREFILL, CACHE_STEPS = 40, (1, 1, 5, 1)
+
 # whole-model level: tiny Transformer per pe_mode, deterministic weights, loss + logits sample
 MODEL_CASES = [
     dict(name="t_rope", pe_mode="rope"),

@@ -193,6 +193,60 @@ class FPoPEGroupedQueryAttention(nn.Module):
         return self.wo(out.view(B, S, self.num_heads * self.head_dim).to(x.dtype))
 
 
+class FPoPEGroupedQueryAttentionWithCache(FPoPEGroupedQueryAttention):
+    """FPoPEGroupedQueryAttention with a KV cache for autoregressive decoding
+    (src/model/fpope_attention.py:184-327).
+
+    The reference caches the already-transformed keys; here the cache holds the RAW content
+    and position halves of K (and V), [B, max_cache_len, Hkv, d], and the kernel transforms
+    the cached keys at use with their absolute positions -- same output, and the phase bias /
+    frequencies stay live.  ``forward(..., use_cache=True)`` appends the new tokens at
+    ``start_pos`` and attends over everything cached so far (key s visible to the new token
+    at position t iff s <= t).
+    """
+
+    def __init__(self, hidden_dim: int, num_heads: int, num_kv_heads: int, head_dim: int = 64, d_rope: int = 32,
+                 use_qk_norm: bool = True, fpope: nn.Module | None = None, max_cache_len: int = 2048):
+        super().__init__(hidden_dim, num_heads, num_kv_heads, head_dim, d_rope, use_qk_norm, fpope)
+        self.max_cache_len = max_cache_len
+        self.k_cache = self.kr_cache = self.v_cache = None
+        self.cache_len = 0
+
+    def reset_cache(self) -> None:
+        self.k_cache = self.kr_cache = self.v_cache = None
+        self.cache_len = 0
+
+    def forward(self, x: torch.Tensor, mask: torch.Tensor | None = None, start_pos: int = 0,
+                use_cache: bool = False) -> torch.Tensor:
+        if not use_cache:
+            return super().forward(x, mask, start_pos)
+        _check_call(x, mask)
+        B, S, _ = x.shape
+        if start_pos + S > self.max_cache_len:
+            raise ValueError(f"start_pos + seq_len = {start_pos + S} exceeds max_cache_len = {self.max_cache_len}")
+        q_c = self.wq_c(x).view(B, S, self.num_heads, self.d_content)
+        k_c = self.wk_c(x).view(B, S, self.num_kv_heads, self.d_content)
+        q_r, k_r = self.wq_r(x), self.wk_r(x)
+        if self.qr_norm is not None:
+            q_r, k_r = self.qr_norm(q_r), self.kr_norm(k_r)
+        dt = _kernel_dtype(q_c)
+        q_r = q_r.to(dt).view(B, S, self.num_heads, self.d_rope)
+        k_r = k_r.to(dt).view(B, S, self.num_kv_heads, self.d_rope)
+        v = self.wv(x).view(B, S, self.num_kv_heads, self.head_dim)
+        if self.k_cache is None or self.k_cache.shape[0] != B or self.k_cache.dtype != dt or self.k_cache.device != x.device:
+            mk = lambda d: torch.zeros(B, self.max_cache_len, self.num_kv_heads, d, dtype=dt, device=x.device)
+            self.k_cache, self.kr_cache, self.v_cache = mk(self.d_content), mk(self.d_rope), mk(self.head_dim)
+        self.k_cache[:, start_pos:start_pos + S] = k_c.to(dt)
+        self.kr_cache[:, start_pos:start_pos + S] = k_r
+        self.v_cache[:, start_pos:start_pos + S] = v.to(dt)
+        self.cache_len = start_pos + S
+        n = self.cache_len
+        out = pe_attention("pope", q_c.to(dt), self.k_cache[:, :n], self.v_cache[:, :n], q_r=q_r,
+                           k_r=self.kr_cache[:, :n], start_pos=start_pos, k_start_pos=0, scale=self.scale,
+                           **self._pe_args())
+        return self.wo(out.view(B, S, self.num_heads * self.head_dim).to(x.dtype))
+
+
 def install(namespace=None) -> None:
     """Rebind the reference's attention classes to the fused ones.
 

@@ -200,6 +200,25 @@ def main():
                 mods[f"{spec['name']}/buf/{bname}"] = buf.float().numpy()
         mods[f"{spec['name']}/state_keys"] = np.array(sorted(m.state_dict().keys()))
         print(spec["name"], tuple(y.shape), float(y.abs().mean()))
+    # cached decoding (src/model/fpope_attention.py:184-327)
+    from src.model.fpope_attention import FPoPEGroupedQueryAttentionWithCache
+    cc = G.CACHE_CASE
+    torch.manual_seed(1500)
+    pe = FoPEPoPEEmbedding(dim=cc["d_rope"], max_seq_len=cc["max_cache_len"], num_fourier_terms=cc["n_fourier"],
+                           fourier_sigma=cc["sigma"], training_length=cc["training_length"],
+                           delta_init=cc["delta_init"])
+    m = FPoPEGroupedQueryAttentionWithCache(cc["hidden"], cc["H"], cc["Hkv"], cc["head_dim"], cc["d_rope"],
+                                            cc["use_qk_norm"], pe, max_cache_len=cc["max_cache_len"]).eval()
+    G.fill_parameters(m, 2500)
+    total = G.CACHE_PREFILL + sum(G.CACHE_STEPS)
+    x = torch.randn(cc["B"], total, cc["hidden"], generator=torch.Generator().manual_seed(3500))
+    outs, pos = [], 0
+    with torch.no_grad():
+        for n in (G.CACHE_PREFILL,) + tuple(G.CACHE_STEPS):
+            outs.append(m(x[:, pos:pos + n], start_pos=pos, use_cache=True))
+            pos += n
+    mods[f"{cc['name']}/y"] = torch.cat(outs, dim=1).numpy()
+    print(cc["name"], tuple(mods[f"{cc['name']}/y"].shape))
     np.savez_compressed(os.path.join(HERE, "modules.npz"), **mods)
 
     models = {}
