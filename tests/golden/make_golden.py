@@ -142,7 +142,7 @@ def build_module(spec, R):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a checkout of the reference project")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     torch.set_num_threads(max(1, os.cpu_count() or 1))

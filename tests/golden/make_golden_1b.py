@@ -25,7 +25,7 @@ from oracle import golden_cases as G  # noqa: E402
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a checkout of the reference project")
     ap.add_argument("--seq-len", type=int, default=G.MODEL_1B_SEQ)
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
