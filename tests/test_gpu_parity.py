@@ -233,3 +233,35 @@ def test_expired_wait_is_reported_and_context_survives():
     assert err <= 2e-2
     assert L.lib.pe_attn_selftest_wait_expiry(None, 2_000_000, None) == 1
     assert L.lib.pe_attn_selftest_wait_expiry(word.data_ptr(), 10, None) == 3
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_bhsd_layout_and_strided_views(dtype):
+    """[B, H, S, d] storage and sliced (non-contiguous batch / head) views are read in place."""
+    from pe_ablations_b200 import check_device_status, pe_attention
+    from oracle import pe_attention_oracle as O
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(7)
+    B, H, Hkv, S, dc, dr, dv = 2, 4, 2, 330, 128, 64, 128
+    mk = lambda h, d: torch.randn(B, S, h, d, generator=g)
+    q, k, q_r, k_r, v = mk(H, dc), mk(Hkv, dc), mk(H, dr), mk(Hkv, dr), mk(Hkv, dv)
+    freqs = O.pope_base_freqs(dr)
+    delta = -torch.rand(dr, generator=g) * 3
+    want = O.attention_core("pope", q, k, v, dtype=dtype, q_r=q_r, k_r=k_r, freqs=freqs, delta=delta).float()
+    tol = TOL[dtype]
+    c = lambda t: t.to(dev, dtype)
+    # (a) [B, H, S, d] contiguous storage
+    t = lambda x: c(x).transpose(1, 2).contiguous()
+    out = pe_attention("pope", t(q), t(k), t(v), q_r=t(q_r), k_r=t(k_r), freqs=freqs, delta=delta, layout="bhsd")
+    assert out.shape == (B, H, S, dv)
+    assert (out.transpose(1, 2).float().cpu() - want).abs().max().item() <= tol
+    # (b) views into wider buffers: padded batch and a fused [q | k | v]-style last dimension
+    big = torch.zeros(B + 1, S, H, dc + 64, dtype=dtype, device=dev)
+    big[1:, :, :, :dc] = c(q)
+    qv = big[1:, :, :, :dc]
+    assert not qv.is_contiguous()
+    out2 = pe_attention("pope", qv, c(k), c(v), q_r=c(q_r), k_r=c(k_r), freqs=freqs, delta=delta)
+    torch.cuda.synchronize()
+    check_device_status()
+    assert (out2.float().cpu() - want).abs().max().item() <= tol

@@ -116,3 +116,29 @@ def test_fope_effective_freqs_host_formula_matches_oracle():
     want = O.fope_effective_freqs(e.base_freqs, e.fourier_coeffs.detach(), 128)
     assert torch.allclose(e.effective_freqs(), want, rtol=1e-6, atol=0)
     assert (want == 0).any()  # the floor clip is active at this size
+
+
+def test_install_rebinds_the_three_attention_classes():
+    import types
+
+    from pe_ablations_b200 import modules as M
+
+    ns = types.SimpleNamespace(GroupedQueryAttention=object, ALiBiAttention=object, FPoPEGroupedQueryAttention=object,
+                               RMSNorm=object)
+    M.install(ns)
+    assert ns.GroupedQueryAttention is M.GroupedQueryAttention
+    assert ns.ALiBiAttention is M.ALiBiAttention
+    assert ns.FPoPEGroupedQueryAttention is M.FPoPEGroupedQueryAttention
+    assert ns.RMSNorm is object      # only the attention classes are replaced
+
+
+def test_cache_module_constructor_and_state_dict():
+    from pe_ablations_b200 import modules as M
+    from pe_ablations_b200 import pe as P
+
+    pe = P.PoPEEmbedding(dim=16, max_seq_len=32)
+    m = M.FPoPEGroupedQueryAttentionWithCache(64, 2, 1, 32, 16, True, pe, max_cache_len=128)
+    base = M.FPoPEGroupedQueryAttention(64, 2, 1, 32, 16, True, pe)
+    assert sorted(m.state_dict().keys()) == sorted(base.state_dict().keys())   # cache buffers are not persistent
+    assert m.cache_len == 0 and m.max_cache_len == 128
+    m.reset_cache()
