@@ -9,7 +9,7 @@ The CUDA library is loaded on first use of any of them and there is no fallback:
 symbol, that first use raises ImportError.  Only ``build_ext`` can be imported without it.
 """
 
-__all__ = ["pe_attention", "ce_loss_sums", "check_device_status", "attention_flops"]
+__all__ = ["pe_attention", "HostStreamedAttention", "ce_loss_sums", "check_device_status", "attention_flops"]
 
 
 def __getattr__(name):

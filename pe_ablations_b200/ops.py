@@ -221,6 +221,86 @@ def pe_attention(
     return out
 
 
+class HostStreamedAttention:
+    """Causal PE-attention over pinned HOST tensors, with the copies hidden behind the kernels.
+
+    The inputs of a long sequence take longer to cross PCIe than the kernel takes to
+    consume them, so the sequence is cut into ``chunks`` row blocks.  Causality makes block
+    c of the queries depend only on key/value blocks 0..c: block c is copied in on one
+    stream, its attention (queries of block c against keys 0..end of c, ``start_pos`` =
+    first row of c) is launched on the caller's stream as soon as the copy has landed, and
+    its output rows go back on a third stream while block c+1 is still arriving.  Each
+    block runs the same kernel over the same 128-key tiles as the one-shot call, so the
+    result is the one ``pe_attention`` gives on device copies of the same tensors.
+
+    The staging tensors (one device copy of every input and of the output) are allocated
+    once here and reused by every call; the caller's stream waits for the last output
+    block before ``__call__`` returns control of it, so work queued afterwards -- and CUDA
+    events recorded around the call -- see the whole transfer + compute.
+    """
+
+    def __init__(self, variant: str, *, B: int, S: int, H: int, Hkv: int, d_c: int, d_r: int, d_v: int,
+                 dtype: torch.dtype, device, chunks: int = 8, **params):
+        if variant not in _VARIANTS:
+            raise ValueError(f"unknown variant {variant!r}")
+        if chunks < 1 or S % chunks != 0:
+            raise ValueError("chunks must divide the sequence length")
+        self.variant, self.params, self.chunks = variant, params, chunks
+        self.device = torch.device(device)
+        self.shape = dict(B=B, S=S, H=H, Hkv=Hkv, d_c=d_c, d_r=d_r, d_v=d_v)
+        mk = lambda h, d: torch.empty(B, S, h, d, dtype=dtype, device=self.device) if d else None  # noqa: E731
+        self.stage = dict(q=mk(H, d_c), k=mk(Hkv, d_c), q_r=mk(H, d_r), k_r=mk(Hkv, d_r), v=mk(Hkv, d_v))
+        self.out = mk(H, d_v)
+        self.h2d = torch.cuda.Stream(self.device)
+        self.d2h = torch.cuda.Stream(self.device)
+
+    def __call__(self, host: dict[str, torch.Tensor], out_host: torch.Tensor) -> torch.Tensor:
+        for name, t in self.stage.items():
+            if t is None:
+                continue
+            h = host[name]
+            if h.is_cuda or not h.is_pinned() or not h.is_contiguous() or h.shape != t.shape or h.dtype != t.dtype:
+                raise ValueError(f"host[{name!r}] must be a pinned contiguous CPU tensor of shape {tuple(t.shape)}")
+        if (out_host.is_cuda or not out_host.is_pinned() or not out_host.is_contiguous()
+                or out_host.shape != self.out.shape):
+            raise ValueError("out_host must be a pinned CPU tensor of the output shape")
+        S, rows = self.shape["S"], self.shape["S"] // self.chunks
+        main = torch.cuda.current_stream(self.device)
+        # the staging tensors may still be read by kernels the caller queued earlier
+        start = torch.cuda.Event()
+        start.record(main)
+        self.h2d.wait_event(start)
+        self.d2h.wait_event(start)
+        st = self.stage
+        for c in range(self.chunks):
+            s0, s1 = c * rows, (c + 1) * rows
+            with torch.cuda.stream(self.h2d):
+                # keys and values first: they are what the block's kernel streams through
+                # one copy per batch entry: each [b, s0:s1] block is contiguous on both sides,
+                # so it is a single DMA transfer with no host-side repacking
+                for name in ("k", "k_r", "v", "q", "q_r"):
+                    if st[name] is not None:
+                        for b in range(self.shape["B"]):
+                            st[name][b, s0:s1].copy_(host[name][b, s0:s1], non_blocking=True)
+                landed = torch.cuda.Event()
+                landed.record(self.h2d)
+            main.wait_event(landed)
+            sl = lambda t, a, b: None if t is None else t[:, a:b]  # noqa: E731
+            pe_attention(self.variant, sl(st["q"], s0, s1), sl(st["k"], 0, s1), st["v"][:, :s1],
+                         q_r=sl(st["q_r"], s0, s1), k_r=sl(st["k_r"], 0, s1),
+                         start_pos=s0, k_start_pos=0, out=self.out[:, s0:s1], **self.params)
+            done = torch.cuda.Event()
+            done.record(main)
+            with torch.cuda.stream(self.d2h):
+                self.d2h.wait_event(done)
+                for b in range(self.shape["B"]):
+                    out_host[b, s0:s1].copy_(self.out[b, s0:s1], non_blocking=True)
+        back = torch.cuda.Event()
+        back.record(self.d2h)
+        main.wait_event(back)
+        return out_host
+
+
 _ce_scratch: dict[tuple[int, int], torch.Tensor] = {}
 
 

@@ -265,3 +265,35 @@ def test_bhsd_layout_and_strided_views(dtype):
     torch.cuda.synchronize()
     check_device_status()
     assert (out2.float().cpu() - want).abs().max().item() <= tol
+
+
+@pytest.mark.parametrize("chunks", [1, 4])
+def test_host_streamed_call_equals_the_device_call(chunks):
+    """Pinned host tensors in, pinned host tensor out, copies pipelined over sequence blocks:
+    bit-identical to the one-shot call on device copies, and within tolerance of the oracle."""
+    from pe_ablations_b200 import HostStreamedAttention, check_device_status, pe_attention
+    from oracle import pe_attention_oracle as O
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(11)
+    B, H, Hkv, S, dc, dr, dv = 2, 4, 2, 2048, 128, 64, 128
+    mk = lambda h, d: torch.randn(B, S, h, d, generator=g).to(torch.bfloat16).pin_memory()
+    host = dict(q=mk(H, dc), k=mk(Hkv, dc), q_r=mk(H, dr), k_r=mk(Hkv, dr), v=mk(Hkv, dv))
+    freqs = O.pope_base_freqs(dr)
+    delta = -torch.rand(dr, generator=g) * 3
+    call = HostStreamedAttention("pope", B=B, S=S, H=H, Hkv=Hkv, d_c=dc, d_r=dr, d_v=dv, dtype=torch.bfloat16,
+                                 device=dev, chunks=chunks, freqs=freqs, delta=delta)
+    out_host = torch.full((B, S, H, dv), float("nan"), dtype=torch.bfloat16).pin_memory()
+    for _ in range(2):                      # the second call reuses the staging tensors
+        call(host, out_host)
+    torch.cuda.synchronize()
+    check_device_status()
+    d = {n: t.to(dev) for n, t in host.items()}
+    one_shot = pe_attention("pope", d["q"], d["k"], d["v"], q_r=d["q_r"], k_r=d["k_r"], freqs=freqs, delta=delta)
+    assert torch.equal(out_host, one_shot.cpu())
+    f = lambda t: t.float()
+    want = O.attention_core("pope", f(host["q"]), f(host["k"]), f(host["v"]), dtype=torch.bfloat16,
+                            q_r=f(host["q_r"]), k_r=f(host["k_r"]), freqs=freqs, delta=delta).float()
+    assert (out_host.float() - want).abs().max().item() <= TOL[torch.bfloat16]
+    with pytest.raises(ValueError):
+        call({**host, "q": host["q"].clone()}, out_host)      # not pinned
