@@ -49,7 +49,7 @@
 extern "C" {
 #endif
 
-#define PE_ATTN_ABI_VERSION 1
+#define PE_ATTN_ABI_VERSION 2
 
 typedef enum pe_attn_variant {
   PE_ATTN_NOPE = 0,   /* no positional transform                                            */
@@ -130,6 +130,10 @@ typedef struct pe_attn_args {
                               /* ORs a non-zero code into it if one of its bounded waits      */
                               /* expires (the output is then invalid); never written on      */
                               /* success.  May be null.                                      */
+  float* lse;                 /* optional [B, H, Sq] fp32, contiguous: natural-log logsumexp  */
+                              /* of each query row's scaled, biased, masked logits -- what    */
+                              /* pe_attn_backward needs to rebuild the probabilities.  May    */
+                              /* be null.                                                    */
 } pe_attn_args;
 
 /* ABI version of the loaded library (PE_ATTN_ABI_VERSION at build time). */
@@ -163,6 +167,43 @@ double pe_attn_flops(const pe_attn_args* args);
  * usable.  Shows on a live GPU that an expired wait is reported, not hung on. */
 #define PE_ATTN_SELFTEST_WAIT_EXPIRED 0x40000000
 int pe_attn_selftest_wait_expiry(int32_t* device_status, int64_t limit_cycles, void* stream);
+
+/* ---- attention backward (the gradient autograd derives from the SDPA call) ------------------
+ *
+ * Gradients of  out = softmax_causal(scale * Q K^T + bias) V  with respect to Q, K and V, for
+ * bf16 operands that already carry their positional transform: the quantity PyTorch's
+ * autograd produces for F.scaled_dot_product_attention at src/model/attention.py:91-96,
+ * src/model/fpope_attention.py:171-177 and for the explicit softmax of
+ * src/model/alibi.py:145-160 (bias = -slope_h * (t - s) when alibi_slopes is given).  The
+ * reference's deleted extension exposed the same step as the backward of
+ * fpope_attention_forward (debug_backward.py:108-124; gradient tolerances 1e-2 there).
+ * The backward of the positional transform itself is left to the caller (the Python host
+ * differentiates its own restatement of the transform).
+ *
+ * q [B,H,Sq,d_qk], k [B,Hkv,Sk,d_qk], v [B,Hkv,Sk,d_v], out / dout [B,H,Sq,d_v]: bf16, element
+ * strides (batch, head, seq), 16-byte aligned, strides multiples of 8.  lse: the forward's
+ * logsumexp output [B,H,Sq] fp32.  dq_accum: fp32 [B,H,Sq,d_qk] contiguous -- cleared and
+ * then accumulated into by the call (atomic adds: bitwise results vary between runs);
+ * dk / dv: bf16 outputs shaped and strided like k / v (each written exactly once); dvec:
+ * fp32 [B,H,Sq] workspace.  (d_qk, d_v) in {(64,64), (128,64), (128,128)}.  Causal rule as
+ * in the forward: key s is visible to query row r iff s <= r + (Sk - Sq). */
+typedef struct pe_attn_bwd_args {
+  uint32_t struct_size;       /* sizeof(pe_attn_bwd_args), checked                            */
+  int32_t B, H, Hkv, Sq, Sk, d_qk, d_v;
+  float scale;
+  const void *q, *k, *v, *out, *dout;
+  int64_t q_stride[3], k_stride[3], v_stride[3], out_stride[3], dout_stride[3];
+  const float* lse;
+  const float* alibi_slopes;  /* [H] fp32 or null                                            */
+  float* dq_accum;
+  void* dk;
+  void* dv;
+  int64_t dk_stride[3], dv_stride[3];
+  float* dvec;
+  int32_t* device_status;     /* as in pe_attn_args; may be null                             */
+} pe_attn_bwd_args;
+
+int pe_attn_backward(const pe_attn_bwd_args* args, void* stream);
 
 /* ---- perplexity evaluation: next-token cross-entropy as loss sums ------------------------
  *

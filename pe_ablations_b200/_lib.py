@@ -28,7 +28,7 @@ EXPORTS = (
     "pe_attn_version", "pe_attn_forward", "pe_attn_validate", "pe_attn_kernel_name",
     "pe_attn_last_error", "pe_attn_status_string", "pe_attn_flops",
     "pe_ce_scratch_bytes", "pe_ce_loss_sums", "pe_ce_static_max_rows", "pe_ce_loss_sums_static",
-    "pe_rmsnorm_forward", "pe_swiglu_forward", "pe_attn_selftest_wait_expiry",
+    "pe_rmsnorm_forward", "pe_swiglu_forward", "pe_attn_selftest_wait_expiry", "pe_attn_backward",
 )
 
 
@@ -47,7 +47,23 @@ class PeAttnArgs(C.Structure):
         ("rotary_table", C.c_void_p), ("table_pos0", C.c_int32), ("table_rows", C.c_int32),
         ("alibi_slopes", C.c_void_p), ("freqs", C.c_void_p), ("delta", C.c_void_p),
         ("fourier_coeffs", C.c_void_p), ("n_fourier", C.c_int32), ("floor_freq", C.c_float),
-        ("ceil_freq", C.c_float), ("device_status", C.c_void_p),
+        ("ceil_freq", C.c_float), ("device_status", C.c_void_p), ("lse", C.c_void_p),
+    ]
+
+
+class PeAttnBwdArgs(C.Structure):
+    """Mirror of ``struct pe_attn_bwd_args``."""
+
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("B", C.c_int32), ("H", C.c_int32), ("Hkv", C.c_int32), ("Sq", C.c_int32), ("Sk", C.c_int32),
+        ("d_qk", C.c_int32), ("d_v", C.c_int32), ("scale", C.c_float),
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p), ("dout", C.c_void_p),
+        ("q_stride", C.c_int64 * 3), ("k_stride", C.c_int64 * 3), ("v_stride", C.c_int64 * 3),
+        ("out_stride", C.c_int64 * 3), ("dout_stride", C.c_int64 * 3),
+        ("lse", C.c_void_p), ("alibi_slopes", C.c_void_p), ("dq_accum", C.c_void_p),
+        ("dk", C.c_void_p), ("dv", C.c_void_p), ("dk_stride", C.c_int64 * 3), ("dv_stride", C.c_int64 * 3),
+        ("dvec", C.c_void_p), ("device_status", C.c_void_p),
     ]
 
 
@@ -84,6 +100,8 @@ def _load() -> C.CDLL:
     lib.pe_swiglu_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_void_p]
     lib.pe_attn_selftest_wait_expiry.restype = C.c_int
     lib.pe_attn_selftest_wait_expiry.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]
+    lib.pe_attn_backward.restype = C.c_int
+    lib.pe_attn_backward.argtypes = [C.POINTER(PeAttnBwdArgs), C.c_void_p]
     lib.pe_ce_static_max_rows.restype = C.c_int
     lib.pe_ce_loss_sums_static.restype = C.c_int
     lib.pe_ce_loss_sums_static.argtypes = [C.c_void_p, C.c_int, C.c_int64, C.c_void_p, C.c_int, C.c_int, C.c_int,

@@ -102,6 +102,7 @@ static int validate(const pe_attn_args* a, KParams* out) {
   k.freqs = a->freqs; k.delta = a->delta; k.coeffs = a->fourier_coeffs; k.n_fourier = a->n_fourier;
   k.floor_freq = a->floor_freq; k.ceil_freq = a->ceil_freq;
   k.status = a->device_status;
+  k.lse = a->lse;
 
   const bool use_tc = a->dtype == PE_ATTN_BF16 && !(a->flags & PE_ATTN_SIMT_CHECK);
   if (use_tc) {
@@ -152,6 +153,55 @@ int pe_attn_selftest_wait_expiry(int32_t* device_status, int64_t limit_cycles, v
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(PE_ATTN_ERR_LAUNCH, "self-test launch failed: %s", cudaGetErrorString(e));
   return PE_ATTN_OK;
+}
+
+int pe_attn_backward(const pe_attn_bwd_args* a, void* stream) {
+  if (a == nullptr) return fail(PE_ATTN_ERR_NULL, "args is null");
+  if (a->struct_size != sizeof(pe_attn_bwd_args))
+    return fail(PE_ATTN_ERR_VARIANT, "struct_size %u does not match this library's %zu", a->struct_size,
+                sizeof(pe_attn_bwd_args));
+  if (a->B < 1 || a->H < 1 || a->Hkv < 1 || a->Sq < 1 || a->Sk < 1)
+    return fail(PE_ATTN_ERR_SHAPE, "B, H, Hkv, Sq, Sk must be positive");
+  if (a->H % a->Hkv != 0) return fail(PE_ATTN_ERR_SHAPE, "H=%d is not a multiple of Hkv=%d", a->H, a->Hkv);
+  if (a->Sk < a->Sq) return fail(PE_ATTN_ERR_SHAPE, "Sk=%d < Sq=%d", a->Sk, a->Sq);
+  if (a->B > 65535 || a->Hkv > 65535) return fail(PE_ATTN_ERR_SHAPE, "B and Hkv must be <= 65535");
+  if (!bwd_supports(a->d_qk, a->d_v))
+    return fail(PE_ATTN_ERR_SHAPE, "backward supports (d_qk, d_v) in {(64,64), (128,64), (128,128)} (got %d, %d)",
+                a->d_qk, a->d_v);
+  struct { const char* name; const void* p; const int64_t* s; } ts[] = {
+      {"q", a->q, a->q_stride},       {"k", a->k, a->k_stride},   {"v", a->v, a->v_stride},
+      {"out", a->out, a->out_stride}, {"dout", a->dout, a->dout_stride},
+      {"dk", a->dk, a->dk_stride},    {"dv", a->dv, a->dv_stride}};
+  for (auto& t : ts) {
+    if (t.p == nullptr) return fail(PE_ATTN_ERR_NULL, "%s is null", t.name);
+    if (!aligned16(t.p)) return fail(PE_ATTN_ERR_ALIGNMENT, "%s is not 16-byte aligned", t.name);
+    for (int i = 0; i < 3; ++i)
+      if (t.s[i] % 8 != 0)
+        return fail(PE_ATTN_ERR_ALIGNMENT, "%s stride[%d]=%lld is not a multiple of 8 elements", t.name, i,
+                    (long long)t.s[i]);
+  }
+  if (a->lse == nullptr || a->dq_accum == nullptr || a->dvec == nullptr)
+    return fail(PE_ATTN_ERR_NULL, "lse, dq_accum and dvec are required");
+  if (!aligned16(a->dq_accum)) return fail(PE_ATTN_ERR_ALIGNMENT, "dq_accum is not 16-byte aligned");
+  int dev = 0, major = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
+      major != 10)
+    return fail(PE_ATTN_ERR_DEVICE, "no sm_100 device is current");
+  BwdParams p;
+  memset(&p, 0, sizeof(p));
+  p.B = a->B; p.H = a->H; p.Hkv = a->Hkv; p.groups = a->H / a->Hkv;
+  p.Sq = a->Sq; p.Sk = a->Sk; p.causal_off = a->Sk - a->Sq;
+  p.scale = a->scale;
+  p.q = make_ref(a->q, a->q_stride);
+  p.k = make_ref(a->k, a->k_stride);
+  p.v = make_ref(a->v, a->v_stride);
+  p.out = make_ref(a->out, a->out_stride);
+  p.dout = make_ref(a->dout, a->dout_stride);
+  p.dk = make_ref(a->dk, a->dk_stride);
+  p.dv = make_ref(a->dv, a->dv_stride);
+  p.lse = a->lse; p.slopes = a->alibi_slopes;
+  p.dq_accum = a->dq_accum; p.dvec = a->dvec; p.status = a->device_status;
+  return launch_bwd(p, a->d_qk, a->d_v, a->alibi_slopes != nullptr, static_cast<cudaStream_t>(stream));
 }
 
 int pe_attn_version(void) { return PE_ATTN_ABI_VERSION; }

@@ -1,0 +1,415 @@
+// Causal attention BACKWARD on the 5th-generation tensor cores (sm_100a): gradients of
+//   out = softmax_causal(scale * Q K^T + bias) V
+// with respect to Q, K and V, for bf16 operands that already carry their positional transform
+// (the [q_c | mu cos | mu sin] rows of the PoPE family, rotated rows of the rotary family, plain
+// rows otherwise; bias = ALiBi's -slope * distance or nothing).  It is the part of the
+// reference's training step that autograd derives from F.scaled_dot_product_attention
+// (src/model/attention.py:91-96, src/model/fpope_attention.py:171-177, src/model/alibi.py:145-160);
+// the transform's own backward stays with the caller.
+//
+// One CTA owns 128 keys of one key/value head and walks over the query blocks that can see
+// them (all query heads of the GQA group in turn).  Per query block, five MMAs:
+//     S  = Q K^T           dP = dO V^T                      (accumulators in TMEM)
+//     P  = exp(scale S + bias - lse),  dS = scale * P o (dP - D)   (4 warps, one row each,
+//                                                            written to shared memory as bf16)
+//     dV += P^T dO         dK += dS^T Q         dQ = dS K
+// Q, K, dO and V tiles are loaded once by TMA in the 128-byte-swizzled layout; the same bytes
+// serve as K-major operands (S, dP) and as MN-major ones (dV, dK, dQ), and P / dS are read
+// K-major for dQ and MN-major (transposed) for dV / dK, so nothing is transposed in memory.
+// dK and dV stay in TMEM for the whole CTA; dQ of each block is added to an fp32 buffer in
+// global memory with vector atomics (its summation order across key blocks is therefore not
+// fixed).  D = rowsum(dO o O) comes from a small kernel that runs first.
+//
+// TMEM columns: S / dQ [0,128)  dP [128,256)  dV [256,256+DV)  dK [256+DV, 256+DV+DQK).
+// Warps 0-3: softmax-gradient math and epilogues; warp 4: TMA; warp 5: TMEM + MMA issue.
+// Every wait is bounded and reports through the device status word.
+
+#include <cuda.h>
+#include <string.h>
+
+#include "pe_attn_tc_common.cuh"
+
+namespace pe_attn {
+namespace {
+
+using namespace ptx;
+using namespace tc;
+
+constexpr int BM = 128;          // query rows per block
+constexpr int BN = 128;          // keys per CTA
+constexpr int NTHREADS = 192;
+constexpr int CH = 128 * 128;    // bytes of one 128-row x 64-column bf16 chunk
+constexpr int TMEM_COLS = 512;
+constexpr int ST_WAIT_BWD = 1 << 9;
+
+enum : int { BAR_KV = 0, BAR_LD, BAR_S, BAR_P, BAR_DQ, BAR_SFREE, NUM_BARS };
+
+template <int DQK, int DV>
+struct BCfg {
+  static constexpr int NQC = DQK / 64, NVC = DV / 64;
+  static constexpr int K_OFF = 1024;
+  static constexpr int V_OFF = K_OFF + NQC * CH;
+  static constexpr int Q_OFF = V_OFF + NVC * CH;
+  static constexpr int DO_OFF = Q_OFF + NQC * CH;
+  static constexpr int P_OFF = DO_OFF + NVC * CH;
+  static constexpr int DS_OFF = P_OFF + 2 * CH;
+  static constexpr int SMEM_BYTES = DS_OFF + 2 * CH + 1024;  // slack to align the base to 1024
+  static_assert(DQK == 64 || DQK == 128, "d_qk must be 64 or 128");
+  static_assert(DV == 64 || DV == 128, "d_v must be 64 or 128");
+  static_assert(256 + DV + DQK <= TMEM_COLS, "TMEM budget exceeded");
+  static_assert(SMEM_BYTES <= 232448, "shared memory budget exceeded");
+};
+
+template <int DQK, int DV, bool ALIBI>
+__global__ void __launch_bounds__(NTHREADS, 1)
+pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO) {
+  using C = BCfg<DQK, DV>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + 256);
+  auto bar = [&](int idx) -> uint32_t { return smem_base + 8u * (uint32_t)idx; };
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int key0 = (int)blockIdx.x * BN, hk = (int)blockIdx.y, b = (int)blockIdx.z;
+  const int n_qblk = (p.Sq + BM - 1) / BM;
+  // query row r sees key s iff s <= r + causal_off: the first block with a row that sees key0
+  int first_row = key0 - p.causal_off;
+  if (first_row < 0) first_row = 0;
+  const int i_first = first_row / BM;
+  const int per_head = n_qblk > i_first ? n_qblk - i_first : 0;
+  const int n_iter = per_head * p.groups;
+
+  auto fail = [&]() {
+    if (p.status != nullptr) atomicOr(p.status, ST_WAIT_BWD);
+  };
+
+  if (tid == 0) {
+    mbar_init(bar(BAR_KV), 1);
+    mbar_init(bar(BAR_LD), 1);
+    mbar_init(bar(BAR_S), 1);
+    mbar_init(bar(BAR_P), 4);
+    mbar_init(bar(BAR_DQ), 1);
+    mbar_init(bar(BAR_SFREE), 4);
+    mbar_fence_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 5) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const uint32_t k_smem = smem_base + C::K_OFF, v_smem = smem_base + C::V_OFF, q_smem = smem_base + C::Q_OFF,
+                 do_smem = smem_base + C::DO_OFF, p_smem = smem_base + C::P_OFF, ds_smem = smem_base + C::DS_OFF;
+  constexpr uint32_t LD_BYTES = (uint32_t)((C::NQC + C::NVC) * CH);
+
+  if (warp == 4) {
+    // ===================== TMA producer =====================
+    if (n_iter > 0) {
+      if (elect_one()) {
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmDO);
+        mbar_arrive_expect_tx(bar(BAR_KV), LD_BYTES);
+#pragma unroll
+        for (int c = 0; c < C::NQC; ++c) tma_load_4d(k_smem + c * CH, &tmK, bar(BAR_KV), c * 64, key0, hk, b);
+#pragma unroll
+        for (int c = 0; c < C::NVC; ++c) tma_load_4d(v_smem + c * CH, &tmV, bar(BAR_KV), c * 64, key0, hk, b);
+      }
+      __syncwarp();
+#pragma unroll 1
+      for (int it = 0; it < n_iter; ++it) {
+        const int h = hk * p.groups + it / per_head, i = i_first + it % per_head;
+        // the previous block's dV / dK / dQ products have finished reading Q and dO
+        if (it > 0 && !__all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_DQ), (uint32_t)((it - 1) & 1)))) { fail(); break; }
+        if (elect_one()) {
+          mbar_arrive_expect_tx(bar(BAR_LD), LD_BYTES);
+#pragma unroll
+          for (int c = 0; c < C::NQC; ++c) tma_load_4d(q_smem + c * CH, &tmQ, bar(BAR_LD), c * 64, i * BM, h, b);
+#pragma unroll
+          for (int c = 0; c < C::NVC; ++c) tma_load_4d(do_smem + c * CH, &tmDO, bar(BAR_LD), c * 64, i * BM, h, b);
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp == 5) {
+    // ===================== MMA issuer =====================
+    constexpr uint32_t IDESC_S = make_idesc_bf16_mn(BM, BN, false, false);    // S, dP: both K-major
+    constexpr uint32_t IDESC_DV = make_idesc_bf16_mn(BN, DV, true, true);     // P^T dO
+    constexpr uint32_t IDESC_DK = make_idesc_bf16_mn(BN, DQK, true, true);    // dS^T Q
+    constexpr uint32_t IDESC_DQ = make_idesc_bf16_mn(BM, DQK, false, true);   // dS K
+    // K-major view: 8-row groups 1024 bytes apart, 16 elements (32 bytes) per K step
+    const uint64_t q_k = make_smem_desc(q_smem, 16, 1024), k_k = make_smem_desc(k_smem, 16, 1024);
+    const uint64_t do_k = make_smem_desc(do_smem, 16, 1024), v_k = make_smem_desc(v_smem, 16, 1024);
+    const uint64_t ds_k = make_smem_desc(ds_smem, 16, 1024);
+    // MN-major view of the same bytes: 64-wide MN chunks CH bytes apart, 16 K rows = 2048 bytes
+    const uint64_t p_mn = make_smem_desc(p_smem, CH, 1024), ds_mn = make_smem_desc(ds_smem, CH, 1024);
+    const uint64_t do_mn = make_smem_desc(do_smem, CH, 1024), q_mn = make_smem_desc(q_smem, CH, 1024);
+    const uint64_t k_mn = make_smem_desc(k_smem, CH, 1024);
+    const uint32_t t_s = tmem_base, t_dp = tmem_base + 128u, t_dv = tmem_base + 256u,
+                   t_dk = tmem_base + 256u + (uint32_t)DV;
+    bool ok = n_iter == 0 || __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_KV), 0));
+    if (!ok) fail();
+#pragma unroll 1
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const uint32_t ph = (uint32_t)(it & 1);
+      ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_LD), ph));
+      // the S columns double as dQ: the previous block's dQ has been read out
+      if (ok && it > 0) ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_SFREE), ph ^ 1u));
+      if (!ok) { fail(); break; }
+      tc_fence_after_sync();
+      if (elect_one()) {
+#pragma unroll
+        for (int c = 0; c < C::NQC; ++c)
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4)
+            mma_ss(t_s, advance_smem_desc(q_k, (uint32_t)(c * CH + k4 * 32)),
+                   advance_smem_desc(k_k, (uint32_t)(c * CH + k4 * 32)), IDESC_S, (c > 0 || k4 > 0) ? 1u : 0u);
+#pragma unroll
+        for (int c = 0; c < C::NVC; ++c)
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4)
+            mma_ss(t_dp, advance_smem_desc(do_k, (uint32_t)(c * CH + k4 * 32)),
+                   advance_smem_desc(v_k, (uint32_t)(c * CH + k4 * 32)), IDESC_S, (c > 0 || k4 > 0) ? 1u : 0u);
+        tc_commit(bar(BAR_S));
+      }
+      __syncwarp();
+      ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_P), ph));
+      if (!ok) { fail(); break; }
+      tc_fence_after_sync();
+      if (elect_one()) {
+#pragma unroll
+        for (int kk = 0; kk < BM / 16; ++kk) {   // 16 query rows per step
+          const uint32_t acc = (it > 0 || kk > 0) ? 1u : 0u;
+          mma_ss(t_dv, advance_smem_desc(p_mn, (uint32_t)(kk * 2048)), advance_smem_desc(do_mn, (uint32_t)(kk * 2048)),
+                 IDESC_DV, acc);
+          mma_ss(t_dk, advance_smem_desc(ds_mn, (uint32_t)(kk * 2048)), advance_smem_desc(q_mn, (uint32_t)(kk * 2048)),
+                 IDESC_DK, acc);
+        }
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk)     // 16 keys per step
+          mma_ss(t_s, advance_smem_desc(ds_k, (uint32_t)((kk >> 2) * CH + (kk & 3) * 32)),
+                 advance_smem_desc(k_mn, (uint32_t)(kk * 2048)), IDESC_DQ, kk > 0 ? 1u : 0u);
+        tc_commit(bar(BAR_DQ));
+      }
+      __syncwarp();
+    }
+  } else {
+    // ===================== softmax gradient + epilogues: thread = row =====================
+    const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
+    const float c2 = p.scale * 1.4426950408889634f;
+    bool ok = true;
+#pragma unroll 1
+    for (int it = 0; it < n_iter; ++it) {
+      const uint32_t ph = (uint32_t)(it & 1);
+      const int h = hk * p.groups + it / per_head, i = i_first + it % per_head;
+      const int row0 = i * BM, row = row0 + tid;
+      const bool row_live = row < p.Sq;
+      const int row_lim = row + p.causal_off;
+      const long long vec_idx = ((long long)b * p.H + h) * p.Sq + row;
+      float l2 = 0.f, dsum = 0.f;
+      if (row_live) {
+        l2 = p.lse[vec_idx] * 1.4426950408889634f;
+        dsum = p.dvec[vec_idx];
+      }
+      float slope2 = 0.f;
+      if constexpr (ALIBI) slope2 = p.slopes[h] * 1.4426950408889634f;
+      const bool need_mask = (key0 + BN - 1 > row0 + p.causal_off) || (key0 + BN > p.Sk) || (row0 + BM > p.Sq);
+
+      ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_S), ph));
+      if (!ok) { fail(); break; }
+      tc_fence_after_sync();
+#pragma unroll 1
+      for (int cb = 0; cb < BN / 32; ++cb) {
+        uint32_t sr[32], dr[32];
+        tmem_ld32(tmem_base + lane_sel + (uint32_t)(cb * 32), sr);
+        tmem_ld32(tmem_base + lane_sel + 128u + (uint32_t)(cb * 32), dr);
+        tmem_wait_ld();
+        uint32_t pp[16], dd[16];
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          float pv[2], dv[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int key = key0 + cb * 32 + c + e;
+            float x = fmaf(__uint_as_float(sr[c + e]), c2, -l2);
+            if constexpr (ALIBI) x = fmaf((float)(key - row_lim), slope2, x);
+            float pe = ex2_approx(x);
+            if (need_mask && (!row_live || key > row_lim || key >= p.Sk)) pe = 0.f;
+            pv[e] = pe;
+            dv[e] = pe * (__uint_as_float(dr[c + e]) - dsum) * p.scale;
+          }
+          pp[c >> 1] = pack_bf16x2(pv[0], pv[1]);
+          dd[c >> 1] = pack_bf16x2(dv[0], dv[1]);
+        }
+        // row ``tid`` of the [query, key] tiles, keys cb*32 .. +31 = four 16-byte slots
+        const uint32_t chunk_off = (uint32_t)((cb >> 1) * CH);
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const uint32_t off = chunk_off + swz(tid, (cb & 1) * 4 + v);
+          sts_v4(p_smem + off, make_uint4(pp[v * 4], pp[v * 4 + 1], pp[v * 4 + 2], pp[v * 4 + 3]));
+          sts_v4(ds_smem + off, make_uint4(dd[v * 4], dd[v * 4 + 1], dd[v * 4 + 2], dd[v * 4 + 3]));
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_P));
+
+      // ---- dQ of this block: TMEM -> fp32 atomics
+      ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_DQ), ph));
+      if (!ok) { fail(); break; }
+      tc_fence_after_sync();
+      float* dq_row = p.dq_accum + vec_idx * DQK;
+#pragma unroll 1
+      for (int cb = 0; cb < DQK / 32; ++cb) {
+        uint32_t qr[32];
+        tmem_ld32(tmem_base + lane_sel + (uint32_t)(cb * 32), qr);
+        tmem_wait_ld();
+        if (row_live) {
+#pragma unroll
+          for (int v = 0; v < 8; ++v)
+            red_add_v4_f32(dq_row + cb * 32 + v * 4, __uint_as_float(qr[v * 4]), __uint_as_float(qr[v * 4 + 1]),
+                           __uint_as_float(qr[v * 4 + 2]), __uint_as_float(qr[v * 4 + 3]));
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_SFREE));
+    }
+
+    // ---- dV and dK of this CTA's keys: thread = key row.  The last BAR_DQ wait above covered
+    // every MMA; with no visible query block the gradients are zero.
+    const int key = key0 + tid;
+    if (ok) {
+      const bool key_live = key < p.Sk;
+      char* dv_dst = reinterpret_cast<char*>(const_cast<void*>(p.dv.ptr)) +
+                     2 * ((long long)b * p.dv.sb + (long long)hk * p.dv.sh + (long long)key * p.dv.ss);
+      char* dk_dst = reinterpret_cast<char*>(const_cast<void*>(p.dk.ptr)) +
+                     2 * ((long long)b * p.dk.sb + (long long)hk * p.dk.sh + (long long)key * p.dk.ss);
+      // tcgen05.ld is warp-collective: every lane loads, live keys store
+      auto flush = [&](char* dst, uint32_t taddr, int ncol) {
+#pragma unroll 1
+        for (int cb = 0; cb < ncol / 32; ++cb) {
+          uint32_t r[32];
+          if (n_iter > 0) {
+            tmem_ld32(taddr + (uint32_t)(cb * 32), r);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) r[c] = 0u;
+          }
+          if (key_live) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+              o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+              o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+              o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+              *reinterpret_cast<uint4*>(dst + (cb * 32 + v * 8) * 2) = o;
+            }
+          }
+        }
+      };
+      flush(dv_dst, tmem_base + lane_sel + 256u, DV);
+      flush(dk_dst, tmem_base + lane_sel + 256u + (uint32_t)DV, DQK);
+    }
+  }
+
+  // after a failed wait give copies in flight time to land before shared memory and TMEM go
+  if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 200000) {
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// D[b, h, row] = sum_d dO[b, row, h, d] * O[b, row, h, d]  (fp32), one warp per row.
+__global__ void bwd_dvec_kernel(const BwdParams p, int dv) {
+  const long long n_rows = (long long)p.B * p.H * p.Sq;
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long r = warp0; r < n_rows; r += n_warps) {
+    const int row = (int)(r % p.Sq);
+    const int h = (int)((r / p.Sq) % p.H), b = (int)(r / ((long long)p.Sq * p.H));
+    const __nv_bfloat16* o = reinterpret_cast<const __nv_bfloat16*>(p.out.ptr) + (long long)b * p.out.sb +
+                             (long long)h * p.out.sh + (long long)row * p.out.ss;
+    const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(p.dout.ptr) + (long long)b * p.dout.sb +
+                             (long long)h * p.dout.sh + (long long)row * p.dout.ss;
+    float acc = 0.f;
+    for (int d = lane * 2; d < dv; d += 64) {
+      const float2 of = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + d));
+      const float2 gf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(g + d));
+      acc = fmaf(of.x, gf.x, fmaf(of.y, gf.y, acc));
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+    if (lane == 0) p.dvec[r] = acc;
+  }
+}
+
+template <int DQK, int DV, bool ALIBI>
+int launch_bwd_instance(const BwdParams& p, cudaStream_t stream) {
+  using C = BCfg<DQK, DV>;
+  auto kern = pe_attn_bwd_kernel<DQK, DV, ALIBI>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (e != cudaSuccess) {
+      set_error("cudaFuncSetAttribute(%d bytes) failed: %s", C::SMEM_BYTES, cudaGetErrorString(e));
+      return PE_ATTN_ERR_LAUNCH;
+    }
+    configured = true;
+  }
+  CUtensorMap tmQ, tmK, tmV, tmDO;
+  if (!encode_map(&tmQ, p.q, DQK, p.Sq, p.H, p.B, BM) || !encode_map(&tmK, p.k, DQK, p.Sk, p.Hkv, p.B, BN) ||
+      !encode_map(&tmV, p.v, DV, p.Sk, p.Hkv, p.B, BN) || !encode_map(&tmDO, p.dout, DV, p.Sq, p.H, p.B, BM)) {
+    set_error("cuTensorMapEncodeTiled failed for a backward operand");
+    return PE_ATTN_ERR_LAUNCH;
+  }
+  cudaError_t e = cudaMemsetAsync(p.dq_accum, 0, sizeof(float) * (size_t)p.B * p.H * p.Sq * DQK, stream);
+  if (e != cudaSuccess) {
+    set_error("clearing dq_accum failed: %s", cudaGetErrorString(e));
+    return PE_ATTN_ERR_LAUNCH;
+  }
+  const long long n_rows = (long long)p.B * p.H * p.Sq;
+  long long dblocks = (n_rows + 7) / 8;
+  if (dblocks > 148 * 16) dblocks = 148 * 16;
+  bwd_dvec_kernel<<<(unsigned)dblocks, 256, 0, stream>>>(p, DV);
+  dim3 grid((unsigned)((p.Sk + BN - 1) / BN), (unsigned)p.Hkv, (unsigned)p.B), block(NTHREADS);
+  kern<<<grid, block, C::SMEM_BYTES, stream>>>(p, tmQ, tmK, tmV, tmDO);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("backward kernel launch failed: %s", cudaGetErrorString(e));
+    return PE_ATTN_ERR_LAUNCH;
+  }
+  return PE_ATTN_OK;
+}
+
+}  // namespace
+
+bool bwd_supports(int d_qk, int d_v) {
+  return (d_qk == 64 && d_v == 64) || (d_qk == 128 && d_v == 64) || (d_qk == 128 && d_v == 128);
+}
+
+int launch_bwd(const BwdParams& p, int d_qk, int d_v, bool alibi, cudaStream_t stream) {
+  if (d_qk == 64 && d_v == 64)
+    return alibi ? launch_bwd_instance<64, 64, true>(p, stream) : launch_bwd_instance<64, 64, false>(p, stream);
+  if (d_qk == 128 && d_v == 64)
+    return alibi ? launch_bwd_instance<128, 64, true>(p, stream) : launch_bwd_instance<128, 64, false>(p, stream);
+  return alibi ? launch_bwd_instance<128, 128, true>(p, stream) : launch_bwd_instance<128, 128, false>(p, stream);
+}
+
+}  // namespace pe_attn

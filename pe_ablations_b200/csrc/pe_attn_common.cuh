@@ -36,6 +36,21 @@ struct KParams {
   int n_fourier;
   float floor_freq, ceil_freq;
   int* status;
+  float* lse;  // optional [B, H, Sq] logsumexp output
+};
+
+// Device-side arguments of the attention backward (operands already transformed).
+struct BwdParams {
+  int B, H, Hkv, groups;
+  int Sq, Sk;
+  int causal_off;          // key s visible to query row r iff s <= r + causal_off
+  float scale;
+  TensorRef q, k, v, out, dout, dk, dv;
+  const float* lse;        // [B, H, Sq] from the forward
+  const float* slopes;     // ALiBi, or null
+  float* dq_accum;         // [B, H, Sq, d_qk] fp32, cleared by the launch
+  float* dvec;             // [B, H, Sq] fp32 workspace
+  int* status;
 };
 
 constexpr float kTwoPi = 6.283185307179586f;
@@ -86,6 +101,9 @@ int launch_tc2(const KParams& p, cudaStream_t stream);  // CTA-pair (cta_group::
 bool tc2_supports(const KParams& p);
 int launch_ce(const void* logits, int dtype, long long row_stride, const long long* targets, int n_rows, int vocab,
               int ignore_index, float* row_loss, unsigned int* counter, double* out, cudaStream_t stream);
+
+bool bwd_supports(int d_qk, int d_v);
+int launch_bwd(const BwdParams& p, int d_qk, int d_v, bool alibi, cudaStream_t stream);
 
 void set_error(const char* fmt, ...);
 

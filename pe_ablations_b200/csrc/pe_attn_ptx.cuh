@@ -164,6 +164,12 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, bool b_mn_m
          ((uint32_t)(M >> 4) << 24);
 }
 
+// Same with either operand MN-major (bit 15: A, bit 16: B), for the transposed products of
+// the backward pass.
+__host__ __device__ constexpr uint32_t make_idesc_bf16_mn(int M, int N, bool a_mn_major, bool b_mn_major) {
+  return make_idesc_bf16(M, N, b_mn_major) | ((a_mn_major ? 1u : 0u) << 15);
+}
+
 // Shared-memory matrix descriptor, 128-byte swizzle:
 //   bits [0,14) start address >> 4, [16,30) leading byte offset >> 4, [32,46) stride byte
 //   offset >> 4, [46,48) version = 1, [61,64) layout = 2 (SWIZZLE_128B).
@@ -328,6 +334,11 @@ __device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {
 }
 __device__ __forceinline__ void sts_v4(uint32_t saddr, uint4 v) {
   asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(saddr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+// four fp32 atomic adds to consecutive, 16-byte aligned global addresses in one instruction
+__device__ __forceinline__ void red_add_v4_f32(float* gptr, float a, float b, float c, float d) {
+  asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(gptr), "f"(a), "f"(b), "f"(c), "f"(d)
                : "memory");
 }
 __device__ __forceinline__ uint4 lds_v4(uint32_t saddr) {

@@ -251,6 +251,7 @@ __global__ void __launch_bounds__(NTHREADS) pe_attn_simt_kernel(const KParams p)
     const int row = m0 + ty + 16 * i;
     if (row >= p.Sq) continue;
     const float inv = 1.f / l_run[i];
+    if (p.lse != nullptr && tx == 0) p.lse[((long long)b * p.H + h) * p.Sq + row] = m_run[i] + logf(l_run[i]);
     const long long off = (long long)b * p.out.sb + (long long)h * p.out.sh + (long long)row * p.out.ss;
 #pragma unroll
     for (int c = 0; c < MAX_VC; ++c) {

@@ -439,6 +439,9 @@ pe_attn_tc_kernel(const KParams p, const int bh_group, const __grid_constant__ C
       if (ok) {
         tc_fence_after_sync();
         const float inv_l = 1.0f / l_sum;
+        if (p.lse != nullptr && row < p.Sq)
+          p.lse[((long long)b * p.H + h) * p.Sq + row] =
+              m_used * (ALIBI ? 1.0f : c2) * 0.6931471805599453f + logf(l_sum);
         const uint32_t o_addr = tmem_base + lane_sel + 256u + (uint32_t)(i * DV);
         char* dst = reinterpret_cast<char*>(const_cast<void*>(p.out.ptr)) +
                     2 * ((long long)b * p.out.sb + (long long)h * p.out.sh + (long long)row * p.out.ss);

@@ -445,6 +445,8 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
       if (ok) {
         tc_fence_after_sync();
         const float inv_l = 1.0f / l_sum;
+        if (p.lse != nullptr && row < p.Sq)
+          p.lse[((long long)b * p.H + h) * p.Sq + row] = m_used * kf * 0.6931471805599453f + logf(l_sum);
         char* dst = reinterpret_cast<char*>(const_cast<void*>(p.out.ptr)) +
                     2 * ((long long)b * p.out.sb + (long long)h * p.out.sh + (long long)row * p.out.ss);
 #pragma unroll 1

@@ -92,6 +92,7 @@ def pe_attention(
     mask: torch.Tensor | None = None,
     simt_check: bool = False,
     single_cta: bool = False,
+    lse: torch.Tensor | None = None,
 ) -> torch.Tensor:
     """Fused causal attention forward with the positional transform applied in-kernel.
 
@@ -103,6 +104,8 @@ def pe_attention(
               halves before softplus; ``freqs`` [d_r] effective frequencies, or base
               frequencies together with ``fourier_coeffs`` [d_r, D_f] (the FoPE mix and the
               ``floor_freq`` clip then run inside the kernel); ``delta`` [d_r] raw phase bias.
+    lse: optional fp32 [B, H, Sq] tensor that receives each row's logsumexp (natural log of the
+         sum of exp(scaled logit + bias) over the visible keys), for a later backward.
     """
     if mask is not None:
         raise NotImplementedError("pe_attention is causal-only: an explicit mask is not supported (no fallback)")
@@ -166,6 +169,10 @@ def pe_attention(
     bind("out", "out_stride", out)
     bind("q_r", "qr_stride", q_r)
     bind("k_r", "kr_stride", k_r)
+    if lse is not None:
+        if lse.dtype != torch.float32 or lse.shape != (B, H, Sq) or not lse.is_contiguous() or lse.device != ref.device:
+            raise ValueError("lse must be a contiguous fp32 [B, H, Sq] tensor on the inputs' device")
+        a.lse = lse.data_ptr()
 
     dev = ref.device
     if variant == "rotary":
@@ -219,6 +226,55 @@ def pe_attention(
     for t in keep[1:]:
         t.record_stream(torch.cuda.current_stream(dev))
     return out
+
+
+def attention_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, dout: torch.Tensor,
+                       lse: torch.Tensor, *, scale: float, alibi_slopes: torch.Tensor | None = None
+                       ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Gradients of ``softmax_causal(scale q k^T + bias) v`` for transformed bf16 operands.
+
+    q [B,Sq,H,d_qk], k [B,Sk,Hkv,d_qk], v [B,Sk,Hkv,d_v], out / dout [B,Sq,H,d_v] (bf16, last
+    dimension contiguous), ``lse`` the forward's [B,H,Sq] logsumexp.  Returns
+    ``(dq fp32 [B,Sq,H,d_qk], dk bf16 like k, dv bf16 like v)``; dq is a view of the
+    [B,H,Sq,d_qk] accumulation buffer the kernel adds into.
+    """
+    for t in (q, k, v, out, dout):
+        if not t.is_cuda or t.dtype != torch.bfloat16:
+            raise TypeError("attention_backward needs bf16 CUDA tensors (there is no other path)")
+    B, Sq, H, d_qk = q.shape
+    _, Sk, Hkv, d_v = v.shape
+    dev = q.device
+    if lse.dtype != torch.float32 or lse.shape != (B, H, Sq) or not lse.is_contiguous():
+        raise ValueError("lse must be a contiguous fp32 [B, H, Sq] tensor")
+    if dout.stride(-1) != 1:
+        dout = dout.contiguous()
+    a = _lib.PeAttnBwdArgs()
+    a.struct_size = C.sizeof(_lib.PeAttnBwdArgs)
+    a.B, a.H, a.Hkv, a.Sq, a.Sk, a.d_qk, a.d_v = B, H, Hkv, Sq, Sk, d_qk, d_v
+    a.scale = float(scale)
+    dq_accum = torch.empty(B, H, Sq, d_qk, dtype=torch.float32, device=dev)
+    dvec = torch.empty(B, H, Sq, dtype=torch.float32, device=dev)
+    dk = torch.empty(B, Sk, Hkv, d_qk, dtype=torch.bfloat16, device=dev)
+    dv = torch.empty(B, Sk, Hkv, d_v, dtype=torch.bfloat16, device=dev)
+    for name, sname, t in (("q", "q_stride", q), ("k", "k_stride", k), ("v", "v_stride", v), ("out", "out_stride", out),
+                           ("dout", "dout_stride", dout), ("dk", "dk_stride", dk), ("dv", "dv_stride", dv)):
+        setattr(a, name, t.data_ptr())
+        getattr(a, sname)[:] = _strides(t, "bshd")
+    a.lse, a.dq_accum, a.dvec = lse.data_ptr(), dq_accum.data_ptr(), dvec.data_ptr()
+    keep = []
+    if alibi_slopes is not None:
+        sl = _f32(alibi_slopes.reshape(-1), dev)
+        keep.append(sl)
+        a.alibi_slopes = sl.data_ptr()
+    with torch.cuda.device(dev):
+        a.device_status = device_status(dev).data_ptr()
+        stream = torch.cuda.current_stream(dev)
+        rc = _lib.lib.pe_attn_backward(C.byref(a), C.c_void_p(stream.cuda_stream))
+    if rc != 0:
+        raise _lib.PeAttnError(rc)
+    for t in keep + [dvec]:
+        t.record_stream(stream)
+    return dq_accum.transpose(1, 2), dk, dv
 
 
 class HostStreamedAttention:

@@ -29,7 +29,7 @@ def test_exports_every_declared_symbol(L):
     assert "pe_attn_forward" in names and len(names) >= 7
     for n in names:
         assert hasattr(L.lib, n), n
-    assert L.lib.pe_attn_version() == 1
+    assert L.lib.pe_attn_version() == 2
 
 
 def _valid_args(L, **over):
