@@ -63,6 +63,25 @@ MODULE_CASES = [
          use_qk_norm=True, delta_init="uniform", n_fourier=8, sigma=0.4, training_length=32),
 ]
 
+# gradients through the reference's attention modules under bf16 autocast (its training
+# precision), at the head dimensions the tensor-core backward covers
+TRAIN_CASES = [
+    dict(name="g_rope", kind="rope", hidden=64, H=4, Hkv=2, head_dim=64, S=160, B=2, use_qk_norm=True),
+    dict(name="g_yarn", kind="yarn", hidden=64, H=2, Hkv=2, head_dim=64, S=144, B=1, use_qk_norm=False,
+         rope_scale=2.0),
+    dict(name="g_nope_d128", kind="nope", hidden=64, H=2, Hkv=1, head_dim=128, S=130, B=2, use_qk_norm=True),
+    dict(name="g_alibi", kind="alibi", hidden=64, H=4, Hkv=2, head_dim=64, S=160, B=2, use_qk_norm=True),
+    dict(name="g_pope", kind="pope", hidden=64, H=4, Hkv=2, head_dim=64, d_rope=32, S=160, B=2,
+         use_qk_norm=True, delta_init="uniform"),
+    dict(name="g_pope_floor", kind="pope_floor", hidden=64, H=2, Hkv=2, head_dim=64, d_rope=32, S=136, B=1,
+         use_qk_norm=True, delta_init="zero", training_length=16),
+    dict(name="g_fpope", kind="fpope", hidden=64, H=4, Hkv=1, head_dim=64, d_rope=32, S=160, B=2,
+         use_qk_norm=True, delta_init="uniform", n_fourier=8, sigma=0.4, training_length=32),
+]
+
+# 2-D parameter gradients are stored for every TRAIN_ROW_STRIDE-th row
+TRAIN_ROW_STRIDE = 2
+
 # cached decoding through the reference's FPoPEGroupedQueryAttentionWithCache: a prefill of
 # CACHE_PREFILL tokens, then steps of the listed lengths, all with use_cache=True
 CACHE_CASE = dict(name="m_fpope_cache", hidden=128, H=4, Hkv=2, head_dim=32, d_rope=16, B=2, use_qk_norm=True,

@@ -11,8 +11,10 @@ Reference classes mirrored (paths inside the reference project):
   FPoPEGroupedQueryAttention  src/model/fpope_attention.py:29-181
   RMSNorm                     src/model/normalization.py:7-27
 
-The fused path is forward-only and causal-only: a ``mask``, or a call that would
-need gradients, raises -- there is no eager fallback.
+The fused path is causal-only: a ``mask`` raises.  Under bf16 autocast the modules also
+train: a call that needs gradients goes through ``autograd.FusedAttentionFunction`` (fused
+forward, tensor-core backward kernel); in fp32, or at head dimensions the backward kernel
+does not have, such a call raises -- there is no eager fallback.
 """
 
 from __future__ import annotations
@@ -58,8 +60,6 @@ class QKNorm(nn.Module):
 def _check_call(x: torch.Tensor, mask) -> None:
     if mask is not None:
         raise NotImplementedError("the fused attention is causal-only; an explicit mask is not supported")
-    if torch.is_grad_enabled() and x.requires_grad:
-        raise RuntimeError("the fused attention is forward-only; run it under torch.no_grad()")
 
 
 def _kernel_dtype(t: torch.Tensor) -> torch.dtype:

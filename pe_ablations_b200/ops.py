@@ -109,6 +109,78 @@ def pe_attention(
     """
     if mask is not None:
         raise NotImplementedError("pe_attention is causal-only: an explicit mask is not supported (no fallback)")
+    kwargs = dict(layout=layout, start_pos=start_pos, k_start_pos=k_start_pos, scale=scale, qk_norm=qk_norm,
+                  qk_norm_eps=qk_norm_eps, rotary_table=rotary_table, table_pos0=table_pos0, mscale=mscale,
+                  alibi_slopes=alibi_slopes, floor_freq=floor_freq, normalize_coeffs=normalize_coeffs,
+                  ceil_freq=ceil_freq, out=out, simt_check=simt_check, single_cta=single_cta)
+    diff = (q, k, v, q_r, k_r, freqs, delta, fourier_coeffs)
+    if torch.is_grad_enabled() and any(isinstance(t, torch.Tensor) and t.requires_grad for t in diff):
+        return _training_call(variant, q, k, v, q_r, k_r, freqs, delta, fourier_coeffs, lse, kwargs)
+    return _forward_impl(variant, q, k, v, q_r=q_r, k_r=k_r, freqs=freqs, delta=delta, fourier_coeffs=fourier_coeffs,
+                         lse=lse, **kwargs)
+
+
+def _training_call(variant, q, k, v, q_r, k_r, freqs, delta, fourier_coeffs, lse, kw):
+    """Route a call that needs gradients through ``autograd.FusedAttentionFunction``."""
+    from .autograd import FusedAttentionFunction
+
+    if variant not in _VARIANTS:
+        raise ValueError(f"unknown variant {variant!r}")
+    if v.dtype != torch.bfloat16 or not v.is_cuda:
+        raise NotImplementedError("gradients are implemented for bf16 CUDA tensors only (run the module under bf16 "
+                                  "autocast); there is no eager fallback")
+    if kw["layout"] != "bshd" or kw["out"] is not None or lse is not None or kw["simt_check"]:
+        raise NotImplementedError("a call that needs gradients takes [B, S, H, d] tensors and owns its outputs")
+    d_qk = (q.shape[-1] if q is not None else 0) + (2 * q_r.shape[-1] if q_r is not None else 0)
+    if (d_qk, v.shape[-1]) not in ((64, 64), (128, 64), (128, 128)):
+        raise NotImplementedError(f"the backward kernel covers (d_qk, d_v) in (64,64), (128,64), (128,128); got "
+                                  f"({d_qk}, {v.shape[-1]})")
+    dev = v.device
+    k_start = kw["start_pos"] if kw["k_start_pos"] is None else kw["k_start_pos"]
+    tab = kw["rotary_table"]
+    if tab is not None:
+        tab = _f32(torch.view_as_real(tab) if tab.is_complex() else tab, dev)
+    o = dict(forward_kwargs={n: kw[n] for n in kw if n not in ("out",)}, start_pos=int(kw["start_pos"]),
+             k_start_pos=int(k_start), table_pos0=int(kw["table_pos0"]), mscale=float(kw["mscale"]),
+             qk_norm=bool(kw["qk_norm"]), qk_norm_eps=float(kw["qk_norm_eps"]), rotary_table=tab,
+             normalize_coeffs=bool(kw["normalize_coeffs"]), floor_freq=float(kw["floor_freq"]),
+             ceil_freq=kw["ceil_freq"], scale=float(kw["scale"]) if kw["scale"] is not None else d_qk ** -0.5,
+             alibi_slopes=kw["alibi_slopes"] if variant == "alibi" else None)
+    on_dev = lambda t: None if t is None else (t if t.device == dev else t.to(dev))
+    return FusedAttentionFunction.apply(variant, o, q, k, v, q_r, k_r, on_dev(freqs), on_dev(delta),
+                                        on_dev(fourier_coeffs))
+
+
+def _forward_impl(
+    variant: str,
+    q: torch.Tensor | None,
+    k: torch.Tensor | None,
+    v: torch.Tensor,
+    *,
+    q_r: torch.Tensor | None = None,
+    k_r: torch.Tensor | None = None,
+    layout: str = "bshd",
+    start_pos: int = 0,
+    k_start_pos: int | None = None,
+    scale: float | None = None,
+    qk_norm: bool = False,
+    qk_norm_eps: float = 1e-6,
+    rotary_table: torch.Tensor | None = None,
+    table_pos0: int = 0,
+    mscale: float = 1.0,
+    alibi_slopes: torch.Tensor | None = None,
+    freqs: torch.Tensor | None = None,
+    delta: torch.Tensor | None = None,
+    fourier_coeffs: torch.Tensor | None = None,
+    floor_freq: float = 0.0,
+    normalize_coeffs: bool = True,
+    ceil_freq: float | None = None,
+    out: torch.Tensor | None = None,
+    simt_check: bool = False,
+    single_cta: bool = False,
+    lse: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """The forward kernel call behind ``pe_attention`` (no autograd bookkeeping)."""
     if variant not in _VARIANTS:
         raise ValueError(f"unknown variant {variant!r}")
     if layout not in ("bshd", "bhsd"):
@@ -116,9 +188,6 @@ def pe_attention(
     ref = v
     if not ref.is_cuda:
         raise RuntimeError("pe_attention needs CUDA tensors: there is no CPU path")
-    for t in (q, k, v, q_r, k_r):
-        if t is not None and t.requires_grad and torch.is_grad_enabled():
-            raise RuntimeError("pe_attention is forward-only: call it under torch.no_grad()")
     if ref.dtype == torch.bfloat16:
         dtype = _lib.BF16
     elif ref.dtype == torch.float32:

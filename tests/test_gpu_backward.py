@@ -100,3 +100,74 @@ def test_forward_logsumexp_output(variant, dims, S):
     want = O.attention_core(variant, q.float(), k.float(), v.float(), dtype=torch.bfloat16, return_lse=True, **okw)[1]
     assert torch.isfinite(lse).all()
     assert (lse.cpu() - want).abs().max().item() <= 2e-2
+
+
+@pytest.fixture(scope="module")
+def grads(golden_dir):
+    import os
+
+    import numpy as np
+
+    return np.load(os.path.join(golden_dir, "module_grads.npz"))
+
+
+def _train_cases():
+    from oracle import golden_cases as G
+
+    return list(enumerate(G.TRAIN_CASES))
+
+
+@pytest.mark.parametrize("i,spec", _train_cases(), ids=lambda s: s["name"] if isinstance(s, dict) else str(s))
+def test_module_gradients_match_reference_autograd(grads, i, spec):
+    """Drop-in module under bf16 autocast, forward + backward, against the reference module's
+    autograd under bf16 autocast (fixture generated by tests/golden/make_golden_grad.py).
+
+    Two bf16 runs of the same step differ by rounding alone; the fixture records how far the
+    reference's own bf16 step sits from its fp32 step for each tensor (about 1e-2 of the
+    tensor's largest gradient).  Bound per tensor: 1e-2 * max|g| + 2 * that distance.
+    """
+    from oracle import golden_cases as G
+    from pe_ablations_b200 import check_device_status
+    from tests.test_modules_cpu import build_module
+
+    torch.manual_seed(7000 + i)
+    m = build_module(spec).train()
+    G.fill_parameters(m, 8000 + i)
+    m = m.cuda()
+    g = torch.Generator().manual_seed(9000 + i)
+    x = torch.randn(spec["B"], spec["S"], spec["hidden"], generator=g).cuda().requires_grad_(True)
+    dy = torch.randn(spec["B"], spec["S"], spec["hidden"], generator=g).cuda()
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = m(x)
+    y.float().backward(dy)
+    torch.cuda.synchronize()
+    check_device_status()
+    name = spec["name"]
+    want_y = torch.from_numpy(grads[f"{name}/y"])
+    assert (y.detach().float().cpu() - want_y).abs().max().item() <= 2e-2 * max(1.0, want_y.abs().max().item())
+    got = {"x": x.grad}
+    got.update({n: p.grad for n, p in m.named_parameters() if p.grad is not None})
+    names = [str(n) for n in grads[f"{name}/grad_names"]]
+    assert sorted(got) == names
+    for n in names:
+        want = torch.from_numpy(grads[f"{name}/grad/{n}"])
+        have = got[n].float().cpu()
+        if have.dim() == 2:
+            have = have[::G.TRAIN_ROW_STRIDE]
+        bound = 1e-2 * float(grads[f"{name}/fp32_max/{n}"]) + 2.0 * float(grads[f"{name}/bf16_noise/{n}"])
+        err = (have - want).abs().max().item()
+        assert err <= bound, f"{name} grad {n}: |diff| {err:.3e} > {bound:.3e}"
+
+
+def test_training_call_refuses_what_the_backward_does_not_cover():
+    from pe_ablations_b200 import pe_attention
+
+    dev = torch.device("cuda", 0)
+    mk = lambda d, dt: torch.randn(1, 64, 2, d, device=dev, dtype=dt, requires_grad=True)
+    with pytest.raises(NotImplementedError):     # fp32 has no backward kernel
+        pe_attention("nope", mk(64, torch.float32), mk(64, torch.float32), mk(64, torch.float32))
+    with pytest.raises(NotImplementedError):     # d_qk = 256 is forward-only
+        pe_attention("pope", mk(128, torch.bfloat16), mk(128, torch.bfloat16), mk(128, torch.bfloat16),
+                     q_r=mk(64, torch.bfloat16), k_r=mk(64, torch.bfloat16), freqs=torch.ones(64))
+    with torch.no_grad():                        # the same call without gradients is fine
+        pe_attention("nope", mk(64, torch.float32), mk(64, torch.float32), mk(64, torch.float32))

@@ -142,3 +142,41 @@ def test_cache_module_constructor_and_state_dict():
     assert sorted(m.state_dict().keys()) == sorted(base.state_dict().keys())   # cache buffers are not persistent
     assert m.cache_len == 0 and m.max_cache_len == 128
     m.reset_cache()
+
+
+def test_training_transform_equals_the_oracle_transform():
+    """The differentiable restatement of the positional transform that the backward pass
+    differentiates (autograd.transformed_operands) builds the same operands as the oracle."""
+    import math
+
+    from oracle import pe_attention_oracle as O
+    from pe_ablations_b200 import autograd as A
+
+    g = torch.Generator().manual_seed(3)
+    B, S, H, Hkv, dc, dr = 2, 37, 4, 2, 64, 32
+    mk = lambda h, d: torch.randn(B, S, h, d, generator=g).to(torch.bfloat16)
+    q, k, q_r, k_r = mk(H, dc), mk(Hkv, dc), mk(H, dr), mk(Hkv, dr)
+    base = O.pope_base_freqs(dr)
+    coeffs = torch.randn(dr, 8, generator=g) * 0.4
+    delta = (torch.rand(dr, generator=g) * 2 - 1) * math.pi
+    o = dict(start_pos=5, k_start_pos=5, normalize_coeffs=True, floor_freq=2 * math.pi / 32, ceil_freq=None)
+    qt, kt = A.transformed_operands("pope", q, k, q_r, k_r, o, base, delta, coeffs)
+    eff = O.fope_effective_freqs(base, coeffs, 32)
+    assert torch.equal(A.effective_freqs(base, coeffs, True, o["floor_freq"], None), eff)
+    want_q = torch.cat([q.float(), O.pope_expand(q_r, 5, eff, None)], dim=-1).to(torch.bfloat16)
+    want_k = torch.cat([k.float(), O.pope_expand(k_r, 5, eff, delta)], dim=-1).to(torch.bfloat16)
+    assert torch.equal(qt.to(torch.bfloat16), want_q) and torch.equal(kt.to(torch.bfloat16), want_k)
+    # rotary + mscale + QKNorm
+    table = O.rotary_table(O.rope_inv_freq(dc), 64)
+    o = dict(start_pos=3, k_start_pos=3, table_pos0=0, mscale=1.07, qk_norm=True, qk_norm_eps=1e-6, rotary_table=table)
+    qt, kt = A.transformed_operands("rotary", q, k, None, None, o, None, None, None)
+    want = O.qk_l2_norm(O.rotary_apply(q.float(), table[3:3 + S], 1.07)).to(torch.bfloat16)
+    assert (qt.float() - want.float()).abs().max().item() <= 2 ** -8
+    # gradients reach the encoding's parameters
+    coeffs.requires_grad_(True)
+    delta.requires_grad_(True)
+    o = dict(start_pos=0, k_start_pos=0, normalize_coeffs=True, floor_freq=2 * math.pi / 32, ceil_freq=None)
+    qt, kt = A.transformed_operands("pope", q, k, q_r, k_r, o, base, delta, coeffs)
+    (qt.float().sum() + kt.float().square().sum()).backward()
+    assert coeffs.grad.abs().sum() > 0 and delta.grad.abs().sum() > 0
+    assert (delta.grad[delta.detach() > 0] == 0).all()          # clamped at use: no gradient above 0
