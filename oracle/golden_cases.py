@@ -79,6 +79,18 @@ TRAIN_CASES = [
          use_qk_norm=True, delta_init="uniform", n_fourier=8, sigma=0.4, training_length=32),
 ]
 
+# one training step of a small Transformer (loss + gradients) per positional-encoding family
+TRAIN_MODEL_BASE = dict(vocab_size=256, hidden_dim=128, num_layers=2, num_heads=2, num_kv_heads=1, head_dim=64,
+                        max_seq_len=192, pope_d_rope=32, fpope_d_rope=32)
+TRAIN_MODEL_CASES = [
+    dict(name="tt_rope", pe_mode="rope"),
+    dict(name="tt_alibi", pe_mode="alibi"),
+    dict(name="tt_fpope", pe_mode="fpope", fpope_delta_init="uniform", fpope_num_fourier_terms=8,
+         fpope_training_length=32),
+]
+TRAIN_MODEL_BATCH, TRAIN_MODEL_SEQ = 2, 192
+TRAIN_MODEL_SAMPLE_STRIDE = 17     # every 17th entry of each flattened gradient is stored
+
 # 2-D parameter gradients are stored for every TRAIN_ROW_STRIDE-th row
 TRAIN_ROW_STRIDE = 2
 

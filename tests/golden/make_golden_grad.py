@@ -75,6 +75,39 @@ def main():
             worst = max(worst, float((gb - gf).abs().max() / (gf.abs().max() + 1e-12)))
         print(spec["name"], "tensors with grad:", len(names),
               "worst bf16-vs-fp32 relative gradient distance: %.3e" % worst)
+    from src.model.transformer import Transformer, TransformerConfig
+
+    for i, spec in enumerate(G.TRAIN_MODEL_CASES):
+        kw = dict(G.TRAIN_MODEL_BASE)
+        kw.update({k: v for k, v in spec.items() if k != "name"})
+        grads, loss = {}, {}
+        for mode in ("bf16", "fp32"):
+            torch.manual_seed(7500 + i)
+            model = Transformer(TransformerConfig(**kw)).train()
+            G.fill_parameters(model, 8500 + i)
+            ids = torch.randint(0, kw["vocab_size"], (G.TRAIN_MODEL_BATCH, G.TRAIN_MODEL_SEQ),
+                                generator=torch.Generator().manual_seed(9500 + i))
+            if mode == "bf16":
+                with torch.autocast("cpu", dtype=torch.bfloat16):
+                    out = model(ids, labels=ids)
+            else:
+                out = model(ids, labels=ids)
+            out["loss"].backward()
+            loss[mode] = float(out["loss"])
+            grads[mode] = {n: p.grad.float().clone() for n, p in model.named_parameters() if p.grad is not None}
+        name = spec["name"]
+        data[f"{name}/loss"] = np.array(loss["bf16"])
+        data[f"{name}/loss_fp32"] = np.array(loss["fp32"])
+        names = sorted(grads["bf16"])
+        data[f"{name}/grad_names"] = np.array(names)
+        for n in names:
+            gb, gf = grads["bf16"][n], grads["fp32"][n]
+            # per tensor: its largest entry, its l2 norm, and a strided sample of its entries
+            data[f"{name}/grad_norm/{n}"] = np.array(float(gb.norm()))
+            data[f"{name}/grad_sample/{n}"] = gb.flatten()[::G.TRAIN_MODEL_SAMPLE_STRIDE].numpy()
+            data[f"{name}/bf16_noise/{n}"] = np.array(float((gb - gf).abs().max()))
+            data[f"{name}/fp32_max/{n}"] = np.array(float(gf.abs().max()))
+        print(name, "loss bf16 %.6f fp32 %.6f" % (loss["bf16"], loss["fp32"]), "tensors:", len(names))
     np.savez_compressed(os.path.join(HERE, "module_grads.npz"), **data)
     print("wrote module_grads.npz", os.path.getsize(os.path.join(HERE, "module_grads.npz")), "bytes")
 

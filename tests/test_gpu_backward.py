@@ -171,3 +171,44 @@ def test_training_call_refuses_what_the_backward_does_not_cover():
                      q_r=mk(64, torch.bfloat16), k_r=mk(64, torch.bfloat16), freqs=torch.ones(64))
     with torch.no_grad():                        # the same call without gradients is fine
         pe_attention("nope", mk(64, torch.float32), mk(64, torch.float32), mk(64, torch.float32))
+
+
+def _train_model_cases():
+    from oracle import golden_cases as G
+
+    return list(enumerate(G.TRAIN_MODEL_CASES))
+
+
+@pytest.mark.parametrize("i,spec", _train_model_cases(), ids=lambda s: s["name"] if isinstance(s, dict) else str(s))
+def test_transformer_training_step_matches_reference(grads, i, spec):
+    """loss.backward() of the Transformer host under bf16 autocast against the reference's
+    Transformer under bf16 autocast: the loss, and a strided sample of every parameter's
+    gradient (bound as in the module test, scaled by the reference's own bf16 noise)."""
+    from oracle import golden_cases as G
+    from pe_ablations_b200 import check_device_status
+    from pe_ablations_b200.model import Transformer, TransformerConfig
+
+    kw = dict(G.TRAIN_MODEL_BASE)
+    kw.update({k: v for k, v in spec.items() if k != "name"})
+    torch.manual_seed(7500 + i)
+    model = Transformer(TransformerConfig(**kw)).train()
+    G.fill_parameters(model, 8500 + i)
+    model = model.cuda()
+    ids = torch.randint(0, kw["vocab_size"], (G.TRAIN_MODEL_BATCH, G.TRAIN_MODEL_SEQ),
+                        generator=torch.Generator().manual_seed(9500 + i)).cuda()
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        out = model(ids, labels=ids)
+    out["loss"].backward()
+    torch.cuda.synchronize()
+    check_device_status()
+    name = spec["name"]
+    assert abs(out["loss"].item() - float(grads[f"{name}/loss"])) <= 2e-3 * float(grads[f"{name}/loss"])
+    got = {n: p.grad for n, p in model.named_parameters() if p.grad is not None}
+    names = [str(n) for n in grads[f"{name}/grad_names"]]
+    assert sorted(got) == names
+    for n in names:
+        want = torch.from_numpy(grads[f"{name}/grad_sample/{n}"])
+        have = got[n].float().cpu().flatten()[::G.TRAIN_MODEL_SAMPLE_STRIDE]
+        bound = 1e-2 * float(grads[f"{name}/fp32_max/{n}"]) + 2.0 * float(grads[f"{name}/bf16_noise/{n}"])
+        err = (have - want).abs().max().item()
+        assert err <= bound, f"{name} grad {n}: |diff| {err:.3e} > {bound:.3e}"
