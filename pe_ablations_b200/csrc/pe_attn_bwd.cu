@@ -8,20 +8,31 @@
 // the transform's own backward stays with the caller.
 //
 // One CTA owns 128 keys of one key/value head and walks over the query blocks that can see
-// them (all query heads of the GQA group in turn).  Per query block, five MMAs:
-//     S  = Q K^T           dP = dO V^T                      (accumulators in TMEM)
-//     P  = exp(scale S + bias - lse),  dS = scale * P o (dP - D)   (4 warps, one row each,
-//                                                            written to shared memory as bf16)
-//     dV += P^T dO         dK += dS^T Q         dQ = dS K
-// Q, K, dO and V tiles are loaded once by TMA in the 128-byte-swizzled layout; the same bytes
-// serve as K-major operands (S, dP) and as MN-major ones (dV, dK, dQ), and P / dS are read
-// K-major for dQ and MN-major (transposed) for dV / dK, so nothing is transposed in memory.
-// dK and dV stay in TMEM for the whole CTA; dQ of each block is added to an fp32 buffer in
-// global memory with vector atomics (its summation order across key blocks is therefore not
-// fixed).  D = rowsum(dO o O) comes from a small kernel that runs first.
+// them (all query heads of the GQA group in turn).  Scores are formed TRANSPOSED, keys on the
+// TMEM lanes and queries along the columns, so that the two probability-shaped operands of
+// the key-side products are already where a tensor-core A operand may live:
+//     S^T  = K Q^T          dP^T = V dO^T                       (SS MMAs, fp32 in TMEM)
+//     P^T  = exp(scale S^T + bias - lse),  dS^T = scale * P^T o (dP^T - D)
+//                           (8 warps: thread = key, half of the query columns each; both
+//                            written back over S^T / dP^T as packed bf16, dS^T also to
+//                            shared memory)
+//     dV  += P^T dO         dK += dS^T Q                        (TS MMAs, A from TMEM)
+//     dQ   = dS K                                               (SS MMA, A = the shared-memory
+//                                                                copy of dS^T read MN-major)
+// Q, K, dO and V tiles are loaded once by TMA in the 128-byte-swizzled layout and the same
+// bytes serve as K-major operands (S^T, dP^T) and as MN-major ones (dV, dK, dQ); nothing is
+// transposed in memory.  Q / dO tiles are double-buffered, so the loads of the next query
+// block overlap this block's math.  dK and dV stay in TMEM for the whole CTA; dQ of each
+// block is added to an fp32 buffer in global memory with vector atomics (its summation order
+// across key blocks is therefore not fixed).  D = rowsum(dO o O) comes from a small kernel
+// that runs first.
 //
-// TMEM columns: S / dQ [0,128)  dP [128,256)  dV [256,256+DV)  dK [256+DV, 256+DV+DQK).
-// Warps 0-3: softmax-gradient math and epilogues; warp 4: TMA; warp 5: TMEM + MMA issue.
+// TMEM columns: S^T / P^T / dQ [0,128)   dP^T / dS^T [128,256)   dV [256,256+DV)
+//               dK [256+DV, 256+DV+DQK).   P^T of query columns [64h, 64h+64) sits in columns
+// [64h, 64h+32) (inside the half of S^T its own warps read), dS^T likewise at 128 + ....
+// dQ overwrites the S^T / P^T columns: it is issued after the dV product that reads P^T, and
+// MMAs of one thread execute in issue order.
+// Warps 0-7: softmax-gradient math and epilogues; warp 8: TMA; warp 9: TMEM + MMA issue.
 // Every wait is bounded and reports through the device status word.
 
 #include <cuda.h>
@@ -37,22 +48,24 @@ using namespace tc;
 
 constexpr int BM = 128;          // query rows per block
 constexpr int BN = 128;          // keys per CTA
-constexpr int NTHREADS = 192;
+constexpr int NCOMPUTE = 256;    // 8 warps
+constexpr int NDRAIN = 128;      // 4 warps
+constexpr int NTHREADS = 512;    // + TMA warp, MMA warp, two idle warps (a full warpgroup for setmaxnreg)
 constexpr int CH = 128 * 128;    // bytes of one 128-row x 64-column bf16 chunk
 constexpr int TMEM_COLS = 512;
+constexpr int TAIL = 2048;       // barriers, TMEM slot, per-block lse / D vectors
 constexpr int ST_WAIT_BWD = 1 << 9;
 
-enum : int { BAR_KV = 0, BAR_LD, BAR_S, BAR_P, BAR_DQ, BAR_SFREE, NUM_BARS };
+enum : int { BAR_KV = 0, BAR_LDFULL = 1, BAR_LDEMPTY = 3, BAR_S = 5, BAR_P = 6, BAR_DQ = 7, BAR_SFREE = 8, BAR_VEC = 9, NUM_BARS = 10 };
 
 template <int DQK, int DV>
 struct BCfg {
   static constexpr int NQC = DQK / 64, NVC = DV / 64;
-  static constexpr int K_OFF = 1024;
+  static constexpr int K_OFF = TAIL;
   static constexpr int V_OFF = K_OFF + NQC * CH;
-  static constexpr int Q_OFF = V_OFF + NVC * CH;
-  static constexpr int DO_OFF = Q_OFF + NQC * CH;
-  static constexpr int P_OFF = DO_OFF + NVC * CH;
-  static constexpr int DS_OFF = P_OFF + 2 * CH;
+  static constexpr int Q_OFF = V_OFF + NVC * CH;             // 2 stages
+  static constexpr int DO_OFF = Q_OFF + 2 * NQC * CH;        // 2 stages
+  static constexpr int DS_OFF = DO_OFF + 2 * NVC * CH;
   static constexpr int SMEM_BYTES = DS_OFF + 2 * CH + 1024;  // slack to align the base to 1024
   static_assert(DQK == 64 || DQK == 128, "d_qk must be 64 or 128");
   static_assert(DV == 64 || DV == 128, "d_v must be 64 or 128");
@@ -69,6 +82,8 @@ pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, c
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + 256);
+  float* lse_s = reinterpret_cast<float*>(smem + 1024);   // [128] log2-scaled logsumexp of the query block
+  float* dsum_s = reinterpret_cast<float*>(smem + 1536);  // [128] D of the query block
   auto bar = [&](int idx) -> uint32_t { return smem_base + 8u * (uint32_t)idx; };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -87,15 +102,19 @@ pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, c
 
   if (tid == 0) {
     mbar_init(bar(BAR_KV), 1);
-    mbar_init(bar(BAR_LD), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar(BAR_LDFULL + s), 1);
+      mbar_init(bar(BAR_LDEMPTY + s), 1);
+    }
     mbar_init(bar(BAR_S), 1);
-    mbar_init(bar(BAR_P), 4);
+    mbar_init(bar(BAR_P), NCOMPUTE / 32);
     mbar_init(bar(BAR_DQ), 1);
-    mbar_init(bar(BAR_SFREE), 4);
+    mbar_init(bar(BAR_SFREE), NDRAIN / 32);
+    mbar_init(bar(BAR_VEC), NCOMPUTE / 32);
     mbar_fence_init();
     fence_proxy_async_smem();
   }
-  if (warp == 5) {
+  if (warp == 13) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
     tmem_relinquish();
   }
@@ -105,10 +124,15 @@ pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, c
   const uint32_t tmem_base = *tmem_slot;
 
   const uint32_t k_smem = smem_base + C::K_OFF, v_smem = smem_base + C::V_OFF, q_smem = smem_base + C::Q_OFF,
-                 do_smem = smem_base + C::DO_OFF, p_smem = smem_base + C::P_OFF, ds_smem = smem_base + C::DS_OFF;
-  constexpr uint32_t LD_BYTES = (uint32_t)((C::NQC + C::NVC) * CH);
+                 do_smem = smem_base + C::DO_OFF, ds_smem = smem_base + C::DS_OFF;
+  constexpr uint32_t Q_STAGE = (uint32_t)(C::NQC * CH), DO_STAGE = (uint32_t)(C::NVC * CH);
+  constexpr uint32_t LD_BYTES = Q_STAGE + DO_STAGE;
 
-  if (warp == 4) {
+  // Each role sits inside the branch that sets its register budget:
+  // 2 x 128 x 136 (softmax) + 128 x 152 (dQ drain) + 128 x 88 (TMA, MMA) = 64 K registers.
+  if (warp >= 12) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
+  if (warp == 12) {
     // ===================== TMA producer =====================
     if (n_iter > 0) {
       if (elect_one()) {
@@ -124,32 +148,36 @@ pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, c
 #pragma unroll 1
       for (int it = 0; it < n_iter; ++it) {
         const int h = hk * p.groups + it / per_head, i = i_first + it % per_head;
-        // the previous block's dV / dK / dQ products have finished reading Q and dO
-        if (it > 0 && !__all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_DQ), (uint32_t)((it - 1) & 1)))) { fail(); break; }
+        const int s = it & 1;
+        // the products of the block that used this stage two iterations ago have finished
+        if (it >= 2 && !__all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_LDEMPTY + s), (uint32_t)(((it >> 1) - 1) & 1)))) {
+          fail();
+          break;
+        }
         if (elect_one()) {
-          mbar_arrive_expect_tx(bar(BAR_LD), LD_BYTES);
+          mbar_arrive_expect_tx(bar(BAR_LDFULL + s), LD_BYTES);
 #pragma unroll
-          for (int c = 0; c < C::NQC; ++c) tma_load_4d(q_smem + c * CH, &tmQ, bar(BAR_LD), c * 64, i * BM, h, b);
+          for (int c = 0; c < C::NQC; ++c)
+            tma_load_4d(q_smem + s * Q_STAGE + c * CH, &tmQ, bar(BAR_LDFULL + s), c * 64, i * BM, h, b);
 #pragma unroll
-          for (int c = 0; c < C::NVC; ++c) tma_load_4d(do_smem + c * CH, &tmDO, bar(BAR_LD), c * 64, i * BM, h, b);
+          for (int c = 0; c < C::NVC; ++c)
+            tma_load_4d(do_smem + s * DO_STAGE + c * CH, &tmDO, bar(BAR_LDFULL + s), c * 64, i * BM, h, b);
         }
         __syncwarp();
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 13) {
     // ===================== MMA issuer =====================
-    constexpr uint32_t IDESC_S = make_idesc_bf16_mn(BM, BN, false, false);    // S, dP: both K-major
-    constexpr uint32_t IDESC_DV = make_idesc_bf16_mn(BN, DV, true, true);     // P^T dO
-    constexpr uint32_t IDESC_DK = make_idesc_bf16_mn(BN, DQK, true, true);    // dS^T Q
-    constexpr uint32_t IDESC_DQ = make_idesc_bf16_mn(BM, DQK, false, true);   // dS K
+    constexpr uint32_t IDESC_ST = make_idesc_bf16_mn(BN, BM, false, false);   // S^T, dP^T: both K-major
+    constexpr uint32_t IDESC_DV = make_idesc_bf16_mn(BN, DV, false, true);    // P^T (TMEM) x dO (MN-major)
+    constexpr uint32_t IDESC_DK = make_idesc_bf16_mn(BN, DQK, false, true);   // dS^T (TMEM) x Q (MN-major)
+    constexpr uint32_t IDESC_DQ = make_idesc_bf16_mn(BM, DQK, true, true);    // dS (MN-major) x K (MN-major)
     // K-major view: 8-row groups 1024 bytes apart, 16 elements (32 bytes) per K step
-    const uint64_t q_k = make_smem_desc(q_smem, 16, 1024), k_k = make_smem_desc(k_smem, 16, 1024);
-    const uint64_t do_k = make_smem_desc(do_smem, 16, 1024), v_k = make_smem_desc(v_smem, 16, 1024);
-    const uint64_t ds_k = make_smem_desc(ds_smem, 16, 1024);
+    const uint64_t k_k = make_smem_desc(k_smem, 16, 1024), v_k = make_smem_desc(v_smem, 16, 1024);
+    const uint64_t q_k0 = make_smem_desc(q_smem, 16, 1024), do_k0 = make_smem_desc(do_smem, 16, 1024);
     // MN-major view of the same bytes: 64-wide MN chunks CH bytes apart, 16 K rows = 2048 bytes
-    const uint64_t p_mn = make_smem_desc(p_smem, CH, 1024), ds_mn = make_smem_desc(ds_smem, CH, 1024);
-    const uint64_t do_mn = make_smem_desc(do_smem, CH, 1024), q_mn = make_smem_desc(q_smem, CH, 1024);
-    const uint64_t k_mn = make_smem_desc(k_smem, CH, 1024);
+    const uint64_t q_mn0 = make_smem_desc(q_smem, CH, 1024), do_mn0 = make_smem_desc(do_smem, CH, 1024);
+    const uint64_t ds_mn = make_smem_desc(ds_smem, CH, 1024), k_mn = make_smem_desc(k_smem, CH, 1024);
     const uint32_t t_s = tmem_base, t_dp = tmem_base + 128u, t_dv = tmem_base + 256u,
                    t_dk = tmem_base + 256u + (uint32_t)DV;
     bool ok = n_iter == 0 || __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_KV), 0));
@@ -157,24 +185,27 @@ pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, c
 #pragma unroll 1
     for (int it = 0; it < n_iter && ok; ++it) {
       const uint32_t ph = (uint32_t)(it & 1);
-      ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_LD), ph));
-      // the S columns double as dQ: the previous block's dQ has been read out
+      const int s = it & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_LDFULL + s), (uint32_t)((it >> 1) & 1)));
+      // the S^T columns double as dQ: the previous block's dQ has been read out
       if (ok && it > 0) ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_SFREE), ph ^ 1u));
       if (!ok) { fail(); break; }
       tc_fence_after_sync();
+      const uint64_t q_k = advance_smem_desc(q_k0, (uint32_t)s * Q_STAGE), do_k = advance_smem_desc(do_k0, (uint32_t)s * DO_STAGE);
+      const uint64_t q_mn = advance_smem_desc(q_mn0, (uint32_t)s * Q_STAGE), do_mn = advance_smem_desc(do_mn0, (uint32_t)s * DO_STAGE);
       if (elect_one()) {
 #pragma unroll
         for (int c = 0; c < C::NQC; ++c)
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4)
-            mma_ss(t_s, advance_smem_desc(q_k, (uint32_t)(c * CH + k4 * 32)),
-                   advance_smem_desc(k_k, (uint32_t)(c * CH + k4 * 32)), IDESC_S, (c > 0 || k4 > 0) ? 1u : 0u);
+            mma_ss(t_s, advance_smem_desc(k_k, (uint32_t)(c * CH + k4 * 32)),
+                   advance_smem_desc(q_k, (uint32_t)(c * CH + k4 * 32)), IDESC_ST, (c > 0 || k4 > 0) ? 1u : 0u);
 #pragma unroll
         for (int c = 0; c < C::NVC; ++c)
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4)
-            mma_ss(t_dp, advance_smem_desc(do_k, (uint32_t)(c * CH + k4 * 32)),
-                   advance_smem_desc(v_k, (uint32_t)(c * CH + k4 * 32)), IDESC_S, (c > 0 || k4 > 0) ? 1u : 0u);
+            mma_ss(t_dp, advance_smem_desc(v_k, (uint32_t)(c * CH + k4 * 32)),
+                   advance_smem_desc(do_k, (uint32_t)(c * CH + k4 * 32)), IDESC_ST, (c > 0 || k4 > 0) ? 1u : 0u);
         tc_commit(bar(BAR_S));
       }
       __syncwarp();
@@ -183,108 +214,157 @@ pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, c
       tc_fence_after_sync();
       if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < BM / 16; ++kk) {   // 16 query rows per step
+        for (int kk = 0; kk < BM / 16; ++kk) {   // 16 query columns per step; packed bf16: 8 TMEM columns
           const uint32_t acc = (it > 0 || kk > 0) ? 1u : 0u;
-          mma_ss(t_dv, advance_smem_desc(p_mn, (uint32_t)(kk * 2048)), advance_smem_desc(do_mn, (uint32_t)(kk * 2048)),
-                 IDESC_DV, acc);
-          mma_ss(t_dk, advance_smem_desc(ds_mn, (uint32_t)(kk * 2048)), advance_smem_desc(q_mn, (uint32_t)(kk * 2048)),
-                 IDESC_DK, acc);
+          const uint32_t a_off = (uint32_t)((kk >> 2) * 64 + (kk & 3) * 8);
+          mma_ts(t_dv, t_s + a_off, advance_smem_desc(do_mn, (uint32_t)(kk * 2048)), IDESC_DV, acc);
+          mma_ts(t_dk, t_dp + a_off, advance_smem_desc(q_mn, (uint32_t)(kk * 2048)), IDESC_DK, acc);
         }
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk)     // 16 keys per step
-          mma_ss(t_s, advance_smem_desc(ds_k, (uint32_t)((kk >> 2) * CH + (kk & 3) * 32)),
-                 advance_smem_desc(k_mn, (uint32_t)(kk * 2048)), IDESC_DQ, kk > 0 ? 1u : 0u);
+          mma_ss(t_s, advance_smem_desc(ds_mn, (uint32_t)(kk * 2048)), advance_smem_desc(k_mn, (uint32_t)(kk * 2048)),
+                 IDESC_DQ, kk > 0 ? 1u : 0u);
         tc_commit(bar(BAR_DQ));
+        tc_commit(bar(BAR_LDEMPTY + s));
       }
       __syncwarp();
     }
+  }
+  } else if (warp >= 8) {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
+  {
+    // ===================== dQ drain: TMEM -> registers -> fp32 atomics (lanes = query rows) ======
+    // Its own warps, so that the atomics of block i overlap the softmax of block i + 1.
+    const int r = tid & 127;
+    const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+#pragma unroll 1
+    for (int it = 0; it < n_iter; ++it) {
+      const int h = hk * p.groups + it / per_head, row = (i_first + it % per_head) * BM + r;
+      if (!__all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_DQ), (uint32_t)(it & 1)))) { fail(); break; }
+      tc_fence_after_sync();
+      uint32_t qr[DQK];
+#pragma unroll
+      for (int cb = 0; cb < DQK / 32; ++cb)
+        tmem_ld32(tmem_base + lane_sel + (uint32_t)(cb * 32), *reinterpret_cast<uint32_t(*)[32]>(&qr[cb * 32]));
+      tmem_wait_ld();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_SFREE));   // the S^T / dQ columns may be overwritten
+      if (row < p.Sq) {
+        float* dq_row = p.dq_accum + (((long long)b * p.H + h) * p.Sq + row) * DQK;
+#pragma unroll
+        for (int v = 0; v < DQK / 4; ++v)
+          red_add_v4_f32(dq_row + v * 4, __uint_as_float(qr[v * 4]), __uint_as_float(qr[v * 4 + 1]),
+                         __uint_as_float(qr[v * 4 + 2]), __uint_as_float(qr[v * 4 + 3]));
+      }
+    }
+  }
   } else {
-    // ===================== softmax gradient + epilogues: thread = row =====================
-    const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 136;");
+  {
+    // ===================== softmax gradient + epilogues =====================
+    // thread = (key lane, half of the query columns)
+    const int r = tid & 127, hh = tid >> 7;
+    const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
     const float c2 = p.scale * 1.4426950408889634f;
+    const int key = key0 + r;
     bool ok = true;
+    // each thread fetches one entry of the block's vectors, one block ahead: log2-scaled lse
+    // (first half of the threads) or scale * D (second half)
+    auto fetch_vec = [&](int it) -> float {
+      const int h = hk * p.groups + it / per_head, row = (i_first + it % per_head) * BM + r;
+      if (row >= p.Sq) return 0.f;
+      const long long idx = ((long long)b * p.H + h) * p.Sq + row;
+      return hh == 0 ? p.lse[idx] * 1.4426950408889634f : p.dvec[idx] * p.scale;
+    };
+    float vec_next = n_iter > 0 ? fetch_vec(0) : 0.f;
 #pragma unroll 1
     for (int it = 0; it < n_iter; ++it) {
       const uint32_t ph = (uint32_t)(it & 1);
       const int h = hk * p.groups + it / per_head, i = i_first + it % per_head;
-      const int row0 = i * BM, row = row0 + tid;
-      const bool row_live = row < p.Sq;
-      const int row_lim = row + p.causal_off;
-      const long long vec_idx = ((long long)b * p.H + h) * p.Sq + row;
-      float l2 = 0.f, dsum = 0.f;
-      if (row_live) {
-        l2 = p.lse[vec_idx] * 1.4426950408889634f;
-        dsum = p.dvec[vec_idx];
+      const int row0 = i * BM;
+      // the vectors of the previous block are dead once all eight warps have handed over its P
+      if (it > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_P), ph ^ 1u));
+        if (!ok) { fail(); break; }
       }
+      (hh == 0 ? lse_s : dsum_s)[r] = vec_next;
+      // rendezvous of the eight warps on a barrier with a bounded wait (a plain bar.sync would
+      // hang the others if one warp had left after an expired wait)
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_VEC));
+      ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_VEC), ph));
+      if (!ok) { fail(); break; }
+      if (it + 1 < n_iter) vec_next = fetch_vec(it + 1);
       float slope2 = 0.f;
       if constexpr (ALIBI) slope2 = p.slopes[h] * 1.4426950408889634f;
       const bool need_mask = (key0 + BN - 1 > row0 + p.causal_off) || (key0 + BN > p.Sk) || (row0 + BM > p.Sq);
+      const bool key_live = key < p.Sk;
 
       ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_S), ph));
       if (!ok) { fail(); break; }
       tc_fence_after_sync();
-#pragma unroll 1
-      for (int cb = 0; cb < BN / 32; ++cb) {
-        uint32_t sr[32], dr[32];
-        tmem_ld32(tmem_base + lane_sel + (uint32_t)(cb * 32), sr);
-        tmem_ld32(tmem_base + lane_sel + 128u + (uint32_t)(cb * 32), dr);
+      // 16 query columns per round, the next round's TMEM loads in flight during the math
+      uint32_t sr[2][16], dr[2][16], pp[16], dd[16];
+      const uint32_t s_col = tmem_base + lane_sel + (uint32_t)(hh * 64), d_col = s_col + 128u;
+      tmem_ld16(s_col, sr[0]);
+      tmem_ld16(d_col, dr[0]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
         tmem_wait_ld();
-        uint32_t pp[16], dd[16];
+        if (j < 3) {
+          tmem_ld16(s_col + (uint32_t)((j + 1) * 16), sr[(j + 1) & 1]);
+          tmem_ld16(d_col + (uint32_t)((j + 1) * 16), dr[(j + 1) & 1]);
+        }
+        const int col0 = hh * 64 + j * 16;
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          float pv[2], dv[2];
+        for (int c = 0; c < 16; c += 4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(lse_s + col0 + c);
+          const float4 d4 = *reinterpret_cast<const float4*>(dsum_s + col0 + c);
+          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dsv[4] = {d4.x, d4.y, d4.z, d4.w};
+          float pv[4], gv[4];
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int key = key0 + cb * 32 + c + e;
-            float x = fmaf(__uint_as_float(sr[c + e]), c2, -l2);
+          for (int e = 0; e < 4; ++e) {
+            const int qc = col0 + c + e;
+            const int row_lim = row0 + qc + p.causal_off;     // last key this query row sees
+            float x = fmaf(__uint_as_float(sr[j & 1][c + e]), c2, -lv[e]);
             if constexpr (ALIBI) x = fmaf((float)(key - row_lim), slope2, x);
             float pe = ex2_approx(x);
-            if (need_mask && (!row_live || key > row_lim || key >= p.Sk)) pe = 0.f;
+            if (need_mask && (!key_live || key > row_lim || row0 + qc >= p.Sq)) pe = 0.f;
             pv[e] = pe;
-            dv[e] = pe * (__uint_as_float(dr[c + e]) - dsum) * p.scale;
+            gv[e] = pe * fmaf(__uint_as_float(dr[j & 1][c + e]), p.scale, -dsv[e]);
           }
-          pp[c >> 1] = pack_bf16x2(pv[0], pv[1]);
-          dd[c >> 1] = pack_bf16x2(dv[0], dv[1]);
+          const int o = (j & 1) * 8 + (c >> 1);
+          pp[o] = pack_bf16x2(pv[0], pv[1]);
+          pp[o + 1] = pack_bf16x2(pv[2], pv[3]);
+          dd[o] = pack_bf16x2(gv[0], gv[1]);
+          dd[o + 1] = pack_bf16x2(gv[2], gv[3]);
         }
-        // row ``tid`` of the [query, key] tiles, keys cb*32 .. +31 = four 16-byte slots
-        const uint32_t chunk_off = (uint32_t)((cb >> 1) * CH);
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          const uint32_t off = chunk_off + swz(tid, (cb & 1) * 4 + v);
-          sts_v4(p_smem + off, make_uint4(pp[v * 4], pp[v * 4 + 1], pp[v * 4 + 2], pp[v * 4 + 3]));
-          sts_v4(ds_smem + off, make_uint4(dd[v * 4], dd[v * 4 + 1], dd[v * 4 + 2], dd[v * 4 + 3]));
+        // dS^T row ``r``, query columns col0 .. +15 = two 16-byte slots of chunk hh
+        const int o = (j & 1) * 8;
+        sts_v4(ds_smem + (uint32_t)(hh * CH) + swz(r, j * 2), make_uint4(dd[o], dd[o + 1], dd[o + 2], dd[o + 3]));
+        sts_v4(ds_smem + (uint32_t)(hh * CH) + swz(r, j * 2 + 1), make_uint4(dd[o + 4], dd[o + 5], dd[o + 6], dd[o + 7]));
+        if (j & 1) {
+          // packed bf16 back over columns this thread has already read
+          tmem_st16(s_col + (uint32_t)((j >> 1) * 16), pp);
+          tmem_st16(d_col + (uint32_t)((j >> 1) * 16), dd);
         }
       }
+      tmem_wait_st();
       fence_proxy_async_smem();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(BAR_P));
-
-      // ---- dQ of this block: TMEM -> fp32 atomics
-      ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_DQ), ph));
-      if (!ok) { fail(); break; }
+    }
+    // every MMA has completed once the last block's dQ product has
+    if (ok && n_iter > 0) {
+      ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_DQ), (uint32_t)((n_iter - 1) & 1)));
+      if (!ok) fail();
       tc_fence_after_sync();
-      float* dq_row = p.dq_accum + vec_idx * DQK;
-#pragma unroll 1
-      for (int cb = 0; cb < DQK / 32; ++cb) {
-        uint32_t qr[32];
-        tmem_ld32(tmem_base + lane_sel + (uint32_t)(cb * 32), qr);
-        tmem_wait_ld();
-        if (row_live) {
-#pragma unroll
-          for (int v = 0; v < 8; ++v)
-            red_add_v4_f32(dq_row + cb * 32 + v * 4, __uint_as_float(qr[v * 4]), __uint_as_float(qr[v * 4 + 1]),
-                           __uint_as_float(qr[v * 4 + 2]), __uint_as_float(qr[v * 4 + 3]));
-        }
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(BAR_SFREE));
     }
 
-    // ---- dV and dK of this CTA's keys: thread = key row.  The last BAR_DQ wait above covered
-    // every MMA; with no visible query block the gradients are zero.
-    const int key = key0 + tid;
+    // ---- dV and dK of this CTA's keys: thread = (key row, half of the columns).  The last
+    // BAR_DQ wait above covered every MMA; with no visible query block the gradients are zero.
     if (ok) {
       const bool key_live = key < p.Sk;
       char* dv_dst = reinterpret_cast<char*>(const_cast<void*>(p.dv.ptr)) +
@@ -293,25 +373,26 @@ pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, c
                      2 * ((long long)b * p.dk.sb + (long long)hk * p.dk.sh + (long long)key * p.dk.ss);
       // tcgen05.ld is warp-collective: every lane loads, live keys store
       auto flush = [&](char* dst, uint32_t taddr, int ncol) {
+        const int c_begin = hh * (ncol / 2), c_end = c_begin + ncol / 2;
 #pragma unroll 1
-        for (int cb = 0; cb < ncol / 32; ++cb) {
-          uint32_t r[32];
+        for (int c0 = c_begin; c0 < c_end; c0 += 32) {
+          uint32_t t[32];
           if (n_iter > 0) {
-            tmem_ld32(taddr + (uint32_t)(cb * 32), r);
+            tmem_ld32(taddr + (uint32_t)c0, t);
             tmem_wait_ld();
           } else {
 #pragma unroll
-            for (int c = 0; c < 32; ++c) r[c] = 0u;
+            for (int c = 0; c < 32; ++c) t[c] = 0u;
           }
           if (key_live) {
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               uint4 o;
-              o.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
-              o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
-              o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
-              o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
-              *reinterpret_cast<uint4*>(dst + (cb * 32 + v * 8) * 2) = o;
+              o.x = pack_bf16x2(__uint_as_float(t[v * 8 + 0]), __uint_as_float(t[v * 8 + 1]));
+              o.y = pack_bf16x2(__uint_as_float(t[v * 8 + 2]), __uint_as_float(t[v * 8 + 3]));
+              o.z = pack_bf16x2(__uint_as_float(t[v * 8 + 4]), __uint_as_float(t[v * 8 + 5]));
+              o.w = pack_bf16x2(__uint_as_float(t[v * 8 + 6]), __uint_as_float(t[v * 8 + 7]));
+              *reinterpret_cast<uint4*>(dst + (c0 + v * 8) * 2) = o;
             }
           }
         }
@@ -320,6 +401,7 @@ pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, c
       flush(dk_dst, tmem_base + lane_sel + 256u + (uint32_t)DV, DQK);
     }
   }
+  }  // register-budget branch
 
   // after a failed wait give copies in flight time to land before shared memory and TMEM go
   if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) {
@@ -329,7 +411,7 @@ pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, c
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 13) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
