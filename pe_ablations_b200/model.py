@@ -5,7 +5,8 @@ and state_dict keys (including the shared positional-encoding module registered 
 the model and under every block's attention), so reference checkpoints load with
 ``strict=True`` and ``model(input_ids, labels=..., start_pos=...)`` returns the same dict.
 Everything except attention is plain torch (cuBLAS linears, elementwise ops); attention is
-the fused kernel.  Forward only.
+the fused kernel.  Under bf16 autocast ``loss.backward()`` works too (tensor-core backward
+kernel, see ``autograd.py``).
 
 Reference mirrored (paths inside the reference project): src/model/transformer.py:21-387,
 src/model/ffn.py:30-68, src/model/embeddings.py:7-34.
