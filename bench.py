@@ -337,6 +337,79 @@ def run_reference(args) -> dict | None:
     }
 
 
+def run_training(args) -> dict:
+    """Secondary workload (``--workload training``): one forward + backward of the fused
+    attention op at the reference's training shape (configs/fpope.yaml: 8 heads, 4 KV heads,
+    head_dim 64, d_rope 32, sequence 512; bf16 autocast precision), through the same autograd
+    path ``loss.backward()`` takes, and the backward kernel alone on prepared operands."""
+    import torch
+
+    import pe_ablations_b200 as P
+    from pe_ablations_b200.ops import attention_backward
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    Bt, Ht, Hkv, St, dc, dr, dv = args.train_batch, 8, 4, args.train_seq, 64, 32, 64
+    d_qk = dc + 2 * dr
+    g = torch.Generator().manual_seed(7)
+    mk = lambda h, d: torch.randn(Bt, St, h, d, generator=g).to(torch.bfloat16).to(dev).requires_grad_(True)
+    q, k, q_r, k_r, v = mk(Ht, dc), mk(Hkv, dc), mk(Ht, dr), mk(Hkv, dr), mk(Hkv, dv)
+    freqs = (10000.0 ** (-(torch.arange(0, dr, dtype=torch.float32) / dr))).to(dev)
+    coeffs = (torch.randn(dr, 64, generator=g) * 0.4).to(dev).requires_grad_(True)
+    delta = (-torch.rand(dr, generator=g) * 3).to(dev).requires_grad_(True)
+    dout = torch.randn(Bt, St, Ht, dv, generator=g).to(torch.bfloat16).to(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def step():
+        out = P.pe_attention("pope", q, k, v, q_r=q_r, k_r=k_r, freqs=freqs, fourier_coeffs=coeffs, delta=delta,
+                             floor_freq=2 * math.pi / 512)
+        out.backward(dout)
+
+    def timed(fn, n):
+        for _ in range(max(args.warmup, 3)):
+            flush.zero_()
+            fn()
+        torch.cuda.synchronize()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+        for e0, e1 in ev:
+            flush.zero_()
+            e0.record()
+            fn()
+            e1.record()
+        torch.cuda.synchronize()
+        return statistics.mean(e0.elapsed_time(e1) for e0, e1 in ev)
+
+    step_ms = timed(step, args.steps)
+    # the backward kernel alone, on operands prepared once
+    from pe_ablations_b200.autograd import transformed_operands
+
+    with torch.no_grad():
+        lse = torch.empty(Bt, Ht, St, dtype=torch.float32, device=dev)
+        o = P.pe_attention("pope", q, k, v, q_r=q_r, k_r=k_r, freqs=freqs, fourier_coeffs=coeffs, delta=delta,
+                           floor_freq=2 * math.pi / 512, lse=lse)
+        opts = dict(start_pos=0, k_start_pos=0, normalize_coeffs=True, floor_freq=2 * math.pi / 512, ceil_freq=None)
+        qt, kt = (t.to(torch.bfloat16) for t in transformed_operands("pope", q, k, q_r, k_r, opts, freqs, delta, coeffs))
+        vv = v.detach()
+    bwd_ms = timed(lambda: attention_backward(qt, kt, vv, o, dout, lse, scale=d_qk ** -0.5), args.steps)
+    P.check_device_status()
+    fwd_flops = Bt * Ht * St * St * (d_qk + dv)
+    bwd_flops = Bt * Ht * St * St * (3 * d_qk + 2 * dv)
+    peak, peak_src = measured_peak()
+    return {
+        "metric": "fused PE-attention forward+backward TFLOP/s (FoPE+PoPE, bf16, reference training shape)",
+        "value": round((fwd_flops + bwd_flops) / (step_ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(step_ms, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"training step of the attention op: B{Bt} H{Ht} Hkv{Hkv} S{St} d_c{dc} d_r{dr} d_v{dv}, "
+                               "fused forward + autograd transform + tensor-core backward",
+                   "l2": "flushed between steps by writing a 256 MiB buffer",
+                   "flops_convention": "B*H*S^2*(d_qk+d_v) forward + B*H*S^2*(3 d_qk + 2 d_v) backward, causal"},
+        "backward_kernel": {"ms": round(bwd_ms, 4), "tflops": round(bwd_flops / (bwd_ms * 1e-3) / 1e12, 2),
+                            "frac_of_peak": round(bwd_flops / (bwd_ms * 1e-3) / 1e12 / peak, 4), "peak": peak,
+                            "peak_source": peak_src, "launches_per_step": 2},
+    }
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -347,8 +420,15 @@ def main():
     ap.add_argument("--no-eval", action="store_true", help="skip the 1B-shape 16k perplexity evaluation")
     ap.add_argument("--eval-sequences", type=int, default=64)
     ap.add_argument("--e2e-chunks", type=int, default=8, help="sequence blocks of the pipelined host-buffer call")
+    ap.add_argument("--workload", default="forward", choices=["forward", "training"],
+                    help="forward: the headline benchmark; training: forward+backward of the attention op (1 GPU)")
+    ap.add_argument("--train-batch", type=int, default=64)
+    ap.add_argument("--train-seq", type=int, default=512)
     args = ap.parse_args()
-    line = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if args.workload == "training" and args.impl == "ours":
+        line = run_training(args)
+    else:
+        line = run_reference(args) if args.impl == "reference" else run_ours(args)
     if line is not None:
         print(json.dumps(line), flush=True)
 

@@ -182,8 +182,9 @@ int pe_attn_selftest_wait_expiry(int32_t* device_status, int64_t limit_cycles, v
  *
  * q [B,H,Sq,d_qk], k [B,Hkv,Sk,d_qk], v [B,Hkv,Sk,d_v], out / dout [B,H,Sq,d_v]: bf16, element
  * strides (batch, head, seq), 16-byte aligned, strides multiples of 8.  lse: the forward's
- * logsumexp output [B,H,Sq] fp32.  dq_accum: fp32 [B,H,Sq,d_qk] contiguous -- cleared and
- * then accumulated into by the call (atomic adds: bitwise results vary between runs);
+ * logsumexp output [B,H,Sq] fp32.  dq_accum: fp32 [B,Sq,H,d_qk] contiguous -- cleared and
+ * then accumulated into by the call (TMA reductions in an order that is not fixed: bitwise
+ * results vary between runs);
  * dk / dv: bf16 outputs shaped and strided like k / v (each written exactly once); dvec:
  * fp32 [B,H,Sq] workspace.  (d_qk, d_v) in {(64,64), (128,64), (128,128)}.  Causal rule as
  * in the forward: key s is visible to query row r iff s <= r + (Sk - Sq). */
@@ -204,6 +205,29 @@ typedef struct pe_attn_bwd_args {
 } pe_attn_bwd_args;
 
 int pe_attn_backward(const pe_attn_bwd_args* args, void* stream);
+
+/* The PoPE-family transform as stand-alone steps of the training path (the backward kernel
+ * reads transformed operands from memory; the forward never writes them).
+ *
+ * pe_pope_expand restates PoPEEmbedding / FoPEPoPEEmbedding .forward_query / .forward_key
+ * (src/model/pope.py:124-183, src/model/fpope.py:266-338) with the content half prepended as
+ * src/model/fpope_attention.py:166-167 does:
+ *   out[b,s,h,:] = [ x_c | softplus(x_r) cos(phi) | softplus(x_r) sin(phi) ],
+ *   phi = fl(fl((pos0 + s) * omega) + clamp(delta, -2 pi, 0))      (delta null: queries).
+ * pe_pope_expand_backward is what autograd derives from it: given grad = d/d out (bf16 or
+ * fp32, PE_ATTN_BF16 / PE_ATTN_FP32) it writes d x_c and d x_r (bf16) and ACCUMULATES
+ * d_omega[c] += sum pos * d phi and d_delta[c] += sum d phi (fp64 [d_r]; d_delta is the
+ * gradient of the CLAMPED bias and may be null; zero both before the first call).
+ * All tensors [B,S,H,*] by element strides (batch, head, seq), 16-byte aligned, strides
+ * multiples of 8; d_r 32 or 64, d_c a multiple of 8 (0 = position-only).  omega: the
+ * effective frequencies [d_r] fp32. */
+int pe_pope_expand(const void* x_c, const int64_t* xc_stride, const void* x_r, const int64_t* xr_stride, void* out,
+                   const int64_t* out_stride, int B, int S, int H, int d_c, int d_r, int pos0, const float* omega,
+                   const float* delta, void* stream);
+int pe_pope_expand_backward(const void* grad, int grad_dtype, const int64_t* grad_stride, const void* x_r,
+                            const int64_t* xr_stride, void* dx_c, const int64_t* dxc_stride, void* dx_r,
+                            const int64_t* dxr_stride, int B, int S, int H, int d_c, int d_r, int pos0,
+                            const float* omega, const float* delta, double* d_omega, double* d_delta, void* stream);
 
 /* ---- perplexity evaluation: next-token cross-entropy as loss sums ------------------------
  *

@@ -5,7 +5,9 @@ logsumexp output.  Backward: the tensor-core backward kernel (``pe_attn_backward
 gradients with respect to the TRANSFORMED operands and V; the positional transform itself is
 re-evaluated here with differentiable torch operations and autograd carries those gradients
 back to the projections and to the encoding's parameters (phase bias, frequencies, Fourier
-coefficients).  It is the gradient the reference's training step obtains by autograd through
+coefficients).  For the PoPE family the transform and its gradient are kernels too
+(``pe_pope_expand`` / ``pe_pope_expand_backward``) and only the d_r-sized frequency mix is left
+to autograd.  It is the gradient the reference's training step obtains by autograd through
 its eager modules (src/model/attention.py:77-96, src/model/alibi.py:137-160,
 src/model/fpope_attention.py:145-177 with src/model/pope.py:124-183 /
 src/model/fpope.py:107-146,266-338, src/model/rope.py:35-57, src/model/normalization.py:44-56).
@@ -108,23 +110,60 @@ class FusedAttentionFunction(torch.autograd.Function):
 
         q, k, v, q_r, k_r, freqs, delta, fourier_coeffs, out, lse = ctx.saved_tensors
         variant, o = ctx.variant, ctx.o
+        dout = dout.to(torch.bfloat16)
+        if variant == "pope":
+            return FusedAttentionFunction._backward_pope(ctx, dout)
         # differentiable re-evaluation of the transform on detached leaves
-        srcs = [q, k, q_r, k_r, freqs, delta, fourier_coeffs]
-        need = [ctx.needs_input_grad[i] for i in (2, 3, 5, 6, 7, 8, 9)]
-        leaves = [None if t is None else t.detach().requires_grad_(n) for t, n in zip(srcs, need)]
+        srcs = [q, k]
+        need = [ctx.needs_input_grad[2], ctx.needs_input_grad[3]]
+        leaves = [t.detach().requires_grad_(n) for t, n in zip(srcs, need)]
         with torch.enable_grad():
-            qt, kt = transformed_operands(variant, leaves[0], leaves[1], leaves[2], leaves[3], o, leaves[4], leaves[5],
-                                          leaves[6])
-        dqt, dkt, dv = attention_backward(qt.detach().to(torch.bfloat16), kt.detach().to(torch.bfloat16), v, out,
-                                          dout.to(torch.bfloat16), lse, scale=o["scale"],
-                                          alibi_slopes=o["alibi_slopes"])
-        wanted = [t for t in leaves if t is not None and t.requires_grad]
+            qt, kt = transformed_operands(variant, leaves[0], leaves[1], None, None, o, None, None, None)
+        dqt, dkt, dv = attention_backward(qt.detach().to(torch.bfloat16), kt.detach().to(torch.bfloat16), v, out, dout,
+                                          lse, scale=o["scale"], alibi_slopes=o["alibi_slopes"])
+        wanted = [t for t in leaves if t.requires_grad]
         # the cast to bf16 is treated as the identity, as autograd treats the reference's own cast
         grads = iter(torch.autograd.grad([qt, kt], wanted, [dqt, dkt.float()], allow_unused=True) if wanted else ())
-        g = [next(grads) if (t is not None and t.requires_grad) else None for t in leaves]
+        g = [next(grads) if t.requires_grad else None for t in leaves]
         cast = lambda grad, like: None if grad is None else grad.to(like.dtype)
-        return (None, None, cast(g[0], q) if q is not None else None, cast(g[1], k) if k is not None else None,
-                dv if ctx.needs_input_grad[4] else None,
-                cast(g[2], q_r) if q_r is not None else None, cast(g[3], k_r) if k_r is not None else None,
-                cast(g[4], freqs) if freqs is not None else None, cast(g[5], delta) if delta is not None else None,
-                cast(g[6], fourier_coeffs) if fourier_coeffs is not None else None)
+        return (None, None, cast(g[0], q), cast(g[1], k), dv if ctx.needs_input_grad[4] else None,
+                None, None, None, None, None)
+
+    @staticmethod
+    def _backward_pope(ctx, dout):
+        """PoPE family: transform and transform-backward as kernels (``pe_pope_expand`` /
+        ``pe_pope_expand_backward``); only the d_r-sized frequency mix goes through autograd."""
+        from .ops import attention_backward, pope_expand, pope_expand_backward
+
+        q, k, v, q_r, k_r, freqs, delta, fourier_coeffs, out, lse = ctx.saved_tensors
+        o = ctx.o
+        dev = v.device
+        need_freq = ctx.needs_input_grad[7] or ctx.needs_input_grad[9]
+        f_leaf = freqs.detach().float().requires_grad_(bool(ctx.needs_input_grad[7]))
+        c_leaf = None if fourier_coeffs is None else fourier_coeffs.detach().float().requires_grad_(
+            bool(ctx.needs_input_grad[9]))
+        with torch.enable_grad():
+            omega = effective_freqs(f_leaf, c_leaf, o["normalize_coeffs"], o["floor_freq"], o["ceil_freq"])
+        om = omega.detach()
+        qt = pope_expand(q, q_r, o["start_pos"], om, None)
+        kt = pope_expand(k, k_r, o["k_start_pos"], om, delta)
+        dqt, dkt, dv = attention_backward(qt, kt, v, out, dout, lse, scale=o["scale"], alibi_slopes=None)
+        d_r = q_r.shape[-1]
+        d_c = 0 if q is None else q.shape[-1]
+        sums = torch.zeros(2, d_r, dtype=torch.float64, device=dev)      # d omega, d clamped delta
+        dq, dq_r = pope_expand_backward(dqt, q_r, d_c, o["start_pos"], om, None, sums[0], None)
+        dk, dk_r = pope_expand_backward(dkt, k_r, d_c, o["k_start_pos"], om, delta, sums[0], sums[1])
+        d_freqs = d_coeffs = d_delta = None
+        if need_freq and omega.requires_grad:
+            wanted = [t for t in (f_leaf, c_leaf) if t is not None and t.requires_grad]
+            got = iter(torch.autograd.grad(omega, wanted, sums[0].float(), allow_unused=True))
+            if f_leaf.requires_grad:
+                d_freqs = next(got)
+            if c_leaf is not None and c_leaf.requires_grad:
+                d_coeffs = next(got)
+        if delta is not None and ctx.needs_input_grad[8]:
+            inside = (delta >= -_TWO_PI) & (delta <= 0.0)                  # torch.clamp passes the gradient here
+            d_delta = (sums[1].float() * inside).to(delta.dtype)
+        cast = lambda grad, like: None if grad is None or like is None else grad.to(like.dtype)
+        return (None, None, dq, dk, dv if ctx.needs_input_grad[4] else None, dq_r, dk_r,
+                cast(d_freqs, freqs), d_delta, cast(d_coeffs, fourier_coeffs))

@@ -22,17 +22,19 @@
 // Q, K, dO and V tiles are loaded once by TMA in the 128-byte-swizzled layout and the same
 // bytes serve as K-major operands (S^T, dP^T) and as MN-major ones (dV, dK, dQ); nothing is
 // transposed in memory.  Q / dO tiles are double-buffered, so the loads of the next query
-// block overlap this block's math.  dK and dV stay in TMEM for the whole CTA; dQ of each
-// block is added to an fp32 buffer in global memory with vector atomics (its summation order
-// across key blocks is therefore not fixed).  D = rowsum(dO o O) comes from a small kernel
-// that runs first.
+// block overlap this block's math.  dK and dV stay in TMEM for the whole CTA.  dQ of each
+// block is drained by four warps of their own: TMEM -> registers -> a staging tile in shared
+// memory (the dS^T buffer, idle at that time) -> TMA reduction (fp32 add) into the global
+// accumulation buffer; the order in which key blocks add is not fixed, so dQ bits vary from
+// run to run.  D = rowsum(dO o O) comes from a small kernel that runs first.
 //
 // TMEM columns: S^T / P^T / dQ [0,128)   dP^T / dS^T [128,256)   dV [256,256+DV)
 //               dK [256+DV, 256+DV+DQK).   P^T of query columns [64h, 64h+64) sits in columns
 // [64h, 64h+32) (inside the half of S^T its own warps read), dS^T likewise at 128 + ....
 // dQ overwrites the S^T / P^T columns: it is issued after the dV product that reads P^T, and
 // MMAs of one thread execute in issue order.
-// Warps 0-7: softmax-gradient math and epilogues; warp 8: TMA; warp 9: TMEM + MMA issue.
+// Warps 0-7: softmax-gradient math and epilogues; warps 8-11: dQ drain; warp 12: TMA;
+// warp 13: TMEM + MMA issue (14, 15 idle: register budgets are set per warpgroup).
 // Every wait is bounded and reports through the device status word.
 
 #include <cuda.h>
@@ -56,7 +58,7 @@ constexpr int TMEM_COLS = 512;
 constexpr int TAIL = 2048;       // barriers, TMEM slot, per-block lse / D vectors
 constexpr int ST_WAIT_BWD = 1 << 9;
 
-enum : int { BAR_KV = 0, BAR_LDFULL = 1, BAR_LDEMPTY = 3, BAR_S = 5, BAR_P = 6, BAR_DQ = 7, BAR_SFREE = 8, BAR_VEC = 9, NUM_BARS = 10 };
+enum : int { BAR_KV = 0, BAR_LDFULL = 1, BAR_LDEMPTY = 3, BAR_S = 5, BAR_P = 6, BAR_DQ = 7, BAR_SFREE = 8, BAR_VEC = 9, BAR_STG = 10, BAR_DRA = 11, BAR_DRB = 12, NUM_BARS = 13 };
 
 template <int DQK, int DV>
 struct BCfg {
@@ -76,7 +78,8 @@ struct BCfg {
 template <int DQK, int DV, bool ALIBI>
 __global__ void __launch_bounds__(NTHREADS, 1)
 pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO) {
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                   const __grid_constant__ CUtensorMap tmDQ) {
   using C = BCfg<DQK, DV>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -111,6 +114,9 @@ pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, c
     mbar_init(bar(BAR_DQ), 1);
     mbar_init(bar(BAR_SFREE), NDRAIN / 32);
     mbar_init(bar(BAR_VEC), NCOMPUTE / 32);
+    mbar_init(bar(BAR_STG), 1);
+    mbar_init(bar(BAR_DRA), NDRAIN / 32);
+    mbar_init(bar(BAR_DRB), 1);
     mbar_fence_init();
     fence_proxy_async_smem();
   }
@@ -233,13 +239,20 @@ pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, c
   } else if (warp >= 8) {
   asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
   {
-    // ===================== dQ drain: TMEM -> registers -> fp32 atomics (lanes = query rows) ======
-    // Its own warps, so that the atomics of block i overlap the softmax of block i + 1.
+    // ===================== dQ drain (lanes = query rows) =====================
+    // TMEM -> registers -> a staging tile in shared memory -> TMA reduction (fp32 add) into the
+    // global accumulation buffer.  The staging tile is the dS^T buffer, idle between this
+    // block's dQ product and the next block's softmax; its own warps, so that the drain of
+    // block i overlaps the S^T product and the softmax of block i + 1.
     const int r = tid & 127;
+    const bool leader = tid == NCOMPUTE;
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
+    constexpr int HALVES = DQK / 64;       // 64 columns (two 32-column boxes, 32 KB) per pass
+    bool dok = true;
+    if (leader) tma_prefetch_desc(&tmDQ);
 #pragma unroll 1
-    for (int it = 0; it < n_iter; ++it) {
-      const int h = hk * p.groups + it / per_head, row = (i_first + it % per_head) * BM + r;
+    for (int it = 0; it < n_iter && dok; ++it) {
+      const int h = hk * p.groups + it / per_head, row0 = (i_first + it % per_head) * BM;
       if (!__all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_DQ), (uint32_t)(it & 1)))) { fail(); break; }
       tc_fence_after_sync();
       uint32_t qr[DQK];
@@ -250,14 +263,32 @@ pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, c
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(BAR_SFREE));   // the S^T / dQ columns may be overwritten
-      if (row < p.Sq) {
-        float* dq_row = p.dq_accum + (((long long)b * p.H + h) * p.Sq + row) * DQK;
 #pragma unroll
-        for (int v = 0; v < DQK / 4; ++v)
-          red_add_v4_f32(dq_row + v * 4, __uint_as_float(qr[v * 4]), __uint_as_float(qr[v * 4 + 1]),
-                         __uint_as_float(qr[v * 4 + 2]), __uint_as_float(qr[v * 4 + 3]));
+      for (int half = 0; half < HALVES; ++half) {
+        const uint32_t ph2 = (uint32_t)((it * HALVES + half) & 1);
+#pragma unroll
+        for (int bx = 0; bx < 2; ++bx)
+#pragma unroll
+          for (int sl = 0; sl < 8; ++sl) {
+            const int c = half * 64 + bx * 32 + sl * 4;
+            sts_v4(ds_smem + (uint32_t)(bx * CH) + swz(r, sl), make_uint4(qr[c], qr[c + 1], qr[c + 2], qr[c + 3]));
+          }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(BAR_DRA));
+        if (!__all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_DRA), ph2))) { fail(); dok = false; break; }
+        if (leader) {
+          tma_reduce_add_4d(&tmDQ, ds_smem, half * 64, row0, h, b);
+          tma_reduce_add_4d(&tmDQ, ds_smem + CH, half * 64 + 32, row0, h, b);
+          bulk_commit_group();
+          bulk_wait_read_all();                       // the tile has been read: it may be rewritten
+          mbar_arrive(bar(BAR_DRB));
+        }
+        if (!__all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_DRB), ph2))) { fail(); dok = false; break; }
       }
+      if (dok && leader) mbar_arrive(bar(BAR_STG));   // the softmax warps may write dS^T again
     }
+    if (leader) bulk_wait_all();                      // every reduction has been performed
   }
   } else {
   asm volatile("setmaxnreg.inc.sync.aligned.u32 136;");
@@ -305,7 +336,7 @@ pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, c
       if (!ok) { fail(); break; }
       tc_fence_after_sync();
       // 16 query columns per round, the next round's TMEM loads in flight during the math
-      uint32_t sr[2][16], dr[2][16], pp[16], dd[16];
+      uint32_t sr[2][16], dr[2][16], pp[16], dall[32];
       const uint32_t s_col = tmem_base + lane_sel + (uint32_t)(hh * 64), d_col = s_col + 128u;
       tmem_ld16(s_col, sr[0]);
       tmem_ld16(d_col, dr[0]);
@@ -337,19 +368,25 @@ pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, c
           const int o = (j & 1) * 8 + (c >> 1);
           pp[o] = pack_bf16x2(pv[0], pv[1]);
           pp[o + 1] = pack_bf16x2(pv[2], pv[3]);
-          dd[o] = pack_bf16x2(gv[0], gv[1]);
-          dd[o + 1] = pack_bf16x2(gv[2], gv[3]);
+          dall[j * 8 + (c >> 1)] = pack_bf16x2(gv[0], gv[1]);
+          dall[j * 8 + (c >> 1) + 1] = pack_bf16x2(gv[2], gv[3]);
         }
-        // dS^T row ``r``, query columns col0 .. +15 = two 16-byte slots of chunk hh
-        const int o = (j & 1) * 8;
-        sts_v4(ds_smem + (uint32_t)(hh * CH) + swz(r, j * 2), make_uint4(dd[o], dd[o + 1], dd[o + 2], dd[o + 3]));
-        sts_v4(ds_smem + (uint32_t)(hh * CH) + swz(r, j * 2 + 1), make_uint4(dd[o + 4], dd[o + 5], dd[o + 6], dd[o + 7]));
         if (j & 1) {
           // packed bf16 back over columns this thread has already read
           tmem_st16(s_col + (uint32_t)((j >> 1) * 16), pp);
-          tmem_st16(d_col + (uint32_t)((j >> 1) * 16), dd);
+          tmem_st16(d_col + (uint32_t)((j >> 1) * 16), *reinterpret_cast<uint32_t(*)[16]>(&dall[(j >> 1) * 16]));
         }
       }
+      // dS^T row ``r`` to shared memory (64 query columns = the eight 16-byte slots of chunk hh),
+      // once the drain warps have let go of the buffer they use as their staging tile
+      if (it > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_STG), ph ^ 1u));
+        if (!ok) { fail(); break; }
+      }
+#pragma unroll
+      for (int sl = 0; sl < 8; ++sl)
+        sts_v4(ds_smem + (uint32_t)(hh * CH) + swz(r, sl),
+               make_uint4(dall[sl * 4], dall[sl * 4 + 1], dall[sl * 4 + 2], dall[sl * 4 + 3]));
       tmem_wait_st();
       fence_proxy_async_smem();
       tc_fence_before_sync();
@@ -455,10 +492,14 @@ int launch_bwd_instance(const BwdParams& p, cudaStream_t stream) {
     }
     configured = true;
   }
-  CUtensorMap tmQ, tmK, tmV, tmDO;
+  CUtensorMap tmQ, tmK, tmV, tmDO, tmDQ;
   if (!encode_map(&tmQ, p.q, DQK, p.Sq, p.H, p.B, BM) || !encode_map(&tmK, p.k, DQK, p.Sk, p.Hkv, p.B, BN) ||
       !encode_map(&tmV, p.v, DV, p.Sk, p.Hkv, p.B, BN) || !encode_map(&tmDO, p.dout, DV, p.Sq, p.H, p.B, BM)) {
     set_error("cuTensorMapEncodeTiled failed for a backward operand");
+    return PE_ATTN_ERR_LAUNCH;
+  }
+  if (!encode_map_f32(&tmDQ, p.dq_accum, DQK, p.Sq, p.H, p.B, BM)) {
+    set_error("cuTensorMapEncodeTiled failed for dq_accum");
     return PE_ATTN_ERR_LAUNCH;
   }
   cudaError_t e = cudaMemsetAsync(p.dq_accum, 0, sizeof(float) * (size_t)p.B * p.H * p.Sq * DQK, stream);
@@ -471,7 +512,7 @@ int launch_bwd_instance(const BwdParams& p, cudaStream_t stream) {
   if (dblocks > 148 * 16) dblocks = 148 * 16;
   bwd_dvec_kernel<<<(unsigned)dblocks, 256, 0, stream>>>(p, DV);
   dim3 grid((unsigned)((p.Sk + BN - 1) / BN), (unsigned)p.Hkv, (unsigned)p.B), block(NTHREADS);
-  kern<<<grid, block, C::SMEM_BYTES, stream>>>(p, tmQ, tmK, tmV, tmDO);
+  kern<<<grid, block, C::SMEM_BYTES, stream>>>(p, tmQ, tmK, tmV, tmDO, tmDQ);
   e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("backward kernel launch failed: %s", cudaGetErrorString(e));

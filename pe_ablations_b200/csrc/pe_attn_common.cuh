@@ -48,7 +48,7 @@ struct BwdParams {
   TensorRef q, k, v, out, dout, dk, dv;
   const float* lse;        // [B, H, Sq] from the forward
   const float* slopes;     // ALiBi, or null
-  float* dq_accum;         // [B, H, Sq, d_qk] fp32, cleared by the launch
+  float* dq_accum;         // [B, Sq, H, d_qk] fp32, cleared by the launch
   float* dvec;             // [B, H, Sq] fp32 workspace
   int* status;
 };

@@ -232,5 +232,19 @@ inline bool encode_map(CUtensorMap* map, const TensorRef& t, int d, int S, int H
   return r == CUDA_SUCCESS;
 }
 
+// Contiguous fp32 [B, S, H, d] tensor as a 4-D TMA tensor (d, S, H, B) with a (32 x rows) box
+// (128-byte rows), 128-byte swizzle: the target of TMA reductions.
+inline bool encode_map_f32(CUtensorMap* map, float* ptr, int d, int S, int H, int B, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)d * 4 * H, (cuuint64_t)d * 4, (cuuint64_t)d * 4 * S * H};
+  cuuint32_t box[4] = {32, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 }  // namespace tc
 }  // namespace pe_attn

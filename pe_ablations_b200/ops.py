@@ -304,8 +304,8 @@ def attention_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: t
 
     q [B,Sq,H,d_qk], k [B,Sk,Hkv,d_qk], v [B,Sk,Hkv,d_v], out / dout [B,Sq,H,d_v] (bf16, last
     dimension contiguous), ``lse`` the forward's [B,H,Sq] logsumexp.  Returns
-    ``(dq fp32 [B,Sq,H,d_qk], dk bf16 like k, dv bf16 like v)``; dq is a view of the
-    [B,H,Sq,d_qk] accumulation buffer the kernel adds into.
+    ``(dq fp32 [B,Sq,H,d_qk], dk bf16 like k, dv bf16 like v)``; dq is the accumulation
+    buffer the kernel adds into.
     """
     for t in (q, k, v, out, dout):
         if not t.is_cuda or t.dtype != torch.bfloat16:
@@ -321,7 +321,7 @@ def attention_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: t
     a.struct_size = C.sizeof(_lib.PeAttnBwdArgs)
     a.B, a.H, a.Hkv, a.Sq, a.Sk, a.d_qk, a.d_v = B, H, Hkv, Sq, Sk, d_qk, d_v
     a.scale = float(scale)
-    dq_accum = torch.empty(B, H, Sq, d_qk, dtype=torch.float32, device=dev)
+    dq_accum = torch.empty(B, Sq, H, d_qk, dtype=torch.float32, device=dev)
     dvec = torch.empty(B, H, Sq, dtype=torch.float32, device=dev)
     dk = torch.empty(B, Sk, Hkv, d_qk, dtype=torch.bfloat16, device=dev)
     dv = torch.empty(B, Sk, Hkv, d_v, dtype=torch.bfloat16, device=dev)
@@ -343,7 +343,59 @@ def attention_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: t
         raise _lib.PeAttnError(rc)
     for t in keep + [dvec]:
         t.record_stream(stream)
-    return dq_accum.transpose(1, 2), dk, dv
+    return dq_accum, dk, dv
+
+
+def _s3(t: torch.Tensor | None):
+    arr = (C.c_int64 * 3)()
+    if t is not None:
+        arr[:] = _strides(t, "bshd")
+    return arr
+
+
+def pope_expand(x_c: torch.Tensor | None, x_r: torch.Tensor, pos0: int, omega: torch.Tensor,
+                delta: torch.Tensor | None) -> torch.Tensor:
+    """[x_c | softplus(x_r) cos(phi) | softplus(x_r) sin(phi)] as one bf16 [B,S,H,d_c+2d_r] tensor
+    (phi = pos * omega + clamp(delta, -2 pi, 0)): the operands the backward kernel reads."""
+    B, S, H, d_r = x_r.shape
+    d_c = 0 if x_c is None else x_c.shape[-1]
+    out = torch.empty(B, S, H, d_c + 2 * d_r, dtype=torch.bfloat16, device=x_r.device)
+    om, dl = _f32(omega, x_r.device), _f32(delta, x_r.device)
+    with torch.cuda.device(x_r.device):
+        stream = torch.cuda.current_stream(x_r.device)
+        rc = _lib.lib.pe_pope_expand(None if x_c is None else x_c.data_ptr(), _s3(x_c), x_r.data_ptr(), _s3(x_r),
+                                     out.data_ptr(), _s3(out), B, S, H, d_c, d_r, int(pos0), om.data_ptr(),
+                                     None if dl is None else dl.data_ptr(), C.c_void_p(stream.cuda_stream))
+    if rc != 0:
+        raise _lib.PeAttnError(rc)
+    for t in (om, dl):
+        if t is not None:
+            t.record_stream(stream)
+    return out
+
+
+def pope_expand_backward(grad: torch.Tensor, x_r: torch.Tensor, d_c: int, pos0: int, omega: torch.Tensor,
+                         delta: torch.Tensor | None, d_omega: torch.Tensor, d_delta: torch.Tensor | None):
+    """Gradient of ``pope_expand``: returns (d x_c or None, d x_r) in bf16 and accumulates the
+    frequency / clamped-phase-bias gradients into the fp64 vectors ``d_omega`` / ``d_delta``."""
+    B, S, H, d_r = x_r.shape
+    dev = x_r.device
+    dx_c = torch.empty(B, S, H, d_c, dtype=torch.bfloat16, device=dev) if d_c else None
+    dx_r = torch.empty(B, S, H, d_r, dtype=torch.bfloat16, device=dev)
+    om, dl = _f32(omega, dev), _f32(delta, dev)
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev)
+        rc = _lib.lib.pe_pope_expand_backward(
+            grad.data_ptr(), _dtype_code(grad), _s3(grad), x_r.data_ptr(), _s3(x_r),
+            None if dx_c is None else dx_c.data_ptr(), _s3(dx_c), dx_r.data_ptr(), _s3(dx_r), B, S, H, d_c, d_r,
+            int(pos0), om.data_ptr(), None if dl is None else dl.data_ptr(), d_omega.data_ptr(),
+            None if d_delta is None else d_delta.data_ptr(), C.c_void_p(stream.cuda_stream))
+    if rc != 0:
+        raise _lib.PeAttnError(rc)
+    for t in (om, dl):
+        if t is not None:
+            t.record_stream(stream)
+    return dx_c, dx_r
 
 
 class HostStreamedAttention:

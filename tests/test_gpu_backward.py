@@ -212,3 +212,45 @@ def test_transformer_training_step_matches_reference(grads, i, spec):
         bound = 1e-2 * float(grads[f"{name}/fp32_max/{n}"]) + 2.0 * float(grads[f"{name}/bf16_noise/{n}"])
         err = (have - want).abs().max().item()
         assert err <= bound, f"{name} grad {n}: |diff| {err:.3e} > {bound:.3e}"
+
+
+@pytest.mark.parametrize("dc,dr", [(64, 32), (128, 64), (0, 32)])
+def test_pope_transform_kernels_match_autograd(dc, dr):
+    """pe_pope_expand / pe_pope_expand_backward against the torch restatement of the transform
+    (autograd.transformed_operands, itself tied to the oracle in tests/test_modules_cpu.py)."""
+    from pe_ablations_b200 import autograd as A
+    from pe_ablations_b200.ops import pope_expand, pope_expand_backward
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(21)
+    B, S, H = 2, 193, 3
+    mk = lambda d: torch.randn(B, S, H, d, generator=g).to(torch.bfloat16).to(dev)
+    x_c = mk(dc) if dc else None
+    x_r = mk(dr)
+    omega = (10000.0 ** (-(torch.arange(dr, dtype=torch.float32) / dr))).to(dev)
+    delta = ((torch.rand(dr, generator=g) * 2 - 1) * math.pi).to(dev)
+    grad = torch.randn(B, S, H, dc + 2 * dr, generator=g).to(dev)
+    for key_side in (False, True):
+        dl = delta if key_side else None
+        xr_leaf = x_r.clone().requires_grad_(True)
+        xc_leaf = None if x_c is None else x_c.clone().requires_grad_(True)
+        om_leaf, dl_leaf = omega.clone().requires_grad_(True), delta.clone().requires_grad_(True)
+        want = A._pope_rows(xc_leaf, xr_leaf, 7, om_leaf, dl_leaf if key_side else None)
+        got = pope_expand(x_c, x_r, 7, omega, dl)
+        assert (got.float() - want.detach()).abs().max().item() <= 2e-2
+        want.backward(grad)
+        sums = torch.zeros(2, dr, dtype=torch.float64, device=dev)
+        for gdt in (torch.float32, torch.bfloat16):
+            sums.zero_()
+            dxc, dxr = pope_expand_backward(grad.to(gdt), x_r, dc, 7, omega, dl, sums[0], sums[1] if key_side else None)
+            tol = 2e-2 if gdt == torch.bfloat16 else 1e-2
+            torch.testing.assert_close(dxr.float(), xr_leaf.grad.float(), rtol=tol, atol=tol)
+            if dc:
+                torch.testing.assert_close(dxc.float(), xc_leaf.grad.float(), rtol=tol, atol=tol)
+            ref_w = om_leaf.grad.double()
+            assert (sums[0] - ref_w).abs().max().item() <= 2e-2 * ref_w.abs().max().item()
+            if key_side:
+                # the kernel returns the gradient of the CLAMPED bias; torch zeroes it outside [-2 pi, 0]
+                inside = (delta >= -2 * math.pi) & (delta <= 0)
+                ref_d = dl_leaf.grad.double()
+                assert ((sums[1] * inside) - ref_d).abs().max().item() <= 2e-2 * max(ref_d.abs().max().item(), 1.0)
