@@ -229,6 +229,22 @@ int pe_pope_expand_backward(const void* grad, int grad_dtype, const int64_t* gra
                             const int64_t* dxr_stride, int B, int S, int H, int d_c, int d_r, int pos0,
                             const float* omega, const float* delta, double* d_omega, double* d_delta, void* stream);
 
+/* The same two steps for the rotary family and QKNorm (src/model/rope.py:35-57 and
+ * rope.py:216-217 for YaRN's mscale, src/model/normalization.py:44-56):
+ *   out = normalise(mscale * rotate(x)),  rotate by rows table_row0 .. of ``table``
+ *   ([table_rows, D/2, 2] fp32 (cos, sin); null = no rotation), normalise = x / (|x|_2 + eps)
+ *   when qk_norm != 0; rounding to bf16 after each step, as the forward kernel does.
+ * The backward takes grad = d/d out (bf16 or fp32) and writes d x (bf16); the roundings are
+ * treated as the identity.  x, out, grad, dx: [B,S,H,D] by element strides (batch, head, seq),
+ * D 64 or 128. */
+int pe_rotary_norm_expand(const void* x, const int64_t* x_stride, void* out, const int64_t* out_stride, int B, int S,
+                          int H, int D, const float* table, int table_row0, int table_rows, float mscale, int qk_norm,
+                          float eps, void* stream);
+int pe_rotary_norm_expand_backward(const void* grad, int grad_dtype, const int64_t* grad_stride, const void* x,
+                                   const int64_t* x_stride, void* dx, const int64_t* dx_stride, int B, int S, int H,
+                                   int D, const float* table, int table_row0, int table_rows, float mscale,
+                                   int qk_norm, float eps, void* stream);
+
 /* ---- perplexity evaluation: next-token cross-entropy as loss sums ------------------------
  *
  * Replaces, for the evaluation path, F.cross_entropy on the shifted logits

@@ -5,9 +5,11 @@ logsumexp output.  Backward: the tensor-core backward kernel (``pe_attn_backward
 gradients with respect to the TRANSFORMED operands and V; the positional transform itself is
 re-evaluated here with differentiable torch operations and autograd carries those gradients
 back to the projections and to the encoding's parameters (phase bias, frequencies, Fourier
-coefficients).  For the PoPE family the transform and its gradient are kernels too
-(``pe_pope_expand`` / ``pe_pope_expand_backward``) and only the d_r-sized frequency mix is left
-to autograd.  It is the gradient the reference's training step obtains by autograd through
+coefficients).  The transforms and their gradients are kernels too (``pe_pope_expand`` /
+``pe_pope_expand_backward`` for the PoPE family, ``pe_rotary_norm_expand`` /
+``..._backward`` for rotation, mscale and QKNorm); only the d_r-sized FoPE frequency mix is left
+to torch autograd.  ``transformed_operands`` is the same transform as differentiable torch
+code: the tests check the kernels against it, and it against the oracle.  It is the gradient the reference's training step obtains by autograd through
 its eager modules (src/model/attention.py:77-96, src/model/alibi.py:137-160,
 src/model/fpope_attention.py:145-177 with src/model/pope.py:124-183 /
 src/model/fpope.py:107-146,266-338, src/model/rope.py:35-57, src/model/normalization.py:44-56).
@@ -113,21 +115,21 @@ class FusedAttentionFunction(torch.autograd.Function):
         dout = dout.to(torch.bfloat16)
         if variant == "pope":
             return FusedAttentionFunction._backward_pope(ctx, dout)
-        # differentiable re-evaluation of the transform on detached leaves
-        srcs = [q, k]
-        need = [ctx.needs_input_grad[2], ctx.needs_input_grad[3]]
-        leaves = [t.detach().requires_grad_(n) for t, n in zip(srcs, need)]
-        with torch.enable_grad():
-            qt, kt = transformed_operands(variant, leaves[0], leaves[1], None, None, o, None, None, None)
-        dqt, dkt, dv = attention_backward(qt.detach().to(torch.bfloat16), kt.detach().to(torch.bfloat16), v, out, dout,
-                                          lse, scale=o["scale"], alibi_slopes=o["alibi_slopes"])
-        wanted = [t for t in leaves if t.requires_grad]
-        # the cast to bf16 is treated as the identity, as autograd treats the reference's own cast
-        grads = iter(torch.autograd.grad([qt, kt], wanted, [dqt, dkt.float()], allow_unused=True) if wanted else ())
-        g = [next(grads) if t.requires_grad else None for t in leaves]
-        cast = lambda grad, like: None if grad is None else grad.to(like.dtype)
-        return (None, None, cast(g[0], q), cast(g[1], k), dv if ctx.needs_input_grad[4] else None,
-                None, None, None, None, None)
+        from .ops import rotary_norm_expand
+
+        tab = o["rotary_table"] if variant == "rotary" else None
+        plain = tab is None and not o["qk_norm"]
+        args_q = (tab, o["start_pos"] - o["table_pos0"], o["mscale"], o["qk_norm"], o["qk_norm_eps"])
+        args_k = (tab, o["k_start_pos"] - o["table_pos0"], o["mscale"], o["qk_norm"], o["qk_norm_eps"])
+        qt = q if plain else rotary_norm_expand(q, *args_q)
+        kt = k if plain else rotary_norm_expand(k, *args_k)
+        dqt, dkt, dv = attention_backward(qt, kt, v, out, dout, lse, scale=o["scale"], alibi_slopes=o["alibi_slopes"])
+        if plain:
+            dq, dk = dqt.to(q.dtype), dkt
+        else:
+            dq = rotary_norm_expand(q, *args_q, grad=dqt)
+            dk = rotary_norm_expand(k, *args_k, grad=dkt)
+        return (None, None, dq, dk, dv if ctx.needs_input_grad[4] else None, None, None, None, None, None)
 
     @staticmethod
     def _backward_pope(ctx, dout):

@@ -166,6 +166,123 @@ __global__ void __launch_bounds__(256) pope_expand_backward_kernel(const XfParam
   }
 }
 
+// ---- rotary family / QKNorm --------------------------------------------------------------
+// expand:   y = normalise(mscale * rotate(x)) with the forward kernel's rounding order (bf16
+//           after the rotation, after mscale and after the normalisation); rotation and
+//           normalisation are both optional (src/model/rope.py:35-57, rope.py:216-217,
+//           src/model/normalization.py:44-56).
+// backward: with r the rotated, scaled row and n = |r|_2,
+//           d r = g / (n + eps) - r (r . g) / (n (n + eps)^2),   d x = mscale * rotate^T(d r);
+//           the roundings are treated as the identity, as autograd treats the casts.
+// thread = (row, 8 columns = 4 rotation pairs); the D/8 threads of a row are neighbours in a
+// warp and reduce the two row sums with shuffles.
+struct RnParams {
+  int B, S, H, row0, qk_norm, grad_bf16;
+  float mscale, eps;
+  TensorRef x, out, grad, dx;
+  const float* table;   // [rows, D/2, 2] (cos, sin) or null: no rotation
+};
+
+template <int D>
+__device__ __forceinline__ void rotated_row(const RnParams& p, const uint4& raw, int s, int cv, float (&r)[8],
+                                            float (&cs)[4], float (&sn)[4]) {
+  uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  if (p.table != nullptr) {
+    const float4* tp = reinterpret_cast<const float4*>(p.table + ((size_t)(p.row0 + s) * (D / 2) + cv * 4) * 2);
+    const float4 t0 = __ldg(tp), t1 = __ldg(tp + 1);
+    cs[0] = t0.x; sn[0] = t0.y; cs[1] = t0.z; sn[1] = t0.w; cs[2] = t1.x; sn[2] = t1.y; cs[3] = t1.z; sn[3] = t1.w;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float x0 = bf16_lo(w[e]), x1 = bf16_hi(w[e]);
+      w[e] = pack_bf16x2(x0 * cs[e] - x1 * sn[e], x0 * sn[e] + x1 * cs[e]);
+      if (p.mscale != 1.0f) w[e] = pack_bf16x2(bf16_lo(w[e]) * p.mscale, bf16_hi(w[e]) * p.mscale);
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    r[2 * e] = bf16_lo(w[e]);
+    r[2 * e + 1] = bf16_hi(w[e]);
+  }
+}
+
+template <int D, bool BACKWARD>
+__global__ void __launch_bounds__(256) rotary_norm_kernel(const RnParams p) {
+  constexpr int VPR = D / 8;
+  const long long n = (long long)p.B * p.S * p.H * VPR;
+  // whole warps stay in the loop together (the shuffles below need all lanes of a row)
+  const long long n_pad = (n + 31) / 32 * 32;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n_pad; idx += stride) {
+    const bool live = idx < n;
+    const long long row = (live ? idx : n - 1) / VPR;
+    const int cv = (int)(idx % VPR);
+    const int h = (int)(row % p.H), s = (int)((row / p.H) % p.S), b = (int)(row / ((long long)p.H * p.S));
+    const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(p.x.ptr) + row_offset(p.x, b, h, s);
+    float r[8], cs[4], sn[4];
+    rotated_row<D>(p, ldg_nc_v4(x + cv * 8), s, cv, r, cs, sn);
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss = fmaf(r[e], r[e], ss);
+    if constexpr (!BACKWARD) {
+      if (p.qk_norm) {
+#pragma unroll
+        for (int d = 1; d < VPR; d <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
+        const float inv = 1.0f / (sqrtf(ss) + p.eps);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) r[e] *= inv;
+      }
+      if (live) {
+        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(p.out.ptr)) + row_offset(p.out, b, h, s);
+        *reinterpret_cast<uint4*>(out + cv * 8) = pack8(r);
+      }
+    } else {
+      // gradient with respect to the normalised row: fp32 [.., D] (queries) or bf16 (keys)
+      float g[8];
+      const long long goff = row_offset(p.grad, b, h, s) + cv * 8;
+      if (p.grad_bf16) {
+        unpack8(ldg_nc_v4(reinterpret_cast<const __nv_bfloat16*>(p.grad.ptr) + goff), g);
+      } else {
+        const float4* gp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.grad.ptr) + goff);
+        const float4 a = __ldg(gp), c = __ldg(gp + 1);
+        g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w; g[4] = c.x; g[5] = c.y; g[6] = c.z; g[7] = c.w;
+      }
+      float dr[8];
+      if (p.qk_norm) {
+        float rg = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) rg = fmaf(r[e], g[e], rg);
+#pragma unroll
+        for (int d = 1; d < VPR; d <<= 1) {
+          ss += __shfl_xor_sync(0xffffffffu, ss, d);
+          rg += __shfl_xor_sync(0xffffffffu, rg, d);
+        }
+        const float nrm = sqrtf(ss), inv = 1.0f / (nrm + p.eps);
+        const float coef = nrm > 0.f ? rg * inv * inv / nrm : 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dr[e] = g[e] * inv - r[e] * coef;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dr[e] = g[e];
+      }
+      float dx[8];
+      if (p.table != nullptr) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          dx[2 * e] = (dr[2 * e] * cs[e] + dr[2 * e + 1] * sn[e]) * p.mscale;
+          dx[2 * e + 1] = (dr[2 * e + 1] * cs[e] - dr[2 * e] * sn[e]) * p.mscale;
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dx[e] = dr[e];
+      }
+      if (live) {
+        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(p.dx.ptr)) + row_offset(p.dx, b, h, s);
+        *reinterpret_cast<uint4*>(out + cv * 8) = pack8(dx);
+      }
+    }
+  }
+}
+
 int check_tensor(const char* name, const void* ptr, const int64_t* s) {
   if (ptr == nullptr) {
     set_error("%s is null", name);
@@ -276,4 +393,70 @@ extern "C" int pe_pope_expand_backward(const void* grad, int grad_dtype, const i
     return PE_ATTN_ERR_LAUNCH;
   }
   return PE_ATTN_OK;
+}
+
+// flags: bit 0 = apply the rotation table, bit 1 = L2-normalise the rows
+static int launch_rotary_norm(bool backward, const void* x, const int64_t* x_stride, void* out, const int64_t* out_stride,
+                              const void* grad, int grad_dtype, const int64_t* grad_stride, int B, int S, int H, int D,
+                              const float* table, int table_row0, int table_rows, float mscale, int qk_norm, float eps,
+                              void* stream) {
+  if (B < 1 || S < 1 || H < 1 || (D != 64 && D != 128)) {
+    set_error("rotary / QKNorm transform: unsupported shape (head dim must be 64 or 128)");
+    return PE_ATTN_ERR_SHAPE;
+  }
+  int rc;
+  if ((rc = check_tensor("x", x, x_stride)) || (rc = check_tensor(backward ? "dx" : "out", out, out_stride))) return rc;
+  if (backward && (rc = check_tensor("grad", grad, grad_stride))) return rc;
+  if (table != nullptr && (table_row0 < 0 || table_row0 + S > table_rows)) {
+    set_error("rotary table rows [%d, %d) do not cover the positions in use", table_row0, table_row0 + S);
+    return PE_ATTN_ERR_SHAPE;
+  }
+  RnParams p;
+  memset(&p, 0, sizeof(p));
+  p.B = B; p.S = S; p.H = H; p.row0 = table_row0;
+  p.mscale = table != nullptr ? mscale : 1.0f; p.eps = eps; p.table = table;
+  p.x = ref_of(x, x_stride);
+  if (backward) {
+    p.dx = ref_of(out, out_stride);
+    p.grad = ref_of(grad, grad_stride);
+    p.qk_norm = qk_norm ? 1 : 0;
+    p.grad_bf16 = grad_dtype == PE_ATTN_BF16 ? 1 : 0;
+  } else {
+    p.out = ref_of(out, out_stride);
+    p.qk_norm = qk_norm ? 1 : 0;
+  }
+  const unsigned grid = grid_for((long long)B * S * H * (D / 8));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (D == 64) {
+    if (backward) rotary_norm_kernel<64, true><<<grid, 256, 0, st>>>(p);
+    else rotary_norm_kernel<64, false><<<grid, 256, 0, st>>>(p);
+  } else {
+    if (backward) rotary_norm_kernel<128, true><<<grid, 256, 0, st>>>(p);
+    else rotary_norm_kernel<128, false><<<grid, 256, 0, st>>>(p);
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("rotary / QKNorm transform launch failed: %s", cudaGetErrorString(e));
+    return PE_ATTN_ERR_LAUNCH;
+  }
+  return PE_ATTN_OK;
+}
+
+extern "C" int pe_rotary_norm_expand(const void* x, const int64_t* x_stride, void* out, const int64_t* out_stride, int B,
+                                     int S, int H, int D, const float* table, int table_row0, int table_rows,
+                                     float mscale, int qk_norm, float eps, void* stream) {
+  return launch_rotary_norm(false, x, x_stride, out, out_stride, nullptr, 0, nullptr, B, S, H, D, table, table_row0,
+                            table_rows, mscale, qk_norm, eps, stream);
+}
+
+extern "C" int pe_rotary_norm_expand_backward(const void* grad, int grad_dtype, const int64_t* grad_stride, const void* x,
+                                              const int64_t* x_stride, void* dx, const int64_t* dx_stride, int B, int S,
+                                              int H, int D, const float* table, int table_row0, int table_rows,
+                                              float mscale, int qk_norm, float eps, void* stream) {
+  if (grad_dtype != PE_ATTN_BF16 && grad_dtype != PE_ATTN_FP32) {
+    set_error("grad_dtype must be PE_ATTN_BF16 or PE_ATTN_FP32");
+    return PE_ATTN_ERR_VARIANT;
+  }
+  return launch_rotary_norm(true, x, x_stride, dx, dx_stride, grad, grad_dtype, grad_stride, B, S, H, D, table,
+                            table_row0, table_rows, mscale, qk_norm, eps, stream);
 }

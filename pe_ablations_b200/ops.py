@@ -398,6 +398,29 @@ def pope_expand_backward(grad: torch.Tensor, x_r: torch.Tensor, d_c: int, pos0: 
     return dx_c, dx_r
 
 
+def rotary_norm_expand(x: torch.Tensor, table: torch.Tensor | None, table_row0: int, mscale: float, qk_norm: bool,
+                       eps: float, grad: torch.Tensor | None = None) -> torch.Tensor:
+    """normalise(mscale * rotate(x)) as a bf16 [B,S,H,D] tensor; with ``grad`` (the gradient with
+    respect to that result, bf16 or fp32) the gradient with respect to ``x`` instead."""
+    B, S, H, D = x.shape
+    out = torch.empty(B, S, H, D, dtype=torch.bfloat16, device=x.device)
+    rows = 0 if table is None else table.shape[0]
+    tptr = None if table is None else table.data_ptr()
+    with torch.cuda.device(x.device):
+        stream = C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
+        if grad is None:
+            rc = _lib.lib.pe_rotary_norm_expand(x.data_ptr(), _s3(x), out.data_ptr(), _s3(out), B, S, H, D, tptr,
+                                                int(table_row0), rows, float(mscale), int(qk_norm), float(eps), stream)
+        else:
+            rc = _lib.lib.pe_rotary_norm_expand_backward(grad.data_ptr(), _dtype_code(grad), _s3(grad), x.data_ptr(),
+                                                         _s3(x), out.data_ptr(), _s3(out), B, S, H, D, tptr,
+                                                         int(table_row0), rows, float(mscale), int(qk_norm),
+                                                         float(eps), stream)
+    if rc != 0:
+        raise _lib.PeAttnError(rc)
+    return out
+
+
 class HostStreamedAttention:
     """Causal PE-attention over pinned HOST tensors, with the copies hidden behind the kernels.
 

@@ -254,3 +254,30 @@ def test_pope_transform_kernels_match_autograd(dc, dr):
                 inside = (delta >= -2 * math.pi) & (delta <= 0)
                 ref_d = dl_leaf.grad.double()
                 assert ((sums[1] * inside) - ref_d).abs().max().item() <= 2e-2 * max(ref_d.abs().max().item(), 1.0)
+
+
+@pytest.mark.parametrize("D,rotate,norm,mscale", [(64, True, True, 1.0), (128, True, False, 1.07), (64, False, True, 1.0),
+                                                  (128, True, True, 1.07)])
+def test_rotary_norm_transform_kernels_match_autograd(D, rotate, norm, mscale):
+    """pe_rotary_norm_expand / ..._backward against the torch restatement (rotation, mscale,
+    QKNorm) and its autograd."""
+    from oracle import pe_attention_oracle as O
+    from pe_ablations_b200 import autograd as A
+    from pe_ablations_b200.ops import rotary_norm_expand
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(33)
+    B, S, H = 2, 171, 3            # 2 * 171 * 3 rows: the last warp is partly idle
+    x = torch.randn(B, S, H, D, generator=g).to(torch.bfloat16).to(dev)
+    table = O.rotary_table(O.rope_inv_freq(D), 256).to(dev) if rotate else None
+    grad = torch.randn(B, S, H, D, generator=g).to(dev)
+    leaf = x.clone().requires_grad_(True)
+    o = dict(start_pos=9, k_start_pos=9, table_pos0=0, mscale=mscale, qk_norm=norm, qk_norm_eps=1e-6, rotary_table=table)
+    want, _ = A.transformed_operands("rotary" if rotate else "nope", leaf, leaf, None, None, o, None, None, None)
+    got = rotary_norm_expand(x, table, 9, mscale, norm, 1e-6)
+    assert (got.float() - want.detach()).abs().max().item() <= 2e-2 * max(1.0, want.detach().abs().max().item())
+    want.backward(grad)
+    for gdt in (torch.float32, torch.bfloat16):
+        dx = rotary_norm_expand(x, table, 9, mscale, norm, 1e-6, grad=grad.to(gdt))
+        tol = 3e-2 if gdt == torch.bfloat16 else 2e-2
+        torch.testing.assert_close(dx.float(), leaf.grad.float(), rtol=tol, atol=tol)
