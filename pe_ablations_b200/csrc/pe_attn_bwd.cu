@@ -85,8 +85,8 @@ pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, c
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + 256);
-  float* lse_s = reinterpret_cast<float*>(smem + 1024);   // [128] log2-scaled logsumexp of the query block
-  float* dsum_s = reinterpret_cast<float*>(smem + 1536);  // [128] D of the query block
+  float* lse_s = reinterpret_cast<float*>(smem + 1024);   // [128] -log2(e) * logsumexp of the query block's rows
+  float* dsum_s = reinterpret_cast<float*>(smem + 1536);  // [128] -scale * D of the query block's rows
   auto bar = [&](int idx) -> uint32_t { return smem_base + 8u * (uint32_t)idx; };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -300,13 +300,13 @@ pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, c
     const float c2 = p.scale * 1.4426950408889634f;
     const int key = key0 + r;
     bool ok = true;
-    // each thread fetches one entry of the block's vectors, one block ahead: log2-scaled lse
-    // (first half of the threads) or scale * D (second half)
+    // each thread fetches one entry of the block's vectors, one block ahead: -log2(e) * lse
+    // (first half of the threads) or -scale * D (second half), the addends of the two FMAs
     auto fetch_vec = [&](int it) -> float {
       const int h = hk * p.groups + it / per_head, row = (i_first + it % per_head) * BM + r;
       if (row >= p.Sq) return 0.f;
       const long long idx = ((long long)b * p.H + h) * p.Sq + row;
-      return hh == 0 ? p.lse[idx] * 1.4426950408889634f : p.dvec[idx] * p.scale;
+      return hh == 0 ? -p.lse[idx] * 1.4426950408889634f : -p.dvec[idx] * p.scale;
     };
     float vec_next = n_iter > 0 ? fetch_vec(0) : 0.f;
 #pragma unroll 1
@@ -330,7 +330,10 @@ pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, c
       float slope2 = 0.f;
       if constexpr (ALIBI) slope2 = p.slopes[h] * 1.4426950408889634f;
       const bool need_mask = (key0 + BN - 1 > row0 + p.causal_off) || (key0 + BN > p.Sk) || (row0 + BM > p.Sq);
-      const bool key_live = key < p.Sk;
+      // query column c of this block sees this thread's key iff c >= c_first (causality; no
+      // column if the key is past Sk) and c < c_end (rows past Sq)
+      const int c_first = key < p.Sk ? key - row0 - p.causal_off : (1 << 30);
+      const int c_end = p.Sq - row0;
 
       ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_S), ph));
       if (!ok) { fail(); break; }
@@ -354,16 +357,28 @@ pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, c
           const float4 d4 = *reinterpret_cast<const float4*>(dsum_s + col0 + c);
           const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dsv[4] = {d4.x, d4.y, d4.z, d4.w};
           float pv[4], gv[4];
+          // packed fp32x2 FMA / MUL (half the issue slots of scalar code); exponentials on the SFU
+          const float2 cc = make_float2(c2, c2), sc = make_float2(p.scale, p.scale);
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
+          for (int e = 0; e < 4; e += 2) {
             const int qc = col0 + c + e;
-            const int row_lim = row0 + qc + p.causal_off;     // last key this query row sees
-            float x = fmaf(__uint_as_float(sr[j & 1][c + e]), c2, -lv[e]);
-            if constexpr (ALIBI) x = fmaf((float)(key - row_lim), slope2, x);
-            float pe = ex2_approx(x);
-            if (need_mask && (!key_live || key > row_lim || row0 + qc >= p.Sq)) pe = 0.f;
-            pv[e] = pe;
-            gv[e] = pe * fmaf(__uint_as_float(dr[j & 1][c + e]), p.scale, -dsv[e]);
+            float2 x = __ffma2_rn(make_float2(__uint_as_float(sr[j & 1][c + e]), __uint_as_float(sr[j & 1][c + e + 1])),
+                                  cc, make_float2(lv[e], lv[e + 1]));
+            if constexpr (ALIBI) {
+              // -slope * (query position - key position), in log2 units
+              x.x = fmaf((float)(key - row0 - p.causal_off - qc), slope2, x.x);
+              x.y = fmaf((float)(key - row0 - p.causal_off - qc - 1), slope2, x.y);
+            }
+            float2 pe = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+            if (need_mask) {
+              if (qc < c_first || qc >= c_end) pe.x = 0.f;
+              if (qc + 1 < c_first || qc + 1 >= c_end) pe.y = 0.f;
+            }
+            const float2 t = __ffma2_rn(make_float2(__uint_as_float(dr[j & 1][c + e]), __uint_as_float(dr[j & 1][c + e + 1])),
+                                        sc, make_float2(dsv[e], dsv[e + 1]));
+            const float2 gg = __fmul2_rn(pe, t);
+            pv[e] = pe.x; pv[e + 1] = pe.y;
+            gv[e] = gg.x; gv[e + 1] = gg.y;
           }
           const int o = (j & 1) * 8 + (c >> 1);
           pp[o] = pack_bf16x2(pv[0], pv[1]);
