@@ -68,7 +68,11 @@ struct BCfg {
   static constexpr int Q_OFF = V_OFF + NVC * CH;             // 2 stages
   static constexpr int DO_OFF = Q_OFF + 2 * NQC * CH;        // 2 stages
   static constexpr int DS_OFF = DO_OFF + 2 * NVC * CH;
-  static constexpr int SMEM_BYTES = DS_OFF + 2 * CH + 1024;  // slack to align the base to 1024
+  // the dQ drain's staging tile: its own 32 KB where shared memory allows (d_v = 64), else the
+  // dS^T buffer, which is idle between a block's dQ product and the next block's softmax
+  static constexpr bool OWN_STAGING = DS_OFF + 4 * CH + 1024 <= 232448;
+  static constexpr int STG_OFF = OWN_STAGING ? DS_OFF + 2 * CH : DS_OFF;
+  static constexpr int SMEM_BYTES = STG_OFF + 2 * CH + 1024;  // slack to align the base to 1024
   static_assert(DQK == 64 || DQK == 128, "d_qk must be 64 or 128");
   static_assert(DV == 64 || DV == 128, "d_v must be 64 or 128");
   static_assert(256 + DV + DQK <= TMEM_COLS, "TMEM budget exceeded");
@@ -130,7 +134,7 @@ pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, c
   const uint32_t tmem_base = *tmem_slot;
 
   const uint32_t k_smem = smem_base + C::K_OFF, v_smem = smem_base + C::V_OFF, q_smem = smem_base + C::Q_OFF,
-                 do_smem = smem_base + C::DO_OFF, ds_smem = smem_base + C::DS_OFF;
+                 do_smem = smem_base + C::DO_OFF, ds_smem = smem_base + C::DS_OFF, stg_smem = smem_base + C::STG_OFF;
   constexpr uint32_t Q_STAGE = (uint32_t)(C::NQC * CH), DO_STAGE = (uint32_t)(C::NVC * CH);
   constexpr uint32_t LD_BYTES = Q_STAGE + DO_STAGE;
 
@@ -241,9 +245,9 @@ pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, c
   {
     // ===================== dQ drain (lanes = query rows) =====================
     // TMEM -> registers -> a staging tile in shared memory -> TMA reduction (fp32 add) into the
-    // global accumulation buffer.  The staging tile is the dS^T buffer, idle between this
-    // block's dQ product and the next block's softmax; its own warps, so that the drain of
-    // block i overlaps the S^T product and the softmax of block i + 1.
+    // global accumulation buffer.  Its own warps, so that the drain of block i overlaps the
+    // S^T product and the softmax of block i + 1.  Without a staging tile of its own the dS^T
+    // buffer serves, idle between this block's dQ product and the next block's softmax stores.
     const int r = tid & 127;
     const bool leader = tid == NCOMPUTE;
     const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;
@@ -271,15 +275,15 @@ pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, c
 #pragma unroll
           for (int sl = 0; sl < 8; ++sl) {
             const int c = half * 64 + bx * 32 + sl * 4;
-            sts_v4(ds_smem + (uint32_t)(bx * CH) + swz(r, sl), make_uint4(qr[c], qr[c + 1], qr[c + 2], qr[c + 3]));
+            sts_v4(stg_smem + (uint32_t)(bx * CH) + swz(r, sl), make_uint4(qr[c], qr[c + 1], qr[c + 2], qr[c + 3]));
           }
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(BAR_DRA));
         if (!__all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_DRA), ph2))) { fail(); dok = false; break; }
         if (leader) {
-          tma_reduce_add_4d(&tmDQ, ds_smem, half * 64, row0, h, b);
-          tma_reduce_add_4d(&tmDQ, ds_smem + CH, half * 64 + 32, row0, h, b);
+          tma_reduce_add_4d(&tmDQ, stg_smem, half * 64, row0, h, b);
+          tma_reduce_add_4d(&tmDQ, stg_smem + CH, half * 64 + 32, row0, h, b);
           bulk_commit_group();
           bulk_wait_read_all();                       // the tile has been read: it may be rewritten
           mbar_arrive(bar(BAR_DRB));
@@ -394,7 +398,7 @@ pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, c
       }
       // dS^T row ``r`` to shared memory (64 query columns = the eight 16-byte slots of chunk hh),
       // once the drain warps have let go of the buffer they use as their staging tile
-      if (it > 0) {
+      if (it > 0 && !C::OWN_STAGING) {
         ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_STG), ph ^ 1u));
         if (!ok) { fail(); break; }
       }
