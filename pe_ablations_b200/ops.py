@@ -315,8 +315,9 @@ def attention_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: t
     dev = q.device
     if lse.dtype != torch.float32 or lse.shape != (B, H, Sq) or not lse.is_contiguous():
         raise ValueError("lse must be a contiguous fp32 [B, H, Sq] tensor")
-    if dout.stride(-1) != 1:
-        dout = dout.contiguous()
+    # TMA wants a 16-byte aligned base and strides that are multiples of 16 bytes
+    tma_ok = lambda t: (t.stride(-1) == 1 and t.data_ptr() % 16 == 0 and all(s % 8 == 0 for s in t.stride()[:-1]))
+    q, k, v, out, dout = (t if tma_ok(t) else t.contiguous() for t in (q, k, v, out, dout))
     a = _lib.PeAttnBwdArgs()
     a.struct_size = C.sizeof(_lib.PeAttnBwdArgs)
     a.B, a.H, a.Hkv, a.Sq, a.Sk, a.d_qk, a.d_v = B, H, Hkv, Sq, Sk, d_qk, d_v
