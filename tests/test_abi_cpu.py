@@ -21,12 +21,13 @@ def L():
 def _declared_functions():
     text = open(os.path.join(ROOT, "include", "pe_attn.h")).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(pe_attn_[a-z_]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(pe_[a-z_]+)\s*\(", text)))
 
 
 def test_exports_every_declared_symbol(L):
     names = _declared_functions()
-    assert "pe_attn_forward" in names and len(names) >= 7
+    assert {"pe_attn_forward", "pe_attn_backward", "pe_ce_loss_sums", "pe_pope_expand_backward",
+            "pe_rotary_norm_expand"} <= set(names) and len(names) >= 18
     for n in names:
         assert hasattr(L.lib, n), n
     assert L.lib.pe_attn_version() == 2
@@ -114,3 +115,48 @@ def test_python_wrapper_refuses_cpu_tensors_and_masks():
         pe_attention("nope", q, q, q, mask=torch.ones(1))
     with pytest.raises(ValueError):
         pe_attention("rope", q, q, q)
+
+
+def _bwd_args(L, **over):
+    a = L.PeAttnBwdArgs()
+    a.struct_size = C.sizeof(L.PeAttnBwdArgs)
+    a.B, a.H, a.Hkv, a.Sq, a.Sk, a.d_qk, a.d_v = 2, 8, 4, 512, 512, 128, 64
+    a.scale = 128 ** -0.5
+    for name in ("q", "k", "v", "out", "dout", "dk", "dv", "lse", "dq_accum", "dvec"):
+        setattr(a, name, 0x10000)
+    for s_, h, d in (("q_stride", 8, 128), ("k_stride", 4, 128), ("v_stride", 4, 64), ("out_stride", 8, 64),
+                     ("dout_stride", 8, 64), ("dk_stride", 4, 128), ("dv_stride", 4, 64)):
+        getattr(a, s_)[:] = (512 * h * d, d, h * d)
+    for k, v in over.items():
+        if k.endswith("_stride"):
+            getattr(a, k)[:] = v
+        else:
+            setattr(a, k, v)
+    return a
+
+
+def test_backward_entry_rejects_bad_arguments_before_touching_the_gpu(L):
+    """Only calls that fail validation: a call that validates would launch on these fake pointers."""
+    bwd = L.lib.pe_attn_backward
+    assert bwd(None, None) == 1
+    assert bwd(C.byref(_bwd_args(L, struct_size=8)), None) == 2
+    assert bwd(C.byref(_bwd_args(L, Sq=600)), None) == 3                      # Sk < Sq
+    assert bwd(C.byref(_bwd_args(L, H=6)), None) == 3                         # H % Hkv
+    assert bwd(C.byref(_bwd_args(L, d_qk=256)), None) == 3                    # forward-only head dim
+    assert b"(64,64), (128,64), (128,128)" in L.lib.pe_attn_last_error()
+    assert bwd(C.byref(_bwd_args(L, dout=None)), None) == 1
+    assert bwd(C.byref(_bwd_args(L, dk=0x10008)), None) == 4
+    assert bwd(C.byref(_bwd_args(L, q_stride=(512 * 8 * 128, 130, 8 * 128))), None) == 4
+    assert bwd(C.byref(_bwd_args(L, lse=None)), None) == 1
+
+
+def test_transform_entries_reject_bad_shapes(L):
+    s3 = (C.c_int64 * 3)(512 * 8 * 32, 32, 8 * 32)
+    rc = L.lib.pe_pope_expand(None, s3, 0x10000, s3, 0x10000, s3, 1, 512, 8, 0, 48, 0, 0x10000, None, None)
+    assert rc == 3 and b"d_r must be 32 or 64" in L.lib.pe_attn_last_error()
+    rc = L.lib.pe_pope_expand(None, s3, None, s3, 0x10000, s3, 1, 512, 8, 0, 32, 0, 0x10000, None, None)
+    assert rc == 1
+    rc = L.lib.pe_rotary_norm_expand(0x10000, s3, 0x10000, s3, 1, 512, 8, 96, None, 0, 0, 1.0, 1, 1e-6, None)
+    assert rc == 3
+    rc = L.lib.pe_rotary_norm_expand(0x10000, s3, 0x10000, s3, 1, 512, 8, 64, 0x10000, 10, 100, 1.0, 1, 1e-6, None)
+    assert rc == 3 and b"do not cover" in L.lib.pe_attn_last_error()
