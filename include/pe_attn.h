@@ -229,6 +229,18 @@ int pe_pope_expand_backward(const void* grad, int grad_dtype, const int64_t* gra
                             const int64_t* dxr_stride, int B, int S, int H, int d_c, int d_r, int pos0,
                             const float* omega, const float* delta, double* d_omega, double* d_delta, void* stream);
 
+/* FoPE's collapse of base frequencies and Fourier coefficients into one effective frequency
+ * per position dimension (FoPEPoPEEmbedding._compute_effective_freqs, src/model/fpope.py:107-146)
+ * and its gradient: omega[c] = base[c] * sum_j a^[c,j] j + base[c], a^ = a / (sum_j |a| + 1e-8)
+ * with PE_ATTN_FOURIER_NORMALIZE, |omega| < floor_freq -> 0, clamp to +-ceil_freq with
+ * PE_ATTN_FOURIER_CEILING.  The backward takes d_omega (fp64 [d_r], as pe_pope_expand_backward
+ * accumulates it) and writes d_coeffs [d_r, n_fourier] and, if not null, d_base [d_r]. */
+int pe_fope_effective_freqs(const float* base, const float* coeffs, int d_r, int n_fourier, unsigned flags,
+                            float floor_freq, float ceil_freq, float* omega, void* stream);
+int pe_fope_effective_freqs_backward(const float* base, const float* coeffs, int d_r, int n_fourier, unsigned flags,
+                                     float floor_freq, float ceil_freq, const double* d_omega, float* d_coeffs,
+                                     float* d_base, void* stream);
+
 /* The same two steps for the rotary family and QKNorm (src/model/rope.py:35-57 and
  * rope.py:216-217 for YaRN's mscale, src/model/normalization.py:44-56):
  *   out = normalise(mscale * rotate(x)),  rotate by rows table_row0 .. of ``table``

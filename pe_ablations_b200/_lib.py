@@ -30,6 +30,7 @@ EXPORTS = (
     "pe_ce_scratch_bytes", "pe_ce_loss_sums", "pe_ce_static_max_rows", "pe_ce_loss_sums_static",
     "pe_rmsnorm_forward", "pe_swiglu_forward", "pe_attn_selftest_wait_expiry", "pe_attn_backward",
     "pe_pope_expand", "pe_pope_expand_backward", "pe_rotary_norm_expand", "pe_rotary_norm_expand_backward",
+    "pe_fope_effective_freqs", "pe_fope_effective_freqs_backward",
 )
 
 
@@ -111,6 +112,12 @@ def _load() -> C.CDLL:
     lib.pe_pope_expand_backward.argtypes = [C.c_void_p, C.c_int, S3, C.c_void_p, S3, C.c_void_p, S3, C.c_void_p, S3,
                                             C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
                                             C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.pe_fope_effective_freqs.restype = C.c_int
+    lib.pe_fope_effective_freqs.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_uint, C.c_float, C.c_float,
+                                            C.c_void_p, C.c_void_p]
+    lib.pe_fope_effective_freqs_backward.restype = C.c_int
+    lib.pe_fope_effective_freqs_backward.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_uint, C.c_float,
+                                                     C.c_float, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.pe_rotary_norm_expand.restype = C.c_int
     lib.pe_rotary_norm_expand.argtypes = [C.c_void_p, S3, C.c_void_p, S3, C.c_int, C.c_int, C.c_int, C.c_int,
                                           C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_int, C.c_float, C.c_void_p]

@@ -7,8 +7,8 @@ re-evaluated here with differentiable torch operations and autograd carries thos
 back to the projections and to the encoding's parameters (phase bias, frequencies, Fourier
 coefficients).  The transforms and their gradients are kernels too (``pe_pope_expand`` /
 ``pe_pope_expand_backward`` for the PoPE family, ``pe_rotary_norm_expand`` /
-``..._backward`` for rotation, mscale and QKNorm); only the d_r-sized FoPE frequency mix is left
-to torch autograd.  ``transformed_operands`` is the same transform as differentiable torch
+``..._backward`` for rotation, mscale and QKNorm, ``pe_fope_effective_freqs`` / ``..._backward``
+for the FoPE frequency mix).  ``transformed_operands`` is the same transform as differentiable torch
 code: the tests check the kernels against it, and it against the oracle.  It is the gradient the reference's training step obtains by autograd through
 its eager modules (src/model/attention.py:77-96, src/model/alibi.py:137-160,
 src/model/fpope_attention.py:145-177 with src/model/pope.py:124-183 /
@@ -42,6 +42,10 @@ def effective_freqs(freqs: torch.Tensor, fourier_coeffs: torch.Tensor | None, no
     if ceil_freq is not None:
         eff = eff.clamp(-ceil_freq, ceil_freq)
     return eff
+
+
+def _f32c(t: torch.Tensor) -> torch.Tensor:
+    return t.detach().to(torch.float32).contiguous()
 
 
 def _rotate(x: torch.Tensor, table: torch.Tensor, row0: int, mscale: float) -> torch.Tensor:
@@ -133,20 +137,16 @@ class FusedAttentionFunction(torch.autograd.Function):
 
     @staticmethod
     def _backward_pope(ctx, dout):
-        """PoPE family: transform and transform-backward as kernels (``pe_pope_expand`` /
-        ``pe_pope_expand_backward``); only the d_r-sized frequency mix goes through autograd."""
-        from .ops import attention_backward, pope_expand, pope_expand_backward
+        """PoPE family: frequency mix, transform and both gradients as kernels."""
+        from .ops import attention_backward, fope_effective_freqs, pope_expand, pope_expand_backward
 
         q, k, v, q_r, k_r, freqs, delta, fourier_coeffs, out, lse = ctx.saved_tensors
         o = ctx.o
         dev = v.device
-        need_freq = ctx.needs_input_grad[7] or ctx.needs_input_grad[9]
-        f_leaf = freqs.detach().float().requires_grad_(bool(ctx.needs_input_grad[7]))
-        c_leaf = None if fourier_coeffs is None else fourier_coeffs.detach().float().requires_grad_(
-            bool(ctx.needs_input_grad[9]))
-        with torch.enable_grad():
-            omega = effective_freqs(f_leaf, c_leaf, o["normalize_coeffs"], o["floor_freq"], o["ceil_freq"])
-        om = omega.detach()
+        base = _f32c(freqs)
+        coeffs = None if fourier_coeffs is None else _f32c(fourier_coeffs)
+        om = base if coeffs is None else fope_effective_freqs(base, coeffs, o["normalize_coeffs"], o["floor_freq"],
+                                                              o["ceil_freq"])
         qt = pope_expand(q, q_r, o["start_pos"], om, None)
         kt = pope_expand(k, k_r, o["k_start_pos"], om, delta)
         dqt, dkt, dv = attention_backward(qt, kt, v, out, dout, lse, scale=o["scale"], alibi_slopes=None)
@@ -156,13 +156,12 @@ class FusedAttentionFunction(torch.autograd.Function):
         dq, dq_r = pope_expand_backward(dqt, q_r, d_c, o["start_pos"], om, None, sums[0], None)
         dk, dk_r = pope_expand_backward(dkt, k_r, d_c, o["k_start_pos"], om, delta, sums[0], sums[1])
         d_freqs = d_coeffs = d_delta = None
-        if need_freq and omega.requires_grad:
-            wanted = [t for t in (f_leaf, c_leaf) if t is not None and t.requires_grad]
-            got = iter(torch.autograd.grad(omega, wanted, sums[0].float(), allow_unused=True))
-            if f_leaf.requires_grad:
-                d_freqs = next(got)
-            if c_leaf is not None and c_leaf.requires_grad:
-                d_coeffs = next(got)
+        if coeffs is None:
+            if ctx.needs_input_grad[7]:
+                d_freqs = sums[0].float()
+        elif ctx.needs_input_grad[7] or ctx.needs_input_grad[9]:
+            d_coeffs, d_freqs = fope_effective_freqs(base, coeffs, o["normalize_coeffs"], o["floor_freq"], o["ceil_freq"],
+                                                     d_omega=sums[0], want_d_base=bool(ctx.needs_input_grad[7]))
         if delta is not None and ctx.needs_input_grad[8]:
             inside = (delta >= -_TWO_PI) & (delta <= 0.0)                  # torch.clamp passes the gradient here
             d_delta = (sums[1].float() * inside).to(delta.dtype)

@@ -473,28 +473,32 @@ pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, c
   }
 }
 
-// D[b, h, row] = sum_d dO[b, row, h, d] * O[b, row, h, d]  (fp32), one warp per row.
-__global__ void bwd_dvec_kernel(const BwdParams p, int dv) {
-  const long long n_rows = (long long)p.B * p.H * p.Sq;
-  const int lane = threadIdx.x & 31;
-  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
-  for (long long r = warp0; r < n_rows; r += n_warps) {
-    const int row = (int)(r % p.Sq);
-    const int h = (int)((r / p.Sq) % p.H), b = (int)(r / ((long long)p.Sq * p.H));
+// D[b, h, row] = sum_d dO[b, row, h, d] * O[b, row, h, d]  (fp32).  Memory-bound: 16 bytes per
+// thread and tensor, the DV / 8 threads of a row are neighbours in a warp and add up with
+// shuffles; rows ordered (batch, position, head) like the tensors.
+template <int DV>
+__global__ void __launch_bounds__(256) bwd_dvec_kernel(const BwdParams p) {
+  constexpr int VPR = DV / 8;
+  const long long n = (long long)p.B * p.Sq * p.H * VPR;
+  const long long n_pad = (n + 31) / 32 * 32;   // whole warps stay in the loop (shuffles)
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n_pad; idx += stride) {
+    const bool live = idx < n;
+    const long long r = (live ? idx : n - 1) / VPR;
+    const int cv = (int)(idx % VPR);
+    const int h = (int)(r % p.H), row = (int)((r / p.H) % p.Sq), b = (int)(r / ((long long)p.H * p.Sq));
     const __nv_bfloat16* o = reinterpret_cast<const __nv_bfloat16*>(p.out.ptr) + (long long)b * p.out.sb +
-                             (long long)h * p.out.sh + (long long)row * p.out.ss;
+                             (long long)h * p.out.sh + (long long)row * p.out.ss + cv * 8;
     const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(p.dout.ptr) + (long long)b * p.dout.sb +
-                             (long long)h * p.dout.sh + (long long)row * p.dout.ss;
+                             (long long)h * p.dout.sh + (long long)row * p.dout.ss + cv * 8;
+    const uint4 ov = ldg_nc_v4(o), gv = ldg_nc_v4(g);
+    const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w}, gw[4] = {gv.x, gv.y, gv.z, gv.w};
     float acc = 0.f;
-    for (int d = lane * 2; d < dv; d += 64) {
-      const float2 of = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + d));
-      const float2 gf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(g + d));
-      acc = fmaf(of.x, gf.x, fmaf(of.y, gf.y, acc));
-    }
 #pragma unroll
-    for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
-    if (lane == 0) p.dvec[r] = acc;
+    for (int e = 0; e < 4; ++e) acc = fmaf(bf16_lo(ow[e]), bf16_lo(gw[e]), fmaf(bf16_hi(ow[e]), bf16_hi(gw[e]), acc));
+#pragma unroll
+    for (int d = 1; d < VPR; d <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+    if (live && cv == 0) p.dvec[((long long)b * p.H + h) * p.Sq + row] = acc;
   }
 }
 
@@ -526,10 +530,9 @@ int launch_bwd_instance(const BwdParams& p, cudaStream_t stream) {
     set_error("clearing dq_accum failed: %s", cudaGetErrorString(e));
     return PE_ATTN_ERR_LAUNCH;
   }
-  const long long n_rows = (long long)p.B * p.H * p.Sq;
-  long long dblocks = (n_rows + 7) / 8;
-  if (dblocks > 148 * 16) dblocks = 148 * 16;
-  bwd_dvec_kernel<<<(unsigned)dblocks, 256, 0, stream>>>(p, DV);
+  long long dblocks = ((long long)p.B * p.H * p.Sq * (DV / 8) + 255) / 256;
+  if (dblocks > 148 * 8) dblocks = 148 * 8;
+  bwd_dvec_kernel<DV><<<(unsigned)dblocks, 256, 0, stream>>>(p);
   dim3 grid((unsigned)((p.Sk + BN - 1) / BN), (unsigned)p.Hkv, (unsigned)p.B), block(NTHREADS);
   kern<<<grid, block, C::SMEM_BYTES, stream>>>(p, tmQ, tmK, tmV, tmDO, tmDQ);
   e = cudaGetLastError();

@@ -283,6 +283,43 @@ __global__ void __launch_bounds__(256) rotary_norm_kernel(const RnParams p) {
   }
 }
 
+// ---- FoPE frequency mix (src/model/fpope.py:107-146) and its gradient -------------------------
+// One thread per position dimension c; d_r and the number of Fourier terms are tens.
+__global__ void fope_freqs_kernel(const KParams p, int d_r, float* omega) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c < d_r) omega[c] = effective_freq(p, c);
+}
+
+// eff = base * W / Z + base with W = sum_j a_j j, Z = sum_j |a_j| + 1e-8 (Z = 1 without
+// normalisation); zero gradient where the floor clip or the ceiling clamp is active.
+__global__ void fope_freqs_backward_kernel(const KParams p, int d_r, const double* d_omega, float* d_coeffs,
+                                           float* d_base) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= d_r) return;
+  const float* a = p.coeffs + (size_t)c * p.n_fourier;
+  const bool normalize = (p.flags & PE_ATTN_FOURIER_NORMALIZE) != 0;
+  double Z = 1.0, W = 0.0;
+  if (normalize) {
+    Z = 1e-8;
+    for (int j = 0; j < p.n_fourier; ++j) Z += fabs((double)a[j]);
+  }
+  for (int j = 0; j < p.n_fourier; ++j) W += (double)a[j] * (j + 1);
+  const double base = p.freqs[c];
+  const double eff = base * W / Z + base;
+  bool pass = fabs(eff) >= (double)p.floor_freq;
+  if ((p.flags & PE_ATTN_FOURIER_CEILING) && fabs(eff) > (double)p.ceil_freq) pass = false;
+  const double g = pass ? d_omega[c] : 0.0;
+  for (int j = 0; j < p.n_fourier; ++j) {
+    double d = (j + 1) / Z;
+    if (normalize) {
+      const double sgn = a[j] > 0.f ? 1.0 : (a[j] < 0.f ? -1.0 : 0.0);
+      d -= W / (Z * Z) * sgn;
+    }
+    d_coeffs[(size_t)c * p.n_fourier + j] = (float)(g * base * d);
+  }
+  if (d_base != nullptr) d_base[c] = (float)(g * (W / Z + 1.0));
+}
+
 int check_tensor(const char* name, const void* ptr, const int64_t* s) {
   if (ptr == nullptr) {
     set_error("%s is null", name);
@@ -459,4 +496,59 @@ extern "C" int pe_rotary_norm_expand_backward(const void* grad, int grad_dtype, 
   }
   return launch_rotary_norm(true, x, x_stride, dx, dx_stride, grad, grad_dtype, grad_stride, B, S, H, D, table,
                             table_row0, table_rows, mscale, qk_norm, eps, stream);
+}
+
+static int fope_params(KParams* k, const float* base, const float* coeffs, int d_r, int n_fourier, unsigned flags,
+                       float floor_freq, float ceil_freq) {
+  if (base == nullptr || coeffs == nullptr) {
+    set_error("base frequencies and fourier_coeffs are required");
+    return PE_ATTN_ERR_NULL;
+  }
+  if (d_r < 1 || d_r > 1024 || n_fourier < 1) {
+    set_error("unsupported d_r / n_fourier");
+    return PE_ATTN_ERR_SHAPE;
+  }
+  memset(k, 0, sizeof(*k));
+  k->flags = PE_ATTN_FOURIER_MIX | (flags & (PE_ATTN_FOURIER_NORMALIZE | PE_ATTN_FOURIER_CEILING));
+  k->freqs = base; k->coeffs = coeffs; k->n_fourier = n_fourier;
+  k->floor_freq = floor_freq; k->ceil_freq = ceil_freq;
+  return PE_ATTN_OK;
+}
+
+extern "C" int pe_fope_effective_freqs(const float* base, const float* coeffs, int d_r, int n_fourier, unsigned flags,
+                                       float floor_freq, float ceil_freq, float* omega, void* stream) {
+  KParams k;
+  int rc = fope_params(&k, base, coeffs, d_r, n_fourier, flags, floor_freq, ceil_freq);
+  if (rc) return rc;
+  if (omega == nullptr) {
+    set_error("omega is null");
+    return PE_ATTN_ERR_NULL;
+  }
+  fope_freqs_kernel<<<(d_r + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(k, d_r, omega);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("pe_fope_effective_freqs launch failed: %s", cudaGetErrorString(e));
+    return PE_ATTN_ERR_LAUNCH;
+  }
+  return PE_ATTN_OK;
+}
+
+extern "C" int pe_fope_effective_freqs_backward(const float* base, const float* coeffs, int d_r, int n_fourier,
+                                                unsigned flags, float floor_freq, float ceil_freq, const double* d_omega,
+                                                float* d_coeffs, float* d_base, void* stream) {
+  KParams k;
+  int rc = fope_params(&k, base, coeffs, d_r, n_fourier, flags, floor_freq, ceil_freq);
+  if (rc) return rc;
+  if (d_omega == nullptr || d_coeffs == nullptr) {
+    set_error("d_omega and d_coeffs are required");
+    return PE_ATTN_ERR_NULL;
+  }
+  fope_freqs_backward_kernel<<<(d_r + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(k, d_r, d_omega, d_coeffs,
+                                                                                            d_base);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("pe_fope_effective_freqs_backward launch failed: %s", cudaGetErrorString(e));
+    return PE_ATTN_ERR_LAUNCH;
+  }
+  return PE_ATTN_OK;
 }

@@ -399,6 +399,33 @@ def pope_expand_backward(grad: torch.Tensor, x_r: torch.Tensor, d_c: int, pos0: 
     return dx_c, dx_r
 
 
+def fope_effective_freqs(base: torch.Tensor, coeffs: torch.Tensor, normalize: bool, floor_freq: float,
+                         ceil_freq: float | None, d_omega: torch.Tensor | None = None, want_d_base: bool = False):
+    """FoPE's effective frequencies [d_r] from base frequencies and Fourier coefficients (fp32,
+    contiguous, on the GPU); with ``d_omega`` (fp64 [d_r]) their gradient instead:
+    ``(d_coeffs, d_base or None)``."""
+    d_r, n_f = coeffs.shape
+    flags = (_lib.FOURIER_NORMALIZE if normalize else 0) | (_lib.FOURIER_CEILING if ceil_freq is not None else 0)
+    ceil = float(ceil_freq) if ceil_freq is not None else 0.0
+    with torch.cuda.device(coeffs.device):
+        stream = C.c_void_p(torch.cuda.current_stream(coeffs.device).cuda_stream)
+        if d_omega is None:
+            omega = torch.empty(d_r, dtype=torch.float32, device=coeffs.device)
+            rc = _lib.lib.pe_fope_effective_freqs(base.data_ptr(), coeffs.data_ptr(), d_r, n_f, flags, float(floor_freq),
+                                                  ceil, omega.data_ptr(), stream)
+            result = omega
+        else:
+            d_coeffs = torch.empty_like(coeffs)
+            d_base = torch.empty_like(base) if want_d_base else None
+            rc = _lib.lib.pe_fope_effective_freqs_backward(
+                base.data_ptr(), coeffs.data_ptr(), d_r, n_f, flags, float(floor_freq), ceil, d_omega.data_ptr(),
+                d_coeffs.data_ptr(), None if d_base is None else d_base.data_ptr(), stream)
+            result = (d_coeffs, d_base)
+    if rc != 0:
+        raise _lib.PeAttnError(rc)
+    return result
+
+
 def rotary_norm_expand(x: torch.Tensor, table: torch.Tensor | None, table_row0: int, mscale: float, qk_norm: bool,
                        eps: float, grad: torch.Tensor | None = None) -> torch.Tensor:
     """normalise(mscale * rotate(x)) as a bf16 [B,S,H,D] tensor; with ``grad`` (the gradient with

@@ -281,3 +281,29 @@ def test_rotary_norm_transform_kernels_match_autograd(D, rotate, norm, mscale):
         dx = rotary_norm_expand(x, table, 9, mscale, norm, 1e-6, grad=grad.to(gdt))
         tol = 3e-2 if gdt == torch.bfloat16 else 2e-2
         torch.testing.assert_close(dx.float(), leaf.grad.float(), rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("normalize,ceiling", [(True, False), (False, False), (True, True)])
+def test_fope_frequency_mix_kernels_match_autograd(normalize, ceiling):
+    """pe_fope_effective_freqs / ..._backward against the torch restatement and its autograd
+    (floor clip and ceiling clamp both active on some dimensions)."""
+    from pe_ablations_b200 import autograd as A
+    from pe_ablations_b200.ops import fope_effective_freqs
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(17)
+    d_r, n_f = 32, 8
+    base = (10000.0 ** (-(torch.arange(d_r, dtype=torch.float32) / d_r)) * 3.0).to(dev)
+    coeffs = (torch.randn(d_r, n_f, generator=g) * (0.4 if normalize else 0.05)).to(dev)
+    coeffs[3, 2] = 0.0                                   # |a| is not differentiable here: torch uses 0
+    floor, ceil = 2 * math.pi / 64, (2.0 if ceiling else None)
+    b_leaf, c_leaf = base.clone().requires_grad_(True), coeffs.clone().requires_grad_(True)
+    want = A.effective_freqs(b_leaf, c_leaf, normalize, floor, ceil)
+    got = fope_effective_freqs(base, coeffs, normalize, floor, ceil)
+    assert (got == 0).any() and (got != 0).any()
+    torch.testing.assert_close(got, want.detach(), rtol=1e-6, atol=1e-7)
+    d_omega = torch.randn(d_r, generator=g, dtype=torch.float64).to(dev)
+    want.backward(d_omega.float())
+    d_coeffs, d_base = fope_effective_freqs(base, coeffs, normalize, floor, ceil, d_omega=d_omega, want_d_base=True)
+    torch.testing.assert_close(d_coeffs, c_leaf.grad, rtol=1e-4, atol=1e-6)
+    torch.testing.assert_close(d_base, b_leaf.grad, rtol=1e-4, atol=1e-6)
