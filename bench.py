@@ -243,7 +243,7 @@ def run_ours(args) -> dict:
                      "launch_ms": round(kernel_ms, 4)},
     }
     if not args.no_eval:
-        ev_line = run_eval(torch, dist, dev, rank, world, args.eval_sequences)
+        ev_line = run_eval(torch, dist, dev, rank, world, args.eval_sequences, not args.eval_graph)
         if ev_line is not None:
             line["eval_1b_16k"] = ev_line
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -253,7 +253,7 @@ def run_ours(args) -> dict:
     return line if rank == 0 else None
 
 
-def run_eval(torch, dist, dev, rank: int, world: int, n_sequences: int):
+def run_eval(torch, dist, dev, rank: int, world: int, n_sequences: int, no_graph: bool = True):
     """Second headline: 1B-shape forward + perplexity, 16k context, sequences sharded over ranks.
 
     Random-init bf16 weights (seeded), ``n_sequences`` x 16384 uniform-random token ids; each
@@ -269,13 +269,15 @@ def run_eval(torch, dist, dev, rank: int, world: int, n_sequences: int):
     ids = torch.randint(0, E.MODEL_1B["vocab_size"], (n_sequences, seq), generator=g)
     mine = E.shard_range(n_sequences, world, rank)
     my_ids = ids[mine.start:mine.stop].to(dev)
-    E.evaluate_shard(model, my_ids[:1])          # warm-up: cuBLAS heuristics, allocator
+    # warm-up (cuBLAS heuristics, allocator) and capture of one sequence's forward into a CUDA graph
+    graphed = None if no_graph else E.GraphedLossSums(model, my_ids[:1])
+    E.evaluate_shard(model, my_ids[:1], graphed=graphed)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    nll, cnt = E.evaluate_shard(model, my_ids)
+    nll, cnt = E.evaluate_shard(model, my_ids, graphed=graphed)
     tot_nll, tot_cnt = E.reduce_loss_sums(nll, cnt)
     e1.record()
     torch.cuda.synchronize()
@@ -292,6 +294,7 @@ def run_eval(torch, dist, dev, rank: int, world: int, n_sequences: int):
             "unit": "tokens/s", "sequences": n_sequences, "seq_len": seq, "ms_total": round(ms, 2),
             "perplexity": round(E.perplexity(tot_nll, tot_cnt), 3), "scaling": "strong",
             "parallelism": f"sequences sharded over {world} GPU(s); one all-reduce of 2 scalars",
+            "launch": "eager" if no_graph else "one CUDA graph per sequence",
             "flops_per_token": 3.52e9}
 
 
@@ -419,6 +422,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-eval", action="store_true", help="skip the 1B-shape 16k perplexity evaluation")
     ap.add_argument("--eval-sequences", type=int, default=64)
+    ap.add_argument("--eval-graph", action="store_true",
+                    help="replay the evaluation forward from a CUDA graph (measured: no gain, the eager path is "
+                         "already GPU-bound)")
     ap.add_argument("--e2e-chunks", type=int, default=8, help="sequence blocks of the pipelined host-buffer call")
     ap.add_argument("--workload", default="forward", choices=["forward", "training"],
                     help="forward: the headline benchmark; training: forward+backward of the attention op (1 GPU)")

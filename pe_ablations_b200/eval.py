@@ -51,14 +51,57 @@ def perplexity(nll_sum: float, count: float) -> float:
 
 
 @torch.no_grad()
-def evaluate_shard(model, input_ids: torch.Tensor, micro_batch: int = 1, autocast_dtype=torch.bfloat16):
-    """NLL sum and token count of this rank's sequences [n, S] (device tensors)."""
+class GraphedLossSums:
+    """``model.loss_sums`` for batches of one fixed shape, captured once into a CUDA graph.
+
+    One 16k-token forward of the 1B shape is about a thousand kernel launches; replayed from a
+    graph they run back to back, without the gaps the Python launch path leaves between them.
+    Two eager runs on a side stream come first (they perform every first-use host step: kernel
+    attributes, TMA descriptor lookups, cuBLAS plans, scratch allocations), then the capture.
+    The token ids are copied into a static buffer before each replay; the two result scalars
+    are static too and must be consumed (added up) before the next replay.
+    """
+
+    def __init__(self, model, example_ids: torch.Tensor, autocast_dtype=torch.bfloat16):
+        dev = example_ids.device
+        self.model, self.autocast_dtype = model, autocast_dtype
+        self.static_ids = example_ids.clone()
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self._run()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.nll, self.cnt = self._run()
+
+    def _run(self):
+        if self.autocast_dtype is not None:
+            with torch.autocast("cuda", dtype=self.autocast_dtype):
+                return self.model.loss_sums(self.static_ids)
+        return self.model.loss_sums(self.static_ids)
+
+    def __call__(self, ids: torch.Tensor):
+        if ids.shape != self.static_ids.shape:
+            raise ValueError(f"captured for token ids of shape {tuple(self.static_ids.shape)}, got {tuple(ids.shape)}")
+        self.static_ids.copy_(ids)
+        self.graph.replay()
+        return self.nll, self.cnt
+
+
+def evaluate_shard(model, input_ids: torch.Tensor, micro_batch: int = 1, autocast_dtype=torch.bfloat16,
+                   graphed: GraphedLossSums | None = None):
+    """NLL sum and token count of this rank's sequences [n, S] (device tensors).  With ``graphed``
+    (captured for ``micro_batch`` sequences of this length) full micro-batches replay the graph."""
     dev = input_ids.device
     nll = torch.zeros((), dtype=torch.float64, device=dev)
     cnt = torch.zeros((), dtype=torch.float64, device=dev)
     for i in range(0, input_ids.shape[0], micro_batch):
         ids = input_ids[i:i + micro_batch]
-        if autocast_dtype is not None and dev.type == "cuda":
+        if graphed is not None and ids.shape == graphed.static_ids.shape:
+            a, c = graphed(ids)
+        elif autocast_dtype is not None and dev.type == "cuda":
             with torch.autocast("cuda", dtype=autocast_dtype):
                 a, c = model.loss_sums(ids)
         else:
@@ -70,11 +113,11 @@ def evaluate_shard(model, input_ids: torch.Tensor, micro_batch: int = 1, autocas
 
 @torch.no_grad()
 def sharded_perplexity(model, all_input_ids: torch.Tensor, rank: int, world: int, micro_batch: int = 1,
-                       autocast_dtype=torch.bfloat16, group=None) -> dict:
+                       autocast_dtype=torch.bfloat16, group=None, graphed: GraphedLossSums | None = None) -> dict:
     """Perplexity of ``all_input_ids`` [N, S] with sequences sharded over ``world`` ranks."""
     mine = shard_range(all_input_ids.shape[0], world, rank)
     ids = all_input_ids[mine.start:mine.stop].to(next(model.parameters()).device, non_blocking=True)
-    nll, cnt = evaluate_shard(model, ids, micro_batch, autocast_dtype)
+    nll, cnt = evaluate_shard(model, ids, micro_batch, autocast_dtype, graphed)
     tot_nll, tot_cnt = reduce_loss_sums(nll, cnt, group)
     return {"nll_sum": tot_nll, "count": tot_cnt, "loss": tot_nll / max(tot_cnt, 1.0),
             "perplexity": perplexity(tot_nll, tot_cnt), "local_sequences": len(mine)}

@@ -185,3 +185,25 @@ def test_fused_swiglu_matches_reference_formula(dtype):
         d = (got.float() - ref.float()).abs()
         assert (d > 0).float().mean().item() < 0.01
         assert (d <= ref.float().abs() * 2 ** -7 + 1e-6).all()
+
+
+def test_graphed_loss_sums_equal_eager():
+    """eval.GraphedLossSums (one CUDA graph per batch shape) gives the eager loss sums."""
+    from pe_ablations_b200 import eval as E
+    from pe_ablations_b200.model import Transformer, TransformerConfig
+
+    cfg = TransformerConfig(vocab_size=512, hidden_dim=256, num_layers=2, num_heads=2, num_kv_heads=2, head_dim=128,
+                            ffn_dim=512, max_seq_len=512, pe_mode="fpope", fpope_d_rope=64,
+                            fpope_num_fourier_terms=8, fpope_training_length=512, fpope_delta_init="uniform")
+    torch.manual_seed(0)
+    model = Transformer(cfg).eval()
+    G.fill_parameters(model, 91)
+    model = model.cuda()
+    ids = torch.randint(0, 512, (3, 512), generator=torch.Generator().manual_seed(2)).cuda()
+    with torch.no_grad():
+        want = E.evaluate_shard(model, ids)
+        graphed = E.GraphedLossSums(model, ids[:1])
+        got = E.evaluate_shard(model, ids, graphed=graphed)
+    torch.cuda.synchronize()
+    assert float(got[1]) == float(want[1]) == 3 * 511
+    assert abs(float(got[0]) - float(want[0])) <= 1e-9 * abs(float(want[0]))
