@@ -50,7 +50,6 @@ def perplexity(nll_sum: float, count: float) -> float:
     return math.exp(nll_sum / count) if count > 0 else float("inf")
 
 
-@torch.no_grad()
 class GraphedLossSums:
     """``model.loss_sums`` for batches of one fixed shape, captured once into a CUDA graph.
 
@@ -62,6 +61,7 @@ class GraphedLossSums:
     are static too and must be consumed (added up) before the next replay.
     """
 
+    @torch.no_grad()
     def __init__(self, model, example_ids: torch.Tensor, autocast_dtype=torch.bfloat16):
         dev = example_ids.device
         self.model, self.autocast_dtype = model, autocast_dtype
@@ -90,6 +90,7 @@ class GraphedLossSums:
         return self.nll, self.cnt
 
 
+@torch.no_grad()
 def evaluate_shard(model, input_ids: torch.Tensor, micro_batch: int = 1, autocast_dtype=torch.bfloat16,
                    graphed: GraphedLossSums | None = None):
     """NLL sum and token count of this rank's sequences [n, S] (device tensors).  With ``graphed``
