@@ -307,3 +307,40 @@ def test_fope_frequency_mix_kernels_match_autograd(normalize, ceiling):
     d_coeffs, d_base = fope_effective_freqs(base, coeffs, normalize, floor, ceil, d_omega=d_omega, want_d_base=True)
     torch.testing.assert_close(d_coeffs, c_leaf.grad, rtol=1e-4, atol=1e-6)
     torch.testing.assert_close(d_base, b_leaf.grad, rtol=1e-4, atol=1e-6)
+
+
+def test_logsumexp_output_of_the_fp32_kernel():
+    from pe_ablations_b200 import pe_attention
+    from oracle import pe_attention_oracle as O
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(8)
+    B, S, H, Hkv, d = 1, 150, 4, 2, 48
+    mk = lambda h: torch.randn(B, S, h, d, generator=g)
+    q, k, v = mk(H), mk(Hkv), mk(Hkv)
+    slopes = O.alibi_slopes(H)
+    lse = torch.full((B, H, S), float("nan"), device=dev)
+    pe_attention("alibi", q.to(dev), k.to(dev), v.to(dev), alibi_slopes=slopes, lse=lse)
+    want = O.attention_core("alibi", q, k, v, slopes=slopes, return_lse=True)[1]
+    assert (lse.cpu() - want).abs().max().item() <= 1e-4
+
+
+def test_backward_accepts_a_strided_upstream_gradient():
+    """dout as autograd hands it over after a transpose: not contiguous, copied before the TMA loads."""
+    from pe_ablations_b200 import pe_attention
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(9)
+    B, S, H, d = 1, 260, 2, 64
+    mk = lambda: torch.randn(B, S, H, d, generator=g).to(torch.bfloat16).to(dev).requires_grad_(True)
+    q, k, v = mk(), mk(), mk()
+    w = torch.randn(B, H, S, d, generator=g).to(torch.bfloat16).to(dev)
+    out = pe_attention("nope", q, k, v)
+    (out.transpose(1, 2) * w).sum().backward()            # upstream gradient arrives as a transposed view
+    g1 = [t.grad.clone() for t in (q, k, v)]
+    for t in (q, k, v):
+        t.grad = None
+    out = pe_attention("nope", q, k, v)
+    out.backward(w.transpose(1, 2).contiguous())
+    for a, b_ in zip(g1, (q.grad, k.grad, v.grad)):
+        torch.testing.assert_close(a.float(), b_.float(), rtol=1e-2, atol=1e-2)
