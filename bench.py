@@ -413,6 +413,91 @@ def run_training(args) -> dict:
     }
 
 
+def run_variants(args) -> dict:
+    """Secondary workload (``--workload variants``): the fused forward of every positional-encoding
+    variant at the configuration the benchmark list gives it (configurations 1-4; NoPE and ALiBi
+    at configuration 2's shape), one GPU, CUDA events, L2 flushed between launches."""
+    import torch
+
+    import pe_ablations_b200 as P
+    from pe_ablations_b200 import pe as PE
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    peak, peak_src = measured_peak()
+    g = torch.Generator().manual_seed(0)
+
+    def tensors(Bv, Sv, Hv, dims, dtype):
+        return [None if d == 0 else torch.randn(Bv, Sv, Hv, d, generator=g).to(dtype).to(dev) for d in dims]
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 3)):
+            flush.zero_()
+            fn()
+        torch.cuda.synchronize()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        for e0, e1 in ev:
+            flush.zero_()
+            e0.record()
+            fn()
+            e1.record()
+        torch.cuda.synchronize()
+        return statistics.mean(e0.elapsed_time(e1) for e0, e1 in ev)
+
+    rows = []
+
+    def add(name, Bv, Hv, Sv, d_c, d_r, d_v, dtype, variant, **kw):
+        q, k, v, q_r, k_r = tensors(Bv, Sv, Hv, (d_c, d_c, d_v, d_r, d_r), dtype)
+        call = lambda: P.pe_attention(variant, q, k, v, q_r=q_r, k_r=k_r, **kw)
+        with torch.no_grad():
+            ms = timed(call)
+        flops = Bv * Hv * Sv * Sv * (d_c + 2 * d_r + d_v)
+        tf = flops / (ms * 1e-3) / 1e12
+        rows.append({"variant": name, "shape": f"B{Bv} H{Hv} S{Sv} d_qk{d_c + 2 * d_r} d_v{d_v}",
+                     "dtype": "bf16" if dtype == torch.bfloat16 else "fp32", "ms": round(ms, 4), "tflops": round(tf, 2),
+                     "frac_of_peak": round(tf / peak, 4) if dtype == torch.bfloat16 else None})
+
+    bf, f32 = torch.bfloat16, torch.float32
+    with torch.no_grad():
+        # configuration 1: PoPE, fp32 (FFMA kernel: no tensor-core roofline applies)
+        pope = PE.PoPEEmbedding(dim=32, max_seq_len=512).to(dev)
+        pope.phase_bias.uniform_(-math.pi, math.pi)
+        add("pope (configuration 1)", 1, 8, 512, 64, 32, 64, f32, "pope", scale=128 ** -0.5, **pope.kernel_args())
+        # configuration 2: RoPE / NTK (scale 4) / YaRN (scale 4), plus NoPE and ALiBi at the same shape
+        for name, rope in (("rope (configuration 2)", PE.RotaryEmbedding(64, 2048, 10000.0)),
+                           ("rope-ntk (configuration 2)", PE.NTKAwareRotaryEmbedding(64, 2048, 10000.0, 4.0)),
+                           ("rope-yarn", PE.YaRNRotaryEmbedding(64, 2048, 10000.0, 4.0, original_max_seq_len=512))):
+            rope = rope.to(dev)
+            add(name, 8, 12, 2048, 64, 0, 64, bf, "rotary", rotary_table=rope.freqs_cis,
+                mscale=float(getattr(rope, "mscale", 1.0)))
+        add("rope + QKNorm", 8, 12, 2048, 64, 0, 64, bf, "rotary", qk_norm=True,
+            rotary_table=PE.RotaryEmbedding(64, 2048, 10000.0).to(dev).freqs_cis)
+        add("nope", 8, 12, 2048, 64, 0, 64, bf, "nope")
+        add("alibi + QKNorm", 8, 12, 2048, 64, 0, 64, bf, "alibi", qk_norm=True, alibi_slopes=PE.alibi_slopes(12).to(dev))
+        # configuration 3: FoPE frequencies driving a rotary table, head_dim 128
+        fope = PE.FoPEPoPEEmbedding(dim=64, max_seq_len=4096, num_fourier_terms=16, fourier_sigma=0.3,
+                                    training_length=4096)
+        ang = torch.outer(torch.arange(4096, dtype=torch.float32), fope.effective_freqs().float().cpu())
+        table = torch.stack((ang.cos(), ang.sin()), dim=-1).to(dev)
+        add("fope-rotary (configuration 3)", 4, 16, 4096, 128, 0, 128, bf, "rotary", rotary_table=table)
+        # the reference's own attention shape (head_dim 64, d_rope 32) at a long context
+        fp = PE.FoPEPoPEEmbedding(dim=32, max_seq_len=4096, num_fourier_terms=64, fourier_sigma=0.4,
+                                  training_length=512, delta_init="uniform").to(dev)
+        add("fope+pope, head_dim 64 / d_rope 32", 8, 8, 4096, 64, 32, 64, bf, "pope", **fp.kernel_args())
+        # configuration 4
+        fp4 = PE.FoPEPoPEEmbedding(dim=64, max_seq_len=S, num_fourier_terms=N_FOURIER, fourier_sigma=SIGMA,
+                                   training_length=S, delta_init="uniform").to(dev)
+        add("fope+pope (configuration 4)", B, H, S, D_C, D_R, D_V, bf, "pope", **fp4.kernel_args())
+    P.check_device_status()
+    return {"metric": "fused PE-attention forward TFLOP/s per variant", "unit": "TFLOP/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "higher_is_better": True, "data": "synthetic",
+            "config": {"workload": "every variant at its benchmark configuration, one launch per step",
+                       "l2": "flushed between steps by writing a 256 MiB buffer",
+                       "flops_convention": "B*H*S^2*(d_qk+d_v), causal"},
+            "peak": peak, "peak_source": peak_src, "variants": rows}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -426,13 +511,16 @@ def main():
                     help="replay the evaluation forward from a CUDA graph (measured: no gain, the eager path is "
                          "already GPU-bound)")
     ap.add_argument("--e2e-chunks", type=int, default=8, help="sequence blocks of the pipelined host-buffer call")
-    ap.add_argument("--workload", default="forward", choices=["forward", "training"],
-                    help="forward: the headline benchmark; training: forward+backward of the attention op (1 GPU)")
+    ap.add_argument("--workload", default="forward", choices=["forward", "training", "variants"],
+                    help="forward: the headline benchmark; training: forward+backward of the attention op (1 GPU); "
+                         "variants: the forward of every variant at its benchmark configuration (1 GPU)")
     ap.add_argument("--train-batch", type=int, default=64)
     ap.add_argument("--train-seq", type=int, default=512)
     args = ap.parse_args()
     if args.workload == "training" and args.impl == "ours":
         line = run_training(args)
+    elif args.workload == "variants" and args.impl == "ours":
+        line = run_variants(args)
     else:
         line = run_reference(args) if args.impl == "reference" else run_ours(args)
     if line is not None:
