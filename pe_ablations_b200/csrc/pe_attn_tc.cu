@@ -549,7 +549,9 @@ pe_attn_tc_kernel(const KParams p, const int bh_group, const __grid_constant__ C
     } else if constexpr (MODE == MODE_XFORM) {
       // raw rows and table entries of the next tile are requested before the wait for its stage
       XformRegs<DC> xr;
-      if (n_tiles > 0) xform_load<DC>(p, xr, p.k, b, hk, 0, p.Sk, p.k_pos0, tg);
+      XformCursor<DC> cur;
+      xform_cursor_init<DC>(p, cur, p.k, b, hk, 0, p.k_pos0, BLOCK_N, tg);
+      if (n_tiles > 0) xform_load_next<DC>(p, xr, cur, p.Sk, BLOCK_N);
 #pragma unroll 1
       for (int j = 0; j < n_tiles; ++j) {
         const int s = j & 1;
@@ -559,8 +561,7 @@ pe_attn_tc_kernel(const KParams p, const int bh_group, const __grid_constant__ C
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(BAR_KFULL + s));
-        if (j + 1 < n_tiles)
-          xform_load<DC>(p, xr, p.k, b, hk, (j + 1) * BLOCK_N, p.Sk, p.k_pos0 + (j + 1) * BLOCK_N, tg);
+        if (j + 1 < n_tiles) xform_load_next<DC>(p, xr, cur, p.Sk, BLOCK_N);
       }
     }
   }

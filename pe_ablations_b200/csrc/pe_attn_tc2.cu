@@ -555,7 +555,9 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
       // raw rows and table entries of the next tile are requested before the wait for its stage
       XformRegs<DC> xr;
       const int rbase = (int)rank * HALF_N;
-      if (n_tiles > 0) xform_load<DC>(p, xr, p.k, b, hk, rbase, p.Sk, p.k_pos0 + rbase, tg);
+      XformCursor<DC> cur;
+      xform_cursor_init<DC>(p, cur, p.k, b, hk, rbase, p.k_pos0 + rbase, BLOCK_N, tg);
+      if (n_tiles > 0) xform_load_next<DC>(p, xr, cur, p.Sk, BLOCK_N);
 #pragma unroll 1
       for (int j = 0; j < n_tiles; ++j) {
         const int s = j & 1;
@@ -565,10 +567,7 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(lbar(BAR_KFULL + s));
-        if (j + 1 < n_tiles) {
-          const int r0 = (j + 1) * BLOCK_N + rbase;
-          xform_load<DC>(p, xr, p.k, b, hk, r0, p.Sk, p.k_pos0 + r0, tg);
-        }
+        if (j + 1 < n_tiles) xform_load_next<DC>(p, xr, cur, p.Sk, BLOCK_N);
       }
     }
   }

@@ -76,58 +76,118 @@ __device__ __forceinline__ void xform_load(const KParams& p, XformRegs<DC>& x, c
   }
 }
 
+// The same loads for a walk over consecutive slabs of one (batch, head): the addresses are
+// worked out once and advanced by constants, which leaves about ten instructions per pass
+// (the four warps that build K tiles get few issue slots beside the softmax warps).
+template <int DC>
+struct XformCursor {
+  const char* raw;      // this thread's 8 columns of its first row of the current slab
+  const float4* tab;    // the matching (cos, sin) table entries
+  long long raw_step, raw_slab;   // bytes between a thread's rows / between slabs
+  int row;              // global index of the thread's first row in the current slab
+};
+
+template <int DC>
+__device__ __forceinline__ void xform_cursor_init(const KParams& p, XformCursor<DC>& c, const TensorRef& content, int b,
+                                                  int head, int row0, int pos_row0, int slab_stride_rows, int tg) {
+  using X = XformRegs<DC>;
+  const int cv = tg % X::VPR, r_in = tg / X::VPR;
+  c.raw = reinterpret_cast<const char*>(content.ptr) +
+          2 * ((long long)b * content.sb + (long long)head * content.sh + (long long)cv * 8 +
+               (long long)(row0 + r_in) * content.ss);
+  c.raw_step = 2 * (long long)X::RPP * content.ss;
+  c.raw_slab = 2 * (long long)slab_stride_rows * content.ss;
+  c.tab = p.table == nullptr ? nullptr
+                             : reinterpret_cast<const float4*>(p.table) +
+                                   ((long long)(pos_row0 + r_in - p.table_pos0) * (DC / 2) + cv * 4) / 2;
+  c.row = row0 + r_in;
+}
+
+// loads the current slab and moves the cursor ``slab_stride_rows`` rows on
+template <int DC>
+__device__ __forceinline__ void xform_load_next(const KParams& p, XformRegs<DC>& x, XformCursor<DC>& c, int n_rows,
+                                                int slab_stride_rows) {
+  using X = XformRegs<DC>;
+  const bool rotary = p.variant == PE_ATTN_ROTARY;
+#pragma unroll
+  for (int k = 0; k < X::PASSES; ++k) {
+    const bool live = c.row + k * X::RPP < n_rows;
+    x.raw[k] = live ? ldg_nc_v4(c.raw + k * c.raw_step) : make_uint4(0, 0, 0, 0);
+    x.t0[k] = x.t1[k] = make_float4(1.f, 0.f, 1.f, 0.f);
+    if (rotary && live) {
+      const float4* tp = c.tab + (long long)k * X::RPP * (DC / 4);
+      x.t0[k] = __ldg(tp);
+      x.t1[k] = __ldg(tp + 1);
+    }
+  }
+  c.raw += c.raw_slab;
+  if (rotary) c.tab += (long long)slab_stride_rows * (DC / 4);
+  c.row += slab_stride_rows;
+}
+
 template <int DC>
 __device__ __forceinline__ void xform_finish(const KParams& p, XformRegs<DC>& x, uint32_t base, uint32_t chunk_stride,
                                              int row0, int n_rows, int tg) {
+  // Rotation, mscale and normalisation in fp32 with the packed fp32x2 FMA / MUL of sm_100 (a
+  // quarter of the issue slots of the scalar, round-after-every-step version this replaces: the
+  // four warps that build K tiles were the bottleneck of the rotary / QKNorm variants at
+  // head_dim 64); one rounding to bf16 at the end.
   using X = XformRegs<DC>;
   const int cv = tg % X::VPR, r_in = tg / X::VPR;
   const bool rotary = p.variant == PE_ATTN_ROTARY;
   const bool norm = (p.flags & PE_ATTN_QK_NORM) != 0;
-  float ss[X::PASSES];
+  const float2 ms2 = make_float2(p.mscale, p.mscale);
+  constexpr int GROUP = 4;   // rows (passes) in flight at a time: bounds the live registers
+  static_assert(X::PASSES % GROUP == 0, "passes per slab must be a multiple of 4");
 #pragma unroll
-  for (int k = 0; k < X::PASSES; ++k) {
-    uint32_t w[4] = {x.raw[k].x, x.raw[k].y, x.raw[k].z, x.raw[k].w};
-    if (rotary) {
+  for (int k0 = 0; k0 < X::PASSES; k0 += GROUP) {
+    float2 v[GROUP][4];
+    float ss[GROUP];
+#pragma unroll
+    for (int g = 0; g < GROUP; ++g) {
+      const int k = k0 + g;
+      const uint32_t w[4] = {x.raw[k].x, x.raw[k].y, x.raw[k].z, x.raw[k].w};
       const float cs[4] = {x.t0[k].x, x.t0[k].z, x.t1[k].x, x.t1[k].z};
       const float sn[4] = {x.t0[k].y, x.t0[k].w, x.t1[k].y, x.t1[k].w};
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float x0 = bf16_lo(w[e]), x1 = bf16_hi(w[e]);
-        const float o0 = x0 * cs[e] - x1 * sn[e];
-        const float o1 = x0 * sn[e] + x1 * cs[e];
-        w[e] = pack_bf16x2(o0, o1);
-        if (p.mscale != 1.0f) w[e] = pack_bf16x2(bf16_lo(w[e]) * p.mscale, bf16_hi(w[e]) * p.mscale);
+        float2 o = make_float2(x0, x1);
+        if (rotary) {
+          // (x0 c - x1 s, x0 s + x1 c)
+          o = __ffma2_rn(make_float2(x0, x0), make_float2(cs[e], sn[e]),
+                         __fmul2_rn(make_float2(-x1, x1), make_float2(sn[e], cs[e])));
+          if (p.mscale != 1.0f) o = __fmul2_rn(o, ms2);
+        }
+        v[g][e] = o;
+      }
+      float2 acc = __fmul2_rn(v[g][0], v[g][0]);
+#pragma unroll
+      for (int e = 1; e < 4; ++e) acc = __ffma2_rn(v[g][e], v[g][e], acc);
+      ss[g] = acc.x + acc.y;
+    }
+    if (norm) {
+      // row sum of squares across the VPR lanes that share a row (warp-level reduction)
+#pragma unroll
+      for (int g = 0; g < GROUP; ++g) {
+#pragma unroll
+        for (int d = 1; d < X::VPR; d <<= 1) ss[g] += __shfl_xor_sync(0xffffffffu, ss[g], d);
       }
     }
-    float acc = 0.f;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float x0 = bf16_lo(w[e]), x1 = bf16_hi(w[e]);
-      acc = fmaf(x0, x0, acc);
-      acc = fmaf(x1, x1, acc);
+    for (int g = 0; g < GROUP; ++g) {
+      const int r = r_in + (k0 + g) * X::RPP;
+      if (norm) {
+        const float inv = 1.0f / (sqrtf(ss[g]) + p.eps);
+        const float2 inv2 = make_float2(inv, inv);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[g][e] = __fmul2_rn(v[g][e], inv2);
+      }
+      const int col = cv * 8;
+      sts_v4(base + (col / 64) * chunk_stride + swz(r, (col % 64) / 8),
+             make_uint4(pack_bf16x2(v[g][0].x, v[g][0].y), pack_bf16x2(v[g][1].x, v[g][1].y),
+                        pack_bf16x2(v[g][2].x, v[g][2].y), pack_bf16x2(v[g][3].x, v[g][3].y)));
     }
-    ss[k] = acc;
-    x.raw[k] = make_uint4(w[0], w[1], w[2], w[3]);
-  }
-  if (norm) {
-    // row sum of squares across the VPR lanes that share a row (warp-level reduction)
-#pragma unroll
-    for (int k = 0; k < X::PASSES; ++k) {
-#pragma unroll
-      for (int d = 1; d < X::VPR; d <<= 1) ss[k] += __shfl_xor_sync(0xffffffffu, ss[k], d);
-    }
-  }
-#pragma unroll
-  for (int k = 0; k < X::PASSES; ++k) {
-    const int r = r_in + k * X::RPP;
-    uint32_t w[4] = {x.raw[k].x, x.raw[k].y, x.raw[k].z, x.raw[k].w};
-    if (norm) {
-      const float inv = 1.0f / (sqrtf(ss[k]) + p.eps);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) w[e] = pack_bf16x2(bf16_lo(w[e]) * inv, bf16_hi(w[e]) * inv);
-    }
-    const int col = cv * 8;
-    sts_v4(base + (col / 64) * chunk_stride + swz(r, (col % 64) / 8), make_uint4(w[0], w[1], w[2], w[3]));
   }
 }
 
