@@ -322,13 +322,24 @@ pe_attn_tc_kernel(const KParams p, const int bh_group, const __grid_constant__ C
     const int tg = tid - 128 - i * BLOCK_M;
     const int ntile = nt[i];
     if (ntile > 0) {
-      if constexpr (HAS_XFORM) {
+      if constexpr (MODE == MODE_XFORM && DC <= 64) {
+        // both 64-row halves of the query tile: all loads first, then the math (two register
+        // sets: affordable at head_dim 64 only)
+        const int r0 = m0 + i * BLOCK_M;
+        XformRegs<DC> xa, xb;
+        xform_load<DC>(p, xa, p.q, b, h, r0, p.Sq, p.q_pos0 + r0, tg);
+        xform_load<DC>(p, xb, p.q, b, h, r0 + 64, p.Sq, p.q_pos0 + r0 + 64, tg);
+        xform_finish<DC>(p, xa, q_smem + i * C::Q_TILE_BYTES, C::Q_CHUNK_BYTES, r0, p.Sq, tg);
+        xform_finish<DC>(p, xb, q_smem + i * C::Q_TILE_BYTES + 64 * 128, C::Q_CHUNK_BYTES, r0 + 64, p.Sq, tg);
+      } else if constexpr (HAS_XFORM) {
 #pragma unroll 1
         for (int half = 0; half < 2; ++half) {
           const int r0 = m0 + i * BLOCK_M + half * 64;
           build_slab<DC, DR, MODE>(p, q_smem + i * C::Q_TILE_BYTES + half * 64 * 128, C::Q_CHUNK_BYTES, p.q, p.qr, b,
                                    h, r0, p.Sq, p.q_pos0 + r0, false, freq_s, delta_s, tg);
         }
+      }
+      if constexpr (HAS_XFORM) {
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(BAR_QFULL + i));

@@ -178,7 +178,10 @@ __device__ __forceinline__ void xform_finish(const KParams& p, XformRegs<DC>& x,
     for (int g = 0; g < GROUP; ++g) {
       const int r = r_in + (k0 + g) * X::RPP;
       if (norm) {
-        const float inv = 1.0f / (sqrtf(ss[g]) + p.eps);
+        // special-function-unit square root and reciprocal: 2 ulp, far inside a bf16 rounding
+        float nrm;
+        asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(nrm) : "f"(ss[g]));
+        const float inv = __fdividef(1.0f, nrm + p.eps);
         const float2 inv2 = make_float2(inv, inv);
 #pragma unroll
         for (int e = 0; e < 4; ++e) v[g][e] = __fmul2_rn(v[g][e], inv2);
