@@ -55,6 +55,15 @@ def measured_peak():
         return FALLBACK_BF16_TFLOPS, "fallback (1.59 PFLOP/s)"
 
 
+def measured_sustained_peak():
+    """cuBLAS bf16 throughput of a seconds-long loop under the power cap, or None."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["bf16_tflops_sustained"])
+    except Exception:
+        return None
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
 
@@ -239,6 +248,10 @@ def run_ours(args) -> dict:
                      "achieved": round(kernel_tflops, 2), "peak": peak, "unit": "TFLOP/s",
                      "frac": round(kernel_tflops / peak, 4), "peak_source": peak_src,
                      "frac_of_nominal_2250": round(kernel_tflops / 2250.0, 4),
+                     # context only: what cuBLAS sustains under the same 1 kW cap (the kernel, too,
+                     # runs power-capped for the whole timed region)
+                     "frac_of_sustained_cublas": (round(kernel_tflops / measured_sustained_peak(), 4)
+                                                  if measured_sustained_peak() else None),
                      "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH // world,   # compulsory-traffic kernel: scales with the heads per rank
                      "launch_ms": round(kernel_ms, 4)},
     }
