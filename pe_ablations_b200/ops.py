@@ -461,10 +461,12 @@ class HostStreamedAttention:
     block runs the same kernel over the same 128-key tiles as the one-shot call, so the
     result is the one ``pe_attention`` gives on device copies of the same tensors.
 
-    The staging tensors (one device copy of every input and of the output) are allocated
-    once here and reused by every call; the caller's stream waits for the last output
-    block before ``__call__`` returns control of it, so work queued afterwards -- and CUDA
-    events recorded around the call -- see the whole transfer + compute.
+    The staging tensors (device copies of every input and of the output) are allocated once
+    here, in two sets that calls use in turn: the copy-in of call n + 1 may start while the last
+    kernel and the copy-out of call n are still running, and waits only for the kernels of call
+    n - 1, which read the set it is about to overwrite.  The caller's stream waits for the last
+    output block before ``__call__`` returns control of it, so work queued afterwards -- and
+    CUDA events recorded around the call -- see the whole transfer + compute.
     """
 
     def __init__(self, variant: str, *, B: int, S: int, H: int, Hkv: int, d_c: int, d_r: int, d_v: int,
@@ -477,29 +479,31 @@ class HostStreamedAttention:
         self.device = torch.device(device)
         self.shape = dict(B=B, S=S, H=H, Hkv=Hkv, d_c=d_c, d_r=d_r, d_v=d_v)
         mk = lambda h, d: torch.empty(B, S, h, d, dtype=dtype, device=self.device) if d else None  # noqa: E731
-        self.stage = dict(q=mk(H, d_c), k=mk(Hkv, d_c), q_r=mk(H, d_r), k_r=mk(Hkv, d_r), v=mk(Hkv, d_v))
-        self.out = mk(H, d_v)
+        self.sets = [dict(stage=dict(q=mk(H, d_c), k=mk(Hkv, d_c), q_r=mk(H, d_r), k_r=mk(Hkv, d_r), v=mk(Hkv, d_v)),
+                          out=mk(H, d_v), kernels_done=None, copied_out=None) for _ in range(2)]
+        self.calls = 0
         self.h2d = torch.cuda.Stream(self.device)
         self.d2h = torch.cuda.Stream(self.device)
 
     def __call__(self, host: dict[str, torch.Tensor], out_host: torch.Tensor) -> torch.Tensor:
-        for name, t in self.stage.items():
+        cur = self.sets[self.calls % 2]
+        self.calls += 1
+        st, out_dev = cur["stage"], cur["out"]
+        for name, t in st.items():
             if t is None:
                 continue
             h = host[name]
             if h.is_cuda or not h.is_pinned() or not h.is_contiguous() or h.shape != t.shape or h.dtype != t.dtype:
                 raise ValueError(f"host[{name!r}] must be a pinned contiguous CPU tensor of shape {tuple(t.shape)}")
         if (out_host.is_cuda or not out_host.is_pinned() or not out_host.is_contiguous()
-                or out_host.shape != self.out.shape):
+                or out_host.shape != out_dev.shape):
             raise ValueError("out_host must be a pinned CPU tensor of the output shape")
         S, rows = self.shape["S"], self.shape["S"] // self.chunks
         main = torch.cuda.current_stream(self.device)
-        # the staging tensors may still be read by kernels the caller queued earlier
-        start = torch.cuda.Event()
-        start.record(main)
-        self.h2d.wait_event(start)
-        self.d2h.wait_event(start)
-        st = self.stage
+        # this set's previous user: its kernels read the input copies, its copy-out read ``out``
+        if cur["kernels_done"] is not None:
+            self.h2d.wait_event(cur["kernels_done"])
+            main.wait_event(cur["copied_out"])
         for c in range(self.chunks):
             s0, s1 = c * rows, (c + 1) * rows
             with torch.cuda.stream(self.h2d):
@@ -516,15 +520,17 @@ class HostStreamedAttention:
             sl = lambda t, a, b: None if t is None else t[:, a:b]  # noqa: E731
             pe_attention(self.variant, sl(st["q"], s0, s1), sl(st["k"], 0, s1), st["v"][:, :s1],
                          q_r=sl(st["q_r"], s0, s1), k_r=sl(st["k_r"], 0, s1),
-                         start_pos=s0, k_start_pos=0, out=self.out[:, s0:s1], **self.params)
+                         start_pos=s0, k_start_pos=0, out=out_dev[:, s0:s1], **self.params)
             done = torch.cuda.Event()
             done.record(main)
             with torch.cuda.stream(self.d2h):
                 self.d2h.wait_event(done)
                 for b in range(self.shape["B"]):
-                    out_host[b, s0:s1].copy_(self.out[b, s0:s1], non_blocking=True)
+                    out_host[b, s0:s1].copy_(out_dev[b, s0:s1], non_blocking=True)
+        cur["kernels_done"] = done
         back = torch.cuda.Event()
         back.record(self.d2h)
+        cur["copied_out"] = back
         main.wait_event(back)
         return out_host
 

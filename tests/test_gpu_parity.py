@@ -284,7 +284,7 @@ def test_host_streamed_call_equals_the_device_call(chunks):
     call = HostStreamedAttention("pope", B=B, S=S, H=H, Hkv=Hkv, d_c=dc, d_r=dr, d_v=dv, dtype=torch.bfloat16,
                                  device=dev, chunks=chunks, freqs=freqs, delta=delta)
     out_host = torch.full((B, S, H, dv), float("nan"), dtype=torch.bfloat16).pin_memory()
-    for _ in range(2):                      # the second call reuses the staging tensors
+    for _ in range(3):                      # the third call reuses the first staging set
         call(host, out_host)
     torch.cuda.synchronize()
     check_device_status()
