@@ -46,6 +46,11 @@ CASES = [
     ("alibi_d64", 1, 4, 4, 384, 384, 64, 64, True),
     ("cached_prefix_sq_lt_sk", 1, 2, 1, 200, 328, 128, 64, False),
     ("one_block", 2, 2, 2, 96, 96, 64, 64, False),
+    ("single_row", 1, 2, 2, 1, 1, 64, 64, False),
+    ("gqa_8_to_1_s129", 1, 8, 1, 129, 129, 128, 64, False),
+    ("alibi_d128_cached", 2, 4, 2, 131, 400, 128, 128, True),
+    ("many_blocks_1153", 1, 2, 2, 1153, 1153, 64, 64, False),
+    ("many_blocks_2100_d128", 1, 2, 1, 2100, 2100, 128, 128, False),
 ]
 
 
@@ -68,9 +73,13 @@ def test_backward_matches_autograd(case):
     torch.cuda.synchronize()
     check_device_status()
     assert dq.shape == q.shape and dk.shape == k.shape and dv_.shape == v.shape
-    torch.testing.assert_close(dv_.float().cpu(), dv_w, **TOL)
-    torch.testing.assert_close(dk.float().cpu(), dk_w, **TOL)
-    torch.testing.assert_close(dq.float().cpu(), dq_w, **TOL)
+    # P and dS enter the products rounded to bf16; a gradient entry sums up to Sk of them, so the
+    # absolute floor grows like the square root of the sequence length beyond the 512 the
+    # reference's own comparison ran at
+    tol = dict(rtol=TOL["rtol"], atol=TOL["atol"] * max(1.0, math.sqrt(Sk / 512)))
+    torch.testing.assert_close(dv_.float().cpu(), dv_w, **tol)
+    torch.testing.assert_close(dk.float().cpu(), dk_w, **tol)
+    torch.testing.assert_close(dq.float().cpu(), dq_w, **tol)
 
 
 @pytest.mark.parametrize("variant,dims", [("nope", (64, 0, 64)), ("nope", (128, 0, 128)), ("pope", (64, 32, 64)),
