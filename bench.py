@@ -210,8 +210,11 @@ def run_ours(args) -> dict:
     # ---- end-to-end: host buffers in, host buffer out -----------------------------------
     # the library's host-buffer call: sequence blocks are copied in, attended and copied
     # back on three streams, so the step costs about what its host->device bytes cost
+    in_bytes = sum(v.numel() * v.element_size() for v in host.values())
+    # blocks of about 32 MiB: smaller ones cost more in launches and events than they hide
+    chunks = args.e2e_chunks or max(2, min(8, in_bytes // (32 << 20)))
     streamed = P.HostStreamedAttention("pope", B=B, S=S, H=heads, Hkv=heads, d_c=D_C, d_r=D_R, d_v=D_V,
-                                       dtype=torch.bfloat16, device=dev, chunks=args.e2e_chunks, **dparams)
+                                       dtype=torch.bfloat16, device=dev, chunks=chunks, **dparams)
     out_host = torch.empty(B, S, heads, D_V, dtype=torch.bfloat16).pin_memory()
 
     def e2e_step():
@@ -241,7 +244,7 @@ def run_ours(args) -> dict:
                    "flops_per_step": FLOPS_PER_STEP, "flops_convention": "B*H*S^2*(d_qk+d_v), causal"},
         "e2e": {"value": round(FLOPS_PER_STEP / (e2e_ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
                 "ms_per_step": round(e2e_ms, 3), "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
-                "chunks": args.e2e_chunks, "call": "HostStreamedAttention (copy-in / attend / copy-out pipelined over sequence blocks)"},
+                "chunks": chunks, "call": "HostStreamedAttention (copy-in / attend / copy-out pipelined over sequence blocks)"},
         "gpu_launches": args.steps,
         "clocks": clocks,
         "roofline": {"bound": "tensor", "kernel": "pe_attn_tc2_kernel<128,64,POPE> (CTA pair, cta_group::2)",
@@ -426,6 +429,78 @@ def run_training(args) -> dict:
     }
 
 
+def measured_hbm_peak():
+    """Measured copy bandwidth in GB/s, or the fallback figure."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:
+        return 6650.0, "fallback (6.65 TB/s)"
+
+
+def run_decode(args) -> dict:
+    """Secondary workload (``--workload decode``): one generated token of the 1B shape's attention
+    (16 heads, d_c 128 / d_r 64 / d_v 128, FoPE+PoPE, bf16) against a cache of ``--decode-cache``
+    keys, batch ``--decode-batch``: the split-KV kernel and, beside it, the query-tiled kernel
+    on the same call.  HBM-bound: the algorithmic bytes are the raw cached K halves and V, read
+    once (B * Hkv * Sk * (d_c + d_r + d_v) * 2)."""
+    import torch
+
+    import pe_ablations_b200 as P
+    from pe_ablations_b200 import pe as PE
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    Bd, Hd, Sk = args.decode_batch, H, args.decode_cache
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    g = torch.Generator().manual_seed(11)
+    mk = lambda Sv, d: torch.randn(Bd, Sv, Hd, d, generator=g).to(torch.bfloat16).to(dev)
+    q, q_r = mk(1, D_C), mk(1, D_R)
+    k, k_r, v = mk(Sk, D_C), mk(Sk, D_R), mk(Sk, D_V)
+    fp4 = PE.FoPEPoPEEmbedding(dim=D_R, max_seq_len=Sk, num_fourier_terms=N_FOURIER, fourier_sigma=SIGMA,
+                               training_length=Sk, delta_init="uniform").to(dev)
+    kw = dict(q_r=q_r, k_r=k_r, start_pos=Sk - 1, k_start_pos=0, **fp4.kernel_args())
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 3)):
+            flush.zero_()
+            fn()
+        torch.cuda.synchronize()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        for e0, e1 in ev:
+            flush.zero_()
+            e0.record()
+            fn()
+            e1.record()
+        torch.cuda.synchronize()
+        return statistics.mean(e0.elapsed_time(e1) for e0, e1 in ev)
+
+    with torch.no_grad():
+        split_ms = timed(lambda: P.pe_attention("pope", q, k, v, split_kv=True, **kw))
+        tiled_ms = timed(lambda: P.pe_attention("pope", q, k, v, split_kv=False, **kw))
+        a = P.pe_attention("pope", q, k, v, split_kv=True, **kw)
+        b = P.pe_attention("pope", q, k, v, split_kv=False, **kw)
+    torch.cuda.synchronize()
+    P.check_device_status()
+    nbytes = Bd * Hd * Sk * (D_C + D_R + D_V) * 2
+    peak, peak_src = measured_hbm_peak()
+    gbs = nbytes / (split_ms * 1e-3) / 1e9
+    return {
+        "metric": "cached-decode attention tokens/s (FoPE+PoPE, bf16, one new token per sequence)",
+        "value": round(Bd / (split_ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(split_ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"decode step of one attention layer: B{Bd} H{Hd} Sq1 Sk{Sk} d_c{D_C} d_r{D_R} d_v{D_V}",
+                   "l2": "flushed between steps by writing a 256 MiB buffer"},
+        "roofline": {"bound": "hbm", "kernel": "pe_attn_decode_kernel<128,64,128,POPE,1> + decode_merge_kernel",
+                     "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / peak, 4),
+                     "peak_source": peak_src, "algorithmic_bytes": nbytes, "traffic": None},
+        "query_tiled_kernel": {"ms": round(tiled_ms, 4), "speedup_of_split_kv": round(tiled_ms / split_ms, 2)},
+        "max_abs_diff_between_kernels": round((a.float() - b.float()).abs().max().item(), 5),
+        "gpu_launches": 2 * args.steps,
+    }
+
+
 def run_variants(args) -> dict:
     """Secondary workload (``--workload variants``): the fused forward of every positional-encoding
     variant at the configuration the benchmark list gives it (configurations 1-4; NoPE and ALiBi
@@ -523,10 +598,14 @@ def main():
     ap.add_argument("--eval-graph", action="store_true",
                     help="replay the evaluation forward from a CUDA graph (measured: no gain, the eager path is "
                          "already GPU-bound)")
-    ap.add_argument("--e2e-chunks", type=int, default=8, help="sequence blocks of the pipelined host-buffer call")
-    ap.add_argument("--workload", default="forward", choices=["forward", "training", "variants"],
+    ap.add_argument("--e2e-chunks", type=int, default=0,
+                    help="sequence blocks of the pipelined host-buffer call (0: about 32 MiB of input per block, 2 to 8)")
+    ap.add_argument("--decode-batch", type=int, default=8, help="sequences in the decode workload")
+    ap.add_argument("--decode-cache", type=int, default=16384, help="cached keys per sequence in the decode workload")
+    ap.add_argument("--workload", default="forward", choices=["forward", "training", "variants", "decode"],
                     help="forward: the headline benchmark; training: forward+backward of the attention op (1 GPU); "
-                         "variants: the forward of every variant at its benchmark configuration (1 GPU)")
+                         "variants: the forward of every variant at its benchmark configuration (1 GPU); "
+                         "decode: one generated token against a long cache, split-KV kernel (1 GPU)")
     ap.add_argument("--train-batch", type=int, default=64)
     ap.add_argument("--train-seq", type=int, default=512)
     args = ap.parse_args()
@@ -534,6 +613,8 @@ def main():
         line = run_training(args)
     elif args.workload == "variants" and args.impl == "ours":
         line = run_variants(args)
+    elif args.workload == "decode" and args.impl == "ours":
+        line = run_decode(args)
     else:
         line = run_reference(args) if args.impl == "reference" else run_ours(args)
     if line is not None:
