@@ -160,6 +160,19 @@ const char* pe_attn_status_string(int status);
 /* Algorithmic FLOPs of one call: B * H * (causal pairs) * 2 * (d_c + 2 d_r + d_v). */
 double pe_attn_flops(const pe_attn_args* args);
 
+/* Decode step against a cached K/V (the per-token call of the reference's cache modules,
+ * src/model/fpope_attention.py:180-271: new rows appended to the cache, the new queries attend
+ * to all of it).  Same arguments, variants and result as pe_attn_forward (bf16 only), for calls
+ * with at most 8 query rows per K/V head (H / Hkv * Sq <= 8): the keys of every (batch,
+ * K/V head) are cut into splits that separate CTAs stream from memory once, and a second
+ * kernel merges the splits' partial outputs by their logsumexp.  ``workspace`` is device
+ * memory of at least pe_attn_decode_workspace_bytes(args) bytes (16-byte aligned) that the
+ * call may overwrite; it must stay untouched until the stream has run the call.
+ * pe_attn_decode_workspace_bytes returns 0 when ``args`` does not validate or is not such a
+ * call (pe_attn_last_error says why); pe_attn_decode then returns the error code. */
+size_t pe_attn_decode_workspace_bytes(const pe_attn_args* args);
+int pe_attn_decode(const pe_attn_args* args, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Failure-reporting self-test (no counterpart in the reference).  Launches one warp that
  * waits, with the same bounded wait the attention kernels use, on a barrier nothing ever
  * signals.  After ``limit_cycles`` SM clocks the wait gives up, the kernel ORs

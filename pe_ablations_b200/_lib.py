@@ -31,6 +31,7 @@ EXPORTS = (
     "pe_rmsnorm_forward", "pe_swiglu_forward", "pe_attn_selftest_wait_expiry", "pe_attn_backward",
     "pe_pope_expand", "pe_pope_expand_backward", "pe_rotary_norm_expand", "pe_rotary_norm_expand_backward",
     "pe_fope_effective_freqs", "pe_fope_effective_freqs_backward",
+    "pe_attn_decode_workspace_bytes", "pe_attn_decode",
 )
 
 
@@ -81,6 +82,10 @@ def _load() -> C.CDLL:
     lib.pe_attn_version.restype = C.c_int
     lib.pe_attn_forward.restype = C.c_int
     lib.pe_attn_forward.argtypes = [C.POINTER(PeAttnArgs), C.c_void_p]
+    lib.pe_attn_decode_workspace_bytes.restype = C.c_size_t
+    lib.pe_attn_decode_workspace_bytes.argtypes = [C.POINTER(PeAttnArgs)]
+    lib.pe_attn_decode.restype = C.c_int
+    lib.pe_attn_decode.argtypes = [C.POINTER(PeAttnArgs), C.c_void_p, C.c_size_t, C.c_void_p]
     lib.pe_attn_validate.restype = C.c_int
     lib.pe_attn_validate.argtypes = [C.POINTER(PeAttnArgs)]
     lib.pe_attn_kernel_name.restype = C.c_char_p

@@ -240,6 +240,38 @@ double pe_attn_flops(const pe_attn_args* a) {
   return (double)a->B * a->H * pairs * 2.0 * (a->d_c + 2 * a->d_r + a->d_v);
 }
 
+// checks of the decode entry points beyond validate()
+static int validate_decode(const pe_attn_args* args, KParams* k) {
+  const int rc = validate(args, k);
+  if (rc != PE_ATTN_OK) return rc;
+  if (args->dtype != PE_ATTN_BF16 || (args->flags & PE_ATTN_SIMT_CHECK))
+    return fail(PE_ATTN_ERR_VARIANT, "the split-KV path is bf16 only");
+  if (!decode_supports(*k))
+    return fail(PE_ATTN_ERR_SHAPE, "the split-KV path takes at most 8 query rows per K/V head (got H/Hkv * Sq = %d)",
+                k->groups * k->Sq);
+  return PE_ATTN_OK;
+}
+
+size_t pe_attn_decode_workspace_bytes(const pe_attn_args* args) {
+  KParams k;
+  if (validate_decode(args, &k) != PE_ATTN_OK) return 0;
+  return decode_workspace_bytes(k);
+}
+
+int pe_attn_decode(const pe_attn_args* args, void* workspace, size_t workspace_bytes, void* stream) {
+  KParams k;
+  const int rc = validate_decode(args, &k);
+  if (rc != PE_ATTN_OK) return rc;
+  if (workspace == nullptr) return fail(PE_ATTN_ERR_NULL, "workspace is null");
+  if (!aligned16(workspace)) return fail(PE_ATTN_ERR_ALIGNMENT, "workspace is not 16-byte aligned");
+  int dev = 0, major = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess || major != 10)
+    return fail(PE_ATTN_ERR_DEVICE, "no sm_100 device is current");
+  g_error[0] = 0;
+  return launch_decode(k, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
 int pe_attn_forward(const pe_attn_args* args, void* stream) {
   KParams k;
   const int rc = validate(args, &k);

@@ -102,6 +102,10 @@ bool tc2_supports(const KParams& p);
 int launch_ce(const void* logits, int dtype, long long row_stride, const long long* targets, int n_rows, int vocab,
               int ignore_index, float* row_loss, unsigned int* counter, double* out, cudaStream_t stream);
 
+bool decode_supports(const KParams& p);   // split-KV path: bf16 shapes of the tcgen05 kernels, <= 8 rows per K/V head
+size_t decode_workspace_bytes(const KParams& p);
+int launch_decode(const KParams& p, void* workspace, size_t workspace_bytes, cudaStream_t stream);
+
 bool bwd_supports(int d_qk, int d_v);
 int launch_bwd(const BwdParams& p, int d_qk, int d_v, bool alibi, cudaStream_t stream);
 

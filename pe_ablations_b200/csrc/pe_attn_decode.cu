@@ -1,0 +1,557 @@
+// Split-KV forward for decode steps: a handful of query rows against a long cached K/V.
+//
+// With one to eight query rows per K/V head (one new token, or a short chunk, times the GQA
+// ratio) the work is a single pass over the cache: HBM-bound, no tensor-core shape.  The
+// query-tiled kernels give such a call one CTA per head; this one cuts the keys of every
+// (batch, K/V head) into splits so that about two CTAs per SM stream the cache, each keeping
+// its own running maximum, sum and un-normalised output, and a second small kernel merges the
+// splits (the same logsumexp algebra as between key tiles).
+//
+// One CTA = 256 threads, tiles of 64 keys, 2-4 TMA stages (raw K halves and V, 128-byte
+// swizzle; 64-byte swizzle for a 32-column positional half).  Per tile:
+//   scores   thread = (key, quarter of the 16-byte column slots): reads its key's slots from the
+//            swizzled tile (conflict-free: 8 consecutive keys per quarter-warp), applies the
+//            positional transform in registers (rotation / L2 norm factor / softplus magnitude
+//            and phase), multiplies with the query rows held in shared memory as fp32 (already
+//            transformed, scaled by scale * log2 e), two shuffles join the quarters
+//   softmax  warp r owns query row r: tile maximum, rescale factor, probabilities in place
+//   values   warp w owns keys 8w..8w+7, lane = 4 (or 2) value columns: O_w += p * V
+// and after the last tile the eight per-warp outputs are summed through shared memory.
+// Two block-wide barriers per tile (scores are double-buffered); the refill of a stage is
+// issued after the next tile's first barrier, when every thread has left the stage.
+//
+// The transforms restate src/model/rope.py:35-57, src/model/normalization.py:44-56,
+// src/model/pope.py:124-183 and src/model/fpope.py:266-338 of the reference; the call is what
+// its cache modules do per generated token (src/model/fpope_attention.py:180-271).
+#include <cstring>
+
+#include "pe_attn_tc_common.cuh"
+
+namespace pe_attn {
+namespace {
+
+using namespace ptx;
+using namespace tc;
+
+constexpr int TK = 64;             // keys per tile
+constexpr int NT = 256;            // threads per CTA
+constexpr int NWARP = NT / 32;
+constexpr int MAX_ROWS = 8;        // query rows per K/V head (GQA ratio x Sq)
+constexpr int MAX_SPLITS = 64;
+constexpr int TARGET_CTAS = 296;   // two co-resident CTAs on each of 148 SMs
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+struct DecodeParams {
+  int rows, n_splits, tiles_per_split;
+  float* part_o;    // [B*H*Sq, n_splits, d_v]
+  float2* part_ml;  // [B*H*Sq, n_splits] (running maximum in log2 units, sum)
+};
+
+template <int DC, int DR, int DV, int R_T>
+struct DCfg {
+  static constexpr int DQK = DC + 2 * DR;
+  static constexpr int K_BYTES = TK * DC * 2;
+  static constexpr int V_BYTES = TK * DV * 2;
+  static constexpr int KR_BYTES = TK * DR * 2;
+  static constexpr int STAGE_BYTES = K_BYTES + V_BYTES + KR_BYTES;
+  static constexpr int NSTAGE = STAGE_BYTES >= 32768 ? 2 : (STAGE_BYTES >= 20480 ? 3 : 4);
+  static constexpr int RED_BYTES = NWARP * R_T * DV * 4;   // end-of-kernel reduction, reuses the stages
+  static_assert(RED_BYTES <= NSTAGE * STAGE_BYTES, "reduction buffer must fit the stages");
+  static_assert(STAGE_BYTES % 1024 == 0, "stages keep the 1024-byte swizzle alignment");
+  // after the stages: query rows, two score buffers, per-row state, frequencies, barriers
+  static constexpr int OFF_Q = NSTAGE * STAGE_BYTES;
+  static constexpr int OFF_S = OFF_Q + R_T * DQK * 4;
+  static constexpr int OFF_ROW = OFF_S + 2 * R_T * TK * 4;   // m, l, alpha, slope, limit: 5 x R_T words
+  static constexpr int OFF_FREQ = OFF_ROW + 5 * R_T * 4;
+  static constexpr int OFF_BAR = (OFF_FREQ + 2 * (DR > 0 ? DR : 1) * 4 + 7) & ~7;
+  static constexpr int SMEM_BYTES = OFF_BAR + NSTAGE * 8 + 1024;   // + slack for the 1024-byte alignment
+};
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    f[2 * e] = bf16_lo(w[e]);
+    f[2 * e + 1] = bf16_hi(w[e]);
+  }
+}
+__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+__device__ __forceinline__ float warp_sum(float x) {
+#pragma unroll
+  for (int d = 16; d >= 1; d >>= 1) x += __shfl_xor_sync(0xffffffffu, x, d);
+  return x;
+}
+__device__ __forceinline__ float warp_max(float x) {
+#pragma unroll
+  for (int d = 16; d >= 1; d >>= 1) x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, d));
+  return x;
+}
+__device__ __forceinline__ uint2 lds_v2(uint32_t a) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds_u32(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+
+// One query row, transformed as the forward kernels transform it (rounded to bf16 once), times
+// scale * log2 e, as fp32 in shared memory.  One warp per row.
+template <int DC, int DR, int MODE>
+__device__ void build_query_row(const KParams& p, float* dst, int b, int h, int qi, const float* freq_s, int lane) {
+  const float sc = p.scale * kLog2e;
+  const int pos = p.q_pos0 + qi;
+  if constexpr (DC > 0) {
+    const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.q.ptr) + (long long)b * p.q.sb +
+                               (long long)h * p.q.sh + (long long)qi * p.q.ss;
+    constexpr int PPL = DC / 64;   // pairs per lane
+    float o[PPL][2];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < PPL; ++i) {
+      const int pr = lane + 32 * i;
+      float x0 = __bfloat162float(src[2 * pr]), x1 = __bfloat162float(src[2 * pr + 1]);
+      if (MODE == MODE_XFORM && p.variant == PE_ATTN_ROTARY) {
+        const float2 cs = reinterpret_cast<const float2*>(p.table)[(size_t)(pos - p.table_pos0) * (DC / 2) + pr];
+        const float r0 = x0 * cs.x - x1 * cs.y, r1 = x0 * cs.y + x1 * cs.x;
+        x0 = r0 * p.mscale;
+        x1 = r1 * p.mscale;
+      }
+      o[i][0] = x0;
+      o[i][1] = x1;
+      ss = fmaf(x0, x0, fmaf(x1, x1, ss));
+    }
+    float inv = 1.0f;
+    if (MODE == MODE_XFORM && (p.flags & PE_ATTN_QK_NORM)) inv = 1.0f / (sqrtf(warp_sum(ss)) + p.eps);
+#pragma unroll
+    for (int i = 0; i < PPL; ++i) {
+      const int pr = lane + 32 * i;
+      dst[2 * pr] = round_bf16(o[i][0] * inv) * sc;
+      dst[2 * pr + 1] = round_bf16(o[i][1] * inv) * sc;
+    }
+  }
+  if constexpr (MODE == MODE_POPE) {
+    const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.qr.ptr) + (long long)b * p.qr.sb +
+                               (long long)h * p.qr.sh + (long long)qi * p.qr.ss;
+    for (int c = lane; c < DR; c += 32) {
+      const float mu = softplus_fast(__bfloat162float(src[c]));
+      float sn, cs;
+      sincos_reduced(__fmul_rn((float)pos, freq_s[c]), &sn, &cs);   // queries carry no phase bias
+      dst[DC + c] = round_bf16(mu * cs) * sc;
+      dst[DC + DR + c] = round_bf16(mu * sn) * sc;
+    }
+  }
+}
+
+template <int DC, int DR, int DV, int MODE, int R_T>
+__global__ void __launch_bounds__(NT, 2)
+pe_attn_decode_kernel(const KParams p, const DecodeParams dp, const __grid_constant__ CUtensorMap tmK,
+                      const __grid_constant__ CUtensorMap tmKR, const __grid_constant__ CUtensorMap tmV) {
+  using C = DCfg<DC, DR, DV, R_T>;
+  constexpr int DQK = C::DQK;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_u32 = smem_u32(smem_raw);
+  const uint32_t base = (raw_u32 + 1023u) & ~1023u;
+  uint8_t* gen = smem_raw + (base - raw_u32);
+  float* sQ = reinterpret_cast<float*>(gen + C::OFF_Q);
+  float* sS = reinterpret_cast<float*>(gen + C::OFF_S);
+  float* sM = reinterpret_cast<float*>(gen + C::OFF_ROW);
+  float* sL = sM + R_T;
+  float* sAlpha = sL + R_T;
+  float* sSlope = sAlpha + R_T;
+  int* sLim = reinterpret_cast<int*>(sSlope + R_T);
+  float* freq_s = reinterpret_cast<float*>(gen + C::OFF_FREQ);
+  float* delta_s = freq_s + (DR > 0 ? DR : 1);
+  const uint32_t bar0 = base + C::OFF_BAR;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int R = dp.rows;
+  const int tile0 = split * dp.tiles_per_split;
+  int n_tiles = (p.Sk + TK - 1) / TK - tile0;
+  if (n_tiles > dp.tiles_per_split) n_tiles = dp.tiles_per_split;
+  if (n_tiles < 0) n_tiles = 0;
+
+  auto issue = [&](int t) {   // one thread
+    const int stage = t % C::NSTAGE;
+    const uint32_t dst = base + stage * C::STAGE_BYTES, bar = bar0 + stage * 8;
+    const int row = (tile0 + t) * TK;
+    mbar_arrive_expect_tx(bar, C::STAGE_BYTES);
+#pragma unroll
+    for (int c = 0; c < DC / 64; ++c) tma_load_4d(dst + c * 8192, &tmK, bar, c * 64, row, hk, b);
+#pragma unroll
+    for (int c = 0; c < DV / 64; ++c) tma_load_4d(dst + C::K_BYTES + c * 8192, &tmV, bar, c * 64, row, hk, b);
+    if constexpr (DR > 0) tma_load_4d(dst + C::K_BYTES + C::V_BYTES, &tmKR, bar, 0, row, hk, b);
+  };
+
+  if (tid == 0) {
+    for (int s = 0; s < C::NSTAGE; ++s) mbar_init(bar0 + s * 8, 1);
+    mbar_fence_init();
+    for (int t = 0; t < C::NSTAGE && t < n_tiles; ++t) issue(t);
+  }
+  if constexpr (MODE == MODE_POPE) {
+    for (int c = tid; c < DR; c += NT) {
+      freq_s[c] = effective_freq(p, c);
+      delta_s[c] = clamped_delta(p, c);
+    }
+  }
+  if (tid < R_T) {
+    const int r = tid;
+    const int g = r / p.Sq, qi = r - g * p.Sq;
+    sM[r] = -INFINITY;
+    sL[r] = 0.f;
+    sAlpha[r] = 1.f;
+    sSlope[r] = (p.variant == PE_ATTN_ALIBI && r < R) ? p.slopes[hk * p.groups + g] * kLog2e : 0.f;
+    sLim[r] = r < R ? qi + p.causal_off : -1;   // last visible key of the row
+  }
+  __syncthreads();
+  for (int r = warp; r < R_T; r += NWARP) {
+    if (r < R) {
+      const int g = r / p.Sq, qi = r - g * p.Sq;
+      build_query_row<DC, DR, MODE>(p, sQ + r * DQK, b, hk * p.groups + g, qi, freq_s, lane);
+    } else {
+      for (int c = lane; c < DQK; c += 32) sQ[r * DQK + c] = 0.f;
+    }
+  }
+
+  // scores: this thread's key and column quarter
+  const int part = lane >> 3, key_local = warp * 8 + (lane & 7);
+  [[maybe_unused]] float om[DR > 0 ? DR / 32 : 1][8], dl[DR > 0 ? DR / 32 : 1][8];
+  if constexpr (MODE == MODE_POPE) {
+#pragma unroll
+    for (int i = 0; i < DR / 32; ++i)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        om[i][e] = freq_s[(part + 4 * i) * 8 + e];
+        dl[i][e] = delta_s[(part + 4 * i) * 8 + e];
+      }
+  }
+  const bool rotary = MODE == MODE_XFORM && p.variant == PE_ATTN_ROTARY;
+  const bool norm = MODE == MODE_XFORM && (p.flags & PE_ATTN_QK_NORM);
+  const bool alibi = p.variant == PE_ATTN_ALIBI;
+
+  // values: this thread's columns
+  constexpr int CPT = DV / 32;
+  float acc_o[R_T][CPT];
+#pragma unroll
+  for (int r = 0; r < R_T; ++r)
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) acc_o[r][c] = 0.f;
+  const uint32_t v_lane_off = DV == 128 ? (uint32_t)((lane >> 4) * 8192 + (lane & 1) * 8) : (uint32_t)((lane & 3) * 4);
+  const int v_slot = DV == 128 ? ((lane & 15) >> 1) : (lane >> 2);
+
+  __syncthreads();   // query rows complete
+  bool bad = false;
+
+  for (int t = 0; t < n_tiles; ++t) {
+    const int stage = t % C::NSTAGE;
+    const uint32_t sb = base + stage * C::STAGE_BYTES;
+    const bool ok = bad ? mbar_wait_for(bar0 + stage * 8, (t / C::NSTAGE) & 1, 100000)
+                        : mbar_wait(bar0 + stage * 8, (t / C::NSTAGE) & 1);
+    if (!ok && !bad) {
+      bad = true;
+      if (p.status != nullptr) atomicOr(p.status, ST_WAIT_KFULL);
+    }
+    const int kg = (tile0 + t) * TK + key_local;
+    float acc[R_T];
+#pragma unroll
+    for (int r = 0; r < R_T; ++r) acc[r] = 0.f;
+    float nrm2 = 0.f;
+
+    if constexpr (DC > 0) {
+#pragma unroll
+      for (int i = 0; i < DC / 32; ++i) {
+        const int slot_g = part + 4 * i;
+        const int chunk = slot_g >> 3, slot = slot_g & 7;
+        float kf[8];
+        unpack8(lds_v4(sb + chunk * 8192 + key_local * 128 + ((slot ^ (key_local & 7)) << 4)), kf);
+        if constexpr (MODE == MODE_XFORM) {
+          if (rotary) {
+            const int krow = (kg < p.Sk ? kg : p.Sk - 1) + p.k_pos0 - p.table_pos0;
+            const float4* tp = reinterpret_cast<const float4*>(p.table + ((size_t)krow * (DC / 2) + slot_g * 4) * 2);
+            const float4 t0 = __ldg(tp), t1 = __ldg(tp + 1);
+            const float cs[4] = {t0.x, t0.z, t1.x, t1.z}, sn[4] = {t0.y, t0.w, t1.y, t1.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float x0 = kf[2 * e], x1 = kf[2 * e + 1];
+              kf[2 * e] = x0 * cs[e] - x1 * sn[e];
+              kf[2 * e + 1] = x0 * sn[e] + x1 * cs[e];
+            }
+          }
+#pragma unroll
+          for (int e = 0; e < 8; ++e) nrm2 = fmaf(kf[e], kf[e], nrm2);
+        }
+#pragma unroll
+        for (int r = 0; r < R_T; ++r) {
+          const float4 q0 = *reinterpret_cast<const float4*>(sQ + r * DQK + slot_g * 8);
+          const float4 q1 = *reinterpret_cast<const float4*>(sQ + r * DQK + slot_g * 8 + 4);
+          float a = acc[r];
+          a = fmaf(q0.x, kf[0], a); a = fmaf(q0.y, kf[1], a); a = fmaf(q0.z, kf[2], a); a = fmaf(q0.w, kf[3], a);
+          a = fmaf(q1.x, kf[4], a); a = fmaf(q1.y, kf[5], a); a = fmaf(q1.z, kf[6], a); a = fmaf(q1.w, kf[7], a);
+          acc[r] = a;
+        }
+      }
+    }
+    if constexpr (MODE == MODE_POPE) {
+      const uint32_t sbr = sb + C::K_BYTES + C::V_BYTES;
+      const float pos = (float)(p.k_pos0 + kg);
+#pragma unroll
+      for (int i = 0; i < DR / 32; ++i) {
+        const int rs = part + 4 * i;
+        const uint32_t addr = DR == 64 ? sbr + key_local * 128 + ((rs ^ (key_local & 7)) << 4)
+                                       : sbr + key_local * 64 + ((rs ^ ((key_local >> 1) & 3)) << 4);
+        float x[8], kc[8], ks[8];
+        unpack8(lds_v4(addr), x);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float mu = softplus_fast(x[e]);
+          float sn, cs;
+          // phase = fl(fl(pos * freq) + delta), the reference's rounding order
+          sincos_reduced(__fadd_rn(__fmul_rn(pos, om[i][e]), dl[i][e]), &sn, &cs);
+          kc[e] = mu * cs;
+          ks[e] = mu * sn;
+        }
+#pragma unroll
+        for (int r = 0; r < R_T; ++r) {
+          const float* qc = sQ + r * DQK + DC + rs * 8;
+          const float* qs = qc + DR;
+          const float4 c0 = *reinterpret_cast<const float4*>(qc), c1 = *reinterpret_cast<const float4*>(qc + 4);
+          const float4 s0 = *reinterpret_cast<const float4*>(qs), s1 = *reinterpret_cast<const float4*>(qs + 4);
+          float a = acc[r];
+          a = fmaf(c0.x, kc[0], a); a = fmaf(c0.y, kc[1], a); a = fmaf(c0.z, kc[2], a); a = fmaf(c0.w, kc[3], a);
+          a = fmaf(c1.x, kc[4], a); a = fmaf(c1.y, kc[5], a); a = fmaf(c1.z, kc[6], a); a = fmaf(c1.w, kc[7], a);
+          a = fmaf(s0.x, ks[0], a); a = fmaf(s0.y, ks[1], a); a = fmaf(s0.z, ks[2], a); a = fmaf(s0.w, ks[3], a);
+          a = fmaf(s1.x, ks[4], a); a = fmaf(s1.y, ks[5], a); a = fmaf(s1.z, ks[6], a); a = fmaf(s1.w, ks[7], a);
+          acc[r] = a;
+        }
+      }
+    }
+    // join the four column quarters of a key (lanes l, l^8, l^16, l^24)
+#pragma unroll
+    for (int r = 0; r < R_T; ++r) {
+      acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], 8);
+      acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], 16);
+    }
+    float kfac = 1.0f;
+    if constexpr (MODE == MODE_XFORM) {
+      kfac = p.mscale;   // k' = mscale * rot(k), then k' / (|k'| + eps)
+      if (norm) {
+        nrm2 += __shfl_xor_sync(0xffffffffu, nrm2, 8);
+        nrm2 += __shfl_xor_sync(0xffffffffu, nrm2, 16);
+        float nr;
+        asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(nr) : "f"(nrm2));
+        kfac = __fdividef(p.mscale, fmaf(p.mscale, nr, p.eps));
+      }
+    }
+    float* sSt = sS + (t & 1) * R_T * TK;
+    if (part == 0) {
+#pragma unroll
+      for (int r = 0; r < R_T; ++r) {
+        const int lim = sLim[r];
+        float s = acc[r] * kfac;
+        if (alibi) s = fmaf(-sSlope[r], (float)(lim - kg), s);
+        sSt[r * TK + key_local] = kg <= lim ? s : -INFINITY;
+      }
+    }
+    __syncthreads();   // scores of tile t written; every thread has left tile t-1
+    if (tid == 0 && t >= 1 && t - 1 + C::NSTAGE < n_tiles) issue(t - 1 + C::NSTAGE);
+
+    if (warp < R_T) {
+      const int r = warp;
+      const float s0 = sSt[r * TK + lane], s1 = sSt[r * TK + lane + 32];
+      const float m_old = sM[r];
+      const float m_new = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
+      const bool empty = m_new == -INFINITY;
+      const float p0 = empty ? 0.f : ex2_approx(s0 - m_new), p1 = empty ? 0.f : ex2_approx(s1 - m_new);
+      const float alpha = empty ? 1.f : ex2_approx(m_old - m_new);
+      sSt[r * TK + lane] = p0;
+      sSt[r * TK + lane + 32] = p1;
+      const float psum = warp_sum(p0 + p1);
+      if (lane == 0) {
+        sM[r] = m_new;
+        sL[r] = sL[r] * alpha + psum;
+        sAlpha[r] = alpha;
+      }
+    }
+    __syncthreads();   // probabilities and rescale factors of tile t
+
+    const uint32_t sbv = sb + C::K_BYTES + v_lane_off;
+#pragma unroll
+    for (int r = 0; r < R_T; ++r) {
+      const float al = sAlpha[r];
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) acc_o[r][c] *= al;
+    }
+#pragma unroll
+    for (int jj = 0; jj < 8; ++jj) {
+      const int j = warp * 8 + jj;
+      float vv[CPT];
+      if constexpr (DV == 128) {
+        const uint2 w = lds_v2(sbv + j * 128 + ((v_slot ^ (j & 7)) << 4));
+        vv[0] = bf16_lo(w.x); vv[1] = bf16_hi(w.x); vv[2] = bf16_lo(w.y); vv[3] = bf16_hi(w.y);
+      } else {
+        const uint32_t w = lds_u32(sbv + j * 128 + ((v_slot ^ (j & 7)) << 4));
+        vv[0] = bf16_lo(w); vv[1] = bf16_hi(w);
+      }
+#pragma unroll
+      for (int r = 0; r < R_T; ++r) {
+        const float pr = sSt[r * TK + j];
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) acc_o[r][c] = fmaf(pr, vv[c], acc_o[r][c]);
+      }
+    }
+  }
+
+  // sum the eight warps' partial outputs (the stages are idle: every issued tile was waited for)
+  __syncthreads();
+  float* red = reinterpret_cast<float*>(gen);
+#pragma unroll
+  for (int r = 0; r < R_T; ++r)
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) red[(warp * R_T + r) * DV + lane * CPT + c] = acc_o[r][c];
+  __syncthreads();
+  for (int idx = tid; idx < R * DV; idx += NT) {
+    const int r = idx / DV, col = idx - r * DV;
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < NWARP; ++w) s += red[(w * R_T + r) * DV + col];
+    const int g = r / p.Sq, qi = r - g * p.Sq;
+    const long long row = ((long long)b * p.H + hk * p.groups + g) * p.Sq + qi;
+    dp.part_o[(row * dp.n_splits + split) * DV + col] = s;
+    if (col == 0) dp.part_ml[row * dp.n_splits + split] = make_float2(sM[r], sL[r]);
+  }
+}
+
+// out = sum_i 2^(m_i - M) O_i / sum_i 2^(m_i - M) l_i per (batch, head, query row)
+template <int DV>
+__global__ void __launch_bounds__(DV) decode_merge_kernel(const KParams p, const DecodeParams dp) {
+  const long long row = blockIdx.x;
+  const int col = threadIdx.x;
+  const float2* ml = dp.part_ml + row * dp.n_splits;
+  float M = -INFINITY;
+  for (int i = 0; i < dp.n_splits; ++i) M = fmaxf(M, ml[i].x);
+  float L = 0.f, o = 0.f;
+  for (int i = 0; i < dp.n_splits; ++i) {
+    const float2 v = ml[i];
+    const float w = v.x == -INFINITY ? 0.f : ex2_approx(v.x - M);
+    L = fmaf(w, v.y, L);
+    o = fmaf(w, dp.part_o[(row * dp.n_splits + i) * DV + col], o);
+  }
+  const int qi = (int)(row % p.Sq);
+  const int h = (int)((row / p.Sq) % p.H), b = (int)(row / ((long long)p.Sq * p.H));
+  __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(p.out.ptr)) + (long long)b * p.out.sb +
+                       (long long)h * p.out.sh + (long long)qi * p.out.ss;
+  out[col] = __float2bfloat16_rn(o / L);
+  if (p.lse != nullptr && col == 0) p.lse[row] = (M + log2f(L)) * kLn2;
+}
+
+// tensor map of a [B, H, S, d] bf16 tensor with a (cols x 64 rows) box
+bool encode_box(CUtensorMap* map, const TensorRef& t, int d, int S, int H, int B, int box_cols) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)t.ss * 2, (cuuint64_t)t.sh * 2, (cuuint64_t)t.sb * 2};
+  for (int i = 0; i < 3; ++i)
+    if (strides[i] == 0 || strides[i] % 16 != 0) strides[i] = (cuuint64_t)d * 2;   // size-1 dimensions
+  cuuint32_t box[4] = {(cuuint32_t)box_cols, TK, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(t.ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+void plan(const KParams& p, DecodeParams* dp) {
+  const int total = (p.Sk + TK - 1) / TK;
+  long long want = TARGET_CTAS / ((long long)p.B * p.Hkv);
+  if (want > MAX_SPLITS) want = MAX_SPLITS;
+  if (want > total / 2) want = total / 2;   // at least two tiles per split
+  if (want < 1) want = 1;
+  dp->tiles_per_split = (total + (int)want - 1) / (int)want;
+  dp->n_splits = (total + dp->tiles_per_split - 1) / dp->tiles_per_split;
+  dp->rows = p.groups * p.Sq;
+}
+
+template <int DC, int DR, int DV, int MODE, int R_T>
+int launch_instance(const KParams& p, const DecodeParams& dp, cudaStream_t stream) {
+  using C = DCfg<DC, DR, DV, R_T>;
+  auto kern = pe_attn_decode_kernel<DC, DR, DV, MODE, R_T>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (e != cudaSuccess) {
+      set_error("cudaFuncSetAttribute(%d bytes) failed: %s", C::SMEM_BYTES, cudaGetErrorString(e));
+      return PE_ATTN_ERR_LAUNCH;
+    }
+    configured = true;
+  }
+  CUtensorMap tmK, tmKR, tmV;
+  memset(&tmK, 0, sizeof(tmK));
+  memset(&tmKR, 0, sizeof(tmKR));
+  bool ok = encode_box(&tmV, p.v, DV, p.Sk, p.Hkv, p.B, 64);
+  if (DC > 0) ok = ok && encode_box(&tmK, p.k, DC, p.Sk, p.Hkv, p.B, 64);
+  if (DR > 0) ok = ok && encode_box(&tmKR, p.kr, DR, p.Sk, p.Hkv, p.B, DR);
+  if (!ok) {
+    set_error("cuTensorMapEncodeTiled failed for the cached k / k_r / v");
+    return PE_ATTN_ERR_LAUNCH;
+  }
+  dim3 grid(dp.n_splits, p.Hkv, p.B);
+  kern<<<grid, NT, C::SMEM_BYTES, stream>>>(p, dp, tmK, tmKR, tmV);
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) {
+    decode_merge_kernel<DV><<<(unsigned)((long long)p.B * p.H * p.Sq), DV, 0, stream>>>(p, dp);
+    e = cudaGetLastError();
+  }
+  if (e != cudaSuccess) {
+    set_error("split-KV kernel launch failed: %s", cudaGetErrorString(e));
+    return PE_ATTN_ERR_LAUNCH;
+  }
+  return PE_ATTN_OK;
+}
+
+template <int DC, int DR, int DV, int MODE>
+int launch_rows(const KParams& p, const DecodeParams& dp, cudaStream_t stream) {
+  if (dp.rows <= 1) return launch_instance<DC, DR, DV, MODE, 1>(p, dp, stream);
+  if (dp.rows <= 2) return launch_instance<DC, DR, DV, MODE, 2>(p, dp, stream);
+  if (dp.rows <= 4) return launch_instance<DC, DR, DV, MODE, 4>(p, dp, stream);
+  return launch_instance<DC, DR, DV, MODE, 8>(p, dp, stream);
+}
+
+}  // namespace
+
+bool decode_supports(const KParams& p) {
+  return tc_supports(p) && (long long)p.groups * p.Sq <= MAX_ROWS;
+}
+
+size_t decode_workspace_bytes(const KParams& p) {
+  DecodeParams dp;
+  plan(p, &dp);
+  return (size_t)p.B * p.H * p.Sq * dp.n_splits * (p.d_v + 2) * sizeof(float);
+}
+
+int launch_decode(const KParams& p, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  DecodeParams dp;
+  plan(p, &dp);
+  const size_t rows = (size_t)p.B * p.H * p.Sq;
+  if (workspace_bytes < decode_workspace_bytes(p)) {
+    set_error("workspace of %zu bytes is smaller than the %zu this call needs", workspace_bytes, decode_workspace_bytes(p));
+    return PE_ATTN_ERR_TOO_LARGE;
+  }
+  dp.part_ml = reinterpret_cast<float2*>(workspace);
+  dp.part_o = reinterpret_cast<float*>(workspace) + rows * dp.n_splits * 2;
+  if (p.variant == PE_ATTN_POPE) {
+    if (p.d_c == 64 && p.d_r == 32) return launch_rows<64, 32, 64, MODE_POPE>(p, dp, stream);
+    if (p.d_c == 128 && p.d_r == 64) return launch_rows<128, 64, 128, MODE_POPE>(p, dp, stream);
+    if (p.d_c == 128 && p.d_r == 32) return launch_rows<128, 32, 128, MODE_POPE>(p, dp, stream);
+    if (p.d_c == 0 && p.d_r == 32) return launch_rows<0, 32, 64, MODE_POPE>(p, dp, stream);
+    return launch_rows<0, 64, 128, MODE_POPE>(p, dp, stream);
+  }
+  const bool xform = p.variant == PE_ATTN_ROTARY || (p.flags & PE_ATTN_QK_NORM);
+  if (p.d_c == 64)
+    return xform ? launch_rows<64, 0, 64, MODE_XFORM>(p, dp, stream) : launch_rows<64, 0, 64, MODE_PLAIN>(p, dp, stream);
+  return xform ? launch_rows<128, 0, 128, MODE_XFORM>(p, dp, stream) : launch_rows<128, 0, 128, MODE_PLAIN>(p, dp, stream);
+}
+
+}  // namespace pe_attn

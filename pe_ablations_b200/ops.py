@@ -93,6 +93,7 @@ def pe_attention(
     simt_check: bool = False,
     single_cta: bool = False,
     lse: torch.Tensor | None = None,
+    split_kv: bool | None = None,
 ) -> torch.Tensor:
     """Fused causal attention forward with the positional transform applied in-kernel.
 
@@ -106,13 +107,17 @@ def pe_attention(
               ``floor_freq`` clip then run inside the kernel); ``delta`` [d_r] raw phase bias.
     lse: optional fp32 [B, H, Sq] tensor that receives each row's logsumexp (natural log of the
          sum of exp(scaled logit + bias) over the visible keys), for a later backward.
+    split_kv: decode steps (bf16, at most 8 query rows per K/V head, i.e. H / Hkv * Sq <= 8) go to
+         the split-KV kernel, which streams the cached keys with the whole GPU instead of one
+         CTA per head.  None picks it for such calls when Sk >= 256; True requires it (raises
+         if the call is not of that shape); False keeps the query-tiled kernels.
     """
     if mask is not None:
         raise NotImplementedError("pe_attention is causal-only: an explicit mask is not supported (no fallback)")
     kwargs = dict(layout=layout, start_pos=start_pos, k_start_pos=k_start_pos, scale=scale, qk_norm=qk_norm,
                   qk_norm_eps=qk_norm_eps, rotary_table=rotary_table, table_pos0=table_pos0, mscale=mscale,
                   alibi_slopes=alibi_slopes, floor_freq=floor_freq, normalize_coeffs=normalize_coeffs,
-                  ceil_freq=ceil_freq, out=out, simt_check=simt_check, single_cta=single_cta)
+                  ceil_freq=ceil_freq, out=out, simt_check=simt_check, single_cta=single_cta, split_kv=split_kv)
     diff = (q, k, v, q_r, k_r, freqs, delta, fourier_coeffs)
     if torch.is_grad_enabled() and any(isinstance(t, torch.Tensor) and t.requires_grad for t in diff):
         return _training_call(variant, q, k, v, q_r, k_r, freqs, delta, fourier_coeffs, lse, kwargs)
@@ -179,6 +184,7 @@ def _forward_impl(
     simt_check: bool = False,
     single_cta: bool = False,
     lse: torch.Tensor | None = None,
+    split_kv: bool | None = None,
 ) -> torch.Tensor:
     """The forward kernel call behind ``pe_attention`` (no autograd bookkeeping)."""
     if variant not in _VARIANTS:
@@ -288,7 +294,20 @@ def _forward_impl(
         if dtype == _lib.BF16 and not simt_check:
             a.device_status = device_status(dev).data_ptr()
         stream = torch.cuda.current_stream(dev).cuda_stream
-        rc = _lib.lib.pe_attn_forward(C.byref(a), C.c_void_p(stream))
+        use_split = False
+        if split_kv or (split_kv is None and dtype == _lib.BF16 and not simt_check and not single_cta
+                        and (H // max(Hkv, 1)) * Sq <= 8 and Sk >= 256):
+            ws_bytes = _lib.lib.pe_attn_decode_workspace_bytes(C.byref(a))
+            use_split = ws_bytes > 0
+            if split_kv and not use_split:
+                raise _lib.PeAttnError(_lib.lib.pe_attn_decode(C.byref(a), None, 0, C.c_void_p(stream)))
+        if use_split:
+            # partial outputs of the key splits; a fresh block from the caching allocator is
+            # ordered after its previous use on this stream
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+            rc = _lib.lib.pe_attn_decode(C.byref(a), C.c_void_p(ws.data_ptr()), C.c_size_t(ws_bytes), C.c_void_p(stream))
+        else:
+            rc = _lib.lib.pe_attn_forward(C.byref(a), C.c_void_p(stream))
     if rc != 0:
         raise _lib.PeAttnError(rc)
     # parameter tensors created here stay referenced until the stream has used them

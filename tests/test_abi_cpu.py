@@ -160,3 +160,24 @@ def test_transform_entries_reject_bad_shapes(L):
     assert rc == 3
     rc = L.lib.pe_rotary_norm_expand(0x10000, s3, 0x10000, s3, 1, 512, 8, 64, 0x10000, 10, 100, 1.0, 1, 1e-6, None)
     assert rc == 3 and b"do not cover" in L.lib.pe_attn_last_error()
+
+
+def test_decode_entry_plans_and_rejects_without_touching_the_gpu(L):
+    """``pe_attn_decode_workspace_bytes`` is host arithmetic; ``pe_attn_decode`` refuses a null
+    workspace and calls that are not decode steps before any launch."""
+    one_token = _valid_args(L, Sq=1, Sk=16384)
+    n = L.lib.pe_attn_decode_workspace_bytes(C.byref(one_token))
+    rows = 2 * 16
+    assert n > 0 and n % (rows * (128 + 2) * 4) == 0           # rows x splits x (d_v + max + sum) floats
+    splits = n // (rows * (128 + 2) * 4)
+    assert 1 <= splits <= 64 and splits * 2 * 16 <= 296        # about two CTAs per SM
+    assert L.lib.pe_attn_decode_workspace_bytes(C.byref(_valid_args(L, Sq=1, Sk=1))) == rows * 130 * 4
+    # too many rows per K/V head, fp32, invalid arguments
+    assert L.lib.pe_attn_decode_workspace_bytes(C.byref(_valid_args(L, Sq=9, Sk=1024))) == 0
+    assert b"at most 8 query rows" in L.lib.pe_attn_last_error()
+    assert L.lib.pe_attn_decode_workspace_bytes(C.byref(_valid_args(L, Sq=1, dtype=L.FP32))) == 0
+    assert L.lib.pe_attn_decode_workspace_bytes(C.byref(_valid_args(L, Sq=1, Hkv=3))) == 0
+    assert L.lib.pe_attn_decode_workspace_bytes(None) == 0
+    assert L.lib.pe_attn_decode(C.byref(one_token), None, 0, None) == 1            # null workspace
+    assert L.lib.pe_attn_decode(C.byref(_valid_args(L, Sq=9)), None, 0, None) == 3  # shape
+    assert L.lib.pe_attn_decode(None, None, 0, None) == 1
