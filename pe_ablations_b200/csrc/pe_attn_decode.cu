@@ -8,17 +8,20 @@
 // splits (the same logsumexp algebra as between key tiles).
 //
 // One CTA = 256 threads, tiles of 64 keys, 2-4 TMA stages (raw K halves and V, 128-byte
-// swizzle; 64-byte swizzle for a 32-column positional half).  Per tile:
-//   scores   thread = (key, quarter of the 16-byte column slots): reads its key's slots from the
+// swizzle; 64-byte swizzle for a 32-column positional half).  Warp w owns keys 8w..8w+7 of
+// every tile, start to end, with its own running maximum, sum and output, so the warps never
+// wait for each other inside a tile:
+//   scores   lane = (key, quarter of the 16-byte column slots): reads its key's slots from the
 //            swizzled tile (conflict-free: 8 consecutive keys per quarter-warp), applies the
 //            positional transform in registers (rotation / L2 norm factor / softplus magnitude
 //            and phase), multiplies with the query rows held in shared memory as fp32 (already
-//            transformed, scaled by scale * log2 e), two shuffles join the quarters
-//   softmax  warp r owns query row r: tile maximum, rescale factor, probabilities in place
-//   values   warp w owns keys 8w..8w+7, lane = 4 (or 2) value columns: O_w += p * V
-// and after the last tile the eight per-warp outputs are summed through shared memory.
-// Two block-wide barriers per tile (scores are double-buffered); the refill of a stage is
-// issued after the next tile's first barrier, when every thread has left the stage.
+//            transformed, scaled by scale * log2 e); two shuffles join the quarters
+//   softmax  maximum over the warp's 8 keys by shuffles, rescale, probabilities in registers
+//   values   lane = 4 (or 2) value columns: O_w += p_j * V_j for the 8 keys, p_j by shuffle
+// A warp that is done with a tile adds one to the stage's counter; the warp that brings it to
+// eight issues the TMA refill of that stage (no producer warp, no block-wide barrier in the
+// loop).  After the last tile the eight warps' (max, sum, output) are merged through shared
+// memory and written as the split's partial result.
 //
 // The transforms restate src/model/rope.py:35-57, src/model/normalization.py:44-56,
 // src/model/pope.py:124-183 and src/model/fpope.py:266-338 of the reference; the call is what
@@ -56,15 +59,15 @@ struct DCfg {
   static constexpr int KR_BYTES = TK * DR * 2;
   static constexpr int STAGE_BYTES = K_BYTES + V_BYTES + KR_BYTES;
   static constexpr int NSTAGE = STAGE_BYTES >= 32768 ? 2 : (STAGE_BYTES >= 20480 ? 3 : 4);
-  static constexpr int RED_BYTES = NWARP * R_T * DV * 4;   // end-of-kernel reduction, reuses the stages
+  static constexpr int RED_BYTES = NWARP * R_T * (DV + 2) * 4;   // end-of-kernel merge, reuses the stages
   static_assert(RED_BYTES <= NSTAGE * STAGE_BYTES, "reduction buffer must fit the stages");
   static_assert(STAGE_BYTES % 1024 == 0, "stages keep the 1024-byte swizzle alignment");
-  // after the stages: query rows, two score buffers, per-row state, frequencies, barriers
+  // after the stages: query rows, per-row slope and causal limit, frequencies, stage counters, barriers
   static constexpr int OFF_Q = NSTAGE * STAGE_BYTES;
-  static constexpr int OFF_S = OFF_Q + R_T * DQK * 4;
-  static constexpr int OFF_ROW = OFF_S + 2 * R_T * TK * 4;   // m, l, alpha, slope, limit: 5 x R_T words
-  static constexpr int OFF_FREQ = OFF_ROW + 5 * R_T * 4;
-  static constexpr int OFF_BAR = (OFF_FREQ + 2 * (DR > 0 ? DR : 1) * 4 + 7) & ~7;
+  static constexpr int OFF_ROW = OFF_Q + R_T * DQK * 4;
+  static constexpr int OFF_FREQ = OFF_ROW + 2 * R_T * 4;
+  static constexpr int OFF_CNT = OFF_FREQ + 2 * (DR > 0 ? DR : 1) * 4;
+  static constexpr int OFF_BAR = (OFF_CNT + NSTAGE * 4 + 7) & ~7;
   static constexpr int SMEM_BYTES = OFF_BAR + NSTAGE * 8 + 1024;   // + slack for the 1024-byte alignment
 };
 
@@ -80,11 +83,6 @@ __device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(_
 __device__ __forceinline__ float warp_sum(float x) {
 #pragma unroll
   for (int d = 16; d >= 1; d >>= 1) x += __shfl_xor_sync(0xffffffffu, x, d);
-  return x;
-}
-__device__ __forceinline__ float warp_max(float x) {
-#pragma unroll
-  for (int d = 16; d >= 1; d >>= 1) x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, d));
   return x;
 }
 __device__ __forceinline__ uint2 lds_v2(uint32_t a) {
@@ -157,12 +155,9 @@ pe_attn_decode_kernel(const KParams p, const DecodeParams dp, const __grid_const
   const uint32_t base = (raw_u32 + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - raw_u32);
   float* sQ = reinterpret_cast<float*>(gen + C::OFF_Q);
-  float* sS = reinterpret_cast<float*>(gen + C::OFF_S);
-  float* sM = reinterpret_cast<float*>(gen + C::OFF_ROW);
-  float* sL = sM + R_T;
-  float* sAlpha = sL + R_T;
-  float* sSlope = sAlpha + R_T;
+  float* sSlope = reinterpret_cast<float*>(gen + C::OFF_ROW);
   int* sLim = reinterpret_cast<int*>(sSlope + R_T);
+  int* sCnt = reinterpret_cast<int*>(gen + C::OFF_CNT);
   float* freq_s = reinterpret_cast<float*>(gen + C::OFF_FREQ);
   float* delta_s = freq_s + (DR > 0 ? DR : 1);
   const uint32_t bar0 = base + C::OFF_BAR;
@@ -188,7 +183,10 @@ pe_attn_decode_kernel(const KParams p, const DecodeParams dp, const __grid_const
   };
 
   if (tid == 0) {
-    for (int s = 0; s < C::NSTAGE; ++s) mbar_init(bar0 + s * 8, 1);
+    for (int s = 0; s < C::NSTAGE; ++s) {
+      mbar_init(bar0 + s * 8, 1);
+      sCnt[s] = 0;
+    }
     mbar_fence_init();
     for (int t = 0; t < C::NSTAGE && t < n_tiles; ++t) issue(t);
   }
@@ -201,9 +199,6 @@ pe_attn_decode_kernel(const KParams p, const DecodeParams dp, const __grid_const
   if (tid < R_T) {
     const int r = tid;
     const int g = r / p.Sq, qi = r - g * p.Sq;
-    sM[r] = -INFINITY;
-    sL[r] = 0.f;
-    sAlpha[r] = 1.f;
     sSlope[r] = (p.variant == PE_ATTN_ALIBI && r < R) ? p.slopes[hk * p.groups + g] * kLog2e : 0.f;
     sLim[r] = r < R ? qi + p.causal_off : -1;   // last visible key of the row
   }
@@ -240,6 +235,12 @@ pe_attn_decode_kernel(const KParams p, const DecodeParams dp, const __grid_const
   for (int r = 0; r < R_T; ++r)
 #pragma unroll
     for (int c = 0; c < CPT; ++c) acc_o[r][c] = 0.f;
+  float m_run[R_T], l_lane[R_T];   // maximum over the warp's keys so far; this lane's key's share of the sum
+#pragma unroll
+  for (int r = 0; r < R_T; ++r) {
+    m_run[r] = -INFINITY;
+    l_lane[r] = 0.f;
+  }
   const uint32_t v_lane_off = DV == 128 ? (uint32_t)((lane >> 4) * 8192 + (lane & 1) * 8) : (uint32_t)((lane & 3) * 4);
   const int v_slot = DV == 128 ? ((lane & 15) >> 1) : (lane >> 2);
 
@@ -346,45 +347,29 @@ pe_attn_decode_kernel(const KParams p, const DecodeParams dp, const __grid_const
         kfac = __fdividef(p.mscale, fmaf(p.mscale, nr, p.eps));
       }
     }
-    float* sSt = sS + (t & 1) * R_T * TK;
-    if (part == 0) {
-#pragma unroll
-      for (int r = 0; r < R_T; ++r) {
-        const int lim = sLim[r];
-        float s = acc[r] * kfac;
-        if (alibi) s = fmaf(-sSlope[r], (float)(lim - kg), s);
-        sSt[r * TK + key_local] = kg <= lim ? s : -INFINITY;
-      }
-    }
-    __syncthreads();   // scores of tile t written; every thread has left tile t-1
-    if (tid == 0 && t >= 1 && t - 1 + C::NSTAGE < n_tiles) issue(t - 1 + C::NSTAGE);
-
-    if (warp < R_T) {
-      const int r = warp;
-      const float s0 = sSt[r * TK + lane], s1 = sSt[r * TK + lane + 32];
-      const float m_old = sM[r];
-      const float m_new = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
-      const bool empty = m_new == -INFINITY;
-      const float p0 = empty ? 0.f : ex2_approx(s0 - m_new), p1 = empty ? 0.f : ex2_approx(s1 - m_new);
-      const float alpha = empty ? 1.f : ex2_approx(m_old - m_new);
-      sSt[r * TK + lane] = p0;
-      sSt[r * TK + lane + 32] = p1;
-      const float psum = warp_sum(p0 + p1);
-      if (lane == 0) {
-        sM[r] = m_new;
-        sL[r] = sL[r] * alpha + psum;
-        sAlpha[r] = alpha;
-      }
-    }
-    __syncthreads();   // probabilities and rescale factors of tile t
-
-    const uint32_t sbv = sb + C::K_BYTES + v_lane_off;
+    // online softmax over the warp's 8 keys (every lane of a quarter holds the same values)
+    float pr[R_T];
 #pragma unroll
     for (int r = 0; r < R_T; ++r) {
-      const float al = sAlpha[r];
+      const int lim = sLim[r];
+      float sc = acc[r] * kfac;
+      if (alibi) sc = fmaf(-sSlope[r], (float)(lim - kg), sc);
+      sc = kg <= lim ? sc : -INFINITY;
+      float tmax = sc;
+      tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+      tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+      tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 4));
+      const float m_new = fmaxf(m_run[r], tmax);
+      const bool empty = m_new == -INFINITY;
+      const float alpha = empty ? 1.f : ex2_approx(m_run[r] - m_new);
+      pr[r] = empty ? 0.f : ex2_approx(sc - m_new);
+      l_lane[r] = fmaf(l_lane[r], alpha, pr[r]);
+      m_run[r] = m_new;
 #pragma unroll
-      for (int c = 0; c < CPT; ++c) acc_o[r][c] *= al;
+      for (int c = 0; c < CPT; ++c) acc_o[r][c] *= alpha;
     }
+
+    const uint32_t sbv = sb + C::K_BYTES + v_lane_off;
 #pragma unroll
     for (int jj = 0; jj < 8; ++jj) {
       const int j = warp * 8 + jj;
@@ -398,54 +383,102 @@ pe_attn_decode_kernel(const KParams p, const DecodeParams dp, const __grid_const
       }
 #pragma unroll
       for (int r = 0; r < R_T; ++r) {
-        const float pr = sSt[r * TK + j];
+        const float pj = __shfl_sync(0xffffffffu, pr[r], jj);
 #pragma unroll
-        for (int c = 0; c < CPT; ++c) acc_o[r][c] = fmaf(pr, vv[c], acc_o[r][c]);
+        for (int c = 0; c < CPT; ++c) acc_o[r][c] = fmaf(pj, vv[c], acc_o[r][c]);
+      }
+    }
+
+    // this warp has left the stage; the last of the eight refills it
+    __threadfence_block();
+    __syncwarp();
+    if (lane == 0) {
+      if (atomicAdd(&sCnt[stage], 1) == NWARP - 1) {
+        sCnt[stage] = 0;
+        if (t + C::NSTAGE < n_tiles) {
+          fence_proxy_async_smem();
+          issue(t + C::NSTAGE);
+        }
       }
     }
   }
 
-  // sum the eight warps' partial outputs (the stages are idle: every issued tile was waited for)
+  // merge the eight warps' (max, sum, output); the stages are idle: every issued tile was waited for
   __syncthreads();
   float* red = reinterpret_cast<float*>(gen);
+  float2* red_ml = reinterpret_cast<float2*>(red + NWARP * R_T * DV);
 #pragma unroll
-  for (int r = 0; r < R_T; ++r)
+  for (int r = 0; r < R_T; ++r) {
 #pragma unroll
     for (int c = 0; c < CPT; ++c) red[(warp * R_T + r) * DV + lane * CPT + c] = acc_o[r][c];
+    float l = l_lane[r];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    l += __shfl_xor_sync(0xffffffffu, l, 4);
+    if (lane == 0) red_ml[warp * R_T + r] = make_float2(m_run[r], l);
+  }
   __syncthreads();
   for (int idx = tid; idx < R * DV; idx += NT) {
     const int r = idx / DV, col = idx - r * DV;
-    float s = 0.f;
+    float M = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < NWARP; ++w) s += red[(w * R_T + r) * DV + col];
+    for (int w = 0; w < NWARP; ++w) M = fmaxf(M, red_ml[w * R_T + r].x);
+    float o = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < NWARP; ++w) {
+      const float2 ml = red_ml[w * R_T + r];
+      const float wt = ml.x == -INFINITY ? 0.f : ex2_approx(ml.x - M);
+      l = fmaf(wt, ml.y, l);
+      o = fmaf(wt, red[(w * R_T + r) * DV + col], o);
+    }
     const int g = r / p.Sq, qi = r - g * p.Sq;
     const long long row = ((long long)b * p.H + hk * p.groups + g) * p.Sq + qi;
-    dp.part_o[(row * dp.n_splits + split) * DV + col] = s;
-    if (col == 0) dp.part_ml[row * dp.n_splits + split] = make_float2(sM[r], sL[r]);
+    dp.part_o[(row * dp.n_splits + split) * DV + col] = o;
+    if (col == 0) dp.part_ml[row * dp.n_splits + split] = make_float2(M, l);
   }
 }
 
 // out = sum_i 2^(m_i - M) O_i / sum_i 2^(m_i - M) l_i per (batch, head, query row)
 template <int DV>
 __global__ void __launch_bounds__(DV) decode_merge_kernel(const KParams p, const DecodeParams dp) {
+  __shared__ float wt[MAX_SPLITS];
+  __shared__ float inv_l, lse2;
   const long long row = blockIdx.x;
-  const int col = threadIdx.x;
-  const float2* ml = dp.part_ml + row * dp.n_splits;
-  float M = -INFINITY;
-  for (int i = 0; i < dp.n_splits; ++i) M = fmaxf(M, ml[i].x);
-  float L = 0.f, o = 0.f;
-  for (int i = 0; i < dp.n_splits; ++i) {
-    const float2 v = ml[i];
-    const float w = v.x == -INFINITY ? 0.f : ex2_approx(v.x - M);
-    L = fmaf(w, v.y, L);
-    o = fmaf(w, dp.part_o[(row * dp.n_splits + i) * DV + col], o);
+  const int col = threadIdx.x, ns = dp.n_splits;
+  if (col < 32) {   // one warp: weights of the splits (n_splits <= 64)
+    const float2 a = col < ns ? dp.part_ml[row * ns + col] : make_float2(-INFINITY, 0.f);
+    const float2 c = col + 32 < ns ? dp.part_ml[row * ns + col + 32] : make_float2(-INFINITY, 0.f);
+    float M = fmaxf(a.x, c.x);
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, d));
+    const float wa = a.x == -INFINITY ? 0.f : ex2_approx(a.x - M), wc = c.x == -INFINITY ? 0.f : ex2_approx(c.x - M);
+    wt[col] = wa;
+    wt[col + 32] = wc;
+    const float L = warp_sum(wa * a.y + wc * c.y);
+    if (col == 0) {
+      inv_l = 1.0f / L;
+      lse2 = M + log2f(L);
+    }
   }
+  __syncthreads();
+  const float* po = dp.part_o + row * ns * DV + col;
+  float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;   // four loads in flight
+  int i = 0;
+  for (; i + 4 <= ns; i += 4) {
+    const float x0 = po[(long long)i * DV], x1 = po[(long long)(i + 1) * DV], x2 = po[(long long)(i + 2) * DV],
+                x3 = po[(long long)(i + 3) * DV];
+    o0 = fmaf(wt[i], x0, o0);
+    o1 = fmaf(wt[i + 1], x1, o1);
+    o2 = fmaf(wt[i + 2], x2, o2);
+    o3 = fmaf(wt[i + 3], x3, o3);
+  }
+  for (; i < ns; ++i) o0 = fmaf(wt[i], po[(long long)i * DV], o0);
   const int qi = (int)(row % p.Sq);
   const int h = (int)((row / p.Sq) % p.H), b = (int)(row / ((long long)p.Sq * p.H));
   __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(p.out.ptr)) + (long long)b * p.out.sb +
                        (long long)h * p.out.sh + (long long)qi * p.out.ss;
-  out[col] = __float2bfloat16_rn(o / L);
-  if (p.lse != nullptr && col == 0) p.lse[row] = (M + log2f(L)) * kLn2;
+  out[col] = __float2bfloat16_rn(((o0 + o1) + (o2 + o3)) * inv_l);
+  if (p.lse != nullptr && col == 0) p.lse[row] = lse2 * kLn2;
 }
 
 // tensor map of a [B, H, S, d] bf16 tensor with a (cols x 64 rows) box
@@ -463,13 +496,38 @@ bool encode_box(CUtensorMap* map, const TensorRef& t, int d, int S, int H, int B
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// How many splits: with few (batch, K/V head) problems, as many as fill the 296 CTA slots once
+// (at least two tiles each); with many, splits of at least MIN_TILES tiles chosen so that the
+// CTA count comes close to a whole number of waves -- short CTAs keep the last wave's idle
+// time small and a new CTA's prologue runs under its neighbour's streaming.
 void plan(const KParams& p, DecodeParams* dp) {
+  constexpr int MIN_TILES = 16;
   const int total = (p.Sk + TK - 1) / TK;
-  long long want = TARGET_CTAS / ((long long)p.B * p.Hkv);
-  if (want > MAX_SPLITS) want = MAX_SPLITS;
-  if (want > total / 2) want = total / 2;   // at least two tiles per split
-  if (want < 1) want = 1;
-  dp->tiles_per_split = (total + (int)want - 1) / (int)want;
+  const long long problems = (long long)p.B * p.Hkv;
+  int by_len = total / MIN_TILES;
+  if (by_len > MAX_SPLITS) by_len = MAX_SPLITS;
+  if (by_len < 1) by_len = 1;
+  int want;
+  if (problems * by_len <= TARGET_CTAS) {
+    long long w = TARGET_CTAS / problems;
+    if (w > MAX_SPLITS) w = MAX_SPLITS;
+    if (w > total / 2) w = total / 2;   // at least two tiles per split
+    want = w < 1 ? 1 : (int)w;
+  } else {
+    want = 1;
+    double best = 0.0;
+    for (int n = 1; n <= by_len; ++n) {
+      const long long ctas = problems * n;
+      const long long waves = (ctas + TARGET_CTAS - 1) / TARGET_CTAS;
+      // occupied share of the waves, with a mild preference for more, shorter CTAs
+      const double eff = (double)ctas / (double)(waves * TARGET_CTAS) + 1e-3 * n;
+      if (eff > best) {
+        best = eff;
+        want = n;
+      }
+    }
+  }
+  dp->tiles_per_split = (total + want - 1) / want;
   dp->n_splits = (total + dp->tiles_per_split - 1) / dp->tiles_per_split;
   dp->rows = p.groups * p.Sq;
 }

@@ -30,9 +30,12 @@ __device__ __forceinline__ float softplus_fast(float x) {
   return fmaxf(x, 0.f) + lg2_approx(1.0f + e) * 0.6931471805599453f;
 }
 
-// sin / cos of a large fp32 angle: two-term Cody-Waite reduction by 2 pi, then MUFU
+// sin / cos of a large fp32 angle: two-term Cody-Waite reduction by 2 pi, then MUFU.  The
+// rounding to the nearest whole turn is two additions of 1.5 * 2^23 (exact for |turns| < 2^22,
+// ties to even like rintf) instead of a round instruction, which would take a slot of the
+// special-function pipe beside the four this transform already needs per element.
 __device__ __forceinline__ void sincos_reduced(float x, float* s, float* c) {
-  const float k = rintf(x * 0.15915494309189535f);
+  const float k = __fadd_rn(__fadd_rn(x * 0.15915494309189535f, 12582912.0f), -12582912.0f);
   float r = fmaf(k, -6.2831854820251465f, x);
   r = fmaf(k, 1.7484556000744883e-7f, r);
   *s = __sinf(r);
