@@ -484,6 +484,31 @@ def run_decode(args) -> dict:
     P.check_device_status()
     nbytes = Bd * Hd * Sk * (D_C + D_R + D_V) * 2
     peak, peak_src = measured_hbm_peak()
+
+    # the other variants' decode steps (one token, same cache length), split-KV kernel only
+    others = []
+
+    def other(name, variant, Hq, Hk, d_c, d_r, d_v, **okw):
+        mk2 = lambda Sv, h, d: None if d == 0 else torch.randn(Bd, Sv, h, d, generator=g).to(torch.bfloat16).to(dev)
+        oq, ok_, ov = mk2(1, Hq, d_c), mk2(Sk, Hk, d_c), mk2(Sk, Hk, d_v)
+        oqr, okr = mk2(1, Hq, d_r), mk2(Sk, Hk, d_r)
+        with torch.no_grad():
+            ms = timed(lambda: P.pe_attention(variant, oq, ok_, ov, q_r=oqr, k_r=okr, start_pos=Sk - 1, k_start_pos=0,
+                                              split_kv=True, **okw))
+        nb = Bd * Hk * Sk * (d_c + d_r + d_v) * 2
+        others.append({"variant": name, "shape": f"B{Bd} H{Hq} Hkv{Hk} Sk{Sk} d_c{d_c} d_r{d_r} d_v{d_v}",
+                       "ms": round(ms, 4), "GB/s": round(nb / (ms * 1e-3) / 1e9, 1),
+                       "frac": round(nb / (ms * 1e-3) / 1e9 / peak, 4)})
+
+    rope = PE.RotaryEmbedding(64, Sk, 10000.0).to(dev)
+    other("rope, head_dim 64", "rotary", 12, 12, 64, 0, 64, rotary_table=rope.freqs_cis)
+    other("rope + QKNorm, head_dim 64", "rotary", 12, 12, 64, 0, 64, rotary_table=rope.freqs_cis, qk_norm=True)
+    other("nope, head_dim 128", "nope", 16, 16, 128, 0, 128)
+    other("alibi, head_dim 128, 4:1 GQA", "alibi", 16, 4, 128, 0, 128, alibi_slopes=PE.alibi_slopes(16).to(dev))
+    fp2 = PE.FoPEPoPEEmbedding(dim=32, max_seq_len=Sk, num_fourier_terms=64, fourier_sigma=0.4, training_length=512,
+                               delta_init="uniform").to(dev)
+    other("fope+pope, head_dim 64 / d_rope 32, 2:1 GQA", "pope", 8, 4, 64, 32, 64, **fp2.kernel_args())
+    P.check_device_status()
     gbs = nbytes / (split_ms * 1e-3) / 1e9
     return {
         "metric": "cached-decode attention tokens/s (FoPE+PoPE, bf16, one new token per sequence)",
@@ -497,6 +522,7 @@ def run_decode(args) -> dict:
                      "peak_source": peak_src, "algorithmic_bytes": nbytes, "traffic": None},
         "query_tiled_kernel": {"ms": round(tiled_ms, 4), "speedup_of_split_kv": round(tiled_ms / split_ms, 2)},
         "max_abs_diff_between_kernels": round((a.float() - b.float()).abs().max().item(), 5),
+        "other_variants": others,
         "gpu_launches": 2 * args.steps,
     }
 

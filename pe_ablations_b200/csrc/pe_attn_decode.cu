@@ -65,8 +65,8 @@ struct DCfg {
   // after the stages: query rows, per-row slope and causal limit, frequencies, stage counters, barriers
   static constexpr int OFF_Q = NSTAGE * STAGE_BYTES;
   static constexpr int OFF_ROW = OFF_Q + R_T * DQK * 4;
-  static constexpr int OFF_FREQ = OFF_ROW + 2 * R_T * 4;
-  static constexpr int OFF_CNT = OFF_FREQ + 2 * (DR > 0 ? DR : 1) * 4;
+  static constexpr int OFF_FREQ = (OFF_ROW + 2 * R_T * 4 + 15) & ~15;   // read as float4
+  static constexpr int OFF_CNT = OFF_FREQ + 4 * (DR > 0 ? DR : 4) * 4;   // frequency, phase bias, cos / sin of one tile's advance
   static constexpr int OFF_BAR = (OFF_CNT + NSTAGE * 4 + 7) & ~7;
   static constexpr int SMEM_BYTES = OFF_BAR + NSTAGE * 8 + 1024;   // + slack for the 1024-byte alignment
 };
@@ -159,7 +159,9 @@ pe_attn_decode_kernel(const KParams p, const DecodeParams dp, const __grid_const
   int* sLim = reinterpret_cast<int*>(sSlope + R_T);
   int* sCnt = reinterpret_cast<int*>(gen + C::OFF_CNT);
   float* freq_s = reinterpret_cast<float*>(gen + C::OFF_FREQ);
-  float* delta_s = freq_s + (DR > 0 ? DR : 1);
+  float* delta_s = freq_s + (DR > 0 ? DR : 4);
+  float* rot_c = delta_s + (DR > 0 ? DR : 4);
+  float* rot_s = rot_c + (DR > 0 ? DR : 4);
   const uint32_t bar0 = base + C::OFF_BAR;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -194,6 +196,7 @@ pe_attn_decode_kernel(const KParams p, const DecodeParams dp, const __grid_const
     for (int c = tid; c < DR; c += NT) {
       freq_s[c] = effective_freq(p, c);
       delta_s[c] = clamped_delta(p, c);
+      sincos_reduced(__fmul_rn((float)TK, freq_s[c]), &rot_s[c], &rot_c[c]);   // the phase advances TK * freq per tile
     }
   }
   if (tid < R_T) {
@@ -214,27 +217,23 @@ pe_attn_decode_kernel(const KParams p, const DecodeParams dp, const __grid_const
 
   // scores: this thread's key and column quarter
   const int part = lane >> 3, key_local = warp * 8 + (lane & 7);
-  [[maybe_unused]] float om[DR > 0 ? DR / 32 : 1][8], dl[DR > 0 ? DR / 32 : 1][8];
-  if constexpr (MODE == MODE_POPE) {
-#pragma unroll
-    for (int i = 0; i < DR / 32; ++i)
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        om[i][e] = freq_s[(part + 4 * i) * 8 + e];
-        dl[i][e] = delta_s[(part + 4 * i) * 8 + e];
-      }
-  }
+  // PoPE: (cos, sin) of this lane's key's phase for its columns, advanced from tile to tile by a
+  // rotation (the key position grows by TK per tile) and recomputed from the position every
+  // RESEED tiles, which bounds the accumulated rounding to about RESEED * 5e-7 rad -- well under
+  // the rounding of fl(pos * freq) itself at long contexts
+  constexpr int NRS = DR > 0 ? DR / 32 : 1, RESEED = 64;
+  [[maybe_unused]] float2 ph_c[NRS][4], ph_s[NRS][4];
   const bool rotary = MODE == MODE_XFORM && p.variant == PE_ATTN_ROTARY;
   const bool norm = MODE == MODE_XFORM && (p.flags & PE_ATTN_QK_NORM);
   const bool alibi = p.variant == PE_ATTN_ALIBI;
 
   // values: this thread's columns
   constexpr int CPT = DV / 32;
-  float acc_o[R_T][CPT];
+  float2 acc_o[R_T][CPT / 2];
 #pragma unroll
   for (int r = 0; r < R_T; ++r)
 #pragma unroll
-    for (int c = 0; c < CPT; ++c) acc_o[r][c] = 0.f;
+    for (int c = 0; c < CPT / 2; ++c) acc_o[r][c] = make_float2(0.f, 0.f);
   float m_run[R_T], l_lane[R_T];   // maximum over the warp's keys so far; this lane's key's share of the sum
 #pragma unroll
   for (int r = 0; r < R_T; ++r) {
@@ -257,9 +256,9 @@ pe_attn_decode_kernel(const KParams p, const DecodeParams dp, const __grid_const
       if (p.status != nullptr) atomicOr(p.status, ST_WAIT_KFULL);
     }
     const int kg = (tile0 + t) * TK + key_local;
-    float acc[R_T];
+    float2 acc2[R_T];   // even / odd columns
 #pragma unroll
-    for (int r = 0; r < R_T; ++r) acc[r] = 0.f;
+    for (int r = 0; r < R_T; ++r) acc2[r] = make_float2(0.f, 0.f);
     float nrm2 = 0.f;
 
     if constexpr (DC > 0) {
@@ -289,31 +288,57 @@ pe_attn_decode_kernel(const KParams p, const DecodeParams dp, const __grid_const
         for (int r = 0; r < R_T; ++r) {
           const float4 q0 = *reinterpret_cast<const float4*>(sQ + r * DQK + slot_g * 8);
           const float4 q1 = *reinterpret_cast<const float4*>(sQ + r * DQK + slot_g * 8 + 4);
-          float a = acc[r];
-          a = fmaf(q0.x, kf[0], a); a = fmaf(q0.y, kf[1], a); a = fmaf(q0.z, kf[2], a); a = fmaf(q0.w, kf[3], a);
-          a = fmaf(q1.x, kf[4], a); a = fmaf(q1.y, kf[5], a); a = fmaf(q1.z, kf[6], a); a = fmaf(q1.w, kf[7], a);
-          acc[r] = a;
+          float2 a = acc2[r];
+          a = __ffma2_rn(make_float2(q0.x, q0.y), make_float2(kf[0], kf[1]), a);
+          a = __ffma2_rn(make_float2(q0.z, q0.w), make_float2(kf[2], kf[3]), a);
+          a = __ffma2_rn(make_float2(q1.x, q1.y), make_float2(kf[4], kf[5]), a);
+          a = __ffma2_rn(make_float2(q1.z, q1.w), make_float2(kf[6], kf[7]), a);
+          acc2[r] = a;
         }
       }
     }
     if constexpr (MODE == MODE_POPE) {
       const uint32_t sbr = sb + C::K_BYTES + C::V_BYTES;
+      const bool reseed = (t % RESEED) == 0;
       const float pos = (float)(p.k_pos0 + kg);
 #pragma unroll
       for (int i = 0; i < DR / 32; ++i) {
         const int rs = part + 4 * i;
         const uint32_t addr = DR == 64 ? sbr + key_local * 128 + ((rs ^ (key_local & 7)) << 4)
                                        : sbr + key_local * 64 + ((rs ^ ((key_local >> 1) & 3)) << 4);
-        float x[8], kc[8], ks[8];
-        unpack8(lds_v4(addr), x);
+        const uint4 raw = lds_v4(addr);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+        if (reseed) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float mu = softplus_fast(x[e]);
-          float sn, cs;
-          // phase = fl(fl(pos * freq) + delta), the reference's rounding order
-          sincos_reduced(__fadd_rn(__fmul_rn(pos, om[i][e]), dl[i][e]), &sn, &cs);
-          kc[e] = mu * cs;
-          ks[e] = mu * sn;
+          for (int e = 0; e < 4; ++e) {
+            // phase = fl(fl(pos * freq) + delta), the reference's rounding order
+            const int c = rs * 8 + 2 * e;
+            sincos_reduced(__fadd_rn(__fmul_rn(pos, freq_s[c]), delta_s[c]), &ph_s[i][e].x, &ph_c[i][e].x);
+            sincos_reduced(__fadd_rn(__fmul_rn(pos, freq_s[c + 1]), delta_s[c + 1]), &ph_s[i][e].y, &ph_c[i][e].y);
+          }
+        } else {
+          const float4 c01 = *reinterpret_cast<const float4*>(rot_c + rs * 8), c23 = *reinterpret_cast<const float4*>(rot_c + rs * 8 + 4);
+          const float4 s01 = *reinterpret_cast<const float4*>(rot_s + rs * 8), s23 = *reinterpret_cast<const float4*>(rot_s + rs * 8 + 4);
+          const float2 rc[4] = {make_float2(c01.x, c01.y), make_float2(c01.z, c01.w), make_float2(c23.x, c23.y), make_float2(c23.z, c23.w)};
+          const float2 rsn[4] = {make_float2(s01.x, s01.y), make_float2(s01.z, s01.w), make_float2(s23.x, s23.y), make_float2(s23.z, s23.w)};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 c0 = ph_c[i][e], s0 = ph_s[i][e];
+            ph_c[i][e] = __ffma2_rn(c0, rc[e], __fmul2_rn(make_float2(-s0.x, -s0.y), rsn[e]));
+            ph_s[i][e] = __ffma2_rn(s0, rc[e], __fmul2_rn(c0, rsn[e]));
+          }
+        }
+        float2 kc[4], ks[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          // magnitude: softplus of the raw position half, two columns per instruction
+          const float2 x = make_float2(bf16_lo(w[e]), bf16_hi(w[e]));
+          const float2 tt = __fmul2_rn(x, make_float2(kLog2e, kLog2e));
+          const float2 u = __fadd2_rn(make_float2(ex2_approx(-fabsf(tt.x)), ex2_approx(-fabsf(tt.y))), make_float2(1.0f, 1.0f));
+          const float2 mu = __ffma2_rn(make_float2(lg2_approx(u.x), lg2_approx(u.y)), make_float2(kLn2, kLn2),
+                                       make_float2(fmaxf(x.x, 0.f), fmaxf(x.y, 0.f)));
+          kc[e] = __fmul2_rn(mu, ph_c[i][e]);
+          ks[e] = __fmul2_rn(mu, ph_s[i][e]);
         }
 #pragma unroll
         for (int r = 0; r < R_T; ++r) {
@@ -321,15 +346,22 @@ pe_attn_decode_kernel(const KParams p, const DecodeParams dp, const __grid_const
           const float* qs = qc + DR;
           const float4 c0 = *reinterpret_cast<const float4*>(qc), c1 = *reinterpret_cast<const float4*>(qc + 4);
           const float4 s0 = *reinterpret_cast<const float4*>(qs), s1 = *reinterpret_cast<const float4*>(qs + 4);
-          float a = acc[r];
-          a = fmaf(c0.x, kc[0], a); a = fmaf(c0.y, kc[1], a); a = fmaf(c0.z, kc[2], a); a = fmaf(c0.w, kc[3], a);
-          a = fmaf(c1.x, kc[4], a); a = fmaf(c1.y, kc[5], a); a = fmaf(c1.z, kc[6], a); a = fmaf(c1.w, kc[7], a);
-          a = fmaf(s0.x, ks[0], a); a = fmaf(s0.y, ks[1], a); a = fmaf(s0.z, ks[2], a); a = fmaf(s0.w, ks[3], a);
-          a = fmaf(s1.x, ks[4], a); a = fmaf(s1.y, ks[5], a); a = fmaf(s1.z, ks[6], a); a = fmaf(s1.w, ks[7], a);
-          acc[r] = a;
+          float2 a = acc2[r];
+          a = __ffma2_rn(make_float2(c0.x, c0.y), kc[0], a);
+          a = __ffma2_rn(make_float2(c0.z, c0.w), kc[1], a);
+          a = __ffma2_rn(make_float2(c1.x, c1.y), kc[2], a);
+          a = __ffma2_rn(make_float2(c1.z, c1.w), kc[3], a);
+          a = __ffma2_rn(make_float2(s0.x, s0.y), ks[0], a);
+          a = __ffma2_rn(make_float2(s0.z, s0.w), ks[1], a);
+          a = __ffma2_rn(make_float2(s1.x, s1.y), ks[2], a);
+          a = __ffma2_rn(make_float2(s1.z, s1.w), ks[3], a);
+          acc2[r] = a;
         }
       }
     }
+    float acc[R_T];
+#pragma unroll
+    for (int r = 0; r < R_T; ++r) acc[r] = acc2[r].x + acc2[r].y;
     // join the four column quarters of a key (lanes l, l^8, l^16, l^24)
 #pragma unroll
     for (int r = 0; r < R_T; ++r) {
@@ -366,26 +398,27 @@ pe_attn_decode_kernel(const KParams p, const DecodeParams dp, const __grid_const
       l_lane[r] = fmaf(l_lane[r], alpha, pr[r]);
       m_run[r] = m_new;
 #pragma unroll
-      for (int c = 0; c < CPT; ++c) acc_o[r][c] *= alpha;
+      for (int c = 0; c < CPT / 2; ++c) acc_o[r][c] = __fmul2_rn(acc_o[r][c], make_float2(alpha, alpha));
     }
 
     const uint32_t sbv = sb + C::K_BYTES + v_lane_off;
 #pragma unroll
     for (int jj = 0; jj < 8; ++jj) {
       const int j = warp * 8 + jj;
-      float vv[CPT];
+      float2 vv[CPT / 2];
       if constexpr (DV == 128) {
         const uint2 w = lds_v2(sbv + j * 128 + ((v_slot ^ (j & 7)) << 4));
-        vv[0] = bf16_lo(w.x); vv[1] = bf16_hi(w.x); vv[2] = bf16_lo(w.y); vv[3] = bf16_hi(w.y);
+        vv[0] = make_float2(bf16_lo(w.x), bf16_hi(w.x));
+        vv[1] = make_float2(bf16_lo(w.y), bf16_hi(w.y));
       } else {
         const uint32_t w = lds_u32(sbv + j * 128 + ((v_slot ^ (j & 7)) << 4));
-        vv[0] = bf16_lo(w); vv[1] = bf16_hi(w);
+        vv[0] = make_float2(bf16_lo(w), bf16_hi(w));
       }
 #pragma unroll
       for (int r = 0; r < R_T; ++r) {
         const float pj = __shfl_sync(0xffffffffu, pr[r], jj);
 #pragma unroll
-        for (int c = 0; c < CPT; ++c) acc_o[r][c] = fmaf(pj, vv[c], acc_o[r][c]);
+        for (int c = 0; c < CPT / 2; ++c) acc_o[r][c] = __ffma2_rn(make_float2(pj, pj), vv[c], acc_o[r][c]);
       }
     }
 
@@ -410,7 +443,8 @@ pe_attn_decode_kernel(const KParams p, const DecodeParams dp, const __grid_const
 #pragma unroll
   for (int r = 0; r < R_T; ++r) {
 #pragma unroll
-    for (int c = 0; c < CPT; ++c) red[(warp * R_T + r) * DV + lane * CPT + c] = acc_o[r][c];
+    for (int c = 0; c < CPT / 2; ++c)
+      *reinterpret_cast<float2*>(red + (warp * R_T + r) * DV + lane * CPT + 2 * c) = acc_o[r][c];
     float l = l_lane[r];
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);

@@ -42,6 +42,26 @@ __device__ __forceinline__ void sincos_reduced(float x, float* s, float* c) {
   *c = __cosf(r);
 }
 
+// PoPE expansion of two adjacent position columns at once with the packed fp32x2 instructions
+// of sm_100 (one issue slot for two multiplies / adds / FMAs): magnitude mu = softplus(x),
+// phase = fl(fl(pos * freq) + bias), result (mu cos, mu sin).  Same operations and roundings as
+// softplus_fast and sincos_reduced element by element; about 29 instructions per pair against 42.
+__device__ __forceinline__ void pope_pair(float2 x, float pos, float2 freq, float2 bias, float2* kc, float2* ks) {
+  const float2 t = __fmul2_rn(x, make_float2(1.4426950408889634f, 1.4426950408889634f));
+  const float2 u = __fadd2_rn(make_float2(ex2_approx(-fabsf(t.x)), ex2_approx(-fabsf(t.y))), make_float2(1.0f, 1.0f));
+  const float2 mu = __ffma2_rn(make_float2(lg2_approx(u.x), lg2_approx(u.y)),
+                               make_float2(0.6931471805599453f, 0.6931471805599453f),
+                               make_float2(fmaxf(x.x, 0.f), fmaxf(x.y, 0.f)));
+  const float2 ph = __fadd2_rn(__fmul2_rn(make_float2(pos, pos), freq), bias);
+  const float2 turns = __fmul2_rn(ph, make_float2(0.15915494309189535f, 0.15915494309189535f));
+  const float2 k = __fadd2_rn(__fadd2_rn(turns, make_float2(12582912.0f, 12582912.0f)),
+                              make_float2(-12582912.0f, -12582912.0f));
+  float2 r = __ffma2_rn(k, make_float2(-6.2831854820251465f, -6.2831854820251465f), ph);
+  r = __ffma2_rn(k, make_float2(1.7484556000744883e-7f, 1.7484556000744883e-7f), r);
+  *kc = __fmul2_rn(mu, make_float2(__cosf(r.x), __cosf(r.y)));
+  *ks = __fmul2_rn(mu, make_float2(__sinf(r.x), __sinf(r.y)));
+}
+
 // byte offset of the 16-byte slot ``slot`` (0..7) of row ``r`` inside a 128B-swizzled chunk
 __device__ __forceinline__ uint32_t swz(int r, int slot) { return (uint32_t)(r * 128 + ((slot ^ (r & 7)) << 4)); }
 
@@ -235,15 +255,15 @@ __device__ __forceinline__ void build_slab(const KParams& p, uint32_t base, uint
       const uint32_t w[4] = {raw[k].x, raw[k].y, raw[k].z, raw[k].w};
       float oc[8], os[8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float x = (e & 1) ? bf16_hi(w[e >> 1]) : bf16_lo(w[e >> 1]);
-        const float mu = live ? softplus_fast(x) : 0.f;
+      for (int e = 0; e < 4; ++e) {
         // phase = fl(fl(pos * freq) + delta), the reference's rounding order
-        const float ph = __fadd_rn(__fmul_rn(pos, f[e]), dl[e]);
-        float sn, cs;
-        sincos_reduced(ph, &sn, &cs);
-        oc[e] = mu * cs;
-        os[e] = mu * sn;
+        float2 c2, s2;
+        pope_pair(make_float2(bf16_lo(w[e]), bf16_hi(w[e])), pos, make_float2(f[2 * e], f[2 * e + 1]),
+                  make_float2(dl[2 * e], dl[2 * e + 1]), &c2, &s2);
+        oc[2 * e] = live ? c2.x : 0.f;
+        oc[2 * e + 1] = live ? c2.y : 0.f;
+        os[2 * e] = live ? s2.x : 0.f;
+        os[2 * e + 1] = live ? s2.y : 0.f;
       }
       const uint4 vc = make_uint4(pack_bf16x2(oc[0], oc[1]), pack_bf16x2(oc[2], oc[3]), pack_bf16x2(oc[4], oc[5]),
                                   pack_bf16x2(oc[6], oc[7]));
