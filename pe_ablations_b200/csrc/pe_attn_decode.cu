@@ -246,7 +246,34 @@ pe_attn_decode_kernel(const KParams p, const DecodeParams dp, const __grid_const
   __syncthreads();   // query rows complete
   bool bad = false;
 
+  // rotary: the (cos, sin) table entries of this lane's key and columns, fetched one tile ahead
+  constexpr int NCS = DC > 0 ? DC / 32 : 1;
+  [[maybe_unused]] float4 tab_next[NCS][2], tab_cur[NCS][2];
+  auto load_table = [&](int t) {
+    const int kg_t = (tile0 + t) * TK + key_local;
+    const long long krow = (long long)(kg_t < p.Sk ? kg_t : p.Sk - 1) + p.k_pos0 - p.table_pos0;
+#pragma unroll
+    for (int i = 0; i < NCS; ++i) {
+      const float4* tp = reinterpret_cast<const float4*>(p.table + (krow * (DC / 2) + (part + 4 * i) * 4) * 2);
+      tab_next[i][0] = __ldg(tp);
+      tab_next[i][1] = __ldg(tp + 1);
+    }
+  };
+  if constexpr (MODE == MODE_XFORM) {
+    if (rotary && n_tiles > 0) load_table(0);
+  }
+
   for (int t = 0; t < n_tiles; ++t) {
+    if constexpr (MODE == MODE_XFORM) {
+      if (rotary) {
+#pragma unroll
+        for (int i = 0; i < NCS; ++i) {
+          tab_cur[i][0] = tab_next[i][0];
+          tab_cur[i][1] = tab_next[i][1];
+        }
+        if (t + 1 < n_tiles) load_table(t + 1);
+      }
+    }
     const int stage = t % C::NSTAGE;
     const uint32_t sb = base + stage * C::STAGE_BYTES;
     const bool ok = bad ? mbar_wait_for(bar0 + stage * 8, (t / C::NSTAGE) & 1, 100000)
@@ -270,19 +297,22 @@ pe_attn_decode_kernel(const KParams p, const DecodeParams dp, const __grid_const
         unpack8(lds_v4(sb + chunk * 8192 + key_local * 128 + ((slot ^ (key_local & 7)) << 4)), kf);
         if constexpr (MODE == MODE_XFORM) {
           if (rotary) {
-            const int krow = (kg < p.Sk ? kg : p.Sk - 1) + p.k_pos0 - p.table_pos0;
-            const float4* tp = reinterpret_cast<const float4*>(p.table + ((size_t)krow * (DC / 2) + slot_g * 4) * 2);
-            const float4 t0 = __ldg(tp), t1 = __ldg(tp + 1);
+            const float4 t0 = tab_cur[i][0], t1 = tab_cur[i][1];
             const float cs[4] = {t0.x, t0.z, t1.x, t1.z}, sn[4] = {t0.y, t0.w, t1.y, t1.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
+              // (x0 c - x1 s, x0 s + x1 c)
               const float x0 = kf[2 * e], x1 = kf[2 * e + 1];
-              kf[2 * e] = x0 * cs[e] - x1 * sn[e];
-              kf[2 * e + 1] = x0 * sn[e] + x1 * cs[e];
+              const float2 o = __ffma2_rn(make_float2(x0, x0), make_float2(cs[e], sn[e]),
+                                          __fmul2_rn(make_float2(-x1, x1), make_float2(sn[e], cs[e])));
+              kf[2 * e] = o.x;
+              kf[2 * e + 1] = o.y;
             }
           }
+          if (norm) {
 #pragma unroll
-          for (int e = 0; e < 8; ++e) nrm2 = fmaf(kf[e], kf[e], nrm2);
+            for (int e = 0; e < 8; ++e) nrm2 = fmaf(kf[e], kf[e], nrm2);
+          }
         }
 #pragma unroll
         for (int r = 0; r < R_T; ++r) {
