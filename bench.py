@@ -212,7 +212,11 @@ def run_ours(args) -> dict:
     # back on three streams, so the step costs about what its host->device bytes cost
     in_bytes = sum(v.numel() * v.element_size() for v in host.values())
     # blocks of about 32 MiB: smaller ones cost more in launches and events than they hide
-    chunks = args.e2e_chunks or max(2, min(8, in_bytes // (32 << 20)))
+    chunks = args.e2e_chunks
+    if not chunks:   # a power of two, so that it divides the sequence length
+        chunks = 2
+        while chunks * 2 <= min(8, in_bytes // (32 << 20)):
+            chunks *= 2
     streamed = P.HostStreamedAttention("pope", B=B, S=S, H=heads, Hkv=heads, d_c=D_C, d_r=D_R, d_v=D_V,
                                        dtype=torch.bfloat16, device=dev, chunks=chunks, **dparams)
     out_host = torch.empty(B, S, heads, D_V, dtype=torch.bfloat16).pin_memory()
