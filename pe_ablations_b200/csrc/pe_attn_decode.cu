@@ -256,7 +256,7 @@ pe_attn_decode_kernel(const KParams p, const DecodeParams dp, const __grid_const
   // rotation (the key position grows by TK per tile) and recomputed from the position every
   // RESEED tiles, which bounds the accumulated rounding to about RESEED * 5e-7 rad -- well under
   // the rounding of fl(pos * freq) itself at long contexts
-  constexpr int NRS = DR > 0 ? DR / 32 : 1, RESEED = 64;
+  constexpr int NRS = DR > 0 ? DR / 32 : 1, RESEED = 16;
   [[maybe_unused]] float2 ph_c[NRS][4], ph_s[NRS][4];
   const bool rotary = MODE == MODE_XFORM && p.variant == PE_ATTN_ROTARY;
   const bool norm = MODE == MODE_XFORM && (p.flags & PE_ATTN_QK_NORM);
