@@ -281,9 +281,14 @@ int pe_rotary_norm_expand_backward(const void* grad, int grad_dtype, const int64
  *             logsumexp(logits[r, 0:vocab]) - logits[r, target[r]]
  *   out[1] += number of such rows
  *
+ * Like F.cross_entropy, a row whose logits hold NaN or +inf makes the sum non-finite (it is
+ * not dropped) and -inf logits count as probability zero.  A target outside [0, vocab) that
+ * is not ignore_index is the caller's error: its row is scored as NaN, so the sums come out
+ * NaN (torch raises a device assert there).
+ *
  * logits: device [n_rows, vocab] of ``dtype`` (pe_attn_dtype), rows ``row_stride`` elements
- * apart (16-byte aligned rows are read fastest; any element-aligned pitch works).  targets: device int64 [n_rows].  out: device
- * double[2], accumulated (zero it before the first chunk).  scratch: device buffer of
+ * apart (16-byte aligned rows are read fastest; any element-aligned pitch works).  targets:
+ * device int64 [n_rows].  out: device double[2], accumulated (zero it before the first chunk).  scratch: device buffer of
  * pe_ce_scratch_bytes(n_rows) bytes, 256-byte aligned, whose first 256 bytes are zero on
  * entry (the kernel leaves them zero, so one cudaMemset after allocation is enough).
  * Calls that share a scratch buffer must be ordered on one stream. */
@@ -324,6 +329,7 @@ int pe_swiglu_forward(const void* gate, const void* up, void* y, int dtype, int6
  *     start at zero and the rest is overwritten before it is read, so consecutive calls
  *     on one stream are safe; calls that can overlap on the GPU (different streams, or
  *     several host threads) would race on it and must be serialised by the caller.
+ *     A call that is refused (bad arguments, too many rows) touches nothing of the array.
  *   - logits / targets / out as for pe_ce_loss_sums; the caller still owns all three. */
 int pe_ce_static_max_rows(void);
 int pe_ce_loss_sums_static(const void* logits, int dtype, int64_t row_stride, const int64_t* targets, int n_rows,

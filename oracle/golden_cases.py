@@ -43,6 +43,16 @@ CORE_CASES = [
     Case("g_alibi_bf16", "alibi", BF16, 1, 4, 4, 257, 64, 0, 64, seed=34, qk_norm=True),
 ]
 
+# position-only cases run through the reference's explicit cosine-sum attention
+# (src/model/fpope.py:208-244,341-418); fixtures in tests/golden/cos_sum.npz
+COS_SUM_CASES = [
+    Case("cs_fpope_fp32", "pope", FP32, 1, 4, 1, 128, 0, 32, 64, seed=14, pope_kind="fpope",
+         training_length=128, n_fourier=16, fourier_sigma=0.3),
+    Case("cs_pope_fp32", "pope", FP32, 1, 4, 2, 160, 0, 16, 32, seed=11, training_length=64),
+    Case("cs_fpope_pos0_fp32", "pope", FP32, 2, 2, 2, 70, 0, 16, 32, seed=15, pos0=37, pope_kind="fpope",
+         training_length=64, n_fourier=8, fourier_sigma=0.4),
+]
+
 # the CPU-runnable benchmark configuration at full size; rows are subsampled in the fixture
 FULL_CASES = [(CONFIGS["cfg1_pope_fp32"], 8), (CONFIGS["cfg1_pope_fp32_posonly"], 8)]
 TABLE_ROW_STRIDE = 8   # rotary tables are stored every 8th row

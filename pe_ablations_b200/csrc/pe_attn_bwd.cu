@@ -506,14 +506,15 @@ template <int DQK, int DV, bool ALIBI>
 int launch_bwd_instance(const BwdParams& p, cudaStream_t stream) {
   using C = BCfg<DQK, DV>;
   auto kern = pe_attn_bwd_kernel<DQK, DV, ALIBI>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  int cfg_dev;
+  if (configured.pending(&cfg_dev)) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (e != cudaSuccess) {
       set_error("cudaFuncSetAttribute(%d bytes) failed: %s", C::SMEM_BYTES, cudaGetErrorString(e));
       return PE_ATTN_ERR_LAUNCH;
     }
-    configured = true;
+    configured.mark(cfg_dev);
   }
   CUtensorMap tmQ, tmK, tmV, tmDO, tmDQ;
   if (!encode_map(&tmQ, p.q, DQK, p.Sq, p.H, p.B, BM) || !encode_map(&tmK, p.k, DQK, p.Sk, p.Hkv, p.B, BN) ||

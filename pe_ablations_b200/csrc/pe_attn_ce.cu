@@ -4,8 +4,11 @@
 //   out[0] += sum over scored rows of (logsumexp(logits[r, :]) - logits[r, target[r]])
 //   out[1] += number of scored rows (target != ignore_index)
 // to a caller-owned pair of doubles, which is what a sharded evaluation reduces across
-// ranks.  It reads each logit exactly once in its stored type (bf16 or fp32); the eager
-// path it replaces upcasts the chunk to fp32 and materialises the log-softmax.
+// ranks.  Rows with non-finite losses (NaN or +inf logits) are scored and make the sum
+// non-finite, as the eager cross-entropy does; -inf logits count as probability zero; a
+// target outside [0, vocab) other than ignore_index makes the sum NaN.  It reads each
+// logit exactly once in its stored type (bf16 or fp32); the eager path it replaces upcasts
+// the chunk to fp32 and materialises the log-softmax.
 //
 // One CTA streams one row at a time (grid-stride over rows) with 16-byte loads and an
 // online logsumexp per thread, then warp-shuffle and shared-memory reductions.  Row
@@ -43,7 +46,7 @@ __device__ __forceinline__ void online_add(float& m, float& s, float x) {
   if (x > m) {
     s = s * __expf(m - x) + 1.0f;
     m = x;
-  } else {
+  } else if (x != -INFINITY) {  // a -inf logit adds nothing (and -inf - -inf would be NaN)
     s += __expf(x - m);
   }
 }
@@ -90,6 +93,7 @@ __global__ void __launch_bounds__(CE_THREADS) ce_loss_sums_kernel(const CeParams
       float vm = x[0];
 #pragma unroll
       for (int e = 1; e < VEC; ++e) vm = fmaxf(vm, x[e]);
+      if (vm == -INFINITY) continue;  // eight -inf logits add nothing (NaN is not -inf and goes on)
       if (vm > m) {
         s *= __expf(m - vm);
         m = vm;
@@ -108,11 +112,12 @@ __global__ void __launch_bounds__(CE_THREADS) ce_loss_sums_kernel(const CeParams
     if (tid == 0) {
       float mm = sm_m[0], ss = sm_s[0];
       for (int w = 1; w < CE_THREADS / 32; ++w) online_merge(mm, ss, sm_m[w], sm_s[w]);
-      float loss = 0.f;
-      if (tgt != (long long)p.ignore_index && tgt >= 0 && tgt < p.vocab) {
-        loss = (mm + logf(ss)) - scalar_at((int)tgt);
-      } else {
-        loss = -1.0f;  // marks an unscored row (a real loss is never negative)
+      // -inf marks an ignored row: a scored row's loss is finite, +inf or NaN, never -inf
+      float loss = -INFINITY;
+      if (tgt != (long long)p.ignore_index) {
+        // a target outside [0, vocab) is an error of the caller: it is scored as NaN, so the
+        // sums (and the perplexity) come out NaN instead of silently skipping the row
+        loss = (tgt >= 0 && tgt < p.vocab) ? (mm + logf(ss)) - scalar_at((int)tgt) : __int_as_float(0x7fc00000);
       }
       p.row_loss[row] = loss;
     }
@@ -131,7 +136,7 @@ __global__ void __launch_bounds__(CE_THREADS) ce_loss_sums_kernel(const CeParams
   double acc = 0.0, cnt = 0.0;
   for (int r = tid; r < p.n_rows; r += CE_THREADS) {
     const float l = reinterpret_cast<volatile float*>(p.row_loss)[r];
-    if (l >= 0.f) { acc += (double)l; cnt += 1.0; }
+    if (l != -INFINITY) { acc += (double)l; cnt += 1.0; }  // NaN and +inf losses reach the sum
   }
   __shared__ double red_a[CE_THREADS], red_c[CE_THREADS];
   red_a[tid] = acc;
@@ -212,7 +217,9 @@ int pe_ce_loss_sums(const void* logits, int dtype, int64_t row_stride, const int
 
 // Device address of g_ce_static_scratch on the current device.  In host code the array's
 // name is only a handle for the runtime, never a device pointer, so the address is asked
-// for once per device (with that device current) and remembered.
+// for once per device (with that device current) and remembered for the life of the
+// process (a cudaDeviceReset would invalidate it; the library does not support being used
+// across one).
 static int static_scratch_address(void** ptr) {
   static std::mutex mu;
   static void* cached[64] = {nullptr};
@@ -245,8 +252,12 @@ int pe_ce_loss_sums_static(const void* logits, int dtype, int64_t row_stride, co
                        "pe_ce_loss_sums with your own scratch", n_rows, pe_attn::CE_STATIC_MAX_ROWS);
     return PE_ATTN_ERR_TOO_LARGE;
   }
+  // every check comes before the shared array is touched: a call that is refused must not
+  // disturb a valid call that is using the array on another stream
+  int rc = pe_attn::check(logits, dtype, row_stride, reinterpret_cast<const long long*>(targets), n_rows, vocab, out);
+  if (rc != PE_ATTN_OK) return rc;
   void* scratch = nullptr;
-  const int rc = static_scratch_address(&scratch);
+  rc = static_scratch_address(&scratch);
   if (rc != PE_ATTN_OK) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // the array keeps whatever the previous call left: the counter block must start at zero

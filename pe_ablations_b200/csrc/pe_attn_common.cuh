@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/pe_attn.h"
 
 namespace pe_attn {
@@ -110,5 +112,20 @@ bool bwd_supports(int d_qk, int d_v);
 int launch_bwd(const BwdParams& p, int d_qk, int d_v, bool alibi, cudaStream_t stream);
 
 void set_error(const char* fmt, ...);
+
+// Function attributes (the dynamic shared-memory limit) are per device, so "already set" is
+// remembered per device ordinal: one bit each for devices 0..63, always set again beyond that.
+struct PerDeviceOnce {
+  std::atomic<unsigned long long> done{0ull};
+  // true when the current device still needs its one-time setup; *dev receives its ordinal
+  bool pending(int* dev) const {
+    *dev = 0;
+    if (cudaGetDevice(dev) != cudaSuccess || *dev < 0 || *dev >= 64) return true;
+    return !((done.load(std::memory_order_acquire) >> *dev) & 1ull);
+  }
+  void mark(int dev) {
+    if (dev >= 0 && dev < 64) done.fetch_or(1ull << dev, std::memory_order_release);
+  }
+};
 
 }  // namespace pe_attn

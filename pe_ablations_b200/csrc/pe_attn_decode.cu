@@ -635,14 +635,15 @@ template <int DC, int DR, int DV, int MODE, int R_T>
 int launch_instance(const KParams& p, const DecodeParams& dp, cudaStream_t stream) {
   using C = DCfg<DC, DR, DV, R_T>;
   auto kern = pe_attn_decode_kernel<DC, DR, DV, MODE, R_T>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  int cfg_dev;
+  if (configured.pending(&cfg_dev)) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (e != cudaSuccess) {
       set_error("cudaFuncSetAttribute(%d bytes) failed: %s", C::SMEM_BYTES, cudaGetErrorString(e));
       return PE_ATTN_ERR_LAUNCH;
     }
-    configured = true;
+    configured.mark(cfg_dev);
   }
   CUtensorMap tmK, tmKR, tmV;
   memset(&tmK, 0, sizeof(tmK));

@@ -598,14 +598,15 @@ template <int DC, int DR, int DV, int MODE, bool ALIBI>
 int launch_instance(const KParams& p, cudaStream_t stream) {
   using C = Cfg<DC, DR, DV>;
   auto kern = pe_attn_tc_kernel<DC, DR, DV, MODE, ALIBI>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  int cfg_dev;
+  if (configured.pending(&cfg_dev)) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (e != cudaSuccess) {
       set_error("cudaFuncSetAttribute(%d bytes) failed: %s", C::SMEM_BYTES, cudaGetErrorString(e));
       return PE_ATTN_ERR_LAUNCH;
     }
-    configured = true;
+    configured.mark(cfg_dev);
   }
   CUtensorMap tmQ, tmK, tmV;
   memset(&tmQ, 0, sizeof(tmQ));

@@ -593,14 +593,15 @@ template <int DC, int DR, int MODE, bool ALIBI>
 int launch_instance2(const KParams& p, cudaStream_t stream) {
   using C = Cfg2<DC, DR>;
   auto kern = pe_attn_tc2_kernel<DC, DR, MODE, ALIBI>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  int cfg_dev;
+  if (configured.pending(&cfg_dev)) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (e != cudaSuccess) {
       set_error("cudaFuncSetAttribute(%d bytes) failed: %s", C::SMEM_BYTES, cudaGetErrorString(e));
       return PE_ATTN_ERR_LAUNCH;
     }
-    configured = true;
+    configured.mark(cfg_dev);
   }
   CUtensorMap tmQ, tmK, tmV;
   memset(&tmQ, 0, sizeof(tmQ));

@@ -13,6 +13,7 @@ their token counts / total tokens)); ``perplexity`` computes the same quantity f
 
 from __future__ import annotations
 
+import datetime
 import math
 
 import torch
@@ -37,12 +38,55 @@ def shard_heads(num_heads: int, num_kv_heads: int, world: int, rank: int) -> tup
     return range(kv.start * g, kv.stop * g), kv
 
 
-def reduce_loss_sums(nll_sum: torch.Tensor, count: torch.Tensor, group=None) -> tuple[float, float]:
-    """All-reduce (SUM) of the two scalars over ``group``; identity without a process group."""
-    buf = torch.stack([nll_sum.double().reshape(()), count.double().reshape(())])
+REDUCE_TIMEOUT_S = 120.0
+
+
+def _local_kernel_status(buf: torch.Tensor) -> int:
+    """This rank's kernel status code at the host synchronisation the reduction needs anyway."""
+    if not buf.is_cuda:
+        return 0
+    from .ops import poll_device_status
+
+    return poll_device_status(buf.device)
+
+
+def reduce_loss_sums(nll_sum: torch.Tensor, count: torch.Tensor, group=None,
+                     timeout_s: float | None = REDUCE_TIMEOUT_S, status: int | None = None) -> tuple[float, float]:
+    """All-reduce (SUM) of the two scalars over ``group``; identity without a process group.
+
+    Two failures are made loud here, at the one place where every rank meets:
+
+    * a kernel of ANY rank that reported an expired wait (its outputs, and so its sums, are
+      garbage): each rank adds its status flag (``status``, default: read from this rank's
+      device) as a third element, and every rank raises after the reduction if the total is
+      non-zero;
+    * a rank that is gone (it raised, exited or never joined): the reduction is issued
+      asynchronously and waited for at most ``timeout_s`` seconds, after which the survivors
+      raise instead of waiting for the process group's default timeout (minutes).
+    """
+    code = _local_kernel_status(nll_sum) if status is None else int(status)
+    buf = torch.stack([nll_sum.double().reshape(()), count.double().reshape(()),
+                       torch.tensor(1.0 if code else 0.0, dtype=torch.float64, device=nll_sum.device)])
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
-        dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group)
-    nll, cnt = buf.tolist()
+        try:
+            work = dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group, async_op=True)
+            ok = work.wait() if timeout_s is None else work.wait(datetime.timedelta(seconds=float(timeout_s)))
+            if ok is False:
+                raise RuntimeError("the all-reduce did not complete")
+        except Exception as e:     # gloo / NCCL raise their own error types for a lost peer or a timeout
+            raise RuntimeError(f"loss-sum reduction failed or timed out after {timeout_s} s: a rank of the "
+                               f"evaluation is gone or stuck ({type(e).__name__}: {e})") from e
+    nll, cnt, bad = buf.tolist()
+    if code or bad != 0.0:
+        if code:
+            from .ops import check_device_status
+
+            try:
+                check_device_status(nll_sum.device)      # clears this rank's word
+            except RuntimeError:
+                pass
+        raise RuntimeError(f"{int(round(bad)) or 1} rank(s) reported expired waits in the attention kernels "
+                           f"(this rank's code 0x{code:x}); the reduced sums are invalid")
     return nll, cnt
 
 
@@ -114,12 +158,15 @@ def evaluate_shard(model, input_ids: torch.Tensor, micro_batch: int = 1, autocas
 
 @torch.no_grad()
 def sharded_perplexity(model, all_input_ids: torch.Tensor, rank: int, world: int, micro_batch: int = 1,
-                       autocast_dtype=torch.bfloat16, group=None, graphed: GraphedLossSums | None = None) -> dict:
-    """Perplexity of ``all_input_ids`` [N, S] with sequences sharded over ``world`` ranks."""
+                       autocast_dtype=torch.bfloat16, group=None, graphed: GraphedLossSums | None = None,
+                       timeout_s: float | None = REDUCE_TIMEOUT_S) -> dict:
+    """Perplexity of ``all_input_ids`` [N, S] with sequences sharded over ``world`` ranks.  Raises on
+    every rank if any rank's kernels reported an expired wait, or if a rank does not arrive at
+    the reduction within ``timeout_s`` seconds (see ``reduce_loss_sums``)."""
     mine = shard_range(all_input_ids.shape[0], world, rank)
     ids = all_input_ids[mine.start:mine.stop].to(next(model.parameters()).device, non_blocking=True)
     nll, cnt = evaluate_shard(model, ids, micro_batch, autocast_dtype, graphed)
-    tot_nll, tot_cnt = reduce_loss_sums(nll, cnt, group)
+    tot_nll, tot_cnt = reduce_loss_sums(nll, cnt, group, timeout_s)
     return {"nll_sum": tot_nll, "count": tot_cnt, "loss": tot_nll / max(tot_cnt, 1.0),
             "perplexity": perplexity(tot_nll, tot_cnt), "local_sequences": len(mine)}
 

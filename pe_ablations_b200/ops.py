@@ -20,30 +20,58 @@ import torch
 from . import _lib
 
 _VARIANTS = {"nope": _lib.NOPE, "rotary": _lib.ROTARY, "alibi": _lib.ALIBI, "pope": _lib.POPE}
-_status_words: dict[tuple[int, int], torch.Tensor] = {}
+_status_words: dict[int, torch.Tensor] = {}      # one int32 word per device, for all streams
 
 
 def device_status(device: torch.device) -> torch.Tensor:
-    """The int32 word (one per device and stream) the tensor-core kernel reports expired waits into."""
+    """The int32 word of ``device`` that the tensor-core kernels OR a code into when a bounded
+    wait runs out.  One word per device serves every stream (the kernels only ever OR into it).
+
+    It is created, zeroed and waited for on first use; that first use must not happen during
+    CUDA-graph capture (the zeroing would be recorded and every replay would wipe the previous
+    replay's report), so capture raises until one eager call has been made on the device.
+    """
     dev = torch.device(device)
     idx = dev.index if dev.index is not None else torch.cuda.current_device()
-    key = (idx, torch.cuda.current_stream(idx).cuda_stream)
-    w = _status_words.get(key)
+    w = _status_words.get(idx)
     if w is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("the first pe_attn call on a device creates its status word and cannot be captured "
+                               "into a CUDA graph: run one eager call on this device before capturing")
         w = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
-        _status_words[key] = w
+        torch.cuda.current_stream(idx).synchronize()      # visible to every stream from here on
+        _status_words[idx] = w
     return w
 
 
-def check_device_status(device: torch.device | None = None) -> None:
-    """Synchronise and raise if any kernel on ``device`` reported an expired wait."""
-    for (idx, _), w in list(_status_words.items()):
+def poll_device_status(device: torch.device | None = None) -> int:
+    """Synchronise ``device`` (default: every device used so far) and return the OR of the status
+    words, leaving them as they are.  0 means that no kernel reported an expired wait."""
+    code = 0
+    for idx, w in list(_status_words.items()):
         if device is not None and torch.device(device).index not in (None, idx):
             continue
-        code = int(w.item())
-        if code != 0:
-            w.zero_()
-            raise RuntimeError(f"pe_attn tensor-core kernel reported expired waits, code 0x{code:x}; output invalid")
+        torch.cuda.synchronize(idx)
+        code |= int(w.item()) & 0xFFFFFFFF
+    return code
+
+
+def check_device_status(device: torch.device | None = None) -> None:
+    """Synchronise and raise if any kernel on ``device`` reported an expired wait.
+
+    A non-zero word makes every later tensor-core launch on the device return without writing
+    its output, so results produced after the expiry are garbage until this is called: it
+    clears the word and raises.  The library calls it wherever it synchronises with the host
+    anyway (``eval.reduce_loss_sums``, ``HostStreamedAttention.synchronize``); code that calls
+    ``pe_attention`` or the modules directly calls it once per step, where it reads its result.
+    """
+    code = poll_device_status(device)
+    if code != 0:
+        for idx, w in list(_status_words.items()):
+            if device is None or torch.device(device).index in (None, idx):
+                w.zero_()
+        raise RuntimeError(f"pe_attn tensor-core kernel reported expired waits, code 0x{code:x}; every output "
+                           "produced on this device since the last check is invalid")
 
 
 def _strides(t: torch.Tensor, layout: str) -> tuple[int, int, int]:
@@ -551,10 +579,20 @@ class HostStreamedAttention:
         back.record(self.d2h)
         cur["copied_out"] = back
         main.wait_event(back)
+        self._last_back = back
         return out_host
 
+    def synchronize(self) -> None:
+        """Block until the last call's output has landed in host memory, then raise if a kernel
+        reported an expired wait (the output is invalid in that case)."""
+        back = getattr(self, "_last_back", None)
+        if back is not None:
+            back.synchronize()
+        check_device_status(self.device)
 
-_ce_scratch: dict[tuple[int, int], torch.Tensor] = {}
+
+_ce_scratch: dict[tuple[int, int], torch.Tensor] = {}     # (device, stream) -> scratch, at most _CE_SCRATCH_MAX
+_CE_SCRATCH_MAX = 16
 
 
 def ce_loss_sums(logits: torch.Tensor, targets: torch.Tensor, out: torch.Tensor | None = None,
@@ -589,6 +627,11 @@ def ce_loss_sums(logits: torch.Tensor, targets: torch.Tensor, out: torch.Tensor 
         if scratch is None or scratch.numel() < need:
             # zeroed once: the kernel leaves the counter word at zero after every call
             scratch = torch.zeros(max(need, 1 << 16), dtype=torch.uint8, device=dev)
+            _ce_scratch.pop(key, None)
+            while len(_ce_scratch) >= _CE_SCRATCH_MAX:
+                # oldest stream first; its block goes back to the caching allocator, which orders
+                # the reuse after that stream's kernels
+                _ce_scratch.pop(next(iter(_ce_scratch)))
             _ce_scratch[key] = scratch
         rc = _lib.lib.pe_ce_loss_sums(logits.data_ptr(), dtype, logits.stride(0), targets.data_ptr(), n, vocab,
                                       int(ignore_index), scratch.data_ptr(), out.data_ptr(),

@@ -114,22 +114,36 @@ def test_split_kv_matches_oracle(case):
                 fourier=fourier, with_lse=True) <= 2e-2
 
 
-def test_split_kv_agrees_with_query_tiled_kernel_on_long_cache():
-    """16k cached keys, one token, 16 heads: both kernels against each other (no oracle at this size)."""
+@pytest.mark.parametrize("fourier", [False, True], ids=["pope", "fope_mix"])
+def test_split_kv_and_query_tiled_kernels_match_oracle_on_long_cache(fourier):
+    """16384 cached keys, one new token at position 16383, 16 heads x batch 2: both kernels
+    against the oracle on the same tensors, output and logsumexp."""
     from pe_ablations_b200 import check_device_status, pe_attention
 
     dev = torch.device("cuda", 0)
     g = torch.Generator().manual_seed(104)
     B, H, Sk = 2, 16, 16384
-    mk = lambda S, d: torch.randn(B, S, H, d, generator=g).to(dev, BF16)
+    mk = lambda S, d: torch.randn(B, S, H, d, generator=g).to(BF16)
     q, k, v, q_r, k_r = mk(1, 128), mk(Sk, 128), mk(Sk, 128), mk(1, 64), mk(Sk, 64)
-    freqs, delta = O.pope_base_freqs(64), -torch.rand(64, generator=g) * 3
-    kw = dict(q_r=q_r, k_r=k_r, freqs=freqs, delta=delta, start_pos=Sk - 1, k_start_pos=0)
-    a = pe_attention("pope", q, k, v, split_kv=True, **kw)
-    b = pe_attention("pope", q, k, v, split_kv=False, **kw)
-    torch.cuda.synchronize()
-    check_device_status()
-    assert (a.float() - b.float()).abs().max().item() <= 2e-2 * max(1.0, b.float().abs().max().item())
+    base = O.pope_base_freqs(64)
+    delta = (torch.rand(64, generator=g) * 2 - 1) * torch.pi
+    kw, eff = dict(freqs=base), base
+    if fourier:
+        coeffs = torch.randn(64, 16, generator=g) * 0.3
+        eff = O.fope_effective_freqs(base, coeffs, training_length=Sk)
+        kw.update(fourier_coeffs=coeffs, floor_freq=2 * torch.pi / Sk)
+    f = lambda t: t.float()
+    want, want_lse = O.attention_core("pope", f(q), f(k), f(v), dtype=BF16, q_r=f(q_r), k_r=f(k_r), freqs=eff,
+                                      delta=delta, pos0=Sk - 1, k_pos0=0, return_lse=True)
+    c = lambda t: t.to(dev)
+    for split in (True, False):
+        lse = torch.full((B, H, 1), float("nan"), device=dev)
+        got = pe_attention("pope", c(q), c(k), c(v), q_r=c(q_r), k_r=c(k_r), delta=delta, start_pos=Sk - 1,
+                           k_start_pos=0, split_kv=split, lse=lse, **kw)
+        torch.cuda.synchronize()
+        check_device_status()
+        assert (got.float().cpu() - want.float()).abs().max().item() <= 2e-2, f"split_kv={split}"
+        assert (lse.cpu() - want_lse).abs().max().item() <= 2e-2, f"split_kv={split} (lse)"
 
 
 def test_split_kv_refuses_wide_calls():

@@ -107,6 +107,37 @@ def test_ce_loss_sums_matches_torch(dtype, n, vocab):
     assert abs(out2[0].item() - want2) <= 2e-6 * abs(want2)
 
 
+def test_ce_loss_sums_non_finite_logits_behave_like_torch():
+    """NaN logits give a NaN sum (the row is not dropped), -inf logits count as probability
+    zero, an out-of-range target makes the sum NaN."""
+    from pe_ablations_b200 import ce_loss_sums
+
+    g = torch.Generator().manual_seed(5)
+    n, vocab = 40, 4099
+    logits = (torch.randn(n, vocab, generator=g) * 3).cuda()
+    tgt = torch.randint(8, vocab, (n,), generator=g).cuda()
+    masked = logits.clone()
+    masked[:, :8] = float("-inf")               # a whole 16-byte vector of -inf at the start of every row
+    masked[3, 100:2000] = float("-inf")
+    for dtype in (torch.float32, torch.bfloat16):
+        x = masked.to(dtype)
+        want = torch.nn.functional.cross_entropy(x.double(), tgt, reduction="sum").item()
+        out = ce_loss_sums(x, tgt)
+        assert int(out[1].item()) == n
+        assert abs(out[0].item() - want) <= 2e-6 * abs(want)
+    bad = logits.clone()
+    bad[7, 11] = float("nan")
+    out = ce_loss_sums(bad, tgt)
+    assert torch.isnan(out[0]).item() and int(out[1].item()) == n
+    tgt2 = tgt.clone()
+    tgt2[5] = vocab                             # outside the vocabulary and not ignore_index
+    out = ce_loss_sums(logits, tgt2)
+    assert torch.isnan(out[0]).item()
+    out = ce_loss_sums(logits, tgt)             # the scratch counter is intact afterwards
+    want = torch.nn.functional.cross_entropy(logits.double(), tgt, reduction="sum").item()
+    assert abs(out[0].item() - want) <= 2e-6 * abs(want)
+
+
 def test_1b_shape_16k_loss_matches_reference(golden_dir):
     """The 1B-shape FoPE+PoPE decoder on one 16k sequence against the loss the reference itself
     produced (fp32, CPU, eager) on the same weights and ids.

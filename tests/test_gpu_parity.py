@@ -195,6 +195,75 @@ def test_full_size_config4_properties():
     assert (op.float().cpu() - want).abs().max().item() <= 2e-2
 
 
+@pytest.mark.parametrize("single_cta", [False, True], ids=["cta_pair", "single_cta"])
+def test_config4_last_rows_match_oracle(single_cta):
+    """BASELINE configuration 4's LAST 512 query rows (positions 15872..16383) against all 16384
+    keys: where phases reach 16k * omega and the tile-base rotations of the K transform matter
+    most.  Four (batch, head) slices, FoPE mix inside the kernel, delta ~ U(-pi, pi)."""
+    from pe_ablations_b200 import check_device_status, pe_attention
+    from oracle import pe_attention_oracle as O
+
+    B, H, S, Sq, dc, dr, dv = 2, 2, 16384, 512, 128, 64, 128
+    g = torch.Generator().manual_seed(401)
+    mk = lambda s, d: torch.randn(B, s, H, d, generator=g).to(torch.bfloat16)
+    q, q_r, k, k_r, v = mk(Sq, dc), mk(Sq, dr), mk(S, dc), mk(S, dr), mk(S, dv)
+    delta = (torch.rand(dr, generator=g) * 2 - 1) * torch.pi
+    coeffs = torch.randn(dr, 16, generator=g) * 0.3
+    base = O.pope_base_freqs(dr)
+    eff = O.fope_effective_freqs(base, coeffs, training_length=S)
+    want = O.attention_core("pope", q.float(), k.float(), v.float(), dtype=torch.bfloat16, q_r=q_r.float(),
+                            k_r=k_r.float(), freqs=eff, delta=delta, pos0=S - Sq, k_pos0=0).float()
+    dev = torch.device("cuda", 0)
+    got = pe_attention("pope", q.to(dev), k.to(dev), v.to(dev), q_r=q_r.to(dev), k_r=k_r.to(dev), freqs=base,
+                       fourier_coeffs=coeffs, floor_freq=2 * torch.pi / S, delta=delta, start_pos=S - Sq,
+                       k_start_pos=0, single_cta=single_cta)
+    torch.cuda.synchronize()
+    check_device_status()
+    assert (got.float().cpu() - want).abs().max().item() <= 2e-2
+
+
+@pytest.mark.parametrize("single_cta", [False, True], ids=["cta_pair", "single_cta"])
+def test_config3_last_rows_match_oracle(single_cta):
+    """BASELINE configuration 3 (FoPE frequencies through the rotary table, head_dim 128): the last
+    512 query rows of a 4096-token sequence against all keys."""
+    from pe_ablations_b200 import check_device_status, pe_attention
+    from oracle import pe_attention_oracle as O
+
+    B, H, S, Sq, D = 1, 4, 4096, 512, 128
+    g = torch.Generator().manual_seed(402)
+    mk = lambda s: torch.randn(B, s, H, D, generator=g).to(torch.bfloat16)
+    q, k, v = mk(Sq), mk(S), mk(S)
+    coeffs = torch.randn(D // 2, 16, generator=g) * 0.3
+    table = O.rotary_table(O.fope_effective_freqs(O.pope_base_freqs(D // 2), coeffs, training_length=S), S)
+    want = O.attention_core("rotary", q.float(), k.float(), v.float(), dtype=torch.bfloat16, table=table,
+                            table_pos0=0, pos0=S - Sq, k_pos0=0).float()
+    dev = torch.device("cuda", 0)
+    got = pe_attention("rotary", q.to(dev), k.to(dev), v.to(dev), rotary_table=table, table_pos0=0,
+                       start_pos=S - Sq, k_start_pos=0, single_cta=single_cta)
+    torch.cuda.synchronize()
+    check_device_status()
+    assert (got.float().cpu() - want).abs().max().item() <= 2e-2
+
+
+@pytest.mark.parametrize("case", G.COS_SUM_CASES, ids=lambda c: c.name)
+def test_fp32_kernel_matches_cos_sum_reference(golden_dir, case):
+    """The fp32 kernel (cos/sin expansion + dense product) against the reference's explicit
+    cosine-sum attention, a formulation it shares nothing with; and against its restatement."""
+    from oracle import pe_attention_oracle as O
+    from pe_ablations_b200 import pe_attention
+
+    ref = np.load(os.path.join(golden_dir, "cos_sum.npz"))
+    inp = make_inputs(case)
+    dev = torch.device("cuda", 0)
+    kw = dict(freqs=inp["freqs"], delta=inp["delta"], start_pos=case.pos0, scale=case.d_r ** -0.5)
+    got = pe_attention("pope", None, None, inp["v"].to(dev), q_r=inp["q_r"].to(dev), k_r=inp["k_r"].to(dev), **kw)
+    torch.cuda.synchronize()
+    got = got.cpu()
+    assert (got - torch.from_numpy(ref[f"{case.name}/out"])).abs().max().item() <= 1e-4
+    again = O.cos_sum_attention(inp["q_r"], inp["k_r"], inp["v"], inp["freqs"], inp["delta"], pos0=case.pos0)
+    assert (got - again).abs().max().item() <= 1e-4
+
+
 def test_abi_rejects_bad_arguments_on_gpu():
     from pe_ablations_b200 import pe_attention
     from pe_ablations_b200._lib import PeAttnError

@@ -95,3 +95,42 @@ def test_alibi_slopes_non_power_of_two():
     s = O.alibi_slopes(12)
     assert s.shape == (12,)
     assert torch.allclose(s[:8], torch.tensor([2.0 ** (-(i + 1)) for i in range(8)]))
+
+
+# ---- the explicit cosine-sum formulation: an oracle that shares nothing with the GEMM form ----
+@pytest.fixture(scope="module")
+def cos_sum(golden_dir):
+    return np.load(os.path.join(golden_dir, "cos_sum.npz"))
+
+
+@pytest.mark.parametrize("case", G.COS_SUM_CASES, ids=lambda c: c.name)
+def test_cos_sum_oracle_matches_reference(cos_sum, case):
+    """``cos_sum_attention`` against the reference's own ``pope_attention`` output."""
+    inp = make_inputs(case)
+    want = torch.from_numpy(cos_sum[f"{case.name}/out"])
+    assert torch.allclose(inp["freqs"], torch.from_numpy(cos_sum[f"{case.name}/freqs"]), rtol=3e-6, atol=1e-9)
+    got = O.cos_sum_attention(inp["q_r"], inp["k_r"], inp["v"], inp["freqs"], inp["delta"], pos0=case.pos0)
+    assert got.shape == want.shape
+    assert (got - want).abs().max().item() <= 2e-5
+
+
+@pytest.mark.parametrize("case", G.COS_SUM_CASES, ids=lambda c: c.name)
+def test_gemm_form_oracle_agrees_with_cos_sum_reference(cos_sum, case):
+    """The concatenated cos/sin restatement (what the kernels implement) gives the same attention
+    as the reference's cosine-sum path: cos(a - b) = cos a cos b + sin a sin b, in fp32."""
+    inp = make_inputs(case)
+    want = torch.from_numpy(cos_sum[f"{case.name}/out"])
+    got = O.attention_core("pope", None, None, inp["v"], q_r=inp["q_r"], k_r=inp["k_r"], pos0=case.pos0,
+                           freqs=inp["freqs"], delta=inp["delta"], scale=case.d_r ** -0.5)
+    # phases up to ~|pos| * freq: the two sides round pos * freq differently
+    assert (got - want).abs().max().item() <= 5e-5
+
+
+def test_cos_sum_with_content_halves_equals_gemm_form():
+    case = G.CORE_CASES[3]                      # g_fpope_fp32: content 64 + position 32, GQA 4:1
+    assert case.name == "g_fpope_fp32"
+    inp = make_inputs(case)
+    a = oracle_output(case, inp)
+    b = O.cos_sum_attention(inp["q_r"], inp["k_r"], inp["v"], inp["freqs"], inp["delta"], q=inp["q"], k=inp["k"],
+                            scale=case.d_qk ** -0.5)
+    assert (a - b).abs().max().item() <= 2e-5

@@ -64,6 +64,50 @@ def test_static_scratch_entry_point_matches_regular_one_twice():
         assert abs(got[0].item() - ref) <= 2e-6 * abs(ref)
 
 
+def test_static_scratch_entry_point_allocates_nothing():
+    """What the entry point is for: once the first call on the device has looked up the array's
+    address, a call changes neither the driver's free-memory figure nor torch's allocator
+    counters (a cudaMalloc anywhere below the C ABI would show in the first, a torch
+    allocation in the second)."""
+    from pe_ablations_b200 import _lib as L
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator().manual_seed(98)
+    logits = (torch.randn(2048, 8192, generator=g) * 2).to(torch.bfloat16).to(dev)
+    tgt = torch.randint(0, 8192, (2048,), generator=g).to(dev)
+    out = torch.zeros(2, dtype=torch.float64, device=dev)
+    assert _call_static(L, logits, tgt, out) == 0, L.lib.pe_attn_last_error()      # the set-up call
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info(dev)
+    stats0 = torch.cuda.memory_stats(dev)
+    for _ in range(3):
+        assert _call_static(L, logits, tgt, out) == 0, L.lib.pe_attn_last_error()
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info(dev)
+    stats1 = torch.cuda.memory_stats(dev)
+    assert free1 == free0
+    for key in ("allocation.all.allocated", "segment.all.allocated", "allocated_bytes.all.allocated"):
+        assert stats1[key] == stats0[key], key
+    assert int(out[1].item()) == 4 * 2048
+
+
+def test_static_scratch_entry_point_refused_call_leaves_the_array_alone():
+    """A call with bad arguments is refused before the shared array is touched."""
+    from pe_ablations_b200 import _lib as L
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    logits = torch.zeros(4, 8, dtype=torch.float32, device=dev)
+    tgt = torch.zeros(4, dtype=torch.int64, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    rc = L.lib.pe_ce_loss_sums_static(logits.data_ptr(), L.FP32, 8, tgt.data_ptr(), 4, 8, -100, None, C.c_void_p(stream))
+    assert rc == 1                          # PE_ATTN_ERR_NULL: no output pointer
+    rc = L.lib.pe_ce_loss_sums_static(logits.data_ptr(), 9, 8, tgt.data_ptr(), 4, 8, -100, logits.data_ptr(),
+                                      C.c_void_p(stream))
+    assert rc != 0                          # unknown dtype
+
+
 def test_static_scratch_entry_point_rejects_oversized_chunks():
     from pe_ablations_b200 import _lib as L
 
