@@ -16,8 +16,13 @@ inside the timed region.
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
   python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
 
-``--impl reference`` times the reference's eager data flow (CPU port under oracle/) on the
-host cores, on a bounded slice of the same workload.
+``--impl reference`` times the reference's eager data flow on the host cores (the reference's
+own modules when oracle/_ref holds them, else the CPU port under oracle/), on a bounded slice
+of the same workload: always one (batch, head) slice at the full sequence length.
+
+The default line also carries compact summaries of the secondary workloads (every variant's
+forward beside the reference's live GPU data flow -- ATen positional ops + SDPA -- on the same
+GPU, one decode step, one training step) and a ``parity`` figure against the CPU oracle.
 """
 
 from __future__ import annotations
@@ -40,9 +45,9 @@ N_FOURIER, SIGMA = 16, 0.3
 FLOPS_PER_STEP = float(B) * H * S * S * (D_C + 2 * D_R + D_V)
 METRIC = "fused PE-attention TFLOP/s (FoPE+PoPE causal forward, bf16, B2 H16 S16384 d_qk256 d_v128)"
 WORKLOAD = "config 4: FoPE+PoPE causal attention forward, bf16, B2 H16 S16384 d_c128 d_r64 d_v128"
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the tcgen05 kernel on this
-# workload, from the ncu capture summarised in profiles/pe_attn_tc_kernel_config4_fopepope.md
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 669_989_888
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of pe_attn_tc2_kernel on this
+# workload (ncu --set full capture of the CTA-pair kernel: 546.7 MB read + 121.0 MB written)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 667_700_000
 FALLBACK_BF16_TFLOPS = 1590.0
 
 
@@ -112,6 +117,40 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def bench_config(world: int) -> dict:
+    """The ``config`` object of the JSON line; both arms print the same one."""
+    return {"workload": WORKLOAD, "parallelism": f"heads sharded over {world} GPU(s), {H // world} heads each",
+            "l2": "flushed between steps by writing a 256 MiB buffer",
+            "flops_per_step": FLOPS_PER_STEP, "flops_convention": "B*H*S^2*(d_qk+d_v), causal"}
+
+
+def bind_host_memory_near_gpu(torch, local_rank: int) -> dict:
+    """Best effort: run this process on the CPUs of the GPU's NUMA node before its pinned buffers
+    are allocated and first touched, so that host<->device copies do not cross the socket link.
+    Only affinity is used (no memory-policy call); a failure leaves everything as it was."""
+    info = {"gpu_numa_node": None, "bound": False}
+    try:
+        pr = torch.cuda.get_device_properties(local_rank)
+        bdf = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+            node = int(f.read().strip())
+        info["gpu_numa_node"] = node
+        if node < 0:
+            return info
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                a, _, b = part.partition("-")
+                cpus.update(range(int(a), int(b or a) + 1))
+        allowed = os.sched_getaffinity(0) & cpus
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+            info["bound"], info["cpus"] = True, len(allowed)
+    except Exception as e:   # no sysfs entry, no permission, a cpuset without local CPUs ...
+        info["note"] = f"{type(e).__name__}"
+    return info
+
+
 def make_inputs(torch, heads: int, seed: int, pinned: bool):
     """Seeded N(0,1) inputs for ``heads`` heads of the workload, on the host (bf16)."""
     g = torch.Generator().manual_seed(seed)
@@ -151,6 +190,7 @@ def run_ours(args) -> dict:
     if H % world != 0:
         raise SystemExit(f"{H} heads do not shard over {world} GPUs")
     heads = H // world
+    numa = bind_host_memory_near_gpu(torch, local_rank)
 
     host, params = make_inputs(torch, heads, seed=1000 + rank, pinned=True)
     dparams = {k: (v.to(dev) if hasattr(v, "to") else v) for k, v in params.items()}
@@ -211,12 +251,9 @@ def run_ours(args) -> dict:
     # the library's host-buffer call: sequence blocks are copied in, attended and copied
     # back on three streams, so the step costs about what its host->device bytes cost
     in_bytes = sum(v.numel() * v.element_size() for v in host.values())
-    # blocks of about 32 MiB: smaller ones cost more in launches and events than they hide
-    chunks = args.e2e_chunks
-    if not chunks:   # a power of two, so that it divides the sequence length
-        chunks = 2
-        while chunks * 2 <= min(8, in_bytes // (32 << 20)):
-            chunks *= 2
+    # at least four row blocks per rank at every N, so that copy-in, kernels and copy-out
+    # overlap; eight where a rank holds enough for 32 MiB blocks
+    chunks = args.e2e_chunks or (8 if in_bytes >= (256 << 20) else 4)
     streamed = P.HostStreamedAttention("pope", B=B, S=S, H=heads, Hkv=heads, d_c=D_C, d_r=D_R, d_v=D_V,
                                        dtype=torch.bfloat16, device=dev, chunks=chunks, **dparams)
     out_host = torch.empty(B, S, heads, D_V, dtype=torch.bfloat16).pin_memory()
@@ -235,6 +272,7 @@ def run_ours(args) -> dict:
     e1.record()
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
+    streamed.synchronize()      # raises if a kernel reported an expired wait
     h2d = sum(v.numel() * v.element_size() for v in host.values())
     d2h = out_host.numel() * out_host.element_size()
 
@@ -243,12 +281,12 @@ def run_ours(args) -> dict:
         "metric": METRIC, "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "parallelism": f"heads sharded over {world} GPU(s), {heads} heads each",
-                   "l2": "flushed between steps by writing a 256 MiB buffer",
-                   "flops_per_step": FLOPS_PER_STEP, "flops_convention": "B*H*S^2*(d_qk+d_v), causal"},
+        "config": bench_config(world),
         "e2e": {"value": round(FLOPS_PER_STEP / (e2e_ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
                 "ms_per_step": round(e2e_ms, 3), "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
-                "chunks": chunks, "call": "HostStreamedAttention (copy-in / attend / copy-out pipelined over sequence blocks)"},
+                "chunks": chunks, "host_gbs_per_gpu": round((h2d + d2h) / (e2e_ms * 1e-3) / 1e9, 1),
+                "host_numa": numa,
+                "call": "HostStreamedAttention (copy-in / attend / copy-out pipelined over sequence blocks)"},
         "gpu_launches": args.steps,
         "clocks": clocks,
         "roofline": {"bound": "tensor", "kernel": "pe_attn_tc2_kernel<128,64,POPE> (CTA pair, cta_group::2)",
@@ -260,7 +298,9 @@ def run_ours(args) -> dict:
                      "frac_of_sustained_cublas": (round(kernel_tflops / measured_sustained_peak(), 4)
                                                   if measured_sustained_peak() else None),
                      "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH // world,   # compulsory-traffic kernel: scales with the heads per rank
-                     "launch_ms": round(kernel_ms, 4)},
+                     "launch_ms": round(kernel_ms, 4),
+                     # CTA pairs of 512 query rows per launch over the GPU's pair slots (1 CTA/SM)
+                     "waves": round(B * heads * (S // 512) / (torch.cuda.get_device_properties(dev).multi_processor_count // 2), 2)},
     }
     if not args.no_eval:
         ev_line = run_eval(torch, dist, dev, rank, world, args.eval_sequences, not args.eval_graph)
@@ -268,6 +308,21 @@ def run_ours(args) -> dict:
             line["eval_1b_16k"] = ev_line
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(budget_s=20.0)
+        line["parity"] = parity_vs_oracle(torch, dten, dparams, out)
+    if rank == 0 and world == 1 and not args.no_secondary:
+        del dten, out, streamed
+        torch.cuda.empty_cache()
+        sub = argparse.Namespace(**vars(args))
+        sub.steps, sub.warmup = min(args.steps, 10), 3
+        v = run_variants(sub)
+        line["variants"] = {"peak": v["peak"], "rows": v["variants"], "gpu_eager": v["gpu_eager"]}
+        d = run_decode(sub)
+        line["decode"] = {"workload": d["config"]["workload"], "tokens_per_s": d["value"], "ms_per_step": d["ms_per_step"],
+                          "roofline": d["roofline"], "query_tiled_kernel": d["query_tiled_kernel"],
+                          "other_variants": d["other_variants"]}
+        t = run_training(sub)
+        line["training"] = {"workload": t["config"]["workload"], "tflops": t["value"], "ms_per_step": t["ms_per_step"],
+                            "backward_kernel": t["backward_kernel"]}
     if world > 1:
         dist.destroy_process_group()
     return line if rank == 0 else None
@@ -319,45 +374,75 @@ def run_eval(torch, dist, dev, rank: int, world: int, n_sequences: int, no_graph
 
 
 def cpu_baseline(budget_s: float) -> dict:
-    """The reference's eager data flow on the host cores, on a bounded slice of the workload."""
+    """The reference's eager data flow on the host cores, on a bounded slice of the workload:
+    one of the 32 (batch, head) slices at the full sequence length."""
     from oracle.cpu_baseline import time_cfg4_sample
 
-    probe = time_cfg4_sample(2048, 1)
-    est_16k = probe["seconds"] * 64 * 1.5
-    seq = 16384 if est_16k <= budget_s else (8192 if est_16k / 4 <= budget_s else 4096)
-    r = time_cfg4_sample(seq, 1)
+    r = time_cfg4_sample(S, 1)
     return {"value": round(r["flops"] / r["seconds"] / 1e12, 5), "unit": "TFLOP/s", "cores": r["threads"],
-            "kind": "port", "seconds": round(r["seconds"], 3),
-            "sample": f"1 of the {B * H} (batch, head) slices at sequence {seq} (eager fp32 transform + bf16 SDPA on CPU)"}
+            "kind": r["kind"], "seconds": round(r["seconds"], 3),
+            "sample": f"1 of the {B * H} (batch, head) slices at sequence {S} (eager fp32 transform + bf16 SDPA on CPU)"}
+
+
+def parity_vs_oracle(torch, dten, dparams, out) -> dict:
+    """Max abs error of the timed launch's output against the CPU oracle on rows that the oracle
+    can afford: the first and the last 512 query rows (the last ones against all 16384 keys) of
+    four (batch, head) slices.  Runs outside every timed region; the oracle is only the checker."""
+    from oracle import pe_attention_oracle as O
+
+    tol, rows = 2e-2, 512
+    eff = O.fope_effective_freqs(dparams["freqs"].cpu(), dparams["fourier_coeffs"].cpu(), training_length=S)
+    delta = dparams["delta"].cpu()
+    heads = dten["q"].shape[2]
+    worst = {"prefix": 0.0, "tail": 0.0}
+    for b, h in ((0, 0), (0, heads - 1), (1, 0), (1, heads - 1)):
+        f = lambda name, lo, hi: dten[name][b:b + 1, lo:hi, h:h + 1].float().cpu()
+        for part, (q0, k1) in (("prefix", (0, rows)), ("tail", (S - rows, S))):
+            want = O.attention_core("pope", f("q", q0, q0 + rows), f("k", 0, k1), f("v", 0, k1), dtype=torch.bfloat16,
+                                    q_r=f("q_r", q0, q0 + rows), k_r=f("k_r", 0, k1), freqs=eff, delta=delta,
+                                    pos0=q0, k_pos0=0)
+            got = out[b:b + 1, q0:q0 + rows, h:h + 1].float().cpu()
+            worst[part] = max(worst[part], (got - want.float()).abs().max().item())
+    err = max(worst.values())
+    return {"max_abs_err": round(err, 6), "max_abs_err_prefix": round(worst["prefix"], 6),
+            "max_abs_err_tail": round(worst["tail"], 6), "tolerance": tol, "ok": bool(err <= tol),
+            "rows": f"query rows 0..{rows - 1} and {S - rows}..{S - 1} of 4 (batch, head) slices vs the CPU oracle"}
 
 
 def run_reference(args) -> dict | None:
+    """The reference arm: always one (batch, head) slice of the workload at the FULL sequence
+    length per step.  A host too slow for ``--steps`` such passes in a few minutes runs fewer
+    passes (and says so), never a shorter sequence."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return None
     from oracle.cpu_baseline import time_cfg4_sample
 
-    probe = time_cfg4_sample(2048, 1)
-    n = args.steps + args.warmup
-    est_16k = probe["seconds"] * 64 * 1.5
-    seq = 16384
-    while seq > 2048 and est_16k * (seq / 16384) ** 2 * n > 150.0:
-        seq //= 2
-    for _ in range(args.warmup):
-        time_cfg4_sample(seq, 1)
-    t = [time_cfg4_sample(seq, 1) for _ in range(args.steps)]
+    budget_s = 200.0
+    first = time_cfg4_sample(S, 1)
+    fit = max(1, int(budget_s / max(first["seconds"], 1e-3)))
+    warm = max(0, min(args.warmup - 1, fit // 4))
+    steps = max(1, min(args.steps, fit - warm))
+    for _ in range(warm):
+        time_cfg4_sample(S, 1)
+    t = [time_cfg4_sample(S, 1) for _ in range(steps)]
     sec = sum(x["seconds"] for x in t) / len(t)
     val = t[0]["flops"] / sec / 1e12
-    sample = f"per step: 1 of the {B * H} (batch, head) slices at sequence {seq}, reference eager data flow on CPU"
-    return {
+    kind = t[0]["kind"]
+    sample = (f"per step: 1 of the {B * H} (batch, head) slices at sequence {S}, the reference's eager data flow on CPU "
+              f"({'its own modules from oracle/_ref' if kind == 'reference' else 'CPU port of it'})")
+    line = {
         "impl": "reference", "metric": METRIC, "value": round(val, 5), "unit": "TFLOP/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 2), "higher_is_better": True,
+        "steps": steps, "warmup": warm + 1, "ms_per_step": round(sec * 1e3, 2), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample": sample},
-        "cpu_baseline": {"value": round(val, 5), "unit": "TFLOP/s", "cores": t[0]["threads"], "kind": "port",
+        "config": bench_config(max(1, args.gpus)),
+        "cpu_baseline": {"value": round(val, 5), "unit": "TFLOP/s", "cores": t[0]["threads"], "kind": kind,
                          "sample": sample},
         "e2e": {"value": round(val, 5), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
+    if steps != args.steps or warm + 1 != args.warmup:
+        line["steps_requested"], line["warmup_requested"] = args.steps, args.warmup
+    return line
 
 
 def run_training(args) -> dict:
@@ -549,12 +634,13 @@ def run_variants(args) -> dict:
     def tensors(Bv, Sv, Hv, dims, dtype):
         return [None if d == 0 else torch.randn(Bv, Sv, Hv, d, generator=g).to(dtype).to(dev) for d in dims]
 
-    def timed(fn):
-        for _ in range(max(args.warmup, 3)):
+    def timed(fn, steps=None, warmup=None):
+        for _ in range(max(args.warmup, 3) if warmup is None else warmup):
             flush.zero_()
             fn()
         torch.cuda.synchronize()
-        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+              for _ in range(steps or args.steps)]
         for e0, e1 in ev:
             flush.zero_()
             e0.record()
@@ -565,55 +651,145 @@ def run_variants(args) -> dict:
 
     rows = []
 
-    def add(name, Bv, Hv, Sv, d_c, d_r, d_v, dtype, variant, **kw):
+    def add(name, Bv, Hv, Sv, d_c, d_r, d_v, dtype, variant, eager=None, **kw):
         q, k, v, q_r, k_r = tensors(Bv, Sv, Hv, (d_c, d_c, d_v, d_r, d_r), dtype)
         call = lambda: P.pe_attention(variant, q, k, v, q_r=q_r, k_r=k_r, **kw)
         with torch.no_grad():
             ms = timed(call)
         flops = Bv * Hv * Sv * Sv * (d_c + 2 * d_r + d_v)
         tf = flops / (ms * 1e-3) / 1e12
-        rows.append({"variant": name, "shape": f"B{Bv} H{Hv} S{Sv} d_qk{d_c + 2 * d_r} d_v{d_v}",
-                     "dtype": "bf16" if dtype == torch.bfloat16 else "fp32", "ms": round(ms, 4), "tflops": round(tf, 2),
-                     "frac_of_peak": round(tf / peak, 4) if dtype == torch.bfloat16 else None})
+        row = {"variant": name, "shape": f"B{Bv} H{Hv} S{Sv} d_qk{d_c + 2 * d_r} d_v{d_v}",
+               "dtype": "bf16" if dtype == torch.bfloat16 else "fp32", "ms": round(ms, 4), "tflops": round(tf, 2),
+               "frac_of_peak": round(tf / peak, 4) if dtype == torch.bfloat16 else None}
+        if eager is not None:
+            # the reference's live GPU data flow on the same tensors, same timing protocol
+            try:
+                with torch.no_grad():
+                    ref_out = eager(q, k, v, q_r, k_r)
+                    got = call()
+                    row["max_abs_diff_vs_gpu_eager"] = round((got.float() - ref_out.float()).abs().max().item(), 5)
+                    del ref_out, got
+                    ems = timed(lambda: eager(q, k, v, q_r, k_r), steps=min(args.steps, 5), warmup=2)
+                row["gpu_eager_ms"] = round(ems, 4)
+                row["gpu_eager_tflops"] = round(flops / (ems * 1e-3) / 1e12, 2)
+                row["speedup_vs_gpu_eager"] = round(ems / ms, 2)
+            except Exception as e:      # e.g. out of memory in the S x S path of the comparator
+                row["gpu_eager_unavailable"] = f"{type(e).__name__}: {str(e)[:120]}"
+                torch.cuda.empty_cache()
+        rows.append(row)
+
+    # ---- the comparator: what the reference itself runs on a GPU (no kernels of this library) ----
+    import torch.nn.functional as F
+
+    def eager_rotate(x, cis):
+        # src/model/rope.py:35-57: complex multiply of interleaved pairs in fp32, type_as
+        xc = torch.view_as_complex(x.float().reshape(*x.shape[:-1], -1, 2))
+        return torch.view_as_real(xc * cis.view(1, x.shape[1], 1, -1)).flatten(3).type_as(x)
+
+    def eager_qknorm(t, eps=1e-6):
+        # src/model/normalization.py:44-56
+        return t / (t.norm(dim=-1, keepdim=True) + eps)
+
+    def eager_rotary(cis=None, mscale=1.0, qk_norm=False):
+        # src/model/attention.py:77-96
+        def run(q, k, v, q_r, k_r):
+            if cis is not None:
+                q, k = eager_rotate(q, cis[: q.shape[1]]), eager_rotate(k, cis[: k.shape[1]])
+                if mscale != 1.0:
+                    q, k = q * mscale, k * mscale
+            q, k, vv = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+            if qk_norm:
+                q, k = eager_qknorm(q), eager_qknorm(k)
+            return F.scaled_dot_product_attention(q, k, vv, attn_mask=None, is_causal=True,
+                                                  scale=1.0 / (q.shape[-1] ** 0.5)).transpose(1, 2)
+        return run
+
+    def eager_alibi(slopes, qk_norm=True):
+        # src/model/alibi.py:86-109,137-160: S x S bias and scores in memory, explicit softmax
+        def run(q, k, v, q_r, k_r):
+            q, k, vv = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+            if qk_norm:
+                q, k = eager_qknorm(q), eager_qknorm(k)
+            Sv = q.shape[2]
+            pos = torch.arange(Sv, device=q.device)
+            rel = (pos.unsqueeze(0) - pos.unsqueeze(1)).abs().float()
+            bias = -slopes.view(1, -1, 1, 1) * rel.view(1, 1, Sv, Sv)
+            scores = torch.matmul(q, k.transpose(-2, -1)) * (q.shape[-1] ** -0.5) + bias.to(q.dtype)
+            mask = torch.triu(torch.ones(Sv, Sv, dtype=torch.bool, device=q.device), diagonal=1)
+            scores = scores.masked_fill(mask, float("-inf"))
+            return torch.matmul(torch.softmax(scores, dim=-1), vv).transpose(1, 2)
+        return run
+
+    def eager_pope(freqs, delta):
+        # src/model/fpope.py:266-338 + src/model/fpope_attention.py:145-177 under bf16 autocast:
+        # fp32 transform, cat with the content halves, operands cast to bf16 for SDPA
+        def run(q, k, v, q_r, k_r):
+            Sv = q_r.shape[1]
+            pos = torch.arange(Sv, dtype=torch.float32, device=q_r.device)
+            ph_q = (pos[:, None] * freqs[None, :]).view(1, Sv, 1, -1)
+            ph_k = (pos[:, None] * freqs[None, :] + delta.clamp(-2 * math.pi, 0.0)[None, :]).view(1, Sv, 1, -1)
+            mu_q, mu_k = F.softplus(q_r.float()), F.softplus(k_r.float())
+            qr = torch.cat([mu_q * ph_q.cos(), mu_q * ph_q.sin()], dim=-1).transpose(1, 2)
+            kr = torch.cat([mu_k * ph_k.cos(), mu_k * ph_k.sin()], dim=-1).transpose(1, 2)
+            dt = v.dtype
+            qq = torch.cat([q.transpose(1, 2), qr], dim=-1).to(dt)
+            kk = torch.cat([k.transpose(1, 2), kr], dim=-1).to(dt)
+            return F.scaled_dot_product_attention(qq, kk, v.transpose(1, 2), attn_mask=None, dropout_p=0.0,
+                                                  is_causal=True, scale=qq.shape[-1] ** -0.5).transpose(1, 2)
+        return run
 
     bf, f32 = torch.bfloat16, torch.float32
     with torch.no_grad():
         # configuration 1: PoPE, fp32 (FFMA kernel: no tensor-core roofline applies)
         pope = PE.PoPEEmbedding(dim=32, max_seq_len=512).to(dev)
         pope.phase_bias.uniform_(-math.pi, math.pi)
-        add("pope (configuration 1)", 1, 8, 512, 64, 32, 64, f32, "pope", scale=128 ** -0.5, **pope.kernel_args())
+        add("pope (configuration 1)", 1, 8, 512, 64, 32, 64, f32, "pope", scale=128 ** -0.5,
+            eager=eager_pope(pope.effective_freqs.float(), pope.phase_bias.float()), **pope.kernel_args())
         # configuration 2: RoPE / NTK (scale 4) / YaRN (scale 4), plus NoPE and ALiBi at the same shape
         for name, rope in (("rope (configuration 2)", PE.RotaryEmbedding(64, 2048, 10000.0)),
                            ("rope-ntk (configuration 2)", PE.NTKAwareRotaryEmbedding(64, 2048, 10000.0, 4.0)),
                            ("rope-yarn", PE.YaRNRotaryEmbedding(64, 2048, 10000.0, 4.0, original_max_seq_len=512))):
             rope = rope.to(dev)
-            add(name, 8, 12, 2048, 64, 0, 64, bf, "rotary", rotary_table=rope.freqs_cis,
-                mscale=float(getattr(rope, "mscale", 1.0)))
-        add("rope + QKNorm", 8, 12, 2048, 64, 0, 64, bf, "rotary", qk_norm=True,
-            rotary_table=PE.RotaryEmbedding(64, 2048, 10000.0).to(dev).freqs_cis)
-        add("nope", 8, 12, 2048, 64, 0, 64, bf, "nope")
-        add("alibi + QKNorm", 8, 12, 2048, 64, 0, 64, bf, "alibi", qk_norm=True, alibi_slopes=PE.alibi_slopes(12).to(dev))
+            ms_ = float(getattr(rope, "mscale", 1.0))
+            add(name, 8, 12, 2048, 64, 0, 64, bf, "rotary", rotary_table=rope.freqs_cis, mscale=ms_,
+                eager=eager_rotary(rope.freqs_cis, ms_))
+        rope = PE.RotaryEmbedding(64, 2048, 10000.0).to(dev)
+        add("rope + QKNorm", 8, 12, 2048, 64, 0, 64, bf, "rotary", qk_norm=True, rotary_table=rope.freqs_cis,
+            eager=eager_rotary(rope.freqs_cis, qk_norm=True))
+        add("nope", 8, 12, 2048, 64, 0, 64, bf, "nope", eager=eager_rotary())
+        sl = PE.alibi_slopes(12).to(dev)
+        add("alibi + QKNorm", 8, 12, 2048, 64, 0, 64, bf, "alibi", qk_norm=True, alibi_slopes=sl, eager=eager_alibi(sl))
+        # the reference's own training shape (configs/*.yaml: 8 heads, 4 K/V heads, head_dim 64, sequence 512)
+        rope512 = PE.RotaryEmbedding(64, 512, 10000.0).to(dev)
+        add("rope + QKNorm, reference training shape", 64, 8, 512, 64, 0, 64, bf, "rotary", qk_norm=True,
+            rotary_table=rope512.freqs_cis, eager=eager_rotary(rope512.freqs_cis, qk_norm=True))
         # configuration 3: FoPE frequencies driving a rotary table, head_dim 128
         fope = PE.FoPEPoPEEmbedding(dim=64, max_seq_len=4096, num_fourier_terms=16, fourier_sigma=0.3,
                                     training_length=4096)
         ang = torch.outer(torch.arange(4096, dtype=torch.float32), fope.effective_freqs().float().cpu())
-        table = torch.stack((ang.cos(), ang.sin()), dim=-1).to(dev)
-        add("fope-rotary (configuration 3)", 4, 16, 4096, 128, 0, 128, bf, "rotary", rotary_table=table)
+        cis = torch.polar(torch.ones_like(ang), ang).to(dev)
+        add("fope-rotary (configuration 3)", 4, 16, 4096, 128, 0, 128, bf, "rotary", rotary_table=cis,
+            eager=eager_rotary(cis))
         # the reference's own attention shape (head_dim 64, d_rope 32) at a long context
         fp = PE.FoPEPoPEEmbedding(dim=32, max_seq_len=4096, num_fourier_terms=64, fourier_sigma=0.4,
                                   training_length=512, delta_init="uniform").to(dev)
-        add("fope+pope, head_dim 64 / d_rope 32", 8, 8, 4096, 64, 32, 64, bf, "pope", **fp.kernel_args())
+        add("fope+pope, head_dim 64 / d_rope 32", 8, 8, 4096, 64, 32, 64, bf, "pope",
+            eager=eager_pope(fp.effective_freqs().float(), fp.phase_bias.float()), **fp.kernel_args())
         # configuration 4
         fp4 = PE.FoPEPoPEEmbedding(dim=64, max_seq_len=S, num_fourier_terms=N_FOURIER, fourier_sigma=SIGMA,
                                    training_length=S, delta_init="uniform").to(dev)
-        add("fope+pope (configuration 4)", B, H, S, D_C, D_R, D_V, bf, "pope", **fp4.kernel_args())
+        add("fope+pope (configuration 4)", B, H, S, D_C, D_R, D_V, bf, "pope",
+            eager=eager_pope(fp4.effective_freqs().float(), fp4.phase_bias.float()), **fp4.kernel_args())
     P.check_device_status()
     return {"metric": "fused PE-attention forward TFLOP/s per variant", "unit": "TFLOP/s", "n_gpus": 1,
             "steps": args.steps, "warmup": max(args.warmup, 3), "higher_is_better": True, "data": "synthetic",
             "config": {"workload": "every variant at its benchmark configuration, one launch per step",
                        "l2": "flushed between steps by writing a 256 MiB buffer",
                        "flops_convention": "B*H*S^2*(d_qk+d_v), causal"},
-            "peak": peak, "peak_source": peak_src, "variants": rows}
+            "peak": peak, "peak_source": peak_src, "variants": rows,
+            "gpu_eager": "the reference's live GPU data flow on the same tensors and GPU: ATen positional ops "
+                         "(fp32 rotation / softplus-cos-sin expansion, QKNorm, cat, transposes) + "
+                         "F.scaled_dot_product_attention(is_causal=True), or the explicit S x S scores for ALiBi"}
 
 
 def main():
@@ -624,6 +800,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-eval", action="store_true", help="skip the 1B-shape 16k perplexity evaluation")
+    ap.add_argument("--no-secondary", action="store_true",
+                    help="skip the compact variants / decode / training summaries of the default line (1 GPU)")
     ap.add_argument("--eval-sequences", type=int, default=64)
     ap.add_argument("--eval-graph", action="store_true",
                     help="replay the evaluation forward from a CUDA graph (measured: no gain, the eager path is "

@@ -11,8 +11,7 @@ import ctypes as C
 import os
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-# PE_ATTN_LIB points at another build of the same library (development builds)
-LIB_PATH = os.environ.get("PE_ATTN_LIB") or os.path.join(PKG_DIR, "libpe_attn.so")
+LIB_PATH = os.path.join(PKG_DIR, "libpe_attn.so")
 
 # enums (include/pe_attn.h)
 NOPE, ROTARY, ALIBI, POPE = 0, 1, 2, 3
