@@ -229,7 +229,8 @@ const char* pe_attn_kernel_name(const pe_attn_args* args) {
   if (args->dtype != PE_ATTN_BF16 || (args->flags & PE_ATTN_SIMT_CHECK)) return "ffma";
   KParams k;
   validate(args, &k);
-  return (tc2_supports(k) && k.Sq > 256 && !(k.flags & PE_ATTN_SINGLE_CTA)) ? "tcgen05-pair" : "tcgen05";
+  if (tc2_supports(k) && k.Sq > 256 && !(k.flags & PE_ATTN_SINGLE_CTA)) return "tcgen05-pair";
+  return (tc4_supports(k) && !(k.flags & PE_ATTN_SINGLE_CTA)) ? "tcgen05-four-tile" : "tcgen05";
 }
 
 double pe_attn_flops(const pe_attn_args* a) {

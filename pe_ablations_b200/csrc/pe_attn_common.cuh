@@ -101,6 +101,8 @@ int launch_tc(const KParams& p, cudaStream_t stream);
 bool tc_supports(const KParams& p);
 int launch_tc2(const KParams& p, cudaStream_t stream);  // CTA-pair (cta_group::2) variant, d_v = 128
 bool tc2_supports(const KParams& p);
+int launch_tc4(const KParams& p, cudaStream_t stream);  // four query tiles per CTA, d_v = 64
+bool tc4_supports(const KParams& p);
 int launch_ce(const void* logits, int dtype, long long row_stride, const long long* targets, int n_rows, int vocab,
               int ignore_index, float* row_loss, unsigned int* counter, double* out, cudaStream_t stream);
 

@@ -662,6 +662,8 @@ bool tc_supports(const KParams& p) {
 int launch_tc(const KParams& p, cudaStream_t stream) {
   // long sequences at d_v = 128 go to the CTA-pair kernel (two CTAs share every K/V tile)
   if (tc2_supports(p) && p.Sq > 256 && !(p.flags & PE_ATTN_SINGLE_CTA)) return launch_tc2(p, stream);
+  // head_dim 64: four query tiles per CTA once there are enough query rows to fill them
+  if (tc4_supports(p) && !(p.flags & PE_ATTN_SINGLE_CTA)) return launch_tc4(p, stream);
   if (p.variant == PE_ATTN_POPE) {
     if (p.d_c == 64 && p.d_r == 32) return launch_instance<64, 32, 64, MODE_POPE, false>(p, stream);
     if (p.d_c == 128 && p.d_r == 64) return launch_instance<128, 64, 128, MODE_POPE, false>(p, stream);

@@ -148,7 +148,7 @@ __device__ __forceinline__ void xform_load_next(const KParams& p, XformRegs<DC>&
   c.row += slab_stride_rows;
 }
 
-template <int DC>
+template <int DC, int GROUP = 4>   // GROUP: rows (passes) in flight at a time, bounds the live registers
 __device__ __forceinline__ void xform_finish(const KParams& p, XformRegs<DC>& x, uint32_t base, uint32_t chunk_stride,
                                              int row0, int n_rows, int tg) {
   // Rotation, mscale and normalisation in fp32 with the packed fp32x2 FMA / MUL of sm_100 (a
@@ -160,8 +160,7 @@ __device__ __forceinline__ void xform_finish(const KParams& p, XformRegs<DC>& x,
   const bool rotary = p.variant == PE_ATTN_ROTARY;
   const bool norm = (p.flags & PE_ATTN_QK_NORM) != 0;
   const float2 ms2 = make_float2(p.mscale, p.mscale);
-  constexpr int GROUP = 4;   // rows (passes) in flight at a time: bounds the live registers
-  static_assert(X::PASSES % GROUP == 0, "passes per slab must be a multiple of 4");
+  static_assert(X::PASSES % GROUP == 0, "passes per slab must be a multiple of the group size");
 #pragma unroll
   for (int k0 = 0; k0 < X::PASSES; k0 += GROUP) {
     float2 v[GROUP][4];

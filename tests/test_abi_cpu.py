@@ -59,7 +59,10 @@ def test_struct_layout_matches_and_valid_args_pass(L):
     assert L.lib.pe_attn_kernel_name(C.byref(a)) == b"tcgen05-pair"
     assert L.lib.pe_attn_kernel_name(C.byref(_valid_args(L, flags=L.SINGLE_CTA))) == b"tcgen05"
     assert L.lib.pe_attn_kernel_name(C.byref(_valid_args(L, Sq=200, Sk=200))) == b"tcgen05"
-    assert L.lib.pe_attn_kernel_name(C.byref(_valid_args(L, d_c=64, d_r=32, d_v=64))) == b"tcgen05"
+    assert L.lib.pe_attn_kernel_name(C.byref(_valid_args(L, d_c=64, d_r=32, d_v=64))) == b"tcgen05-four-tile"
+    assert L.lib.pe_attn_kernel_name(C.byref(_valid_args(L, d_c=64, d_r=32, d_v=64, flags=L.SINGLE_CTA))) == b"tcgen05"
+    # too few query rows to fill four tiles: the two-tile kernel keeps the call
+    assert L.lib.pe_attn_kernel_name(C.byref(_valid_args(L, d_c=64, d_r=32, d_v=64, Sq=200, Sk=200))) == b"tcgen05"
     a = _valid_args(L, dtype=L.FP32)
     assert L.lib.pe_attn_kernel_name(C.byref(a)) == b"ffma"
     fl = L.lib.pe_attn_flops(C.byref(a))
