@@ -9,8 +9,12 @@
 // One CTA owns 64 query rows of one (batch, head) and streams 64-key tiles:
 //   load + transform K tile -> S = Q K^T (4x4 per thread) -> online softmax with
 //   16-lane shuffle reductions -> P to shared memory -> O += P V.
-// Shared memory: Q operand [64][d_qk+1], K operand [64][d_qk+1], V [64][d_v],
-// P [64][65], per-dimension frequency / phase-bias vectors.
+// Shared memory: Q and K operands [64][d_qk rounded up to 4, + 4], V [64][d_v rounded up to 4],
+// P [64][68], per-dimension frequency / phase-bias vectors.  The row pitches are multiples of
+// four floats, so both products read their operands with 16-byte shared-memory loads (four
+// steps of the contraction per load; the pitch / 4 is odd at the usual head dims, which keeps
+// the 16 rows of a half-warp on different banks); padded columns hold zeros.  The additions
+// of every dot product still happen in ascending order of the contraction index.
 #include "pe_attn_common.cuh"
 
 namespace pe_attn {
@@ -20,6 +24,9 @@ constexpr int BM = 64;
 constexpr int BN = 64;
 constexpr int NTHREADS = 256;
 constexpr int MAX_VC = 8;  // d_v <= 128: up to 8 output columns per thread (stride 16)
+constexpr int P_LD = BN + 4;
+
+__host__ __device__ constexpr int round4(int x) { return (x + 3) & ~3; }
 
 template <typename T>
 __device__ __forceinline__ float load_elem(const void* base, long long off) {
@@ -44,6 +51,8 @@ __device__ void build_operand_tile(const KParams& p, float* dst, int ld, const T
                                    bool is_key, const float* freq_s, const float* delta_s) {
   const int tid = threadIdx.x;
   const int d_c = p.d_c, d_r = p.d_r;
+  const int n_pad = ld - p.d_qk;   // zero columns behind the operand (at least 4)
+  for (int idx = tid; idx < BM * n_pad; idx += NTHREADS) dst[(idx / n_pad) * ld + p.d_qk + idx % n_pad] = 0.f;
   if (p.variant == PE_ATTN_ROTARY) {
     const int half = d_c >> 1;
     for (int idx = tid; idx < BM * half; idx += NTHREADS) {
@@ -70,35 +79,57 @@ __device__ void build_operand_tile(const KParams& p, float* dst, int ld, const T
       dst[r * ld + 2 * i + 1] = o1;
     }
   } else {
-    for (int idx = tid; idx < BM * d_c; idx += NTHREADS) {
-      const int r = idx / d_c, c = idx - r * d_c;
-      const int row = row0 + r;
-      float x = 0.f;
-      if (row < n_rows) {
-        const long long off = (long long)b * content.sb + (long long)head * content.sh + (long long)row * content.ss;
-        x = load_elem<T>(content.ptr, off + c);
+    // four independent loads in flight per thread before the first store: one at a time, each
+    // load's latency would be paid in full (the stores to ``dst`` cannot be moved past them)
+    const long long base = (long long)b * content.sb + (long long)head * content.sh;
+    for (int idx0 = tid; idx0 < BM * d_c; idx0 += 4 * NTHREADS) {
+      float x[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = idx0 + u * NTHREADS;
+        const int r = idx / d_c, c = idx - r * d_c;
+        x[u] = (idx < BM * d_c && row0 + r < n_rows) ? load_elem<T>(content.ptr, base + (long long)(row0 + r) * content.ss + c)
+                                                     : 0.f;
       }
-      dst[r * ld + c] = x;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = idx0 + u * NTHREADS;
+        const int r = idx / d_c, c = idx - r * d_c;
+        if (idx < BM * d_c) dst[r * ld + c] = x[u];
+      }
     }
   }
   if (p.variant == PE_ATTN_POPE) {
-    for (int idx = tid; idx < BM * d_r; idx += NTHREADS) {
-      const int r = idx / d_r, c = idx - r * d_r;
-      const int row = row0 + r;
-      float oc = 0.f, os = 0.f;
-      if (row < n_rows) {
-        const long long off = (long long)b * posi.sb + (long long)head * posi.sh + (long long)row * posi.ss;
-        const float x = load_elem<T>(posi.ptr, off + c);
-        const float mu = softplus_accurate(x);
-        // phase = fl(fl(pos * freq) + delta): product and sum rounded separately, as the
-        // reference's tensor ops do
-        float phase = __fmul_rn((float)(pos0 + row), freq_s[c]);
-        if (is_key) phase = __fadd_rn(phase, delta_s[c]);
-        oc = round_op<ROUND>(__fmul_rn(mu, cosf(phase)));
-        os = round_op<ROUND>(__fmul_rn(mu, sinf(phase)));
+    const long long base = (long long)b * posi.sb + (long long)head * posi.sh;
+    for (int idx0 = tid; idx0 < BM * d_r; idx0 += 4 * NTHREADS) {
+      float xin[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = idx0 + u * NTHREADS;
+        const int r = idx / d_r, c = idx - r * d_r;
+        xin[u] = (idx < BM * d_r && row0 + r < n_rows) ? load_elem<T>(posi.ptr, base + (long long)(row0 + r) * posi.ss + c) : 0.f;
       }
-      dst[r * ld + d_c + c] = oc;
-      dst[r * ld + d_c + d_r + c] = os;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = idx0 + u * NTHREADS;
+        if (idx >= BM * d_r) break;
+        const int r = idx / d_r, c = idx - r * d_r;
+        const int row = row0 + r;
+        float oc = 0.f, os = 0.f;
+        if (row < n_rows) {
+          const float mu = softplus_accurate(xin[u]);
+          // phase = fl(fl(pos * freq) + delta): product and sum rounded separately, as the
+          // reference's tensor ops do
+          float phase = __fmul_rn((float)(pos0 + row), freq_s[c]);
+          if (is_key) phase = __fadd_rn(phase, delta_s[c]);
+          float sn, cs;
+          sincosf(phase, &sn, &cs);   // the accurate pair: one argument reduction for both
+          oc = round_op<ROUND>(__fmul_rn(mu, cs));
+          os = round_op<ROUND>(__fmul_rn(mu, sn));
+        }
+        dst[r * ld + d_c + c] = oc;
+        dst[r * ld + d_c + d_r + c] = os;
+      }
     }
   }
   if (p.flags & PE_ATTN_QK_NORM) {
@@ -126,16 +157,17 @@ __device__ __forceinline__ void store_elem<__nv_bfloat16>(void* base, long long 
   reinterpret_cast<__nv_bfloat16*>(base)[off] = __float2bfloat16_rn(x);
 }
 
-template <typename T, bool ROUND>
+// VC: output columns per thread (stride 16), the smallest of 2, 4, 8 with 16 VC >= d_v
+template <typename T, bool ROUND, int VC>
 __global__ void __launch_bounds__(NTHREADS) pe_attn_simt_kernel(const KParams p) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   const int dqk = p.d_qk, dv = p.d_v;
-  const int ld = dqk + 1;
+  const int dqk4 = round4(dqk), ld = dqk4 + 4, dvs = round4(dv);
   float* Qs = smem;
   float* Ks = Qs + BM * ld;
   float* Vs = Ks + BN * ld;
-  float* Ps = Vs + BN * dv;
-  float* freq_s = Ps + BM * (BN + 1);
+  float* Ps = Vs + BN * dvs;
+  float* freq_s = Ps + BM * P_LD;
   float* delta_s = freq_s + (p.d_r > 0 ? p.d_r : 1);
 
   const int tid = threadIdx.x;
@@ -155,13 +187,13 @@ __global__ void __launch_bounds__(NTHREADS) pe_attn_simt_kernel(const KParams p)
   }
   build_operand_tile<T, ROUND>(p, Qs, ld, p.q, p.qr, b, h, m0, p.Sq, p.q_pos0, false, freq_s, delta_s);
 
-  float m_run[4], l_run[4], o_acc[4][MAX_VC];
+  float m_run[4], l_run[4], o_acc[4][VC];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     m_run[i] = -INFINITY;
     l_run[i] = 0.f;
 #pragma unroll
-    for (int c = 0; c < MAX_VC; ++c) o_acc[i][c] = 0.f;
+    for (int c = 0; c < VC; ++c) o_acc[i][c] = 0.f;
   }
   const float slope = (p.variant == PE_ATTN_ALIBI) ? p.slopes[h] : 0.f;
 
@@ -170,12 +202,23 @@ __global__ void __launch_bounds__(NTHREADS) pe_attn_simt_kernel(const KParams p)
   for (int n0 = 0; n0 < k_end; n0 += BN) {
     __syncthreads();  // previous tile's reads of Ks / Vs / Ps are done (and Qs is complete)
     build_operand_tile<T, ROUND>(p, Ks, ld, p.k, p.kr, b, hk, n0, p.Sk, p.k_pos0, true, freq_s, delta_s);
-    for (int idx = tid; idx < BN * dv; idx += NTHREADS) {
-      const int r = idx / dv, c = idx - r * dv;
-      const int row = n0 + r;
-      float x = 0.f;
-      if (row < p.Sk) x = load_elem<T>(p.v.ptr, (long long)b * p.v.sb + (long long)hk * p.v.sh + (long long)row * p.v.ss + c);
-      Vs[r * dv + c] = x;
+    {
+      const long long vbase = (long long)b * p.v.sb + (long long)hk * p.v.sh;
+      for (int idx0 = tid; idx0 < BN * dv; idx0 += 4 * NTHREADS) {
+        float x[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int idx = idx0 + u * NTHREADS;
+          const int r = idx / dv, c = idx - r * dv;
+          x[u] = (idx < BN * dv && n0 + r < p.Sk) ? load_elem<T>(p.v.ptr, vbase + (long long)(n0 + r) * p.v.ss + c) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int idx = idx0 + u * NTHREADS;
+          const int r = idx / dv, c = idx - r * dv;
+          if (idx < BN * dv) Vs[r * dvs + c] = x[u];
+        }
+      }
     }
     __syncthreads();
 
@@ -184,16 +227,23 @@ __global__ void __launch_bounds__(NTHREADS) pe_attn_simt_kernel(const KParams p)
     for (int i = 0; i < 4; ++i)
 #pragma unroll
       for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
-    for (int kk = 0; kk < dqk; ++kk) {
-      float a[4], bb[4];
+    for (int kk = 0; kk < dqk4; kk += 4) {
+      float4 a[4], bb[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) a[i] = Qs[(ty + 16 * i) * ld + kk];
+      for (int i = 0; i < 4; ++i) a[i] = *reinterpret_cast<const float4*>(&Qs[(ty + 16 * i) * ld + kk]);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) bb[j] = Ks[(tx + 16 * j) * ld + kk];
+      for (int j = 0; j < 4; ++j) bb[j] = *reinterpret_cast<const float4*>(&Ks[(tx + 16 * j) * ld + kk]);
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) s[i][j] = fmaf(a[i], bb[j], s[i][j]);
+        for (int j = 0; j < 4; ++j) {
+          float acc = s[i][j];
+          acc = fmaf(a[i].x, bb[j].x, acc);
+          acc = fmaf(a[i].y, bb[j].y, acc);
+          acc = fmaf(a[i].z, bb[j].z, acc);
+          acc = fmaf(a[i].w, bb[j].w, acc);
+          s[i][j] = acc;
+        }
     }
 
 #pragma unroll
@@ -219,30 +269,36 @@ __global__ void __launch_bounds__(NTHREADS) pe_attn_simt_kernel(const KParams p)
       for (int j = 0; j < 4; ++j) {
         const float pj = (m_new == -INFINITY) ? 0.f : expf(s[i][j] - m_new);
         psum += pj;
-        Ps[(ty + 16 * i) * (BN + 1) + tx + 16 * j] = pj;
+        Ps[(ty + 16 * i) * P_LD + tx + 16 * j] = pj;
       }
 #pragma unroll
       for (int d = 1; d < 16; d <<= 1) psum += __shfl_xor_sync(0xffffffffu, psum, d);
       l_run[i] = l_run[i] * alpha + psum;
       m_run[i] = m_new;
 #pragma unroll
-      for (int c = 0; c < MAX_VC; ++c) o_acc[i][c] *= alpha;
+      for (int c = 0; c < VC; ++c) o_acc[i][c] *= alpha;
     }
     __syncthreads();
 
-    for (int j = 0; j < BN; ++j) {
-      float a[4], vv[MAX_VC];
+    for (int j = 0; j < BN; j += 4) {
+      float4 a[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) a[i] = Ps[(ty + 16 * i) * (BN + 1) + j];
+      for (int i = 0; i < 4; ++i) a[i] = *reinterpret_cast<const float4*>(&Ps[(ty + 16 * i) * P_LD + j]);
 #pragma unroll
-      for (int c = 0; c < MAX_VC; ++c) {
-        const int col = tx + 16 * c;
-        vv[c] = col < dv ? Vs[j * dv + col] : 0.f;
+      for (int jj = 0; jj < 4; ++jj) {
+        float vv[VC];
+#pragma unroll
+        for (int c = 0; c < VC; ++c) {
+          const int col = tx + 16 * c;
+          vv[c] = col < dv ? Vs[(j + jj) * dvs + col] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float pij = jj == 0 ? a[i].x : jj == 1 ? a[i].y : jj == 2 ? a[i].z : a[i].w;
+#pragma unroll
+          for (int c = 0; c < VC; ++c) o_acc[i][c] = fmaf(pij, vv[c], o_acc[i][c]);
+        }
       }
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int c = 0; c < MAX_VC; ++c) o_acc[i][c] = fmaf(a[i], vv[c], o_acc[i][c]);
     }
   }
 
@@ -254,7 +310,7 @@ __global__ void __launch_bounds__(NTHREADS) pe_attn_simt_kernel(const KParams p)
     if (p.lse != nullptr && tx == 0) p.lse[((long long)b * p.H + h) * p.Sq + row] = m_run[i] + logf(l_run[i]);
     const long long off = (long long)b * p.out.sb + (long long)h * p.out.sh + (long long)row * p.out.ss;
 #pragma unroll
-    for (int c = 0; c < MAX_VC; ++c) {
+    for (int c = 0; c < VC; ++c) {
       const int col = tx + 16 * c;
       if (col < dv) store_elem<T>(const_cast<void*>(p.out.ptr), off + col, o_acc[i][c] * inv);
     }
@@ -264,30 +320,33 @@ __global__ void __launch_bounds__(NTHREADS) pe_attn_simt_kernel(const KParams p)
 }  // namespace
 
 size_t simt_smem_bytes(const KParams& p) {
-  const size_t ld = p.d_qk + 1;
-  const size_t nfl = 2 * (size_t)BM * ld + (size_t)BN * p.d_v + (size_t)BM * (BN + 1) + 2 * (size_t)(p.d_r > 0 ? p.d_r : 1);
+  const size_t ld = round4(p.d_qk) + 4;
+  const size_t nfl = 2 * (size_t)BM * ld + (size_t)BN * round4(p.d_v) + (size_t)BM * P_LD + 2 * (size_t)(p.d_r > 0 ? p.d_r : 1);
   return nfl * sizeof(float);
 }
 
+namespace {
+template <typename T, bool ROUND, int VC>
+cudaError_t launch_simt_instance(const KParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
+  auto kern = pe_attn_simt_kernel<T, ROUND, VC>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  kern<<<grid, dim3(NTHREADS), smem, stream>>>(p);
+  return cudaGetLastError();
+}
+template <typename T, bool ROUND>
+cudaError_t launch_simt_dv(const KParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
+  if (p.d_v <= 32) return launch_simt_instance<T, ROUND, 2>(p, grid, smem, stream);
+  if (p.d_v <= 64) return launch_simt_instance<T, ROUND, 4>(p, grid, smem, stream);
+  return launch_simt_instance<T, ROUND, MAX_VC>(p, grid, smem, stream);
+}
+}  // namespace
+
 int launch_simt(const KParams& p, int dtype, cudaStream_t stream) {
   const size_t smem = simt_smem_bytes(p);
-  dim3 grid((p.Sq + BM - 1) / BM, p.H, p.B), block(NTHREADS);
-  cudaError_t e;
-  if (dtype == PE_ATTN_FP32) {
-    auto kern = pe_attn_simt_kernel<float, false>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) {
-      kern<<<grid, block, smem, stream>>>(p);
-      e = cudaGetLastError();
-    }
-  } else {
-    auto kern = pe_attn_simt_kernel<__nv_bfloat16, true>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) {
-      kern<<<grid, block, smem, stream>>>(p);
-      e = cudaGetLastError();
-    }
-  }
+  dim3 grid((p.Sq + BM - 1) / BM, p.H, p.B);
+  const cudaError_t e = dtype == PE_ATTN_FP32 ? launch_simt_dv<float, false>(p, grid, smem, stream)
+                                              : launch_simt_dv<__nv_bfloat16, true>(p, grid, smem, stream);
   if (e != cudaSuccess) {
     set_error("ffma kernel launch failed: %s", cudaGetErrorString(e));
     return PE_ATTN_ERR_LAUNCH;

@@ -157,10 +157,11 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
   const uint32_t k_smem = smem_base + C::K_OFF;
   const uint32_t v_smem = smem_base + C::V_OFF;
 
-  // Register budget per warpgroup (40 / 160 / 160 / 152 x 128 threads = 64 K registers); each
-  // role sits inside the branch that sets its budget.
+  // Register budget per warpgroup (24 / 160 / 160 / 168 x 128 threads = 64 K registers: the K
+  // transform at d_r = 64 keeps 64 table values per thread and spilled at 152); each role sits
+  // inside the branch that sets its budget.
   if (warp < 4) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 24;");
   if (!run) {
     // nothing to do
   } else if (warp == 0) {
@@ -470,7 +471,7 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
     }
   }
   } else {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
   if (run) {
     // ===================== positional transform of this CTA's 64 keys of every K tile ===========
     const int tg = tid - 384;
