@@ -49,7 +49,7 @@
 extern "C" {
 #endif
 
-#define PE_ATTN_ABI_VERSION 2
+#define PE_ATTN_ABI_VERSION 3
 
 typedef enum pe_attn_variant {
   PE_ATTN_NOPE = 0,   /* no positional transform                                            */
@@ -134,6 +134,8 @@ typedef struct pe_attn_args {
                               /* of each query row's scaled, biased, masked logits -- what    */
                               /* pe_attn_backward needs to rebuild the probabilities.  May    */
                               /* be null.                                                    */
+  void* workspace;            /* optional device scratch for pe_attn_forward (16-byte         */
+  uint64_t workspace_bytes;   /* aligned), see pe_attn_forward_workspace_bytes; may be null   */
 } pe_attn_args;
 
 /* ABI version of the loaded library (PE_ATTN_ABI_VERSION at build time). */
@@ -142,6 +144,14 @@ int pe_attn_version(void);
 /* Validate ``args`` and enqueue the forward on ``stream`` (a cudaStream_t; null = default
  * stream) of the current device.  Replaces the reference code listed at the top. */
 int pe_attn_forward(const pe_attn_args* args, void* stream);
+
+/* Scratch that pe_attn_forward can use for ``args`` (0 for most calls).  A causal launch with
+ * few (batch, head) problems cannot fill the GPU evenly: its longest query blocks decide the run
+ * time.  Given this much workspace the CTA-pair kernel cuts those blocks in two along the keys
+ * and merges the halves (bit-level results differ from the unsplit kernel by fp32 rounding of
+ * the merge; both are within the tolerances).  Without it the call runs unsplit.  The
+ * workspace is only used during the call's own kernels (stream-ordered). */
+size_t pe_attn_forward_workspace_bytes(const pe_attn_args* args);
 
 /* Validate only: same checks and return codes as pe_attn_forward, touches no GPU. */
 int pe_attn_validate(const pe_attn_args* args);

@@ -30,7 +30,7 @@ EXPORTS = (
     "pe_rmsnorm_forward", "pe_swiglu_forward", "pe_attn_selftest_wait_expiry", "pe_attn_backward",
     "pe_pope_expand", "pe_pope_expand_backward", "pe_rotary_norm_expand", "pe_rotary_norm_expand_backward",
     "pe_fope_effective_freqs", "pe_fope_effective_freqs_backward",
-    "pe_attn_decode_workspace_bytes", "pe_attn_decode",
+    "pe_attn_decode_workspace_bytes", "pe_attn_decode", "pe_attn_forward_workspace_bytes",
 )
 
 
@@ -50,6 +50,7 @@ class PeAttnArgs(C.Structure):
         ("alibi_slopes", C.c_void_p), ("freqs", C.c_void_p), ("delta", C.c_void_p),
         ("fourier_coeffs", C.c_void_p), ("n_fourier", C.c_int32), ("floor_freq", C.c_float),
         ("ceil_freq", C.c_float), ("device_status", C.c_void_p), ("lse", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64),
     ]
 
 
@@ -81,6 +82,8 @@ def _load() -> C.CDLL:
     lib.pe_attn_version.restype = C.c_int
     lib.pe_attn_forward.restype = C.c_int
     lib.pe_attn_forward.argtypes = [C.POINTER(PeAttnArgs), C.c_void_p]
+    lib.pe_attn_forward_workspace_bytes.restype = C.c_size_t
+    lib.pe_attn_forward_workspace_bytes.argtypes = [C.POINTER(PeAttnArgs)]
     lib.pe_attn_decode_workspace_bytes.restype = C.c_size_t
     lib.pe_attn_decode_workspace_bytes.argtypes = [C.POINTER(PeAttnArgs)]
     lib.pe_attn_decode.restype = C.c_int

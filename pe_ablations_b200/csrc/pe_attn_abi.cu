@@ -103,6 +103,9 @@ static int validate(const pe_attn_args* a, KParams* out) {
   k.floor_freq = a->floor_freq; k.ceil_freq = a->ceil_freq;
   k.status = a->device_status;
   k.lse = a->lse;
+  k.workspace = static_cast<float*>(a->workspace);
+  k.workspace_bytes = a->workspace != nullptr ? (size_t)a->workspace_bytes : 0;
+  if (a->workspace != nullptr && !aligned16(a->workspace)) return fail(PE_ATTN_ERR_ALIGNMENT, "workspace is not 16-byte aligned");
 
   const bool use_tc = a->dtype == PE_ATTN_BF16 && !(a->flags & PE_ATTN_SIMT_CHECK);
   if (use_tc) {
@@ -231,6 +234,13 @@ const char* pe_attn_kernel_name(const pe_attn_args* args) {
   validate(args, &k);
   if (tc2_supports(k) && k.Sq > 256 && !(k.flags & PE_ATTN_SINGLE_CTA)) return "tcgen05-pair";
   return (tc4_supports(k) && !(k.flags & PE_ATTN_SINGLE_CTA)) ? "tcgen05-four-tile" : "tcgen05";
+}
+
+size_t pe_attn_forward_workspace_bytes(const pe_attn_args* args) {
+  KParams k;
+  if (validate(args, &k) != PE_ATTN_OK) return 0;
+  if (args->dtype != PE_ATTN_BF16 || (args->flags & (PE_ATTN_SIMT_CHECK | PE_ATTN_SINGLE_CTA))) return 0;
+  return (tc2_supports(k) && k.Sq > 256) ? tc2_workspace_bytes(k) : 0;
 }
 
 double pe_attn_flops(const pe_attn_args* a) {

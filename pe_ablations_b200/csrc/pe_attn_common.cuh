@@ -39,6 +39,8 @@ struct KParams {
   float floor_freq, ceil_freq;
   int* status;
   float* lse;  // optional [B, H, Sq] logsumexp output
+  float* workspace;        // optional scratch of the forward (pe_attn_forward_workspace_bytes)
+  size_t workspace_bytes;
 };
 
 // Device-side arguments of the attention backward (operands already transformed).
@@ -101,6 +103,7 @@ int launch_tc(const KParams& p, cudaStream_t stream);
 bool tc_supports(const KParams& p);
 int launch_tc2(const KParams& p, cudaStream_t stream);  // CTA-pair (cta_group::2) variant, d_v = 128
 bool tc2_supports(const KParams& p);
+size_t tc2_workspace_bytes(const KParams& p);
 int launch_tc4(const KParams& p, cudaStream_t stream);  // four query tiles per CTA, d_v = 64
 bool tc4_supports(const KParams& p);
 int launch_ce(const void* logits, int dtype, long long row_stride, const long long* targets, int n_rows, int vocab,

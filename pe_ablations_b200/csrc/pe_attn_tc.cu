@@ -378,9 +378,11 @@ pe_attn_tc_kernel(const KParams p, const int bh_group, const __grid_constant__ C
         }
         const bool need_mask = (key0 + BLOCK_N - 1 > m0 + i * BLOCK_M + p.causal_off) || (key0 + BLOCK_N > p.Sk);
         if (need_mask) {
+          // columns past the row's last visible key (causal limit, end of the keys): one compare each
+          const int last = (row_lim < p.Sk - 1 ? row_lim : p.Sk - 1) - key0;
 #pragma unroll
           for (int c = 0; c < 64; ++c)
-            if (key0 + c > row_lim || key0 + c >= p.Sk) t[c] = -INFINITY;
+            if (c > last) t[c] = -INFINITY;
         }
         float mx0 = fmax3(t[0], t[1], t[2]), mx1 = fmax3(t[3], t[4], t[5]), mx2 = fmax3(t[6], t[7], t[8]),
               mx3 = fmax3(t[9], t[10], t[11]);

@@ -20,9 +20,23 @@
 // Issue order of the leader, per key tile j:  PV_0(j)  QK_0(j+1)  PV_1(j)  QK_1(j+1), so the
 // tensor pipe works on one pair tile while the softmax warps work on the other.
 //
+// Few-wave grids: a pair works through one 512-row block at the pace of its dependency chain,
+// and the longest block of a causal problem needs as many steps as there are key tiles.  When
+// a launch has fewer than about three blocks per pair slot, the longest blocks of every
+// (batch, head) are therefore cut in two along the KEYS: two pairs attend the same rows to the
+// first and the second half of the key tiles, write normalised fp32 partial outputs and
+// logsumexps to a caller-provided workspace, and ``pair_merge_kernel`` combines them.  Work
+// items (parts and whole blocks) are handed out longest first.
+//
 // Every wait is bounded; a CTA that gives up reports through the status word and both CTAs
 // still meet at the final cluster barrier before releasing TMEM.
 #include <cuda.h>
+
+#include <array>
+#include <map>
+#include <mutex>
+#include <queue>
+#include <vector>
 
 #include "pe_attn_tc_common.cuh"
 
@@ -42,6 +56,15 @@ constexpr int KV_STAGES = 2;
 constexpr int NTHREADS = 512;
 constexpr int TMEM_COLS = 512;
 constexpr int TAIL_BYTES = 1024;
+// workspace of one split block: fp32 [2 parts][512 rows][128] partial outputs, then [2][512] logsumexps
+constexpr int SPLIT_ITEM_FLOATS = 2 * PAIR_ROWS * DV + 2 * PAIR_ROWS;
+
+// key tiles the LAST row tile of 512-row block ``sblk`` needs (the block's step count)
+__host__ __device__ __forceinline__ int block_tiles(int sblk, int Sk, int causal_off) {
+  int kend = sblk * PAIR_ROWS + PAIR_ROWS + causal_off;
+  if (kend > Sk) kend = Sk;
+  return (kend + BLOCK_N - 1) / BLOCK_N;
+}
 
 enum : int {
   BAR_QFULL = 0, BAR_KFULL = 2, BAR_KEMPTY = 4, BAR_VFULL = 6, BAR_VEMPTY = 8, BAR_SFULL = 10, BAR_PREADY = 12,
@@ -69,8 +92,9 @@ struct Cfg2 {
 
 template <int DC, int DR, int MODE, bool ALIBI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NTHREADS, 1)
-pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ CUtensorMap tmQ,
-                   const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV) {
+pe_attn_tc2_kernel(const KParams p, const int bh_group, const int n_top, float* const split_ws,
+                   const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV) {
   using C = Cfg2<DC, DR>;
   constexpr bool HAS_TMA_QK = (MODE == MODE_PLAIN) || (MODE == MODE_POPE && DC > 0);
   constexpr bool HAS_XFORM = MODE != MODE_PLAIN;
@@ -89,30 +113,77 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
   const uint32_t rank = cluster_ctarank();          // 0 = leader
   auto lbar = [&](int idx) -> uint32_t { return mapa(bar(idx), 0); };  // the leader's copy of a barrier
 
-  // pair (cluster) index -> (query super-block, batch, head), longest first within head groups
+  // pair (cluster) index -> work item of a (batch, head), longest first within head groups.
+  // Items per (batch, head): the n_top longest blocks as two parts each, the others whole.
   const int n_sblk = (p.Sq + PAIR_ROWS - 1) / PAIR_ROWS;
   const int n_bh = p.B * p.H;
   const int pair = (int)(blockIdx.x >> 1);
-  const int per_group = bh_group * n_sblk;
+  const int per_group = bh_group * (n_sblk + n_top);
   const int grp = pair / per_group, in_grp = pair % per_group;
   const int g_first = grp * bh_group;
   const int g_size = (n_bh - g_first) < bh_group ? (n_bh - g_first) : bh_group;
-  const int sblk = n_sblk - 1 - in_grp / g_size;
+  const int item_rank = in_grp / g_size;   // 0 = the longest item
   const int bh = g_first + in_grp % g_size;
   const int h = bh % p.H, b = bh / p.H;
   const int hk = h / p.groups;
+  int sblk = n_sblk - 1 - item_rank, part = -1;   // part -1: a whole block
+  if (n_top > 0) {
+    // merge of two descending lists (parts of the longest blocks, whole shorter blocks) up to
+    // this item's rank: one thread walks it, everybody reads the answer
+    volatile int* decode_slot = reinterpret_cast<volatile int*>(smem + 264);
+    if (tid == 0) {
+      int ia = 0, ib = n_sblk - n_top - 1, found_blk = 0, found_part = -1;
+      for (int r = 0;; ++r) {
+        int size_a = -1, size_b = -1;
+        if (ia < 2 * n_top) {
+          const int t = block_tiles(n_sblk - 1 - (ia >> 1), p.Sk, p.causal_off);
+          size_a = (ia & 1) ? t - t / 2 : t / 2;
+        }
+        if (ib >= 0) size_b = block_tiles(ib, p.Sk, p.causal_off);
+        const bool take_a = size_a >= size_b;
+        if (r == item_rank) {
+          found_blk = take_a ? n_sblk - 1 - (ia >> 1) : ib;
+          found_part = take_a ? (ia & 1) : -1;
+          break;
+        }
+        if (take_a) ++ia; else --ib;
+      }
+      decode_slot[0] = found_blk;
+      decode_slot[1] = found_part;
+    }
+    __syncthreads();
+    sblk = decode_slot[0];
+    part = decode_slot[1];
+  }
   const int m0 = sblk * PAIR_ROWS;
 
-  // key tiles pair tile i needs: keys [0, min(Sk, last row of the pair tile + 1 + off))
-  int nt[Q_TILES];
+  // key tiles pair tile i needs: keys [0, min(Sk, last row of the pair tile + 1 + off)); a part
+  // of a split block takes the first half of the block's tiles or the rest.  ``jb`` is the
+  // first tile, nt[i] the number of tiles from there on: loops count from 0, the tile they
+  // address is jb + j.
+  int nt[Q_TILES], jb = 0;
+  {
+    const int cut = block_tiles(sblk, p.Sk, p.causal_off) / 2;
+    if (part == 1) jb = cut;
 #pragma unroll
-  for (int i = 0; i < Q_TILES; ++i) {
-    const int first = m0 + i * 2 * BLOCK_M;
-    int kend = first + 2 * BLOCK_M + p.causal_off;
-    if (kend > p.Sk) kend = p.Sk;
-    nt[i] = first < p.Sq ? (kend + BLOCK_N - 1) / BLOCK_N : 0;
+    for (int i = 0; i < Q_TILES; ++i) {
+      const int first = m0 + i * 2 * BLOCK_M;
+      int kend = first + 2 * BLOCK_M + p.causal_off;
+      if (kend > p.Sk) kend = p.Sk;
+      int n = first < p.Sq ? (kend + BLOCK_N - 1) / BLOCK_N : 0;
+      if (part == 0) n = n < cut ? n : cut;
+      if (part == 1) n = n > cut ? n - cut : 0;
+      nt[i] = n;
+    }
   }
   const int n_tiles = nt[1] > nt[0] ? nt[1] : nt[0];
+  // partial results of a part: [512 rows][128] fp32, then the block's logsumexps [2][512]
+  float* const ws_out = part < 0 ? nullptr
+                                 : split_ws + (size_t)(bh * n_top + (n_sblk - 1 - sblk)) * SPLIT_ITEM_FLOATS +
+                                       (size_t)part * PAIR_ROWS * DV;
+  float* const ws_lse = part < 0 ? nullptr
+                                 : split_ws + (size_t)(bh * n_top + (n_sblk - 1 - sblk)) * SPLIT_ITEM_FLOATS +
+                                       (size_t)2 * PAIR_ROWS * DV + (size_t)part * PAIR_ROWS;
 
   auto fail = [&](int code) {
     if (p.status != nullptr) atomicOr(p.status, code);
@@ -194,7 +265,7 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
 #pragma unroll
           for (int c = 0; c < C::NCC; ++c)
             tma_load_4d_pair(k_smem + s * C::K_STAGE_BYTES + c * C::K_CHUNK_BYTES, &tmK, kb, c * 64,
-                             j * BLOCK_N + (int)rank * HALF_N, hk, b);
+                             (jb + j) * BLOCK_N + (int)rank * HALF_N, hk, b);
         }
         __syncwarp();
       }
@@ -210,7 +281,7 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
       if (elect_one()) {
         const uint32_t vb = lbar(BAR_VFULL + s);
         mbar_arrive_expect_tx_cluster(vb, C::V_STAGE_BYTES);
-        tma_load_4d_pair(v_smem + s * C::V_STAGE_BYTES, &tmV, vb, (int)rank * 64, j * BLOCK_N, hk, b);
+        tma_load_4d_pair(v_smem + s * C::V_STAGE_BYTES, &tmV, vb, (int)rank * 64, (jb + j) * BLOCK_N, hk, b);
       }
       __syncwarp();
     }
@@ -347,7 +418,7 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
         ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_SFULL + i), (uint32_t)(j & 1)));
         if (!ok) { fail(ST_WAIT_SFULL); break; }
         tc_fence_after_sync();
-        const int key0 = j * BLOCK_N;
+        const int key0 = (jb + j) * BLOCK_N;
         const bool need_mask = (key0 + BLOCK_N - 1 > row0 + p.causal_off) || (key0 + BLOCK_N > p.Sk);
         float base_bias = 0.f;
         if constexpr (ALIBI) base_bias = slope2 * (float)(key0 - row_lim);
@@ -367,9 +438,11 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
           for (int c = 0; c < BLOCK_N; ++c) t[c] = fmaf(t[c], c2, fmaf((float)c, slope2, base_bias));
         }
         if (need_mask) {
+          // columns past the row's last visible key (causal limit, end of the keys): one compare each
+          const int last = (row_lim < p.Sk - 1 ? row_lim : p.Sk - 1) - key0;
 #pragma unroll
           for (int c = 0; c < BLOCK_N; ++c)
-            if (key0 + c > row_lim || key0 + c >= p.Sk) t[c] = -INFINITY;
+            if (c > last) t[c] = -INFINITY;
         }
         float mx0 = fmax3(t[0], t[1], t[2]), mx1 = fmax3(t[3], t[4], t[5]), mx2 = fmax3(t[6], t[7], t[8]),
               mx3 = fmax3(t[9], t[10], t[11]);
@@ -445,9 +518,11 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
       }
       if (ok) {
         tc_fence_after_sync();
-        const float inv_l = 1.0f / l_sum;
-        if (p.lse != nullptr && row < p.Sq)
-          p.lse[((long long)b * p.H + h) * p.Sq + row] = m_used * kf * 0.6931471805599453f + logf(l_sum);
+        // a part whose keys are all hidden from this row contributes nothing
+        const float inv_l = l_sum > 0.f ? 1.0f / l_sum : 0.f;
+        const float row_lse = l_sum > 0.f ? m_used * kf * 0.6931471805599453f + logf(l_sum) : -INFINITY;
+        if (ws_out != nullptr) ws_lse[row - m0] = row_lse;
+        else if (p.lse != nullptr && row < p.Sq) p.lse[((long long)b * p.H + h) * p.Sq + row] = row_lse;
         char* dst = reinterpret_cast<char*>(const_cast<void*>(p.out.ptr)) +
                     2 * ((long long)b * p.out.sb + (long long)h * p.out.sh + (long long)row * p.out.ss);
 #pragma unroll 1
@@ -455,7 +530,13 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
           uint32_t orow[32];
           tmem_ld32(o_addr + cb * 32, orow);
           tmem_wait_ld();
-          if (row < p.Sq) {
+          if (ws_out != nullptr) {
+            float4* wdst = reinterpret_cast<float4*>(ws_out + (size_t)(row - m0) * DV + cb * 32);
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+              wdst[v] = make_float4(__uint_as_float(orow[v * 4 + 0]) * inv_l, __uint_as_float(orow[v * 4 + 1]) * inv_l,
+                                    __uint_as_float(orow[v * 4 + 2]) * inv_l, __uint_as_float(orow[v * 4 + 3]) * inv_l);
+          } else if (row < p.Sq) {
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               uint4 o;
@@ -496,7 +577,7 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
       uint4 nxt[PASSES];
 #pragma unroll
       for (int k = 0; k < PASSES; ++k) {
-        const int grow = rbase + r_in + k * RPP;
+        const int grow = jb * BLOCK_N + rbase + r_in + k * RPP;
         nxt[k] = grow < p.Sk ? ldg_nc_v4(src + 2 * (long long)grow * p.kr.ss) : make_uint4(0, 0, 0, 0);
       }
       const uint32_t kfull = lbar(BAR_KFULL + 0), kfull1 = lbar(BAR_KFULL + 1);
@@ -509,12 +590,12 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
         if (j + 1 < n_tiles) {
 #pragma unroll
           for (int k = 0; k < PASSES; ++k) {
-            const int grow = (j + 1) * BLOCK_N + rbase + r_in + k * RPP;
+            const int grow = (jb + j + 1) * BLOCK_N + rbase + r_in + k * RPP;
             nxt[k] = grow < p.Sk ? ldg_nc_v4(src + 2 * (long long)grow * p.kr.ss) : make_uint4(0, 0, 0, 0);
           }
         }
         float cb[8], sb[8];
-        const float pos0 = (float)(p.k_pos0 + j * BLOCK_N + rbase);
+        const float pos0 = (float)(p.k_pos0 + (jb + j) * BLOCK_N + rbase);
 #pragma unroll
         for (int e = 0; e < 8; ++e) sincos_reduced(__fmul_rn(pos0, th[e]), &sb[e], &cb[e]);
         const bool ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_KEMPTY + s), (uint32_t)(((j >> 1) & 1) ^ 1)));
@@ -557,14 +638,14 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
       XformRegs<DC> xr;
       const int rbase = (int)rank * HALF_N;
       XformCursor<DC> cur;
-      xform_cursor_init<DC>(p, cur, p.k, b, hk, rbase, p.k_pos0 + rbase, BLOCK_N, tg);
+      xform_cursor_init<DC>(p, cur, p.k, b, hk, jb * BLOCK_N + rbase, p.k_pos0 + jb * BLOCK_N + rbase, BLOCK_N, tg);
       if (n_tiles > 0) xform_load_next<DC>(p, xr, cur, p.Sk, BLOCK_N);
 #pragma unroll 1
       for (int j = 0; j < n_tiles; ++j) {
         const int s = j & 1;
         const bool ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_KEMPTY + s), (uint32_t)(((j >> 1) & 1) ^ 1)));
         if (!ok) { fail(ST_WAIT_KEMPTY); break; }
-        xform_finish<DC>(p, xr, k_smem + s * C::K_STAGE_BYTES, C::K_CHUNK_BYTES, j * BLOCK_N + rbase, p.Sk, tg);
+        xform_finish<DC>(p, xr, k_smem + s * C::K_STAGE_BYTES, C::K_CHUNK_BYTES, (jb + j) * BLOCK_N + rbase, p.Sk, tg);
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(lbar(BAR_KFULL + s));
@@ -588,6 +669,101 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const __grid_constant__ 
     tc_fence_after_sync();
     tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
+}
+
+// Combine the two parts of every split block: out = sum_p w_p O_p with w_p = exp(lse_p - lse),
+// lse = log(sum_p exp(lse_p)).  One warp per row (8 rows per CTA), four output columns per lane.
+constexpr int MERGE_ROWS = 8;
+__global__ void __launch_bounds__(32 * MERGE_ROWS) pair_merge_kernel(const KParams p, const int n_top, const float* const ws) {
+  const int n_sblk = (p.Sq + PAIR_ROWS - 1) / PAIR_ROWS;
+  const int item = blockIdx.y, r = blockIdx.x * MERGE_ROWS + (threadIdx.x >> 5), c = (threadIdx.x & 31) * 4;
+  const int bh = item / n_top, sblk = n_sblk - 1 - item % n_top;
+  const int row = sblk * PAIR_ROWS + r;
+  if (row >= p.Sq) return;
+  const int h = bh % p.H, b = bh / p.H;
+  const float* base = ws + (size_t)item * SPLIT_ITEM_FLOATS;
+  const float l0 = base[2 * PAIR_ROWS * DV + r], l1 = base[2 * PAIR_ROWS * DV + PAIR_ROWS + r];
+  const float lm = fmaxf(l0, l1);
+  const float e0 = lm == -INFINITY ? 0.f : expf(l0 - lm), e1 = lm == -INFINITY ? 0.f : expf(l1 - lm);
+  const float inv = (e0 + e1) > 0.f ? 1.0f / (e0 + e1) : 0.f;
+  const float w0 = e0 * inv, w1 = e1 * inv;
+  const float4 a = *reinterpret_cast<const float4*>(base + (size_t)r * DV + c);
+  const float4 d = *reinterpret_cast<const float4*>(base + (size_t)(PAIR_ROWS + r) * DV + c);
+  uint2 o;
+  o.x = pack_bf16x2(a.x * w0 + d.x * w1, a.y * w0 + d.y * w1);
+  o.y = pack_bf16x2(a.z * w0 + d.z * w1, a.w * w0 + d.w * w1);
+  char* dst = reinterpret_cast<char*>(const_cast<void*>(p.out.ptr)) +
+              2 * ((long long)b * p.out.sb + (long long)h * p.out.sh + (long long)row * p.out.ss + c);
+  *reinterpret_cast<uint2*>(dst) = o;
+  if (p.lse != nullptr && c == 0) p.lse[((long long)b * p.H + h) * p.Sq + row] = lm + logf(e0 + e1);
+}
+
+// Key tiles the greedy hand-out of the work items (longest first, as the kernel orders them) takes
+// on ``pair_slots`` CTA-pair slots when the ``n_top`` longest blocks are cut in two; every item
+// also pays ``fixed`` tiles' worth of prologue and epilogue.
+double split_makespan(const KParams& p, int n_top, int pair_slots, double fixed) {
+  const int n_sblk = (p.Sq + PAIR_ROWS - 1) / PAIR_ROWS;
+  const long long n_bh = (long long)p.B * p.H;
+  std::priority_queue<double, std::vector<double>, std::greater<double>> free_at;
+  for (int i = 0; i < pair_slots; ++i) free_at.push(0.0);
+  double end = 0.0;
+  int ia = 0, ib = n_sblk - n_top - 1;
+  while (ia < 2 * n_top || ib >= 0) {
+    int size_a = -1, size_b = -1;
+    if (ia < 2 * n_top) {
+      const int t = block_tiles(n_sblk - 1 - (ia >> 1), p.Sk, p.causal_off);
+      size_a = (ia & 1) ? t - t / 2 : t / 2;
+    }
+    if (ib >= 0) size_b = block_tiles(ib, p.Sk, p.causal_off);
+    const bool take_a = size_a >= size_b;
+    const int size = take_a ? size_a : size_b;
+    if (take_a) ++ia; else --ib;
+    for (long long k = 0; k < n_bh; ++k) {
+      const double t = free_at.top() + size + fixed;
+      free_at.pop();
+      free_at.push(t);
+      if (t > end) end = t;
+    }
+  }
+  return end;
+}
+
+// How many of the longest blocks of every (batch, head) to cut in two.  A launch with many
+// blocks per pair slot balances by itself; for one with fewer than three per slot the hand-out
+// is simulated for every count and the best one is taken if it beats the unsplit launch by
+// 15 % or more.  Smaller predicted gains do not materialise: the configuration-4 problem on
+// two heads x two batches (128 blocks for 74 slots) was predicted 6 % faster with six blocks
+// split and measured 3 % slower -- the merge pass and the partial results cost time, and an
+// unsplit launch runs its long tail at a higher clock because most SMs are idle by then.
+// Plans are cached.
+int plan_split(const KParams& p, int pair_slots) {
+  const int n_sblk = (p.Sq + PAIR_ROWS - 1) / PAIR_ROWS;
+  const long long n_bh = (long long)p.B * p.H;
+  if (n_sblk < 4 || n_bh * n_sblk >= 3ll * pair_slots) return 0;
+  static std::mutex mu;
+  static std::map<std::array<long long, 5>, int> cache;
+  const std::array<long long, 5> key = {p.Sq, p.Sk, p.causal_off, n_bh, pair_slots};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  const double base = split_makespan(p, 0, pair_slots, 2.0);
+  double best = base;
+  int best_n = 0;
+  for (int n = 1; n < n_sblk; ++n) {
+    if (block_tiles(n_sblk - n, p.Sk, p.causal_off) < 8) break;   // a part keeps a few tiles of its own
+    const double t = split_makespan(p, n, pair_slots, 2.0);
+    if (t < best) { best = t; best_n = n; }
+  }
+  if (best > 0.85 * base) best_n = 0;
+  if (cache.size() > 256) cache.clear();
+  cache[key] = best_n;
+  return best_n;
+}
+
+int pair_slots_of_device() {
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms / 2;
 }
 
 template <int DC, int DR, int MODE, bool ALIBI>
@@ -618,6 +794,8 @@ int launch_instance2(const KParams& p, cudaStream_t stream) {
     }
   }
   const int n_sblk = (p.Sq + PAIR_ROWS - 1) / PAIR_ROWS;
+  int n_top = plan_split(p, pair_slots_of_device());
+  if ((size_t)n_top * p.B * p.H * SPLIT_ITEM_FLOATS * sizeof(float) > p.workspace_bytes || p.workspace == nullptr) n_top = 0;
   const long long kv_bytes_per_head = 2ll * p.Sk * (DC + DR + DV);
   long long by_l2 = (48ll << 20) / (kv_bytes_per_head > 0 ? kv_bytes_per_head : 1);
   long long by_fill = (2 * 74 + n_sblk - 1) / n_sblk;   // 74 CTA pairs fit the GPU at a time
@@ -625,9 +803,14 @@ int launch_instance2(const KParams& p, cudaStream_t stream) {
   if (bh_group < p.groups) bh_group = p.groups;
   if (bh_group > (long long)p.B * p.H) bh_group = (long long)p.B * p.H;
   if (bh_group < 1) bh_group = 1;
-  dim3 grid((unsigned)(2ll * n_sblk * p.H * p.B)), block(NTHREADS);
-  kern<<<grid, block, C::SMEM_BYTES, stream>>>(p, (int)bh_group, tmQ, tmK, tmV);
+  dim3 grid((unsigned)(2ll * (n_sblk + n_top) * p.H * p.B)), block(NTHREADS);
+  kern<<<grid, block, C::SMEM_BYTES, stream>>>(p, (int)bh_group, n_top, p.workspace, tmQ, tmK, tmV);
   cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess && n_top > 0) {
+    pair_merge_kernel<<<dim3(PAIR_ROWS / MERGE_ROWS, (unsigned)(n_top * p.H * p.B)), 32 * MERGE_ROWS, 0, stream>>>(
+        p, n_top, p.workspace);
+    e = cudaGetLastError();
+  }
   if (e != cudaSuccess) {
     set_error("tcgen05 CTA-pair kernel launch failed: %s", cudaGetErrorString(e));
     return PE_ATTN_ERR_LAUNCH;
@@ -649,6 +832,11 @@ bool tc2_supports(const KParams& p) {
   if (p.variant == PE_ATTN_POPE)
     return (p.d_c == 128 && (p.d_r == 64 || p.d_r == 32)) || (p.d_c == 0 && p.d_r == 64);
   return p.d_c == 128;
+}
+
+// Workspace that lets the pair kernel split the longest blocks of a few-wave launch (0: no split planned).
+size_t tc2_workspace_bytes(const KParams& p) {
+  return (size_t)plan_split(p, pair_slots_of_device()) * p.B * p.H * SPLIT_ITEM_FLOATS * sizeof(float);
 }
 
 int launch_tc2(const KParams& p, cudaStream_t stream) {

@@ -122,6 +122,7 @@ def pe_attention(
     single_cta: bool = False,
     lse: torch.Tensor | None = None,
     split_kv: bool | None = None,
+    split_blocks: bool = True,
 ) -> torch.Tensor:
     """Fused causal attention forward with the positional transform applied in-kernel.
 
@@ -139,13 +140,16 @@ def pe_attention(
          the split-KV kernel, which streams the cached keys with the whole GPU instead of one
          CTA per head.  None picks it for such calls when Sk >= 256; True requires it (raises
          if the call is not of that shape); False keeps the query-tiled kernels.
+    split_blocks: let a launch with few (batch, head) problems cut its longest query blocks in two
+         along the keys (a scratch tensor for the partial results is allocated for the call).
     """
     if mask is not None:
         raise NotImplementedError("pe_attention is causal-only: an explicit mask is not supported (no fallback)")
     kwargs = dict(layout=layout, start_pos=start_pos, k_start_pos=k_start_pos, scale=scale, qk_norm=qk_norm,
                   qk_norm_eps=qk_norm_eps, rotary_table=rotary_table, table_pos0=table_pos0, mscale=mscale,
                   alibi_slopes=alibi_slopes, floor_freq=floor_freq, normalize_coeffs=normalize_coeffs,
-                  ceil_freq=ceil_freq, out=out, simt_check=simt_check, single_cta=single_cta, split_kv=split_kv)
+                  ceil_freq=ceil_freq, out=out, simt_check=simt_check, single_cta=single_cta, split_kv=split_kv,
+                  split_blocks=split_blocks)
     diff = (q, k, v, q_r, k_r, freqs, delta, fourier_coeffs)
     if torch.is_grad_enabled() and any(isinstance(t, torch.Tensor) and t.requires_grad for t in diff):
         return _training_call(variant, q, k, v, q_r, k_r, freqs, delta, fourier_coeffs, lse, kwargs)
@@ -213,6 +217,7 @@ def _forward_impl(
     single_cta: bool = False,
     lse: torch.Tensor | None = None,
     split_kv: bool | None = None,
+    split_blocks: bool = True,
 ) -> torch.Tensor:
     """The forward kernel call behind ``pe_attention`` (no autograd bookkeeping)."""
     if variant not in _VARIANTS:
@@ -335,6 +340,12 @@ def _forward_impl(
             ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
             rc = _lib.lib.pe_attn_decode(C.byref(a), C.c_void_p(ws.data_ptr()), C.c_size_t(ws_bytes), C.c_void_p(stream))
         else:
+            # few-wave launches of the CTA-pair kernel split their longest query blocks along the
+            # keys when given scratch for the partial results (stream-ordered, from the allocator)
+            fwd_ws = _lib.lib.pe_attn_forward_workspace_bytes(C.byref(a)) if (dtype == _lib.BF16 and split_blocks) else 0
+            if fwd_ws > 0:
+                ws = torch.empty(fwd_ws, dtype=torch.uint8, device=dev)
+                a.workspace, a.workspace_bytes = ws.data_ptr(), fwd_ws
             rc = _lib.lib.pe_attn_forward(C.byref(a), C.c_void_p(stream))
     if rc != 0:
         raise _lib.PeAttnError(rc)
@@ -506,7 +517,8 @@ class HostStreamedAttention:
     first row of c) is launched on the caller's stream as soon as the copy has landed, and
     its output rows go back on a third stream while block c+1 is still arriving.  Each
     block runs the same kernel over the same 128-key tiles as the one-shot call, so the
-    result is the one ``pe_attention`` gives on device copies of the same tensors.
+    result is the one ``pe_attention`` gives on device copies of the same tensors (to a bf16
+    rounding: launches with few blocks split their longest ones along the keys).
 
     The staging tensors (device copies of every input and of the output) are allocated once
     here, in two sets that calls use in turn: the copy-in of call n + 1 may start while the last

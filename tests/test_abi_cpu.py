@@ -30,7 +30,7 @@ def test_exports_every_declared_symbol(L):
             "pe_rotary_norm_expand"} <= set(names) and len(names) >= 18
     for n in names:
         assert hasattr(L.lib, n), n
-    assert L.lib.pe_attn_version() == 2
+    assert L.lib.pe_attn_version() == 3
 
 
 def _valid_args(L, **over):
@@ -67,6 +67,23 @@ def test_struct_layout_matches_and_valid_args_pass(L):
     assert L.lib.pe_attn_kernel_name(C.byref(a)) == b"ffma"
     fl = L.lib.pe_attn_flops(C.byref(a))
     assert abs(fl - 2 * 16 * (1024 * 1025 / 2) * 2 * 384) < 1e-3 * fl
+
+
+def test_forward_workspace_is_only_asked_for_few_wave_pair_launches(L):
+    # 2 x 16 heads x 2 blocks of 512 rows: plenty of blocks per CTA-pair slot, no split planned
+    assert L.lib.pe_attn_forward_workspace_bytes(C.byref(_valid_args(L))) == 0
+    # one (batch, head) pair of problems over a long sequence: the longest blocks get split
+    few = _valid_args(L, B=1, H=2, Hkv=2, Sq=8192, Sk=8192)
+    n = L.lib.pe_attn_forward_workspace_bytes(C.byref(few))
+    assert n > 0 and n % (2 * 512 * 129 * 4) == 0          # whole items of 2 x 512 x (128 + 1) floats
+    # other kernels never use it
+    assert L.lib.pe_attn_forward_workspace_bytes(C.byref(_valid_args(L, B=1, H=2, Hkv=2, Sq=8192, Sk=8192,
+                                                                  flags=L.SINGLE_CTA))) == 0
+    assert L.lib.pe_attn_forward_workspace_bytes(C.byref(_valid_args(L, B=1, H=2, Hkv=2, Sq=8192, Sk=8192,
+                                                                  dtype=L.FP32))) == 0
+    # a misaligned workspace is refused
+    bad = _valid_args(L, B=1, H=2, Hkv=2, Sq=8192, Sk=8192, workspace=0x10004, workspace_bytes=n)
+    assert L.lib.pe_attn_validate(C.byref(bad)) == 4
 
 
 @pytest.mark.parametrize("over,code", [

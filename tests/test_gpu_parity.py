@@ -126,6 +126,63 @@ def test_cta_pair_and_single_cta_kernels_agree(case):
     assert (pair - single).abs().max().item() <= 2e-2
 
 
+@pytest.mark.parametrize("case", [
+    Case("split_fpope", "pope", BF16, 1, 2, 2, 4096, 128, 64, 128, seed=201, pope_kind="fpope", training_length=4096),
+    Case("split_pope_ragged", "pope", BF16, 1, 3, 3, 3000, 128, 32, 128, seed=202, pos0=70),
+    Case("split_rope_qkn_gqa", "rotary", BF16, 1, 4, 2, 2500, 128, 0, 128, seed=203, qk_norm=True),
+    Case("split_alibi", "alibi", BF16, 2, 2, 2, 2100, 128, 0, 128, seed=204),
+], ids=lambda c: c.name)
+def test_few_wave_launches_split_their_longest_blocks(case):
+    """A launch with few (batch, head) problems: the CTA-pair kernel cuts the longest query blocks
+    in two along the keys and merges the halves (needs the forward workspace, which the Python
+    wrapper provides).  Output and logsumexp against the oracle, and against the unsplit
+    single-CTA kernel."""
+    import ctypes as C
+
+    from pe_ablations_b200 import _lib as L
+    from pe_ablations_b200 import check_device_status, pe_attention
+    from oracle import pe_attention_oracle as O
+    from tests.gpu_util import run_case_on_gpu
+
+    inp = make_inputs(case)
+    # the planner does ask for a workspace at this size
+    a = L.PeAttnArgs()
+    a.struct_size = C.sizeof(L.PeAttnArgs)
+    a.variant = {"pope": L.POPE, "rotary": L.ROTARY, "alibi": L.ALIBI}[case.variant]
+    a.dtype = L.BF16
+    a.B, a.H, a.Hkv, a.Sq, a.Sk, a.d_c, a.d_r, a.d_v = case.B, case.H, case.Hkv, case.S, case.S, case.d_c, case.d_r, case.d_v
+    a.scale = case.d_qk ** -0.5
+    for name in ("q", "k", "v", "out", "q_r", "k_r", "freqs", "rotary_table", "alibi_slopes"):
+        setattr(a, name, 0x10000)
+    a.table_rows = case.pos0 + case.S
+    for sname, d, hh in (("q_stride", case.d_c, case.H), ("k_stride", case.d_c, case.Hkv), ("v_stride", case.d_v, case.Hkv),
+                         ("out_stride", case.d_v, case.H), ("qr_stride", max(case.d_r, 8), case.H),
+                         ("kr_stride", max(case.d_r, 8), case.Hkv)):
+        getattr(a, sname)[:] = (case.S * hh * d, d, hh * d)
+    assert L.lib.pe_attn_forward_workspace_bytes(C.byref(a)) > 0, L.lib.pe_attn_last_error()
+
+    want = oracle_output(case, inp).float()
+    pair = run_case_on_gpu(case, inp)
+    single = run_case_on_gpu(case, inp, single_cta=True)
+    assert (pair - want).abs().max().item() <= 2e-2
+    assert (pair - single).abs().max().item() <= 2e-2
+
+    if case.variant == "pope":     # the merged logsumexp too
+        dev = torch.device("cuda", 0)
+        c = lambda t: t.to(dev, torch.bfloat16)
+        lse = torch.full((case.B, case.H, case.S), float("nan"), device=dev)
+        kw = dict(freqs=inp["base_freqs"], fourier_coeffs=inp["fourier_coeffs"],
+                  floor_freq=2 * torch.pi / case.training_length) if case.pope_kind == "fpope" else dict(freqs=inp["freqs"])
+        pe_attention("pope", c(inp["q"]), c(inp["k"]), c(inp["v"]), q_r=c(inp["q_r"]), k_r=c(inp["k_r"]),
+                     delta=inp["delta"], start_pos=case.pos0, lse=lse, **kw)
+        torch.cuda.synchronize()
+        check_device_status()
+        _, want_lse = O.attention_core("pope", inp["q"], inp["k"], inp["v"], dtype=torch.bfloat16, q_r=inp["q_r"],
+                                       k_r=inp["k_r"], freqs=inp["freqs"], delta=inp["delta"], pos0=case.pos0,
+                                       return_lse=True)
+        assert (lse.cpu() - want_lse).abs().max().item() <= 2e-2
+
+
 def test_fused_fourier_mix_equals_host_mix():
     from tests.gpu_util import run_case_on_gpu
 
@@ -339,7 +396,7 @@ def test_bhsd_layout_and_strided_views(dtype):
 @pytest.mark.parametrize("chunks", [1, 4])
 def test_host_streamed_call_equals_the_device_call(chunks):
     """Pinned host tensors in, pinned host tensor out, copies pipelined over sequence blocks:
-    bit-identical to the one-shot call on device copies, and within tolerance of the oracle."""
+    the one-shot call's result on device copies (to a bf16 ulp), and within tolerance of the oracle."""
     from pe_ablations_b200 import HostStreamedAttention, check_device_status, pe_attention
     from oracle import pe_attention_oracle as O
 
@@ -359,7 +416,9 @@ def test_host_streamed_call_equals_the_device_call(chunks):
     check_device_status()
     d = {n: t.to(dev) for n, t in host.items()}
     one_shot = pe_attention("pope", d["q"], d["k"], d["v"], q_r=d["q_r"], k_r=d["k_r"], freqs=freqs, delta=delta)
-    assert torch.equal(out_host, one_shot.cpu())
+    # same kernel, same tiles; a few-wave launch may cut its longest blocks in two along the keys,
+    # whose merge rounds differently: at most a bf16 ulp apart
+    assert (out_host.float() - one_shot.cpu().float()).abs().max().item() <= 2 ** -7
     f = lambda t: t.float()
     want = O.attention_core("pope", f(host["q"]), f(host["k"]), f(host["v"]), dtype=torch.bfloat16,
                             q_r=f(host["q_r"]), k_r=f(host["k_r"]), freqs=freqs, delta=delta).float()
