@@ -14,8 +14,10 @@ its eager modules (src/model/attention.py:77-96, src/model/alibi.py:137-160,
 src/model/fpope_attention.py:145-177 with src/model/pope.py:124-183 /
 src/model/fpope.py:107-146,266-338, src/model/rope.py:35-57, src/model/normalization.py:44-56).
 
-bf16 only, and only the head dimensions the backward kernel has: (d_qk, d_v) in
-{(64, 64), (128, 64), (128, 128)}.  Anything else raises; there is no eager fallback.
+bf16 only (run the modules under bf16 autocast).  (d_qk, d_v) in {(64, 64), (128, 64), (128, 128)}
+-- every YAML configuration of the reference -- take the tensor-core backward kernel; the other
+head dimensions of the bf16 forward, d_qk = 192 / 256 with d_v = 128 (the 1B shape), take the
+FFMA backward kernels.  fp32 calls that need gradients raise; there is no eager fallback.
 """
 
 from __future__ import annotations

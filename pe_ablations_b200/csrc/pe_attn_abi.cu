@@ -168,9 +168,10 @@ int pe_attn_backward(const pe_attn_bwd_args* a, void* stream) {
   if (a->H % a->Hkv != 0) return fail(PE_ATTN_ERR_SHAPE, "H=%d is not a multiple of Hkv=%d", a->H, a->Hkv);
   if (a->Sk < a->Sq) return fail(PE_ATTN_ERR_SHAPE, "Sk=%d < Sq=%d", a->Sk, a->Sq);
   if (a->B > 65535 || a->Hkv > 65535) return fail(PE_ATTN_ERR_SHAPE, "B and Hkv must be <= 65535");
-  if (!bwd_supports(a->d_qk, a->d_v))
-    return fail(PE_ATTN_ERR_SHAPE, "backward supports (d_qk, d_v) in {(64,64), (128,64), (128,128)} (got %d, %d)",
-                a->d_qk, a->d_v);
+  if (!bwd_supports(a->d_qk, a->d_v) && !bwd_simt_supports(a->d_qk, a->d_v))
+    return fail(PE_ATTN_ERR_SHAPE,
+                "backward supports (d_qk, d_v) in {(64,64), (128,64), (128,128)} on the tensor cores and any "
+                "multiples of 8 up to (256, 128) on the CUDA cores (got %d, %d)", a->d_qk, a->d_v);
   struct { const char* name; const void* p; const int64_t* s; } ts[] = {
       {"q", a->q, a->q_stride},       {"k", a->k, a->k_stride},   {"v", a->v, a->v_stride},
       {"out", a->out, a->out_stride}, {"dout", a->dout, a->dout_stride},

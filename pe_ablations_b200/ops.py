@@ -169,9 +169,9 @@ def _training_call(variant, q, k, v, q_r, k_r, freqs, delta, fourier_coeffs, lse
     if kw["layout"] != "bshd" or kw["out"] is not None or lse is not None or kw["simt_check"]:
         raise NotImplementedError("a call that needs gradients takes [B, S, H, d] tensors and owns its outputs")
     d_qk = (q.shape[-1] if q is not None else 0) + (2 * q_r.shape[-1] if q_r is not None else 0)
-    if (d_qk, v.shape[-1]) not in ((64, 64), (128, 64), (128, 128)):
-        raise NotImplementedError(f"the backward kernel covers (d_qk, d_v) in (64,64), (128,64), (128,128); got "
-                                  f"({d_qk}, {v.shape[-1]})")
+    if d_qk not in (64, 128, 192, 256) or v.shape[-1] not in (64, 128):
+        raise NotImplementedError(f"gradients need d_qk in (64, 128, 192, 256) and d_v in (64, 128) -- the bf16 forward's "
+                                  f"head dims; got ({d_qk}, {v.shape[-1]})")
     dev = v.device
     k_start = kw["start_pos"] if kw["k_start_pos"] is None else kw["k_start_pos"]
     tab = kw["rotary_table"]
@@ -359,6 +359,9 @@ def attention_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: t
                        lse: torch.Tensor, *, scale: float, alibi_slopes: torch.Tensor | None = None
                        ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Gradients of ``softmax_causal(scale q k^T + bias) v`` for transformed bf16 operands.
+
+    (d_qk, d_v) in {(64,64), (128,64), (128,128)} run on the tensor cores; any other multiples of 8
+    up to (256, 128) -- the 1B shape's (256, 128) -- on the CUDA cores (FFMA kernels).
 
     q [B,Sq,H,d_qk], k [B,Sk,Hkv,d_qk], v [B,Sk,Hkv,d_v], out / dout [B,Sq,H,d_v] (bf16, last
     dimension contiguous), ``lse`` the forward's [B,H,Sq] logsumexp.  Returns

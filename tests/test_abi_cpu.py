@@ -162,8 +162,9 @@ def test_backward_entry_rejects_bad_arguments_before_touching_the_gpu(L):
     assert bwd(C.byref(_bwd_args(L, struct_size=8)), None) == 2
     assert bwd(C.byref(_bwd_args(L, Sq=600)), None) == 3                      # Sk < Sq
     assert bwd(C.byref(_bwd_args(L, H=6)), None) == 3                         # H % Hkv
-    assert bwd(C.byref(_bwd_args(L, d_qk=256)), None) == 3                    # forward-only head dim
+    assert bwd(C.byref(_bwd_args(L, d_qk=264)), None) == 3                    # beyond every backward kernel
     assert b"(64,64), (128,64), (128,128)" in L.lib.pe_attn_last_error()
+    assert bwd(C.byref(_bwd_args(L, d_qk=100)), None) == 3                    # not a multiple of 8
     assert bwd(C.byref(_bwd_args(L, dout=None)), None) == 1
     assert bwd(C.byref(_bwd_args(L, dk=0x10008)), None) == 4
     assert bwd(C.byref(_bwd_args(L, q_stride=(512 * 8 * 128, 130, 8 * 128))), None) == 4

@@ -51,6 +51,11 @@ CASES = [
     ("alibi_d128_cached", 2, 4, 2, 131, 400, 128, 128, True),
     ("many_blocks_1153", 1, 2, 2, 1153, 1153, 64, 64, False),
     ("many_blocks_2100_d128", 1, 2, 1, 2100, 2100, 128, 128, False),
+    # head dimensions the tensor-core kernel lacks: the FFMA backward
+    ("ffma_1b_shape_256_128", 1, 2, 2, 600, 600, 256, 128, False),
+    ("ffma_192_128_gqa_cached", 2, 4, 2, 130, 333, 192, 128, False),
+    ("ffma_alibi_d32", 1, 4, 2, 200, 200, 32, 32, True),
+    ("ffma_256_128_ragged_1100", 1, 2, 1, 1100, 1100, 256, 128, False),
 ]
 
 
@@ -175,11 +180,53 @@ def test_training_call_refuses_what_the_backward_does_not_cover():
     mk = lambda d, dt: torch.randn(1, 64, 2, d, device=dev, dtype=dt, requires_grad=True)
     with pytest.raises(NotImplementedError):     # fp32 has no backward kernel
         pe_attention("nope", mk(64, torch.float32), mk(64, torch.float32), mk(64, torch.float32))
-    with pytest.raises(NotImplementedError):     # d_qk = 256 is forward-only
-        pe_attention("pope", mk(128, torch.bfloat16), mk(128, torch.bfloat16), mk(128, torch.bfloat16),
-                     q_r=mk(64, torch.bfloat16), k_r=mk(64, torch.bfloat16), freqs=torch.ones(64))
     with torch.no_grad():                        # the same call without gradients is fine
         pe_attention("nope", mk(64, torch.float32), mk(64, torch.float32), mk(64, torch.float32))
+
+
+@pytest.mark.parametrize("dc,dr", [(128, 64), (128, 32)], ids=["d_qk256", "d_qk192"])
+def test_1b_head_dims_train_through_the_ffma_backward(dc, dr):
+    """FoPE+PoPE attention at the 1B shape's head dims (d_qk 256 / d_v 128, which the tensor-core
+    backward does not have) with gradients: output and every gradient against autograd over the
+    torch restatement of the transform and an explicit fp32 attention."""
+    from pe_ablations_b200 import autograd as A
+    from pe_ablations_b200 import check_device_status, pe_attention
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(77)
+    B, S, H, Hkv, dv = 1, 330, 4, 2, 128
+    mk = lambda h, d: torch.randn(B, S, h, d, generator=g).to(torch.bfloat16)
+    host = dict(q=mk(H, dc), k=mk(Hkv, dc), v=mk(Hkv, dv), q_r=mk(H, dr), k_r=mk(Hkv, dr))
+    freqs = 10000.0 ** (-(torch.arange(dr, dtype=torch.float32) / dr))
+    coeffs = torch.randn(dr, 8, generator=g) * 0.3
+    delta = -torch.rand(dr, generator=g) * 3
+    dout = torch.randn(B, S, H, dv, generator=g).to(torch.bfloat16)
+    floor = 2 * math.pi / 4096
+    scale = (dc + 2 * dr) ** -0.5
+
+    leaf = {n: t.to(dev).requires_grad_(True) for n, t in host.items()}
+    pl = {n: t.to(dev).requires_grad_(True) for n, t in dict(freqs=freqs, coeffs=coeffs, delta=delta).items()}
+    out = pe_attention("pope", leaf["q"], leaf["k"], leaf["v"], q_r=leaf["q_r"], k_r=leaf["k_r"], freqs=pl["freqs"],
+                       fourier_coeffs=pl["coeffs"], delta=pl["delta"], floor_freq=floor)
+    out.backward(dout.to(dev))
+    torch.cuda.synchronize()
+    check_device_status()
+
+    ref = {n: t.float().requires_grad_(True) for n, t in host.items()}
+    rp = {n: t.clone().requires_grad_(True) for n, t in dict(freqs=freqs, coeffs=coeffs, delta=delta).items()}
+    o = dict(start_pos=0, k_start_pos=0, normalize_coeffs=True, floor_freq=floor, ceil_freq=None)
+    qt, kt = A.transformed_operands("pope", ref["q"], ref["k"], ref["q_r"], ref["k_r"], o, rp["freqs"], rp["delta"], rp["coeffs"])
+    kk, vv = kt.repeat_interleave(H // Hkv, dim=2), ref["v"].repeat_interleave(H // Hkv, dim=2)
+    sc = torch.einsum("bqhd,bkhd->bhqk", qt, kk) * scale
+    sc = sc.masked_fill(torch.triu(torch.ones(S, S, dtype=torch.bool), diagonal=1), float("-inf"))
+    want = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(sc, dim=-1), vv)
+    want.backward(dout.float())
+    assert (out.detach().float().cpu() - want.detach()).abs().max().item() <= 2e-2
+    pairs = [(leaf[n].grad, ref[n].grad, n) for n in host] + [(pl[n].grad, rp[n].grad, n) for n in pl]
+    for have, ref_g, name in pairs:
+        bound = 3e-2 * max(ref_g.abs().max().item(), 1e-3)
+        err = (have.float().cpu() - ref_g).abs().max().item()
+        assert err <= bound, f"{name}: |diff| {err:.3e} > {bound:.3e}"
 
 
 def _train_model_cases():
