@@ -792,6 +792,50 @@ def run_variants(args) -> dict:
                          "F.scaled_dot_product_attention(is_causal=True), or the explicit S x S scores for ALiBi"}
 
 
+PROFILE_CASES = {
+    # name: (variant, B, H, Hkv, S, d_c, d_r, d_v, qk_norm) -- each a few hundred MB at most, inputs larger than L2
+    "pair_fpope": ("pope", 1, 4, 4, 16384, 128, 64, 128, False),      # pe_attn_tc2_kernel, the headline loop
+    "pair_fope_rotary": ("rotary", 4, 16, 16, 4096, 128, 0, 128, False),
+    "tile4_nope": ("nope", 4, 16, 16, 8192, 64, 0, 64, False),        # pe_attn_tc4_kernel (2 tiles, 2 CTAs/SM)
+    "tile4_rope_qknorm": ("rotary", 4, 16, 16, 8192, 64, 0, 64, True),
+    "tile4_fpope_gqa": ("pope", 8, 8, 4, 4096, 64, 32, 64, False),
+}
+
+
+def run_profile_case(args) -> dict:
+    """``--workload profile --case NAME``: a few launches of one small case, for ``ncu -k ... -c 1``."""
+    import torch
+
+    import pe_ablations_b200 as P
+    from pe_ablations_b200 import pe as PE
+
+    variant, Bp, Hp, Hkv, Sp, d_c, d_r, d_v, qk_norm = PROFILE_CASES[args.case]
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator().manual_seed(0)
+    mk = lambda h, d: None if d == 0 else torch.randn(Bp, Sp, h, d, generator=g).to(torch.bfloat16).to(dev)
+    q, k, v, q_r, k_r = mk(Hp, d_c), mk(Hkv, d_c), mk(Hkv, d_v), mk(Hp, d_r), mk(Hkv, d_r)
+    kw = {}
+    if variant == "pope":
+        kw = PE.FoPEPoPEEmbedding(dim=d_r, max_seq_len=Sp, num_fourier_terms=N_FOURIER, fourier_sigma=SIGMA,
+                                  training_length=Sp, delta_init="uniform").to(dev).kernel_args()
+    elif variant == "rotary":
+        kw = dict(rotary_table=PE.RotaryEmbedding(d_c, Sp, 10000.0).to(dev).freqs_cis)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.no_grad():
+        for i in range(3):
+            if i == 2:
+                ev0.record()
+            out = P.pe_attention(variant, q, k, v, q_r=q_r, k_r=k_r, qk_norm=qk_norm, **kw)
+        ev1.record()
+    torch.cuda.synchronize()
+    P.check_device_status()
+    ms = ev0.elapsed_time(ev1)
+    flops = Bp * Hp * Sp * Sp * (d_c + 2 * d_r + d_v)
+    return {"workload": "profile", "case": args.case, "shape": f"B{Bp} H{Hp}/{Hkv} S{Sp} d_qk{d_c + 2 * d_r} d_v{d_v}",
+            "ms": round(ms, 4), "tflops": round(flops / (ms * 1e-3) / 1e12, 1), "mean_abs_out": float(out.float().abs().mean())}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -810,14 +854,18 @@ def main():
                     help="sequence blocks of the pipelined host-buffer call (0: about 32 MiB of input per block, 2 to 8)")
     ap.add_argument("--decode-batch", type=int, default=8, help="sequences in the decode workload")
     ap.add_argument("--decode-cache", type=int, default=16384, help="cached keys per sequence in the decode workload")
-    ap.add_argument("--workload", default="forward", choices=["forward", "training", "variants", "decode"],
+    ap.add_argument("--case", default="pair_fpope", choices=sorted(PROFILE_CASES),
+                    help="--workload profile: which small case to launch (for an ncu capture of one kernel)")
+    ap.add_argument("--workload", default="forward", choices=["forward", "training", "variants", "decode", "profile"],
                     help="forward: the headline benchmark; training: forward+backward of the attention op (1 GPU); "
                          "variants: the forward of every variant at its benchmark configuration (1 GPU); "
                          "decode: one generated token against a long cache, split-KV kernel (1 GPU)")
     ap.add_argument("--train-batch", type=int, default=64)
     ap.add_argument("--train-seq", type=int, default=512)
     args = ap.parse_args()
-    if args.workload == "training" and args.impl == "ours":
+    if args.workload == "profile" and args.impl == "ours":
+        line = run_profile_case(args)
+    elif args.workload == "training" and args.impl == "ours":
         line = run_training(args)
     elif args.workload == "variants" and args.impl == "ours":
         line = run_variants(args)
