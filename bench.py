@@ -590,8 +590,10 @@ def run_decode(args) -> dict:
                        "frac": round(nb / (ms * 1e-3) / 1e9 / peak, 4)})
 
     rope = PE.RotaryEmbedding(64, Sk, 10000.0).to(dev)
-    other("rope, head_dim 64", "rotary", 12, 12, 64, 0, 64, rotary_table=rope.freqs_cis)
-    other("rope + QKNorm, head_dim 64", "rotary", 12, 12, 64, 0, 64, rotary_table=rope.freqs_cis, qk_norm=True)
+    other("rope, head_dim 64", "rotary", 12, 12, 64, 0, 64, rotary_table=rope.freqs_cis, table_geometric=True)
+    other("rope + QKNorm, head_dim 64", "rotary", 12, 12, 64, 0, 64, rotary_table=rope.freqs_cis, table_geometric=True,
+          qk_norm=True)
+    other("rope, head_dim 64, every table row read", "rotary", 12, 12, 64, 0, 64, rotary_table=rope.freqs_cis)
     other("nope, head_dim 128", "nope", 16, 16, 128, 0, 128)
     other("alibi, head_dim 128, 4:1 GQA", "alibi", 16, 4, 128, 0, 128, alibi_slopes=PE.alibi_slopes(16).to(dev))
     fp2 = PE.FoPEPoPEEmbedding(dim=32, max_seq_len=Sk, num_fourier_terms=64, fourier_sigma=0.4, training_length=512,

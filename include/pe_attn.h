@@ -71,10 +71,15 @@ enum pe_attn_flags {
                                       /* fourier_coeffs[] inside the kernel (fpope.py:107-146)     */
   PE_ATTN_FOURIER_NORMALIZE = 1 << 2, /* L1-normalise each row of coefficients first               */
   PE_ATTN_FOURIER_CEILING = 1 << 3,   /* clamp effective frequencies to +-ceil_freq                */
+  PE_ATTN_TABLE_GEOMETRIC = 1 << 4,   /* ROTARY: row i of rotary_table is (cos, sin)(i * angle_c),  */
+                                      /* as every table of rope.py is (plain, NTK, YaRN): the       */
+                                      /* decode kernel may then advance a key's rotation from tile  */
+                                      /* to tile instead of reading every row                       */
   PE_ATTN_SIMT_CHECK = 1 << 8,        /* bf16 only: run the FFMA kernel on the bf16 tensors (an    */
                                       /* on-device cross-check for the tensor-core kernels)        */
-  PE_ATTN_SINGLE_CTA = 1 << 9         /* bf16 only: keep the single-CTA tcgen05 kernel where the   */
-                                      /* CTA-pair kernel (d_v = 128, Sq > 256) would be chosen     */
+  PE_ATTN_SINGLE_CTA = 1 << 9         /* bf16 only: keep the two-tile single-CTA tcgen05 kernel     */
+                                      /* where the CTA-pair (d_v = 128, Sq > 256) or the four-tile */
+                                      /* kernel (d_v = 64) would be chosen                         */
 };
 
 typedef enum pe_attn_status {

@@ -20,6 +20,7 @@ QK_NORM = 1 << 0
 FOURIER_MIX = 1 << 1
 FOURIER_NORMALIZE = 1 << 2
 FOURIER_CEILING = 1 << 3
+TABLE_GEOMETRIC = 1 << 4
 SIMT_CHECK = 1 << 8
 SINGLE_CTA = 1 << 9
 

@@ -66,7 +66,9 @@ struct DCfg {
   static constexpr int OFF_Q = NSTAGE * STAGE_BYTES;
   static constexpr int OFF_ROW = OFF_Q + R_T * DQK * 4;
   static constexpr int OFF_FREQ = (OFF_ROW + 2 * R_T * 4 + 15) & ~15;   // read as float4
-  static constexpr int OFF_CNT = OFF_FREQ + 4 * (DR > 0 ? DR : 4) * 4;   // frequency, phase bias, cos / sin of one tile's advance
+  // frequency, phase bias, cos / sin of one tile's advance (PoPE); or the (cos, sin) of one tile's
+  // advance of every rotary column pair (DC floats)
+  static constexpr int OFF_CNT = OFF_FREQ + (4 * (DR > 0 ? DR : 4) * 4 > DC * 4 ? 4 * (DR > 0 ? DR : 4) * 4 : DC * 4);
   static constexpr int OFF_BAR = (OFF_CNT + NSTAGE * 4 + 7) & ~7;
   static constexpr int SMEM_BYTES = OFF_BAR + NSTAGE * 8 + 1024;   // + slack for the 1024-byte alignment
 };
@@ -234,6 +236,16 @@ pe_attn_decode_kernel(const KParams p, const DecodeParams dp, const __grid_const
       }
     }
   }
+  if constexpr (MODE == MODE_XFORM) {
+    // geometric rotary table: (cos, sin) of TK positions per column pair = row (first key of the
+    // split's second tile) x conj(row (its first key)); both rows exist when the split has two tiles
+    if (p.variant == PE_ATTN_ROTARY && (p.flags & PE_ATTN_TABLE_GEOMETRIC) && n_tiles > 1 && tid < DC / 2) {
+      const long long row_a = (long long)tile0 * TK + p.k_pos0 - p.table_pos0;
+      const float2 a = reinterpret_cast<const float2*>(p.table)[row_a * (DC / 2) + tid];
+      const float2 bq = reinterpret_cast<const float2*>(p.table)[(row_a + TK) * (DC / 2) + tid];
+      reinterpret_cast<float2*>(freq_s)[tid] = make_float2(bq.x * a.x + bq.y * a.y, bq.y * a.x - bq.x * a.y);
+    }
+  }
   if (tid < R_T) {
     const int r = tid;
     const int g = r / p.Sq, qi = r - g * p.Sq;
@@ -281,32 +293,42 @@ pe_attn_decode_kernel(const KParams p, const DecodeParams dp, const __grid_const
   __syncthreads();   // query rows complete
   bool bad = false;
 
-  // rotary: the (cos, sin) table entries of this lane's key and columns, fetched one tile ahead
+  // rotary: the (cos, sin) table entries of this lane's key and columns.
+  // For a table that is geometric in the position (row i = angles i * angle_c: every table the
+  // reference builds) the entries are only FETCHED every RESEED tiles and advanced in between
+  // by the rotation of TK positions, like the PoPE phases above: the fp32 table is twice the
+  // bytes of the bf16 keys it rotates, and reading all of it made this path L2-bound.
   constexpr int NCS = DC > 0 ? DC / 32 : 1;
-  [[maybe_unused]] float4 tab_next[NCS][2], tab_cur[NCS][2];
+  [[maybe_unused]] float4 tab_cur[NCS][2];
+  const bool recur = rotary && (p.flags & PE_ATTN_TABLE_GEOMETRIC) && n_tiles > 1;
   auto load_table = [&](int t) {
     const int kg_t = (tile0 + t) * TK + key_local;
     const long long krow = (long long)(kg_t < p.Sk ? kg_t : p.Sk - 1) + p.k_pos0 - p.table_pos0;
 #pragma unroll
     for (int i = 0; i < NCS; ++i) {
       const float4* tp = reinterpret_cast<const float4*>(p.table + (krow * (DC / 2) + (part + 4 * i) * 4) * 2);
-      tab_next[i][0] = __ldg(tp);
-      tab_next[i][1] = __ldg(tp + 1);
+      tab_cur[i][0] = __ldg(tp);
+      tab_cur[i][1] = __ldg(tp + 1);
     }
   };
-  if constexpr (MODE == MODE_XFORM) {
-    if (rotary && n_tiles > 0) load_table(0);
-  }
-
   for (int t = 0; t < n_tiles; ++t) {
     if constexpr (MODE == MODE_XFORM) {
       if (rotary) {
+        if (!recur || (t % RESEED) == 0) {
+          load_table(t);   // issued before the wait for the tile's stage; every tile only for a table that is not geometric
+        } else {
+          // (c, s) <- (c cs - s ss, s cs + c ss) for the four pairs of each slot
 #pragma unroll
-        for (int i = 0; i < NCS; ++i) {
-          tab_cur[i][0] = tab_next[i][0];
-          tab_cur[i][1] = tab_next[i][1];
+          for (int i = 0; i < NCS; ++i) {
+#pragma unroll
+            for (int hlf = 0; hlf < 2; ++hlf) {
+              const float4 c = tab_cur[i][hlf];
+              const float4 st = *reinterpret_cast<const float4*>(freq_s + ((part + 4 * i) * 4 + 2 * hlf) * 2);
+              tab_cur[i][hlf] = make_float4(c.x * st.x - c.y * st.y, c.y * st.x + c.x * st.y,
+                                            c.z * st.z - c.w * st.w, c.w * st.z + c.z * st.w);
+            }
+          }
         }
-        if (t + 1 < n_tiles) load_table(t + 1);
       }
     }
     const int stage = t % C::NSTAGE;

@@ -96,6 +96,8 @@ class GroupedQueryAttention(nn.Module):
         if self.rope is not None:
             variant = "rotary"
             kw["rotary_table"] = self.rope.freqs_cis
+            # every table of the reference's rope classes is angle = position x inverse frequency
+            kw["table_geometric"] = bool(getattr(self.rope, "table_geometric", True))
             scale_qk = getattr(self.rope, "attention_scale", None)
             if scale_qk is None and hasattr(self.rope, "mscale"):
                 scale_qk = float(self.rope.mscale)

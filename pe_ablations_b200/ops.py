@@ -108,6 +108,7 @@ def pe_attention(
     qk_norm_eps: float = 1e-6,
     rotary_table: torch.Tensor | None = None,
     table_pos0: int = 0,
+    table_geometric: bool = False,
     mscale: float = 1.0,
     alibi_slopes: torch.Tensor | None = None,
     freqs: torch.Tensor | None = None,
@@ -128,7 +129,10 @@ def pe_attention(
 
     variant: ``nope`` | ``rotary`` | ``alibi`` | ``pope``.
       rotary: ``rotary_table`` is [rows, d/2, 2] fp32 (cos, sin), row i = position
-              ``table_pos0 + i`` (``torch.view_as_real`` of the reference's ``freqs_cis``).
+              ``table_pos0 + i`` (``torch.view_as_real`` of the reference's ``freqs_cis``);
+              ``table_geometric`` says that row i holds the angles i * angle_c (true for every
+              table the reference builds), which lets the decode kernel advance a key's rotation
+              from tile to tile instead of reading the table row of every key.
       alibi:  ``alibi_slopes`` is [H].
       pope:   ``q``/``k`` are the content halves (or None), ``q_r``/``k_r`` the position
               halves before softplus; ``freqs`` [d_r] effective frequencies, or base
@@ -146,7 +150,8 @@ def pe_attention(
     if mask is not None:
         raise NotImplementedError("pe_attention is causal-only: an explicit mask is not supported (no fallback)")
     kwargs = dict(layout=layout, start_pos=start_pos, k_start_pos=k_start_pos, scale=scale, qk_norm=qk_norm,
-                  qk_norm_eps=qk_norm_eps, rotary_table=rotary_table, table_pos0=table_pos0, mscale=mscale,
+                  qk_norm_eps=qk_norm_eps, rotary_table=rotary_table, table_pos0=table_pos0,
+                  table_geometric=table_geometric, mscale=mscale,
                   alibi_slopes=alibi_slopes, floor_freq=floor_freq, normalize_coeffs=normalize_coeffs,
                   ceil_freq=ceil_freq, out=out, simt_check=simt_check, single_cta=single_cta, split_kv=split_kv,
                   split_blocks=split_blocks)
@@ -204,6 +209,7 @@ def _forward_impl(
     qk_norm_eps: float = 1e-6,
     rotary_table: torch.Tensor | None = None,
     table_pos0: int = 0,
+    table_geometric: bool = False,
     mscale: float = 1.0,
     alibi_slopes: torch.Tensor | None = None,
     freqs: torch.Tensor | None = None,
@@ -294,6 +300,8 @@ def _forward_impl(
         a.rotary_table = tab.data_ptr()
         a.table_pos0 = int(table_pos0)
         a.table_rows = tab.shape[0]
+        if table_geometric:
+            flags |= _lib.TABLE_GEOMETRIC
     if variant == "alibi":
         sl = _f32(alibi_slopes.reshape(-1), dev)
         keep.append(sl)

@@ -146,6 +146,37 @@ def test_split_kv_and_query_tiled_kernels_match_oracle_on_long_cache(fourier):
         assert (lse.cpu() - want_lse).abs().max().item() <= 2e-2, f"split_kv={split} (lse)"
 
 
+@pytest.mark.parametrize("d,Hkv,qk_norm,Sk", [(64, 4, False, 16384), (64, 2, True, 9000), (128, 4, True, 16384),
+                                              (128, 2, False, 4100)])
+def test_split_kv_rotary_with_a_geometric_table(d, Hkv, qk_norm, Sk):
+    """Rotary decode step with ``table_geometric``: the kernel fetches a key's (cos, sin) entries
+    every 16 tiles and advances them by the rotation of one tile in between.  Against the oracle
+    (which reads every table row) and against the same call without the flag."""
+    from pe_ablations_b200 import check_device_status, pe_attention
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(105)
+    B, H = 2, 8
+    mk = lambda S, h: torch.randn(B, S, h, d, generator=g).to(BF16)
+    q, k, v = mk(1, H), mk(Sk, Hkv), mk(Sk, Hkv)
+    table = O.rotary_table(O.rope_inv_freq(d), Sk)
+    f = lambda t: t.float()
+    want, want_lse = O.attention_core("rotary", f(q), f(k), f(v), dtype=BF16, table=table, table_pos0=0, pos0=Sk - 1,
+                                      k_pos0=0, qk_norm=qk_norm, return_lse=True)
+    c = lambda t: t.to(dev)
+    outs = []
+    for geometric in (True, False):
+        lse = torch.full((B, H, 1), float("nan"), device=dev)
+        got = pe_attention("rotary", c(q), c(k), c(v), rotary_table=table, table_pos0=0, table_geometric=geometric,
+                           start_pos=Sk - 1, k_start_pos=0, qk_norm=qk_norm, split_kv=True, lse=lse)
+        torch.cuda.synchronize()
+        check_device_status()
+        assert (got.float().cpu() - want.float()).abs().max().item() <= 2e-2, f"geometric={geometric}"
+        assert (lse.cpu() - want_lse).abs().max().item() <= 2e-2, f"geometric={geometric} (lse)"
+        outs.append(got.float())
+    assert (outs[0] - outs[1]).abs().max().item() <= 8e-3
+
+
 def test_split_kv_refuses_wide_calls():
     from pe_ablations_b200 import pe_attention
     from pe_ablations_b200._lib import PeAttnError
