@@ -325,6 +325,39 @@ int pe_rmsnorm_forward(const void* x, const float* weight, void* y, int dtype, i
                        int64_t y_stride, float eps, void* stream);
 int pe_swiglu_forward(const void* gate, const void* up, void* y, int dtype, int64_t n, void* stream);
 
+/* ---- the two GEMMs of the evaluation path whose results need not exist in HBM ------------------
+ *
+ * One persistent tcgen05 kernel (CTA pairs, 256 x 256 accumulator tiles in TMEM, TMA-staged
+ * operands) with the consumer of the product in its epilogue.  bf16 operands with K contiguous,
+ * 16-byte aligned bases, row strides that are multiples of 8 elements; fp32 accumulation.
+ * ``device_status`` as in pe_attn_args (may be null).
+ *
+ * pe_lm_head_ce_loss_sums replaces the language-model head followed by the cross-entropy
+ * (src/model/transformer.py:358-371, the evaluation's F.cross_entropy on the head's output):
+ *   logits = round_bf16(hidden [n_rows, hidden_dim] * weight [vocab, hidden_dim]^T)
+ *   out[0] += sum over scored rows of (logsumexp(logits[r, :]) - logits[r, targets[r]])
+ *   out[1] += number of scored rows (targets[r] != ignore_index)
+ * with the semantics of pe_ce_loss_sums for non-finite logits and out-of-range targets; the
+ * logits are never written.  ``workspace``: 256-byte aligned device buffer of
+ * pe_lm_head_ce_workspace_bytes(n_rows, vocab) bytes (per-tile partial results: 8 bytes per row
+ * and 256 vocabulary entries), used only by the call's own kernels; calls that share one must be
+ * ordered on one stream.
+ *
+ * pe_swiglu_gemm replaces the feed-forward's two input projections and SwiGLU
+ * (src/model/ffn.py:30-68): y [n_rows, ffn_dim] = cast(cast(silu(cast(x w_gate^T))) * cast(x w_up^T)),
+ * the roundings of the two bf16 projections followed by pe_swiglu_forward.  w_gate, w_up:
+ * [ffn_dim, hidden_dim] with one common row stride.
+ *
+ * pe_gemm_nt: c [m, n] = cast(a [m, k] * b [n, k]^T), the same kernel with a plain store. */
+size_t pe_lm_head_ce_workspace_bytes(int n_rows, int vocab);
+int pe_lm_head_ce_loss_sums(const void* hidden, int64_t hidden_stride, const void* weight, int64_t weight_stride,
+                            const int64_t* targets, int n_rows, int hidden_dim, int vocab, int ignore_index,
+                            void* workspace, size_t workspace_bytes, double* out, int32_t* device_status, void* stream);
+int pe_swiglu_gemm(const void* x, int64_t x_stride, const void* w_gate, const void* w_up, int64_t w_stride, void* y,
+                   int64_t y_stride, int n_rows, int hidden_dim, int ffn_dim, int32_t* device_status, void* stream);
+int pe_gemm_nt(const void* a, int64_t a_stride, const void* b, int64_t b_stride, void* c, int64_t c_stride, int m, int n,
+               int k, int32_t* device_status, void* stream);
+
 /* Same computation as pe_ce_loss_sums for callers that must not allocate.  No counterpart
  * in the reference.
  *

@@ -32,6 +32,7 @@ EXPORTS = (
     "pe_pope_expand", "pe_pope_expand_backward", "pe_rotary_norm_expand", "pe_rotary_norm_expand_backward",
     "pe_fope_effective_freqs", "pe_fope_effective_freqs_backward",
     "pe_attn_decode_workspace_bytes", "pe_attn_decode", "pe_attn_forward_workspace_bytes",
+    "pe_lm_head_ce_workspace_bytes", "pe_lm_head_ce_loss_sums", "pe_swiglu_gemm", "pe_gemm_nt",
 )
 
 
@@ -133,6 +134,18 @@ def _load() -> C.CDLL:
     lib.pe_rotary_norm_expand_backward.argtypes = [C.c_void_p, C.c_int, S3, C.c_void_p, S3, C.c_void_p, S3, C.c_int,
                                                    C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_float,
                                                    C.c_int, C.c_float, C.c_void_p]
+    lib.pe_lm_head_ce_workspace_bytes.restype = C.c_size_t
+    lib.pe_lm_head_ce_workspace_bytes.argtypes = [C.c_int, C.c_int]
+    lib.pe_lm_head_ce_loss_sums.restype = C.c_int
+    lib.pe_lm_head_ce_loss_sums.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_int,
+                                            C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p,
+                                            C.c_void_p]
+    lib.pe_swiglu_gemm.restype = C.c_int
+    lib.pe_swiglu_gemm.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
+                                   C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+    lib.pe_gemm_nt.restype = C.c_int
+    lib.pe_gemm_nt.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int, C.c_int,
+                               C.c_int, C.c_void_p, C.c_void_p]
     lib.pe_ce_static_max_rows.restype = C.c_int
     lib.pe_ce_loss_sums_static.restype = C.c_int
     lib.pe_ce_loss_sums_static.argtypes = [C.c_void_p, C.c_int, C.c_int64, C.c_void_p, C.c_int, C.c_int, C.c_int,

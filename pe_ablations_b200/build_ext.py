@@ -16,7 +16,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libpe_attn.so")
 SOURCES = ["pe_attn_abi.cu", "pe_attn_simt.cu", "pe_attn_tc.cu", "pe_attn_tc2.cu", "pe_attn_tc4.cu", "pe_attn_ce.cu", "pe_attn_elementwise.cu",
-           "pe_attn_bwd.cu", "pe_attn_bwd_simt.cu", "pe_attn_xform.cu", "pe_attn_decode.cu"]
+           "pe_attn_bwd.cu", "pe_attn_bwd_simt.cu", "pe_attn_xform.cu", "pe_attn_decode.cu", "pe_attn_gemm.cu"]
 HEADERS = ["pe_attn_common.cuh", "pe_attn_ptx.cuh", "pe_attn_tc_common.cuh", os.path.join("..", "..", "include", "pe_attn.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

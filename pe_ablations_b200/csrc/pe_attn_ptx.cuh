@@ -252,6 +252,12 @@ __device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cbar, uin
   asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cbar), "r"(bytes)
                : "memory");
 }
+// Same without release semantics, for producers whose arrival only announces bytes that a TMA
+// copy will deliver (nothing written by the arriving thread has to become visible).
+__device__ __forceinline__ void mbar_arrive_expect_tx_cluster_relaxed(uint32_t cbar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.relaxed.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cbar), "r"(bytes)
+               : "memory");
+}
 // 4-D tiled load into THIS CTA's shared memory whose byte count is reported to a barrier that
 // may live in the other CTA of the pair
 __device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cbar, int c0, int c1,

@@ -246,7 +246,7 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const int n_top, float* 
         if (nt[i] == 0) continue;
         if (elect_one()) {
           const uint32_t qb = lbar(BAR_QFULL + i);
-          mbar_arrive_expect_tx_cluster(qb, C::NCC * C::Q_CHUNK_BYTES);
+          mbar_arrive_expect_tx_cluster_relaxed(qb, C::NCC * C::Q_CHUNK_BYTES);
 #pragma unroll
           for (int c = 0; c < C::NCC; ++c)
             tma_load_4d_pair(q_smem + i * C::Q_TILE_BYTES + c * C::Q_CHUNK_BYTES, &tmQ, qb, c * 64,
@@ -261,7 +261,7 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const int n_top, float* 
         if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_KEMPTY + s), ph ^ 1u))) { fail(ST_WAIT_KEMPTY); break; }
         if (elect_one()) {
           const uint32_t kb = lbar(BAR_KFULL + s);
-          mbar_arrive_expect_tx_cluster(kb, C::NCC * C::K_CHUNK_BYTES);
+          mbar_arrive_expect_tx_cluster_relaxed(kb, C::NCC * C::K_CHUNK_BYTES);
 #pragma unroll
           for (int c = 0; c < C::NCC; ++c)
             tma_load_4d_pair(k_smem + s * C::K_STAGE_BYTES + c * C::K_CHUNK_BYTES, &tmK, kb, c * 64,
@@ -280,7 +280,7 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const int n_top, float* 
       if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_VEMPTY + s), ph ^ 1u))) { fail(ST_WAIT_VEMPTY); break; }
       if (elect_one()) {
         const uint32_t vb = lbar(BAR_VFULL + s);
-        mbar_arrive_expect_tx_cluster(vb, C::V_STAGE_BYTES);
+        mbar_arrive_expect_tx_cluster_relaxed(vb, C::V_STAGE_BYTES);
         tma_load_4d_pair(v_smem + s * C::V_STAGE_BYTES, &tmV, vb, (int)rank * 64, (jb + j) * BLOCK_N, hk, b);
       }
       __syncwarp();

@@ -88,6 +88,18 @@ class TokenEmbedding(nn.Module):
         return self.embedding(ids)
 
 
+def _fused_gemm_ok(x: torch.Tensor, *weights: torch.Tensor) -> bool:
+    """Inference on bf16 activations with weights already stored in bf16 (``cast_matmul_weights``):
+    the cases the tensor-core GEMM with a fused epilogue covers.  Everything else (training,
+    fp32, fp32 weights under autocast) takes the library GEMM and the stand-alone kernels."""
+    if not x.is_cuda or x.dtype != torch.bfloat16 or torch.is_grad_enabled() and (
+            x.requires_grad or any(w.requires_grad for w in weights)):
+        return False
+    k = x.shape[-1]
+    return k >= 64 and k % 8 == 0 and all(
+        w.dtype == torch.bfloat16 and w.is_contiguous() and w.shape[0] % 8 == 0 and w.shape[1] == k for w in weights)
+
+
 class FeedForward(nn.Module):
     """SwiGLU: w2(silu(w3 x) * w1 x)."""
 
@@ -98,6 +110,11 @@ class FeedForward(nn.Module):
         self.w3 = nn.Linear(hidden_dim, ffn_dim, bias=False)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if _fused_gemm_ok(x, self.w3.weight, self.w1.weight):
+            # both input projections and SwiGLU in one tensor-core kernel: gate and up never exist
+            from .ops import swiglu_gemm
+
+            return self.w2(swiglu_gemm(x, self.w3.weight, self.w1.weight))
         gate, up = self.w3(x), self.w1(x)
         if gate.is_cuda and not (torch.is_grad_enabled() and gate.requires_grad) and gate.numel() % 8 == 0 \
                 and gate.dtype in (torch.bfloat16, torch.float32):
@@ -197,16 +214,23 @@ class Transformer(nn.Module):
                   chunk_tokens: int = 8192) -> tuple[torch.Tensor, torch.Tensor]:
         """(sum of next-token NLLs, number of scored tokens) for a batch, both fp64 scalars on device.
 
-        The language-model head and the cross-entropy run over ``chunk_tokens`` positions at a
-        time, so the [tokens, vocab] logits never exist in full (1 GB per 16k sequence at the
-        1B shape otherwise).  mean loss = nll_sum / count, perplexity = exp of it.
+        bf16 inference with bf16 weights: one tensor-core kernel computes the head's logits tile by
+        tile and reduces them to the loss in its epilogue (``ops.lm_head_ce_loss_sums``).  Otherwise
+        the head and the cross-entropy kernel run over ``chunk_tokens`` positions at a time, so the
+        [tokens, vocab] logits never exist in full (1 GB per 16k sequence at the 1B shape).
+        mean loss = nll_sum / count, perplexity = exp of it.
         """
-        from .ops import ce_loss_sums
+        from .ops import ce_loss_sums, lm_head_ce_loss_sums
 
         labels = input_ids if labels is None else labels
         h = self.hidden_states(input_ids, start_pos)[:, :-1].reshape(-1, self.config.hidden_dim)
         tgt = labels[:, 1:].reshape(-1)
         sums = torch.zeros(2, dtype=torch.float64, device=h.device)
+        if _fused_gemm_ok(h, self.output.weight):
+            # head GEMM with the cross-entropy in its epilogue: no logits at all
+            for i in range(0, h.shape[0], 65536):
+                lm_head_ce_loss_sums(h[i:i + 65536], self.output.weight, tgt[i:i + 65536], out=sums)
+            return sums[0], sums[1]
         for i in range(0, h.shape[0], chunk_tokens):
             # logits stay in the head's output dtype (bf16 under autocast); the loss kernel
             # reads them once and accumulates in fp32 / fp64

@@ -665,6 +665,102 @@ def ce_loss_sums(logits: torch.Tensor, targets: torch.Tensor, out: torch.Tensor 
     return out
 
 
+def _bf16_matrix(name: str, t: torch.Tensor) -> torch.Tensor:
+    """[rows, K] bf16 CUDA view the tensor-core GEMM can read in place (TMA: 16-byte aligned rows)."""
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: there is no CPU path")
+    if t.dtype != torch.bfloat16:
+        raise TypeError(f"{name} must be bf16 (got {t.dtype})")
+    t = t.reshape(-1, t.shape[-1])
+    if t.stride(1) != 1 or t.stride(0) % 8 != 0 or t.data_ptr() % 16 != 0:
+        t = t.contiguous()
+    return t
+
+
+_head_ws: dict[tuple[int, int], torch.Tensor] = {}     # (device, stream) -> workspace, bounded like _ce_scratch
+
+
+def lm_head_ce_loss_sums(hidden: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor,
+                         out: torch.Tensor | None = None, ignore_index: int = -100) -> torch.Tensor:
+    """``ce_loss_sums(hidden @ weight.T, targets)`` without the logits: the head GEMM runs on the
+    tensor cores with the cross-entropy in its epilogue (src/model/transformer.py:358-371).
+
+    hidden: CUDA bf16 [n, hidden_dim]; weight: CUDA bf16 [vocab, hidden_dim]; targets: CUDA int64 [n];
+    out: CUDA float64 [2] (sum of NLLs, scored rows), accumulated, created zeroed if None.
+    Logits are rounded to bf16 before the loss, as the head's autocast output is.
+    """
+    h = _bf16_matrix("hidden", hidden)
+    w = _bf16_matrix("weight", weight)
+    if h.shape[1] != w.shape[1]:
+        raise ValueError("hidden and weight disagree on hidden_dim")
+    n, vocab = h.shape[0], w.shape[0]
+    targets = targets.reshape(-1).to(torch.int64).contiguous()
+    if targets.numel() != n:
+        raise ValueError("targets must have one entry per row of hidden")
+    dev = h.device
+    if out is None:
+        out = torch.zeros(2, dtype=torch.float64, device=dev)
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev)
+        need = _lib.lib.pe_lm_head_ce_workspace_bytes(n, vocab)
+        key = (dev.index if dev.index is not None else torch.cuda.current_device(), stream.cuda_stream)
+        ws = _head_ws.get(key)
+        if ws is None or ws.numel() < need:
+            ws = torch.empty(need, dtype=torch.uint8, device=dev)
+            _head_ws.pop(key, None)
+            while len(_head_ws) >= _CE_SCRATCH_MAX:
+                _head_ws.pop(next(iter(_head_ws)))
+            _head_ws[key] = ws
+        rc = _lib.lib.pe_lm_head_ce_loss_sums(h.data_ptr(), h.stride(0), w.data_ptr(), w.stride(0), targets.data_ptr(),
+                                              n, h.shape[1], vocab, int(ignore_index), ws.data_ptr(), ws.numel(),
+                                              out.data_ptr(), device_status(dev).data_ptr(),
+                                              C.c_void_p(stream.cuda_stream))
+    if rc != 0:
+        raise _lib.PeAttnError(rc)
+    for t in (h, w, targets):
+        t.record_stream(stream)
+    return out
+
+
+def swiglu_gemm(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """cast(cast(silu(x @ w_gate.T)) * (x @ w_up.T)) in one tensor-core kernel: the feed-forward's
+    two input projections with SwiGLU in the epilogue (src/model/ffn.py:30-68), so the two
+    [tokens, ffn_dim] projections are never written.  bf16; w_gate, w_up: [ffn_dim, hidden_dim]."""
+    x2 = _bf16_matrix("x", x)
+    wg, wu = _bf16_matrix("w_gate", w_gate), _bf16_matrix("w_up", w_up)
+    if wg.shape != wu.shape or wg.stride(0) != wu.stride(0) or wg.shape[1] != x2.shape[1]:
+        raise ValueError("w_gate and w_up must be [ffn_dim, hidden_dim] with equal strides")
+    y = torch.empty(x2.shape[0], wg.shape[0], dtype=torch.bfloat16, device=x2.device)
+    with torch.cuda.device(x2.device):
+        stream = torch.cuda.current_stream(x2.device)
+        rc = _lib.lib.pe_swiglu_gemm(x2.data_ptr(), x2.stride(0), wg.data_ptr(), wu.data_ptr(), wg.stride(0),
+                                     y.data_ptr(), y.stride(0), x2.shape[0], x2.shape[1], wg.shape[0],
+                                     device_status(x2.device).data_ptr(), C.c_void_p(stream.cuda_stream))
+    if rc != 0:
+        raise _lib.PeAttnError(rc)
+    for t in (x2, wg, wu):
+        t.record_stream(stream)
+    return y.view(*x.shape[:-1], wg.shape[0])
+
+
+def gemm_nt(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """a @ b.T for bf16 [m, k] and [n, k] on the same kernel with the plain store epilogue."""
+    a2, b2 = _bf16_matrix("a", a), _bf16_matrix("b", b)
+    if a2.shape[1] != b2.shape[1]:
+        raise ValueError("a and b disagree on k")
+    c = torch.empty(a2.shape[0], b2.shape[0], dtype=torch.bfloat16, device=a2.device)
+    with torch.cuda.device(a2.device):
+        stream = torch.cuda.current_stream(a2.device)
+        rc = _lib.lib.pe_gemm_nt(a2.data_ptr(), a2.stride(0), b2.data_ptr(), b2.stride(0), c.data_ptr(), c.stride(0),
+                                 a2.shape[0], b2.shape[0], a2.shape[1], device_status(a2.device).data_ptr(),
+                                 C.c_void_p(stream.cuda_stream))
+    if rc != 0:
+        raise _lib.PeAttnError(rc)
+    for t in (a2, b2):
+        t.record_stream(stream)
+    return c.view(*a.shape[:-1], b2.shape[0])
+
+
 def _dtype_code(t: torch.Tensor) -> int:
     if t.dtype == torch.bfloat16:
         return _lib.BF16

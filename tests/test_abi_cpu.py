@@ -202,3 +202,34 @@ def test_decode_entry_plans_and_rejects_without_touching_the_gpu(L):
     assert L.lib.pe_attn_decode(C.byref(one_token), None, 0, None) == 1            # null workspace
     assert L.lib.pe_attn_decode(C.byref(_valid_args(L, Sq=9)), None, 0, None) == 3  # shape
     assert L.lib.pe_attn_decode(None, None, 0, None) == 1
+
+
+def test_fused_gemm_entries_plan_and_reject_without_touching_the_gpu(L):
+    """The head + cross-entropy workspace is host arithmetic; all three GEMM entry points check
+    pointers, shapes and alignment before any CUDA call."""
+    ws = L.lib.pe_lm_head_ce_workspace_bytes
+    # counter block + row losses + target logits + (max, sum) per row and 256 vocabulary entries
+    assert ws(16383, 32000) == 256 + 2 * 16384 * 4 + 125 * 16384 * 8
+    assert ws(1, 1) == 256 + 2 * 1024 + 256 * 8 and ws(0, 32000) == 0 and ws(16, 0) == 0
+    head = L.lib.pe_lm_head_ce_loss_sums
+    ok = dict(h=0x10000, hs=2048, w=0x20000, wsd=2048, t=0x30000, n=512, k=2048, v=32000, ig=-100, buf=0x40000,
+              nbytes=ws(512, 32000), out=0x50000)
+
+    def call(**over):
+        a = dict(ok, **over)
+        return head(a["h"], a["hs"], a["w"], a["wsd"], a["t"], a["n"], a["k"], a["v"], a["ig"], a["buf"], a["nbytes"],
+                    a["out"], None, None)
+
+    assert call(t=None) == 1 and call(buf=None) == 1 and call(out=None) == 1 and call(h=None) == 1
+    assert call(n=0) == 3 and call(k=100) == 3 and call(v=0) == 3
+    assert call(hs=2044) == 4 and call(h=0x10008) == 4 and call(buf=0x40010) == 4 and call(hs=1024) == 4
+    assert call(nbytes=ws(512, 32000) - 1) == 3 and b"smaller than" in L.lib.pe_attn_last_error()
+    sw = L.lib.pe_swiglu_gemm
+    assert sw(0x10000, 2048, 0x20000, 0x30000, 2048, None, 5632, 256, 2048, 5632, None, None) == 1
+    assert sw(0x10000, 2048, 0x20000, None, 2048, 0x40000, 5632, 256, 2048, 5632, None, None) == 1
+    assert sw(0x10000, 2048, 0x20000, 0x30000, 2048, 0x40000, 5632, 0, 2048, 5632, None, None) == 3
+    assert sw(0x10000, 2048, 0x20000, 0x30000, 2048, 0x40000, 5630, 256, 2048, 5632, None, None) == 4
+    nt = L.lib.pe_gemm_nt
+    assert nt(0x10000, 2048, 0x20000, 2048, None, 512, 256, 512, 2048, None, None) == 1
+    assert nt(0x10000, 2048, 0x20000, 2048, 0x30000, 512, 256, 500, 2048, None, None) == 3
+    assert nt(0x10004, 2048, 0x20000, 2048, 0x30000, 512, 256, 512, 2048, None, None) == 4
