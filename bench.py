@@ -323,6 +323,7 @@ def run_ours(args) -> dict:
         t = run_training(sub)
         line["training"] = {"workload": t["config"]["workload"], "tflops": t["value"], "ms_per_step": t["ms_per_step"],
                             "backward_kernel": t["backward_kernel"]}
+        line["fused_gemms"] = run_gemm(sub)["rows"]
     if world > 1:
         dist.destroy_process_group()
     return line if rank == 0 else None
@@ -618,6 +619,86 @@ def run_decode(args) -> dict:
     }
 
 
+def run_gemm(args) -> dict:
+    """Secondary workload (``--workload gemm``): the two fused GEMMs of the 1B-shape evaluation,
+    16 384 tokens, against the library GEMM + stand-alone kernel they replace, and the plain-store
+    form of the same kernel against the library GEMM.  One GPU, CUDA events, L2 flushed."""
+    import torch
+
+    import pe_ablations_b200 as P
+    from pe_ablations_b200 import ops
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    peak, peak_src = measured_peak()
+    g = torch.Generator().manual_seed(0)
+    M, K, FFN, V = 16384, 2048, 5632, 32000
+    mk = lambda r, c, s: (torch.randn(r, c, generator=g) * s).to(torch.bfloat16).to(dev)
+    x, wg, wu, wv = mk(M, K, 1.0), mk(FFN, K, 0.02), mk(FFN, K, 0.02), mk(V, K, 0.02)
+    tgt = torch.randint(0, V, (M,), generator=g).to(dev)
+    sums = torch.zeros(2, dtype=torch.float64, device=dev)
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 3)):
+            flush.zero_()
+            fn()
+        torch.cuda.synchronize()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        for e0, e1 in ev:
+            flush.zero_()
+            e0.record()
+            fn()
+            e1.record()
+        torch.cuda.synchronize()
+        return statistics.mean(e0.elapsed_time(e1) for e0, e1 in ev)
+
+    def library_head():
+        for i in range(0, M, 8192):
+            ops.ce_loss_sums(x[i:i + 8192] @ wv.T, tgt[i:i + 8192], out=sums)
+
+    rows = []
+    with torch.no_grad():
+        for name, flops, fused, library, what in (
+                ("lm head + cross-entropy", 2.0 * M * V * K, lambda: ops.lm_head_ce_loss_sums(x, wv, tgt, out=sums),
+                 library_head, "library GEMM (8192-token chunks) + pe_ce_loss_sums"),
+                ("w3 | w1 projections + SwiGLU", 4.0 * M * FFN * K, lambda: ops.swiglu_gemm(x, wg, wu),
+                 lambda: ops.swiglu(x @ wg.T, x @ wu.T), "two library GEMMs + pe_swiglu_forward"),
+                ("plain store, N = 2048", 2.0 * M * 2048 * K, lambda: ops.gemm_nt(x, wv[:2048]),
+                 lambda: x @ wv[:2048].T, "library GEMM")):
+            ms, ms_lib = timed(fused), timed(library)
+            tf = flops / (ms * 1e-3) / 1e12
+            rows.append({"op": name, "shape": f"M{M} K{K}", "ms": round(ms, 4), "tflops": round(tf, 1),
+                         "frac_of_peak": round(tf / peak, 4), "replaces": what, "replaced_ms": round(ms_lib, 4),
+                         "speedup": round(ms_lib / ms, 3)})
+    P.check_device_status()
+    trace = None
+    from pe_ablations_b200 import _lib
+
+    if hasattr(_lib.lib, "pe_gemm_trace_read"):
+        # a library built with -DPE_GEMM_TRACE: clocks per CTA each role spent waiting / issuing
+        import ctypes
+
+        import numpy as np
+
+        buf = np.zeros(148 * 16, dtype=np.int64)
+        _lib.lib.pe_gemm_trace_read(buf.ctypes.data_as(ctypes.c_void_p), 1)
+        with torch.no_grad():
+            ops.gemm_nt(x, wv)
+        _lib.lib.pe_gemm_trace_read(buf.ctypes.data_as(ctypes.c_void_p), 1)
+        t = buf.reshape(148, 16)
+        names = ("producer_total", "producer_wait_free_stage", "producer_issue", "mma_total", "mma_wait_full_stage",
+                 "mma_wait_free_accumulator", "epilogue_total", "epilogue_wait_full_accumulator")
+        trace = {"launch": f"plain store, M{M} N{V} K{K}",
+                 "leader_ctas": {n: int(t[0::2, i].mean()) for i, n in enumerate(names)},
+                 "peer_ctas": {n: int(t[1::2, i].mean()) for i, n in enumerate(names)}}
+    return {"metric": "fused GEMMs of the 1B-shape evaluation (16 384 tokens)", "trace_clocks": trace, "n_gpus": 1, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "dtype": "bf16", "data": "synthetic",
+            "peak": {"tflops": peak, "source": peak_src}, "rows": rows,
+            "config": {"workload": "pe_gemm_pair_kernel: head + cross-entropy, SwiGLU feed-forward input, plain store",
+                       "l2": "flushed between steps by writing a 256 MiB buffer"}}
+
+
 def run_variants(args) -> dict:
     """Secondary workload (``--workload variants``): the fused forward of every positional-encoding
     variant at the configuration the benchmark list gives it (configurations 1-4; NoPE and ALiBi
@@ -858,10 +939,11 @@ def main():
     ap.add_argument("--decode-cache", type=int, default=16384, help="cached keys per sequence in the decode workload")
     ap.add_argument("--case", default="pair_fpope", choices=sorted(PROFILE_CASES),
                     help="--workload profile: which small case to launch (for an ncu capture of one kernel)")
-    ap.add_argument("--workload", default="forward", choices=["forward", "training", "variants", "decode", "profile"],
+    ap.add_argument("--workload", default="forward", choices=["forward", "training", "variants", "decode", "profile", "gemm"],
                     help="forward: the headline benchmark; training: forward+backward of the attention op (1 GPU); "
                          "variants: the forward of every variant at its benchmark configuration (1 GPU); "
-                         "decode: one generated token against a long cache, split-KV kernel (1 GPU)")
+                         "decode: one generated token against a long cache, split-KV kernel (1 GPU); "
+                         "gemm: the evaluation's fused GEMMs against the library path they replace (1 GPU)")
     ap.add_argument("--train-batch", type=int, default=64)
     ap.add_argument("--train-seq", type=int, default=512)
     args = ap.parse_args()
@@ -873,6 +955,8 @@ def main():
         line = run_variants(args)
     elif args.workload == "decode" and args.impl == "ours":
         line = run_decode(args)
+    elif args.workload == "gemm" and args.impl == "ours":
+        line = run_gemm(args)
     else:
         line = run_reference(args) if args.impl == "reference" else run_ours(args)
     if line is not None:

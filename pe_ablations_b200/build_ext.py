@@ -38,9 +38,12 @@ def _stale(target: str, deps: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps if os.path.exists(d))
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile (if stale) and return the path of the shared library."""
+def build(force: bool = False, verbose: bool = False, defines: tuple[str, ...] = ()) -> str:
+    """Compile (if stale) and return the path of the shared library.  ``defines`` adds -D macros
+    to a forced build (e.g. ``PE_GEMM_TRACE``: per-role clock counters in the GEMM kernel, read
+    by ``bench.py --workload gemm``); rebuild with ``--force`` afterwards to drop them."""
     nvcc = _nvcc()
+    force = force or bool(defines)
     srcs = [s for s in SOURCES if os.path.exists(os.path.join(CSRC, s))]
     hdrs = [os.path.join(CSRC, h) for h in HEADERS]
     objs = []
@@ -50,7 +53,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         obj = os.path.join(CSRC, s.replace(".cu", ".o"))
         objs.append(obj)
         if force or _stale(obj, [src] + hdrs):
-            cmd = [nvcc, *NVCC_FLAGS, "-c", src, "-o", obj]
+            cmd = [nvcc, *NVCC_FLAGS, *[f"-D{d}" for d in defines], "-c", src, "-o", obj]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             procs.append((s, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
@@ -70,4 +73,5 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv,
+                defines=tuple(a[2:] for a in sys.argv[1:] if a.startswith("-D"))))

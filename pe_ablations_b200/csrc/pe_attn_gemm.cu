@@ -185,7 +185,11 @@ pe_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA,
           const uint32_t dst = stage0 + (uint32_t)(s * G_STAGE_BYTES);
           // relaxed: the arrival publishes nothing this thread wrote (the tile comes through the
           // async proxy and its complete_tx); with .release each arrival cost about 600 clocks
+#ifdef PE_GEMM_RELEASE_ARRIVE   // the slow form, kept so that the measurement can be repeated
+          mbar_arrive_expect_tx_cluster(fb, G_STAGE_BYTES);
+#else
           mbar_arrive_expect_tx_cluster_relaxed(fb, G_STAGE_BYTES);
+#endif
           tma_load_4d_pair(dst, &tmA, fb, ks * G_BK, a_row, 0, 0);
           tma_load_4d_pair(dst + G_A_BYTES, mapB, fb, ks * G_BK, b_row, 0, 0);
         }
