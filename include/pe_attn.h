@@ -348,15 +348,18 @@ int pe_swiglu_forward(const void* gate, const void* up, void* y, int dtype, int6
  * the roundings of the two bf16 projections followed by pe_swiglu_forward.  w_gate, w_up:
  * [ffn_dim, hidden_dim] with one common row stride.
  *
- * pe_gemm_nt: c [m, n] = cast(a [m, k] * b [n, k]^T), the same kernel with a plain store. */
+ * pe_gemm_nt: c [m, n] = cast(a [m, k] * b [n, k]^T), the same kernel with a plain store; with
+ * ``residual`` [m, n] (may be null; may be ``c`` itself) c = cast(cast(a b^T) + residual), the
+ * output projection (wo, w2) together with the block's residual add
+ * (src/model/transformer.py:176-177). */
 size_t pe_lm_head_ce_workspace_bytes(int n_rows, int vocab);
 int pe_lm_head_ce_loss_sums(const void* hidden, int64_t hidden_stride, const void* weight, int64_t weight_stride,
                             const int64_t* targets, int n_rows, int hidden_dim, int vocab, int ignore_index,
                             void* workspace, size_t workspace_bytes, double* out, int32_t* device_status, void* stream);
 int pe_swiglu_gemm(const void* x, int64_t x_stride, const void* w_gate, const void* w_up, int64_t w_stride, void* y,
                    int64_t y_stride, int n_rows, int hidden_dim, int ffn_dim, int32_t* device_status, void* stream);
-int pe_gemm_nt(const void* a, int64_t a_stride, const void* b, int64_t b_stride, void* c, int64_t c_stride, int m, int n,
-               int k, int32_t* device_status, void* stream);
+int pe_gemm_nt(const void* a, int64_t a_stride, const void* b, int64_t b_stride, void* c, int64_t c_stride,
+               const void* residual, int64_t residual_stride, int m, int n, int k, int32_t* device_status, void* stream);
 
 /* Same computation as pe_ce_loss_sums for callers that must not allocate.  No counterpart
  * in the reference.

@@ -144,8 +144,8 @@ def _load() -> C.CDLL:
     lib.pe_swiglu_gemm.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
                                    C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
     lib.pe_gemm_nt.restype = C.c_int
-    lib.pe_gemm_nt.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int, C.c_int,
-                               C.c_int, C.c_void_p, C.c_void_p]
+    lib.pe_gemm_nt.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
+                               C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
     lib.pe_ce_static_max_rows.restype = C.c_int
     lib.pe_ce_loss_sums_static.restype = C.c_int
     lib.pe_ce_loss_sums_static.argtypes = [C.c_void_p, C.c_int, C.c_int64, C.c_void_p, C.c_int, C.c_int, C.c_int,

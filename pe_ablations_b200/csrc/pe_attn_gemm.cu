@@ -65,6 +65,8 @@ struct GemmParams {
   int gm, pn, rounds, n_iter;   // tile order, see tile_of()
   __nv_bfloat16* out;           // EPI_STORE [M, N], EPI_SWIGLU [M, N / 2]
   long long out_stride;         // elements
+  const __nv_bfloat16* residual; // EPI_STORE, optional [M, N]: C = cast(cast(A B^T) + residual)
+  long long res_stride;
   const long long* targets;     // EPI_CE [M]
   int vocab;                    // EPI_CE: columns >= vocab are padding
   float2* part;                 // EPI_CE [n_ntile][m_pad]: (max, sum of exp(x - max)) per row and tile
@@ -80,6 +82,12 @@ struct GemmParams {
 // row block changing fastest instead, every tile streamed A through L2 and three in ten sectors
 // came from the far half: 0.75 PFLOP/s, whatever the number of stages.)
 __device__ __forceinline__ bool tile_of(const GemmParams& p, int pair, int it, int& mb, int& nb) {
+  if (p.gm == 0) {   // round robin over all pairs, row block fastest
+    const int t = pair + it * p.pn;
+    mb = t % p.n_mblk;
+    nb = t / p.n_mblk;
+    return t < p.n_mblk * p.n_ntile;
+  }
   const int i = pair % p.gm, j = pair / p.gm;
   const int sb = it / p.rounds, r = it - sb * p.rounds;
   mb = sb * p.gm + i;
@@ -350,6 +358,29 @@ pe_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA,
             tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; i += 2) w[i >> 1] = pack_bf16x2(__uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+            if (p.residual != nullptr && row_ok && c0 + c * 32 + 32 <= n_out) {
+              // the residual stream's add (h = x + wo(..), out = h + w2(..)), rounded like the
+              // bf16 add of the projection's bf16 output it replaces
+              const uint4* rp = reinterpret_cast<const uint4*>(p.residual + (size_t)row * p.res_stride + c0 + c * 32);
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) {
+                const uint4 rv = __ldg(rp + q4);
+                const uint32_t rr[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const uint32_t cw = w[q4 * 4 + e];
+                  w[q4 * 4 + e] = pack_bf16x2(bf16_lo(cw) + bf16_lo(rr[e]), bf16_hi(cw) + bf16_hi(rr[e]));
+                }
+              }
+            } else if (p.residual != nullptr && row_ok) {
+              for (int i = 0; i < 32 && c0 + c * 32 + i < n_out; ++i) {
+                const float rv = __bfloat162float(p.residual[(size_t)row * p.res_stride + c0 + c * 32 + i]);
+                const uint32_t cw = w[i >> 1];
+                const float cv = (i & 1) ? bf16_hi(cw) : bf16_lo(cw);
+                const uint32_t nv = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(cv + rv));
+                w[i >> 1] = (i & 1) ? ((cw & 0xFFFFu) | (nv << 16)) : ((cw & 0xFFFF0000u) | nv);
+              }
+            }
           }
           if (row_ok) {
             const int col = c0 + c * 32;
@@ -372,7 +403,7 @@ pe_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA,
       // this warp is done with the accumulator: let the leader's MMA warp reuse it
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(lbar(GB_ACCEMPTY + buf));
+      if (lane == 0) mbar_arrive_cluster_relaxed(lbar(GB_ACCEMPTY + buf));   // TMEM reads, ordered by the tcgen05 fence
       ++it;
     }
     if (warp == 2) TR_ADD(6, TR_T() - tr0);
@@ -492,6 +523,18 @@ int launch_gemm(const GemmParams& p, const void* a, long long a_stride, const vo
       q.rounds = rounds;
       q.n_iter = (int)iters;
     }
+  }
+  // The grid of pairs leaves pairs idle when the column tiles do not divide (8 column tiles at
+  // N = 2048 use 64 of 74 pairs): beyond 8 % more iterations than a plain round robin over all
+  // tiles (row block fastest), take the round robin.  Where both fit, the grid is faster (the
+  // SwiGLU GEMM: 1 479 against 1 271 TFLOP/s), where it does not, the round robin is (N = 2048:
+  // 1 424 against 1 324).
+  const long long linear_iters = ((long long)p.n_mblk * p.n_ntile + pairs - 1) / pairs;
+  if (best * 100 > linear_iters * 108) {
+    q.gm = 0;
+    q.pn = pairs;
+    q.rounds = 1;
+    q.n_iter = (int)linear_iters;
   }
   kern<<<dim3((unsigned)(2 * pairs)), G_THREADS, G_SMEM, stream>>>(q, tmA, tmB, tmB2);
   const cudaError_t e = cudaGetLastError();
@@ -627,8 +670,8 @@ int pe_gemm_trace_read(long long* host, int clear) {
 }
 #endif
 
-int pe_gemm_nt(const void* a, int64_t a_stride, const void* b, int64_t b_stride, void* c, int64_t c_stride, int m, int n,
-               int k, int32_t* device_status, void* stream) {
+int pe_gemm_nt(const void* a, int64_t a_stride, const void* b, int64_t b_stride, void* c, int64_t c_stride,
+               const void* residual, int64_t residual_stride, int m, int n, int k, int32_t* device_status, void* stream) {
   if (c == nullptr) {
     set_error("c is null");
     return PE_ATTN_ERR_NULL;
@@ -640,6 +683,7 @@ int pe_gemm_nt(const void* a, int64_t a_stride, const void* b, int64_t b_stride,
   int rc = check_matrix("a", a, a_stride, k);
   if (rc == PE_ATTN_OK) rc = check_matrix("b", b, b_stride, k);
   if (rc == PE_ATTN_OK) rc = check_matrix("c", c, c_stride, n);
+  if (rc == PE_ATTN_OK && residual != nullptr) rc = check_matrix("residual", residual, residual_stride, n);
   if (rc != PE_ATTN_OK) return rc;
   GemmParams p{};
   p.M = m;
@@ -649,6 +693,8 @@ int pe_gemm_nt(const void* a, int64_t a_stride, const void* b, int64_t b_stride,
   p.n_ntile = (n + G_BN - 1) / G_BN;
   p.out = reinterpret_cast<__nv_bfloat16*>(c);
   p.out_stride = c_stride;
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  p.res_stride = residual_stride;
   p.status = device_status;
   return launch_gemm<EPI_STORE>(p, a, a_stride, b, b_stride, nullptr, n, static_cast<cudaStream_t>(stream));
 }

@@ -40,6 +40,17 @@
 
 #include "pe_attn_tc_common.cuh"
 
+// How the K-transform warps tell the leader's MMA warp that their rows of a K tile are in shared
+// memory.  Every lane has run fence.proxy.async after its stores and the warp has synchronised
+// before lane 0 arrives, so the rows are in this SM's shared memory (there is no cache between
+// the stores and the tensor core's reads) when the arrival leaves; the arrival itself is
+// relaxed because a release at cluster scope costs about 600 clocks per arrival, which sat on
+// the K-ready path of the variants that transform whole K rows (configuration 3: 678 -> 750
+// TFLOP/s).  -DPE_TC2_KFULL_ARRIVE=mbar_arrive_cluster restores the release.
+#ifndef PE_TC2_KFULL_ARRIVE
+#define PE_TC2_KFULL_ARRIVE mbar_arrive_cluster_relaxed
+#endif
+
 namespace pe_attn {
 namespace {
 
@@ -631,7 +642,7 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const int n_top, float* 
         }
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(s ? kfull1 : kfull);
+        if (lane == 0) PE_TC2_KFULL_ARRIVE(s ? kfull1 : kfull);
       }
     } else if constexpr (MODE == MODE_XFORM) {
       // raw rows and table entries of the next tile are requested before the wait for its stage
@@ -648,7 +659,7 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const int n_top, float* 
         xform_finish<DC>(p, xr, k_smem + s * C::K_STAGE_BYTES, C::K_CHUNK_BYTES, (jb + j) * BLOCK_N + rbase, p.Sk, tg);
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(lbar(BAR_KFULL + s));
+        if (lane == 0) PE_TC2_KFULL_ARRIVE(lbar(BAR_KFULL + s));
         if (j + 1 < n_tiles) xform_load_next<DC>(p, xr, cur, p.Sk, BLOCK_N);
       }
     }

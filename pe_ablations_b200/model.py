@@ -88,18 +88,6 @@ class TokenEmbedding(nn.Module):
         return self.embedding(ids)
 
 
-def _fused_gemm_ok(x: torch.Tensor, *weights: torch.Tensor) -> bool:
-    """Inference on bf16 activations with weights already stored in bf16 (``cast_matmul_weights``):
-    the cases the tensor-core GEMM with a fused epilogue covers.  Everything else (training,
-    fp32, fp32 weights under autocast) takes the library GEMM and the stand-alone kernels."""
-    if not x.is_cuda or x.dtype != torch.bfloat16 or torch.is_grad_enabled() and (
-            x.requires_grad or any(w.requires_grad for w in weights)):
-        return False
-    k = x.shape[-1]
-    return k >= 64 and k % 8 == 0 and all(
-        w.dtype == torch.bfloat16 and w.is_contiguous() and w.shape[0] % 8 == 0 and w.shape[1] == k for w in weights)
-
-
 class FeedForward(nn.Module):
     """SwiGLU: w2(silu(w3 x) * w1 x)."""
 
@@ -109,19 +97,18 @@ class FeedForward(nn.Module):
         self.w2 = nn.Linear(ffn_dim, hidden_dim, bias=False)
         self.w3 = nn.Linear(hidden_dim, ffn_dim, bias=False)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if _fused_gemm_ok(x, self.w3.weight, self.w1.weight):
-            # both input projections and SwiGLU in one tensor-core kernel: gate and up never exist
-            from .ops import swiglu_gemm
+    def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """``w2(silu(w3 x) * w1 x)``, plus ``residual`` when the block passes its stream in."""
+        from .ops import fused_gemm_ok, linear_residual, swiglu, swiglu_gemm
 
-            return self.w2(swiglu_gemm(x, self.w3.weight, self.w1.weight))
+        if fused_gemm_ok(x, self.w3.weight, self.w1.weight):
+            # both input projections and SwiGLU in one tensor-core kernel: gate and up never exist
+            return linear_residual(self.w2, swiglu_gemm(x, self.w3.weight, self.w1.weight), residual)
         gate, up = self.w3(x), self.w1(x)
         if gate.is_cuda and not (torch.is_grad_enabled() and gate.requires_grad) and gate.numel() % 8 == 0 \
                 and gate.dtype in (torch.bfloat16, torch.float32):
-            from .ops import swiglu
-
-            return self.w2(swiglu(gate, up))
-        return self.w2(F.silu(gate) * up)
+            return linear_residual(self.w2, swiglu(gate, up), residual)
+        return linear_residual(self.w2, F.silu(gate) * up, residual)
 
 
 def _build_pe(cfg: TransformerConfig):
@@ -173,8 +160,10 @@ class TransformerBlock(nn.Module):
         self.feed_forward = FeedForward(cfg.hidden_dim, cfg.resolved_ffn_dim())
 
     def forward(self, x: torch.Tensor, mask=None, start_pos: int = 0) -> torch.Tensor:
-        x = x + self.attention(self.attention_norm(x), mask, start_pos)
-        return x + self.feed_forward(self.ffn_norm(x))
+        # each block hands its residual stream to the output projection, which adds it (in the
+        # GEMM's epilogue for bf16 inference, as a separate add otherwise)
+        x = self.attention(self.attention_norm(x), mask, start_pos, residual=x)
+        return self.feed_forward(self.ffn_norm(x), residual=x)
 
 
 class Transformer(nn.Module):
@@ -226,7 +215,9 @@ class Transformer(nn.Module):
         h = self.hidden_states(input_ids, start_pos)[:, :-1].reshape(-1, self.config.hidden_dim)
         tgt = labels[:, 1:].reshape(-1)
         sums = torch.zeros(2, dtype=torch.float64, device=h.device)
-        if _fused_gemm_ok(h, self.output.weight):
+        from .ops import fused_gemm_ok
+
+        if fused_gemm_ok(h, self.output.weight):
             # head GEMM with the cross-entropy in its epilogue: no logits at all
             for i in range(0, h.shape[0], 65536):
                 lm_head_ce_loss_sums(h[i:i + 65536], self.output.weight, tgt[i:i + 65536], out=sums)

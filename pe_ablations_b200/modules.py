@@ -22,7 +22,7 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
-from .ops import pe_attention
+from .ops import linear_residual, pe_attention
 from .pe import alibi_slopes
 
 
@@ -84,7 +84,8 @@ class GroupedQueryAttention(nn.Module):
         self.qk_norm = QKNorm(self.head_dim) if use_qk_norm else None
         self.rope = rope
 
-    def forward(self, x: torch.Tensor, mask: torch.Tensor | None = None, start_pos: int = 0) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, mask: torch.Tensor | None = None, start_pos: int = 0,
+                residual: torch.Tensor | None = None) -> torch.Tensor:
         _check_call(x, mask)
         B, S, _ = x.shape
         q = self.wq(x).view(B, S, self.num_heads, self.head_dim)
@@ -105,7 +106,7 @@ class GroupedQueryAttention(nn.Module):
         out = pe_attention(variant, q.to(dt), k.to(dt), v.to(dt), start_pos=start_pos,
                            scale=1.0 / (self.head_dim ** 0.5), qk_norm=self.qk_norm is not None,
                            qk_norm_eps=self.qk_norm.eps if self.qk_norm is not None else 1e-6, **kw)
-        return self.wo(out.view(B, S, self.num_heads * self.head_dim).to(x.dtype))
+        return linear_residual(self.wo, out.view(B, S, self.num_heads * self.head_dim).to(x.dtype), residual)
 
 
 class ALiBiAttention(nn.Module):
@@ -125,7 +126,8 @@ class ALiBiAttention(nn.Module):
         self.qk_norm = QKNorm(self.head_dim) if use_qk_norm else None
         self.register_buffer("alibi_slopes", alibi_slopes(num_heads).view(1, num_heads, 1, 1))
 
-    def forward(self, x: torch.Tensor, mask: torch.Tensor | None = None, start_pos: int = 0) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, mask: torch.Tensor | None = None, start_pos: int = 0,
+                residual: torch.Tensor | None = None) -> torch.Tensor:
         _check_call(x, mask)
         B, S, _ = x.shape
         q = self.wq(x).view(B, S, self.num_heads, self.head_dim)
@@ -136,7 +138,7 @@ class ALiBiAttention(nn.Module):
                            qk_norm=self.qk_norm is not None,
                            qk_norm_eps=self.qk_norm.eps if self.qk_norm is not None else 1e-6,
                            alibi_slopes=self.alibi_slopes)
-        return self.wo(out.view(B, S, self.num_heads * self.head_dim).to(x.dtype))
+        return linear_residual(self.wo, out.view(B, S, self.num_heads * self.head_dim).to(x.dtype), residual)
 
 
 class FPoPEGroupedQueryAttention(nn.Module):
@@ -178,7 +180,8 @@ class FPoPEGroupedQueryAttention(nn.Module):
                         ceil_freq=pe.ceiling_freq if pe.use_ceiling else None)
         return dict(freqs=pe.effective_freqs, delta=pe.phase_bias)
 
-    def forward(self, x: torch.Tensor, mask: torch.Tensor | None = None, start_pos: int = 0) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, mask: torch.Tensor | None = None, start_pos: int = 0,
+                residual: torch.Tensor | None = None) -> torch.Tensor:
         _check_call(x, mask)
         B, S, _ = x.shape
         q_c = self.wq_c(x).view(B, S, self.num_heads, self.d_content)
@@ -192,7 +195,7 @@ class FPoPEGroupedQueryAttention(nn.Module):
         v = self.wv(x).view(B, S, self.num_kv_heads, self.head_dim)
         out = pe_attention("pope", q_c.to(dt), k_c.to(dt), v.to(dt), q_r=q_r, k_r=k_r, start_pos=start_pos,
                            scale=self.scale, **self._pe_args())
-        return self.wo(out.view(B, S, self.num_heads * self.head_dim).to(x.dtype))
+        return linear_residual(self.wo, out.view(B, S, self.num_heads * self.head_dim).to(x.dtype), residual)
 
 
 class FPoPEGroupedQueryAttentionWithCache(FPoPEGroupedQueryAttention):

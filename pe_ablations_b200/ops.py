@@ -665,6 +665,30 @@ def ce_loss_sums(logits: torch.Tensor, targets: torch.Tensor, out: torch.Tensor 
     return out
 
 
+def fused_gemm_ok(x: torch.Tensor, *weights: torch.Tensor) -> bool:
+    """Inference on bf16 activations with weights already stored in bf16
+    (``eval.cast_matmul_weights``): the cases the tensor-core GEMM with a fused epilogue covers.
+    Everything else (training, fp32, fp32 weights under autocast) takes the library GEMM and
+    the stand-alone kernels."""
+    if not x.is_cuda or x.dtype != torch.bfloat16 or torch.is_grad_enabled() and (
+            x.requires_grad or any(w.requires_grad for w in weights)):
+        return False
+    k = x.shape[-1]
+    return k >= 64 and k % 8 == 0 and all(
+        w.dtype == torch.bfloat16 and w.is_contiguous() and w.shape[0] % 8 == 0 and w.shape[1] == k for w in weights)
+
+
+def linear_residual(linear, y: torch.Tensor, residual: torch.Tensor | None) -> torch.Tensor:
+    """``linear(y)``, plus ``residual`` when given: the output projection of a block (wo, w2) and
+    the block's residual add (src/model/transformer.py:176-177).  bf16 inference with bf16 weights
+    and a bf16 residual runs as one tensor-core GEMM with the add in its epilogue."""
+    if residual is not None and residual.dtype == torch.bfloat16 and residual.shape[:-1] == y.shape[:-1] \
+            and linear.bias is None and fused_gemm_ok(y, linear.weight):
+        return gemm_nt(y, linear.weight, residual=residual)
+    out = linear(y)
+    return out if residual is None else residual + out
+
+
 def _bf16_matrix(name: str, t: torch.Tensor) -> torch.Tensor:
     """[rows, K] bf16 CUDA view the tensor-core GEMM can read in place (TMA: 16-byte aligned rows)."""
     if not t.is_cuda:
@@ -743,20 +767,28 @@ def swiglu_gemm(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor) -> to
     return y.view(*x.shape[:-1], wg.shape[0])
 
 
-def gemm_nt(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    """a @ b.T for bf16 [m, k] and [n, k] on the same kernel with the plain store epilogue."""
+def gemm_nt(a: torch.Tensor, b: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+    """a @ b.T for bf16 [.., k] and [n, k] on the same kernel with the plain store epilogue;
+    with ``residual`` [.., n] the result is cast(cast(a @ b.T) + residual): an output projection
+    (wo, w2) together with the block's residual add (src/model/transformer.py:176-177)."""
     a2, b2 = _bf16_matrix("a", a), _bf16_matrix("b", b)
     if a2.shape[1] != b2.shape[1]:
         raise ValueError("a and b disagree on k")
     c = torch.empty(a2.shape[0], b2.shape[0], dtype=torch.bfloat16, device=a2.device)
+    r2 = None
+    if residual is not None:
+        r2 = _bf16_matrix("residual", residual)
+        if r2.shape != c.shape:
+            raise ValueError("residual must have the shape of the result")
     with torch.cuda.device(a2.device):
         stream = torch.cuda.current_stream(a2.device)
         rc = _lib.lib.pe_gemm_nt(a2.data_ptr(), a2.stride(0), b2.data_ptr(), b2.stride(0), c.data_ptr(), c.stride(0),
+                                 None if r2 is None else r2.data_ptr(), 0 if r2 is None else r2.stride(0),
                                  a2.shape[0], b2.shape[0], a2.shape[1], device_status(a2.device).data_ptr(),
                                  C.c_void_p(stream.cuda_stream))
     if rc != 0:
         raise _lib.PeAttnError(rc)
-    for t in (a2, b2):
+    for t in (a2, b2) + (() if r2 is None else (r2,)):
         t.record_stream(stream)
     return c.view(*a.shape[:-1], b2.shape[0])
 

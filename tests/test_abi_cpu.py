@@ -230,6 +230,7 @@ def test_fused_gemm_entries_plan_and_reject_without_touching_the_gpu(L):
     assert sw(0x10000, 2048, 0x20000, 0x30000, 2048, 0x40000, 5632, 0, 2048, 5632, None, None) == 3
     assert sw(0x10000, 2048, 0x20000, 0x30000, 2048, 0x40000, 5630, 256, 2048, 5632, None, None) == 4
     nt = L.lib.pe_gemm_nt
-    assert nt(0x10000, 2048, 0x20000, 2048, None, 512, 256, 512, 2048, None, None) == 1
-    assert nt(0x10000, 2048, 0x20000, 2048, 0x30000, 512, 256, 500, 2048, None, None) == 3
-    assert nt(0x10004, 2048, 0x20000, 2048, 0x30000, 512, 256, 512, 2048, None, None) == 4
+    assert nt(0x10000, 2048, 0x20000, 2048, None, 512, None, 0, 256, 512, 2048, None, None) == 1
+    assert nt(0x10000, 2048, 0x20000, 2048, 0x30000, 512, None, 0, 256, 500, 2048, None, None) == 3
+    assert nt(0x10004, 2048, 0x20000, 2048, 0x30000, 512, None, 0, 256, 512, 2048, None, None) == 4
+    assert nt(0x10000, 2048, 0x20000, 2048, 0x30000, 512, 0x40000, 510, 256, 512, 2048, None, None) == 4   # residual stride

@@ -34,6 +34,22 @@ def test_gemm_nt_matches_fp32_matmul(m, n, k):
     assert (c.float() - want).abs().max().item() <= want.abs().max().item() * 2 ** -7
 
 
+@pytest.mark.parametrize("m,n,k", [(300, 520, 128), (2048, 2048, 512), (129, 264, 72)])
+def test_gemm_nt_adds_a_residual_like_a_bf16_add(m, n, k):
+    """cast(cast(a b^T) + residual): the projection's bf16 output added to a bf16 residual."""
+    from pe_ablations_b200 import check_device_status
+    from pe_ablations_b200.ops import gemm_nt
+
+    a, b, r = _rand((m, k), 31, 0.3), _rand((n, k), 32, 0.3), _rand((m, n), 33, 3.0)
+    c = gemm_nt(a, b, residual=r)
+    check_device_status()
+    want = ((a.float() @ b.float().T).to(BF16) + r).float()
+    assert (c.float() - want).abs().max().item() <= max(want.abs().max().item(), 1.0) * 2 ** -6
+    # in place on the residual stream: c may be the residual's own memory
+    same = gemm_nt(a, b)
+    assert torch.equal(gemm_nt(a, b, residual=torch.zeros_like(same)), same)
+
+
 def test_gemm_nt_reads_strided_views_in_place():
     """Operands that are column slices of wider buffers (row stride > k) and a leading batch dim."""
     from pe_ablations_b200 import check_device_status
@@ -111,6 +127,7 @@ def test_model_takes_the_fused_paths_for_bf16_inference_and_agrees_with_the_unfu
     from pe_ablations_b200 import check_device_status
     from pe_ablations_b200 import model as M
     from pe_ablations_b200.eval import cast_matmul_weights
+    from pe_ablations_b200.ops import fused_gemm_ok
 
     torch.manual_seed(21)
     cfg = M.TransformerConfig(vocab_size=1000, hidden_dim=128, num_layers=2, num_heads=2, num_kv_heads=1, head_dim=64,
@@ -125,11 +142,16 @@ def test_model_takes_the_fused_paths_for_bf16_inference_and_agrees_with_the_unfu
     x = _rand((2, 300, 128), 23)
     with torch.no_grad(), torch.autocast("cuda", dtype=BF16):
         ff16, ff32 = m16.layers[0].feed_forward, m32.layers[0].feed_forward
-        assert M._fused_gemm_ok(x, ff16.w3.weight, ff16.w1.weight) and not M._fused_gemm_ok(x, ff32.w3.weight)
+        assert fused_gemm_ok(x, ff16.w3.weight, ff16.w1.weight) and not fused_gemm_ok(x, ff32.w3.weight)
         y16, y32 = ff16(x), ff32(x)
+        r16, r32 = ff16(x, residual=x), ff32(x, residual=x)          # w2 with the block's residual add
+        b16, b32 = m16.layers[1](x), m32.layers[1](x)                # a whole block: wo and w2 add their residuals
         nll16, cnt16 = m16.loss_sums(ids)
         nll32, cnt32 = m32.loss_sums(ids)
     check_device_status()
     assert (y16.float() - y32.float()).abs().max().item() <= max(y32.float().abs().max().item(), 1.0) * 2 ** -6
+    for got, want in ((r16, r32), (b16, b32)):
+        assert got.dtype == want.dtype == BF16
+        assert (got.float() - want.float()).abs().max().item() <= max(want.float().abs().max().item(), 1.0) * 2 ** -6
     assert cnt16.item() == cnt32.item() == 2 * 299
     assert abs(nll16.item() - nll32.item()) <= 2e-3 * abs(nll32.item())
