@@ -47,6 +47,9 @@
 // relaxed because a release at cluster scope costs about 600 clocks per arrival, which sat on
 // the K-ready path of the variants that transform whole K rows (configuration 3: 678 -> 750
 // TFLOP/s).  -DPE_TC2_KFULL_ARRIVE=mbar_arrive_cluster restores the release.
+#ifndef PE_TC2_P_PARTS
+#define PE_TC2_P_PARTS 4   // 1, 2 or 4
+#endif
 #ifndef PE_TC2_KFULL_ARRIVE
 #define PE_TC2_KFULL_ARRIVE mbar_arrive_cluster_relaxed
 #endif
@@ -79,7 +82,7 @@ __host__ __device__ __forceinline__ int block_tiles(int sblk, int Sk, int causal
 
 enum : int {
   BAR_QFULL = 0, BAR_KFULL = 2, BAR_KEMPTY = 4, BAR_VFULL = 6, BAR_VEMPTY = 8, BAR_SFULL = 10, BAR_PREADY = 12,
-  BAR_ODONE = 14, BAR_MMADONE = 16, NUM_BARS = 17
+  BAR_ODONE = 14, BAR_MMADONE = 16, BAR_PHALF = 17, NUM_BARS = 23   // BAR_PHALF: up to three partial hand-offs x two tiles
 };
 
 template <int DC, int DR>
@@ -209,6 +212,7 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const int n_top, float* 
       mbar_init(bar(BAR_KFULL + i), 2 * (n_tma + n_xf));
       mbar_init(bar(BAR_VFULL + i), 2);
       mbar_init(bar(BAR_PREADY + i), 8);                   // 4 softmax warps x 2 CTAs
+      for (int part = 0; part < 3; ++part) mbar_init(bar(BAR_PHALF + 2 * part + i), 8);   // ... for the earlier parts of P
       mbar_init(bar(BAR_KEMPTY + i), 1);
       mbar_init(bar(BAR_VEMPTY + i), 1);
       mbar_init(bar(BAR_SFULL + i), 1);
@@ -355,6 +359,28 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const int n_top, float* 
 #pragma unroll
       for (int i = 0; i < Q_TILES; ++i) {
         if (j < nt[i]) {
+          // P arrives in PE_TC2_P_PARTS parts: the PV MMAs of a part run under the exponentials
+          // of the next one
+          const uint32_t d = tmem_base + 256u + (uint32_t)(i * DV);
+          const uint32_t a = tmem_base + (uint32_t)(i * BLOCK_N);
+          constexpr int KK_PART = (BLOCK_N / 16) / PE_TC2_P_PARTS;   // MMAs (16 keys each) per part of P
+#pragma unroll
+          for (int part = 0; part + 1 < PE_TC2_P_PARTS; ++part) {
+            if (!__all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_PHALF + 2 * part + i), (uint32_t)(j & 1)))) {
+              fail(ST_WAIT_PREADY);
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            if (elect_one()) {
+#pragma unroll
+              for (int kk = part * KK_PART; kk < (part + 1) * KK_PART; ++kk)
+                mma_ts_pair(d, a + (uint32_t)(kk * 8), advance_smem_desc(vd, (uint32_t)(kk * 16 * 128)), IDESC_PV,
+                            (j > 0 || kk > 0) ? 1u : 0u);
+            }
+            __syncwarp();
+          }
+          if (!ok) break;
           if (!__all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_PREADY + i), (uint32_t)(j & 1)))) {
             fail(ST_WAIT_PREADY);
             ok = false;
@@ -362,10 +388,8 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const int n_top, float* 
           }
           tc_fence_after_sync();
           if (elect_one()) {
-            const uint32_t d = tmem_base + 256u + (uint32_t)(i * DV);
-            const uint32_t a = tmem_base + (uint32_t)(i * BLOCK_N);
 #pragma unroll
-            for (int kk = 0; kk < BLOCK_N / 16; ++kk)
+            for (int kk = (PE_TC2_P_PARTS - 1) * KK_PART; kk < BLOCK_N / 16; ++kk)
               mma_ts_pair(d, a + (uint32_t)(kk * 8), advance_smem_desc(vd, (uint32_t)(kk * 16 * 128)), IDESC_PV,
                           (j > 0 || kk > 0) ? 1u : 0u);
             tc_commit_pair(bar(BAR_ODONE + i), BOTH);
@@ -423,6 +447,7 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const int n_top, float* 
       const uint32_t s_addr = tmem_base + lane_sel + (uint32_t)(i * BLOCK_N);
       const uint32_t o_addr = tmem_base + lane_sel + 256u + (uint32_t)(i * DV);
       const uint32_t pready = lbar(BAR_PREADY + i);
+      const uint32_t ppart = lbar(BAR_PHALF + i);   // part k's barrier is 2 * k barriers (16 bytes each step) further
 
 #pragma unroll 1
       for (int j = 0; j < ntile; ++j) {
@@ -514,6 +539,13 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const int n_top, float* 
             pk[(c >> 1) + 1] = pack_bf16x2(p23.x, p23.y);
           }
           tmem_st16(s_addr + cb * 16, pk);
+          // every BLOCK_N / PE_TC2_P_PARTS keys of P that are in TMEM are handed to the MMA warp
+          if (PE_TC2_P_PARTS > 1 && cb + 1 < BLOCK_N / 32 && (cb + 1) % (4 / PE_TC2_P_PARTS) == 0) {
+            tmem_wait_st();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster_relaxed(ppart + 16u * (uint32_t)((cb + 1) / (4 / PE_TC2_P_PARTS) - 1));
+          }
         }
         const float a0 = acc0.x, a1 = acc0.y, a2 = acc1.x, a3 = acc1.y;
         l_sum += (a0 + a1) + (a2 + a3);

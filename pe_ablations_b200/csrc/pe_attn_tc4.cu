@@ -51,7 +51,8 @@ constexpr int TAIL_BYTES = 1024;  // barriers, TMEM base, frequency / phase-bias
 
 enum : int {
   BAR_QFULL = 0, BAR_KFULL = 4, BAR_KEMPTY = 7, BAR_VFULL = 10, BAR_VEMPTY = 13, BAR_SFULL = 16, BAR_PREADY = 20,
-  BAR_ODONE = 24, BAR_MMADONE = 28, NUM_BARS = 29
+  BAR_ODONE = 24, BAR_MMADONE = 28, NUM_BARS = 29,
+  BAR_PHALF = 34   // four more behind the TMEM / abort words at bytes 256..263: the first 32 keys of P are ready
 };
 
 // Register budgets per warpgroup (see the kernel body): control / softmax / K-transform warps of
@@ -101,6 +102,9 @@ pe_attn_tc4_kernel(const KParams p, const int heads_per_cta, const int bh_group,
   constexpr uint32_t O_COL0 = NT * BLOCK_N;
   constexpr bool HAS_TMA_QK = (MODE == MODE_PLAIN) || (MODE == MODE_POPE && DC > 0);
   constexpr bool HAS_XFORM = MODE != MODE_PLAIN;
+  // hand P to the MMA warp in two halves, except where it measured slower (the PoPE instantiations:
+  // 699 against 680 TFLOP/s at head_dim 64 + 2 x 32, S 4096; the others gain 1-3 %)
+  constexpr int P_PARTS = MODE == MODE_POPE ? 1 : 2;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -160,6 +164,7 @@ pe_attn_tc4_kernel(const KParams p, const int heads_per_cta, const int bh_group,
       mbar_init(bar(BAR_QFULL + i), n_tma + n_xf);
       mbar_init(bar(BAR_SFULL + i), 1);
       mbar_init(bar(BAR_PREADY + i), 4);
+      mbar_init(bar(BAR_PHALF + i), 4);
       mbar_init(bar(BAR_ODONE + i), 1);
     }
     for (int s = 0; s < KV_STAGES; ++s) {
@@ -312,6 +317,25 @@ pe_attn_tc4_kernel(const KParams p, const int heads_per_cta, const int bh_group,
 #pragma unroll
       for (int i = 0; i < NT; ++i) {
         if (j < nt[i]) {
+          // P arrives in two halves of 32 keys (P_PARTS == 2): the first half's PV runs under the
+          // second half's exponentials
+          const uint32_t d = tmem_base + O_COL0 + (uint32_t)(i * DV);
+          const uint32_t a = tmem_base + (uint32_t)(i * BLOCK_N);
+          if constexpr (P_PARTS == 2) {
+            if (!__all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_PHALF + i), (uint32_t)(j & 1)))) {
+              fail(ST_WAIT_PREADY);
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            if (elect_one()) {
+#pragma unroll
+              for (int kk = 0; kk < BLOCK_N / 32; ++kk)
+                mma_ts(d, a + (uint32_t)(kk * 8), advance_smem_desc(vd, (uint32_t)(kk * 16 * 128)), IDESC_PV,
+                       (j > 0 || kk > 0) ? 1u : 0u);
+            }
+            __syncwarp();
+          }
           if (!__all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_PREADY + i), (uint32_t)(j & 1)))) {
             fail(ST_WAIT_PREADY);
             ok = false;
@@ -319,10 +343,8 @@ pe_attn_tc4_kernel(const KParams p, const int heads_per_cta, const int bh_group,
           }
           tc_fence_after_sync();
           if (elect_one()) {
-            const uint32_t d = tmem_base + O_COL0 + (uint32_t)(i * DV);
-            const uint32_t a = tmem_base + (uint32_t)(i * BLOCK_N);
 #pragma unroll
-            for (int kk = 0; kk < BLOCK_N / 16; ++kk)
+            for (int kk = P_PARTS == 2 ? BLOCK_N / 32 : 0; kk < BLOCK_N / 16; ++kk)
               mma_ts(d, a + (uint32_t)(kk * 8), advance_smem_desc(vd, (uint32_t)(kk * 16 * 128)), IDESC_PV,
                      (j > 0 || kk > 0) ? 1u : 0u);
             tc_commit(bar(BAR_ODONE + i));
@@ -470,6 +492,12 @@ pe_attn_tc4_kernel(const KParams p, const int heads_per_cta, const int bh_group,
             pk[(c >> 1) + 1] = pack_bf16x2(p23.x, p23.y);
           }
           tmem_st16(s_addr + cb * 16, pk);
+          if (P_PARTS == 2 && cb == 0) {
+            tmem_wait_st();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(BAR_PHALF + i));
+          }
         }
         l_sum += (acc0.x + acc0.y) + (acc1.x + acc1.y);
         tmem_wait_st();
