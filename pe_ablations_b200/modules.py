@@ -22,7 +22,7 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
-from .ops import linear_residual, pe_attention
+from .ops import linear_residual, pe_attention, projections
 from .pe import alibi_slopes
 
 
@@ -88,9 +88,10 @@ class GroupedQueryAttention(nn.Module):
                 residual: torch.Tensor | None = None) -> torch.Tensor:
         _check_call(x, mask)
         B, S, _ = x.shape
-        q = self.wq(x).view(B, S, self.num_heads, self.head_dim)
-        k = self.wk(x).view(B, S, self.num_kv_heads, self.head_dim)
-        v = self.wv(x).view(B, S, self.num_kv_heads, self.head_dim)
+        q, k, v = projections(self, x, self.wq, self.wk, self.wv)
+        q = q.view(B, S, self.num_heads, self.head_dim)
+        k = k.view(B, S, self.num_kv_heads, self.head_dim)
+        v = v.view(B, S, self.num_kv_heads, self.head_dim)
         dt = _kernel_dtype(q)
         kw = {}
         variant = "nope"
@@ -130,9 +131,10 @@ class ALiBiAttention(nn.Module):
                 residual: torch.Tensor | None = None) -> torch.Tensor:
         _check_call(x, mask)
         B, S, _ = x.shape
-        q = self.wq(x).view(B, S, self.num_heads, self.head_dim)
-        k = self.wk(x).view(B, S, self.num_kv_heads, self.head_dim)
-        v = self.wv(x).view(B, S, self.num_kv_heads, self.head_dim)
+        q, k, v = projections(self, x, self.wq, self.wk, self.wv)
+        q = q.view(B, S, self.num_heads, self.head_dim)
+        k = k.view(B, S, self.num_kv_heads, self.head_dim)
+        v = v.view(B, S, self.num_kv_heads, self.head_dim)
         dt = _kernel_dtype(q)
         out = pe_attention("alibi", q.to(dt), k.to(dt), v.to(dt), scale=self.head_dim ** -0.5,
                            qk_norm=self.qk_norm is not None,
@@ -184,15 +186,15 @@ class FPoPEGroupedQueryAttention(nn.Module):
                 residual: torch.Tensor | None = None) -> torch.Tensor:
         _check_call(x, mask)
         B, S, _ = x.shape
-        q_c = self.wq_c(x).view(B, S, self.num_heads, self.d_content)
-        k_c = self.wk_c(x).view(B, S, self.num_kv_heads, self.d_content)
-        q_r, k_r = self.wq_r(x), self.wk_r(x)
+        q_c, k_c, q_r, k_r, v = projections(self, x, self.wq_c, self.wk_c, self.wq_r, self.wk_r, self.wv)
+        q_c = q_c.view(B, S, self.num_heads, self.d_content)
+        k_c = k_c.view(B, S, self.num_kv_heads, self.d_content)
         if self.qr_norm is not None:
             q_r, k_r = self.qr_norm(q_r), self.kr_norm(k_r)
         dt = _kernel_dtype(q_c)
         q_r = q_r.to(dt).view(B, S, self.num_heads, self.d_rope)
         k_r = k_r.to(dt).view(B, S, self.num_kv_heads, self.d_rope)
-        v = self.wv(x).view(B, S, self.num_kv_heads, self.head_dim)
+        v = v.view(B, S, self.num_kv_heads, self.head_dim)
         out = pe_attention("pope", q_c.to(dt), k_c.to(dt), v.to(dt), q_r=q_r, k_r=k_r, start_pos=start_pos,
                            scale=self.scale, **self._pe_args())
         return linear_residual(self.wo, out.view(B, S, self.num_heads * self.head_dim).to(x.dtype), residual)

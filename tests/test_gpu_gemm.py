@@ -155,3 +155,36 @@ def test_model_takes_the_fused_paths_for_bf16_inference_and_agrees_with_the_unfu
         assert (got.float() - want.float()).abs().max().item() <= max(want.float().abs().max().item(), 1.0) * 2 ** -6
     assert cnt16.item() == cnt32.item() == 2 * 299
     assert abs(nll16.item() - nll32.item()) <= 2e-3 * abs(nll32.item())
+
+
+def test_attention_input_projections_run_as_one_gemm_and_follow_weight_updates():
+    """bf16 inference: q_c | k_c | q_r | k_r | v come out of one GEMM against the concatenated
+    weights (column slices read in place by the norm and attention kernels); the concatenation
+    is rebuilt when a weight changes, and the state_dict does not contain it."""
+    from pe_ablations_b200 import check_device_status
+    from pe_ablations_b200 import model as M
+    from pe_ablations_b200.eval import cast_matmul_weights
+    from pe_ablations_b200.ops import projections
+
+    torch.manual_seed(41)
+    cfg = M.TransformerConfig(vocab_size=512, hidden_dim=128, num_layers=1, num_heads=2, num_kv_heads=1, head_dim=64,
+                              ffn_dim=264, max_seq_len=512, pe_mode="fpope", fpope_d_rope=32, fpope_num_fourier_terms=8,
+                              fpope_training_length=64)
+    with torch.device("cuda"):
+        m = cast_matmul_weights(M.Transformer(cfg).eval())
+    att = m.layers[0].attention
+    x = _rand((2, 200, 128), 42)
+    lins = (att.wq_c, att.wk_c, att.wq_r, att.wk_r, att.wv)
+    with torch.no_grad(), torch.autocast("cuda", dtype=BF16):
+        outs = projections(att, x, *lins)
+        assert outs[1].stride(-2) == sum(l.weight.shape[0] for l in lins)      # slices of one wide result
+        for o, lin in zip(outs, lins):
+            want = lin(x)
+            assert (o.float() - want.float()).abs().max().item() <= max(want.float().abs().max().item(), 1.0) * 2 ** -7
+        y0 = att(x)
+        att.wv.weight.mul_(2.0)                  # in place: same storage, new version
+        y1 = att(x)
+    check_device_status()
+    assert "_wcat" not in m.state_dict() and not any("_wcat" in k for k in m.state_dict())
+    # doubling v doubles the attention output before wo, hence the module output
+    assert (y1.float() - 2.0 * y0.float()).abs().max().item() <= max(y0.float().abs().max().item(), 1.0) * 2 ** -5
