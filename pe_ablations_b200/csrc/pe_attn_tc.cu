@@ -627,15 +627,9 @@ int launch_instance(const KParams& p, cudaStream_t stream) {
   // (batch, head) problems per scheduling group: enough blocks to fill the GPU twice over, but
   // no more heads than keep their K/V (about 48 MB) resident in the 126 MB L2
   const long long kv_bytes_per_head = 2ll * p.Sk * (DC + DR + DV);
-  long long by_l2 = (48ll << 20) / (kv_bytes_per_head > 0 ? kv_bytes_per_head : 1);
-  long long by_fill = (2 * 148 + n_qblk - 1) / n_qblk;
-  long long bh_group = by_fill < by_l2 ? by_fill : by_l2;
-  // a group that is not a multiple of the GQA ratio would split K/V-sharing heads across groups
-  if (bh_group < p.groups) bh_group = p.groups;
-  if (bh_group > (long long)p.B * p.H) bh_group = (long long)p.B * p.H;
-  if (bh_group < 1) bh_group = 1;
+  const int bh_group = balanced_bh_group((long long)p.B * p.H, kv_bytes_per_head, p.groups);
   dim3 grid((unsigned)((long long)n_qblk * p.H * p.B)), block(NTHREADS);
-  kern<<<grid, block, C::SMEM_BYTES, stream>>>(p, (int)bh_group, tmQ, tmK, tmV);
+  kern<<<grid, block, C::SMEM_BYTES, stream>>>(p, bh_group, tmQ, tmK, tmV);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("tcgen05 kernel launch failed: %s", cudaGetErrorString(e));

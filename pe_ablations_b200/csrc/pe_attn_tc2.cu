@@ -840,14 +840,9 @@ int launch_instance2(const KParams& p, cudaStream_t stream) {
   int n_top = plan_split(p, pair_slots_of_device());
   if ((size_t)n_top * p.B * p.H * SPLIT_ITEM_FLOATS * sizeof(float) > p.workspace_bytes || p.workspace == nullptr) n_top = 0;
   const long long kv_bytes_per_head = 2ll * p.Sk * (DC + DR + DV);
-  long long by_l2 = (48ll << 20) / (kv_bytes_per_head > 0 ? kv_bytes_per_head : 1);
-  long long by_fill = (2 * 74 + n_sblk - 1) / n_sblk;   // 74 CTA pairs fit the GPU at a time
-  long long bh_group = by_fill < by_l2 ? by_fill : by_l2;
-  if (bh_group < p.groups) bh_group = p.groups;
-  if (bh_group > (long long)p.B * p.H) bh_group = (long long)p.B * p.H;
-  if (bh_group < 1) bh_group = 1;
+  const int bh_group = balanced_bh_group((long long)p.B * p.H, kv_bytes_per_head, p.groups);
   dim3 grid((unsigned)(2ll * (n_sblk + n_top) * p.H * p.B)), block(NTHREADS);
-  kern<<<grid, block, C::SMEM_BYTES, stream>>>(p, (int)bh_group, n_top, p.workspace, tmQ, tmK, tmV);
+  kern<<<grid, block, C::SMEM_BYTES, stream>>>(p, bh_group, n_top, p.workspace, tmQ, tmK, tmV);
   cudaError_t e = cudaGetLastError();
   if (e == cudaSuccess && n_top > 0) {
     pair_merge_kernel<<<dim3(PAIR_ROWS / MERGE_ROWS, (unsigned)(n_top * p.H * p.B)), 32 * MERGE_ROWS, 0, stream>>>(

@@ -703,16 +703,11 @@ int launch_instance4(const KParams& p, cudaStream_t stream) {
   const int rows_per_cta = (NT / hpc) * BLOCK_M;
   const int n_rblk = (p.Sq + rows_per_cta - 1) / rows_per_cta;
   const long long n_bh = (long long)p.B * (p.H / hpc);
-  // (batch, head-set) problems per scheduling group: enough blocks to fill the GPU twice over,
-  // but no more K/V heads in flight than stay resident in L2 (about 48 MB of the 126 MB)
+  // (batch, head-set) problems per scheduling group: equal groups whose K/V stay in L2 together
   const long long kv_bytes_per_head = 2ll * p.Sk * (DC + DR + DV);
-  long long by_l2 = (48ll << 20) / (kv_bytes_per_head > 0 ? kv_bytes_per_head : 1);
-  long long by_fill = (2 * 148 * (NT == 4 ? 1 : 2) + n_rblk - 1) / n_rblk;
-  long long bh_group = by_fill < by_l2 ? by_fill : by_l2;
-  if (bh_group > n_bh) bh_group = n_bh;
-  if (bh_group < 1) bh_group = 1;
+  const int bh_group = balanced_bh_group(n_bh, kv_bytes_per_head, 1);
   dim3 grid((unsigned)(n_rblk * n_bh)), block(threads_for(NT));
-  kern<<<grid, block, C::SMEM_BYTES, stream>>>(p, hpc, (int)bh_group, tmQ, tmK, tmV);
+  kern<<<grid, block, C::SMEM_BYTES, stream>>>(p, hpc, bh_group, tmQ, tmK, tmV);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("tcgen05 four-tile kernel launch failed: %s", cudaGetErrorString(e));
