@@ -172,7 +172,7 @@ pe_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA,
     int s = 0;
     uint32_t ph = 0;
     bool ok = true;
-    const long long tr0 = TR_T();
+    [[maybe_unused]] const long long tr0 = TR_T();
 #pragma unroll 1
     for (int ti = 0; ti < p.n_iter && ok; ++ti) {
       int mb, nb;
@@ -183,10 +183,10 @@ pe_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA,
       const int b_row = EPI == EPI_SWIGLU ? nb * (G_BN / 2) : nb * G_BN + (int)rank * (G_BN / 2);
 #pragma unroll 1
       for (int ks = 0; ks < k_steps; ++ks) {
-        const long long tw0 = TR_T();
+        [[maybe_unused]] const long long tw0 = TR_T();
         // polled, not suspended: a late refill shortens the pipeline by the wake-up time
         if (!__all_sync(0xffffffffu, PE_GEMM_PRODUCER_WAIT(bar(GB_EMPTY + s), ph ^ 1u))) { fail(ST_WAIT_KEMPTY); ok = false; break; }
-        const long long tw1 = TR_T();
+        [[maybe_unused]] const long long tw1 = TR_T();
         TR_ADD(1, tw1 - tw0);
         if (elect_one()) {
           const uint32_t fb = lbar(GB_FULL + s);
@@ -215,13 +215,13 @@ pe_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA,
       int s = 0, it = 0;
       uint32_t ph = 0;
       bool ok = true;
-      const long long tr0 = TR_T();
+      [[maybe_unused]] const long long tr0 = TR_T();
 #pragma unroll 1
       for (int ti = 0; ti < p.n_iter && ok; ++ti) {
         int mb, nb;
         if (!tile_of(p, pair, ti, mb, nb)) continue;
         const int buf = it & 1;
-        const long long ta0 = TR_T();
+        [[maybe_unused]] const long long ta0 = TR_T();
         // the epilogue warps of both CTAs have read this accumulator's previous tile
         if (!__all_sync(0xffffffffu, mbar_wait_spin(bar(GB_ACCEMPTY + buf), (uint32_t)(((it >> 1) & 1) ^ 1)))) {
           fail(ST_WAIT_PVDONE);
@@ -233,7 +233,7 @@ pe_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA,
         const uint32_t d = tmem_base + (uint32_t)(buf * G_BN);
 #pragma unroll 1
         for (int ks = 0; ks < k_steps; ++ks) {
-          const long long tf0 = TR_T();
+          [[maybe_unused]] const long long tf0 = TR_T();
           if (!__all_sync(0xffffffffu, mbar_wait_spin(bar(GB_FULL + s), ph))) { fail(ST_WAIT_KFULL); ok = false; break; }
           tc_fence_after_sync();
           TR_ADD(4, TR_T() - tf0);
@@ -264,13 +264,13 @@ pe_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA,
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     int it = 0;
     bool ok = true;
-    const long long tr0 = TR_T();
+    [[maybe_unused]] const long long tr0 = TR_T();
 #pragma unroll 1
     for (int ti = 0; ti < p.n_iter && ok; ++ti) {
       int mb, nb;
       if (!tile_of(p, pair, ti, mb, nb)) continue;
       const int buf = it & 1;
-      const long long te0 = TR_T();
+      [[maybe_unused]] const long long te0 = TR_T();
       const int row = mb * 2 * G_BM + (int)rank * G_BM + row_in_cta;
       const bool row_ok = row < p.M;
       if (!__all_sync(0xffffffffu, mbar_wait(bar(GB_ACCFULL + buf), (uint32_t)((it >> 1) & 1)))) {
