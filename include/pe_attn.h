@@ -329,7 +329,8 @@ int pe_swiglu_forward(const void* gate, const void* up, void* y, int dtype, int6
  *
  * One persistent tcgen05 kernel (CTA pairs, 256 x 256 accumulator tiles in TMEM, TMA-staged
  * operands) with the consumer of the product in its epilogue.  bf16 operands with K contiguous,
- * 16-byte aligned bases, row strides that are multiples of 8 elements; fp32 accumulation.
+ * 16-byte aligned bases, row strides that are multiples of 8 elements, K >= 64 and a multiple
+ * of 8; fp32 accumulation.
  * ``device_status`` as in pe_attn_args (may be null).
  *
  * pe_lm_head_ce_loss_sums replaces the language-model head followed by the cross-entropy

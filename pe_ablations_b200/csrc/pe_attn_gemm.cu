@@ -581,8 +581,8 @@ int pe_lm_head_ce_loss_sums(const void* hidden, int64_t hidden_stride, const voi
     set_error("targets, out or workspace is null");
     return PE_ATTN_ERR_NULL;
   }
-  if (n_rows < 1 || vocab < 1 || hidden_dim < 8 || (hidden_dim % 8) != 0) {
-    set_error("need n_rows >= 1, vocab >= 1 and hidden_dim a positive multiple of 8 (got %d, %d, %d)", n_rows, vocab,
+  if (n_rows < 1 || vocab < 1 || hidden_dim < 64 || (hidden_dim % 8) != 0) {
+    set_error("need n_rows >= 1, vocab >= 1 and hidden_dim >= 64, a multiple of 8 (got %d, %d, %d)", n_rows, vocab,
               hidden_dim);
     return PE_ATTN_ERR_SHAPE;
   }
@@ -636,8 +636,8 @@ int pe_swiglu_gemm(const void* x, int64_t x_stride, const void* w_gate, const vo
     set_error("y is null");
     return PE_ATTN_ERR_NULL;
   }
-  if (n_rows < 1 || ffn_dim < 8 || (ffn_dim % 8) != 0 || hidden_dim < 8 || (hidden_dim % 8) != 0) {
-    set_error("need n_rows >= 1 and hidden_dim, ffn_dim positive multiples of 8 (got %d, %d, %d)", n_rows, hidden_dim,
+  if (n_rows < 1 || ffn_dim < 8 || (ffn_dim % 8) != 0 || hidden_dim < 64 || (hidden_dim % 8) != 0) {
+    set_error("need n_rows >= 1, ffn_dim >= 8, hidden_dim >= 64, both multiples of 8 (got %d, %d, %d)", n_rows, hidden_dim,
               ffn_dim);
     return PE_ATTN_ERR_SHAPE;
   }
@@ -676,8 +676,8 @@ int pe_gemm_nt(const void* a, int64_t a_stride, const void* b, int64_t b_stride,
     set_error("c is null");
     return PE_ATTN_ERR_NULL;
   }
-  if (m < 1 || n < 8 || (n % 8) != 0 || k < 8 || (k % 8) != 0) {
-    set_error("need m >= 1 and n, k positive multiples of 8 (got %d, %d, %d)", m, n, k);
+  if (m < 1 || n < 8 || (n % 8) != 0 || k < 64 || (k % 8) != 0) {
+    set_error("need m >= 1, n >= 8, k >= 64 (one 128-byte TMA row), n and k multiples of 8 (got %d, %d, %d)", m, n, k);
     return PE_ATTN_ERR_SHAPE;
   }
   int rc = check_matrix("a", a, a_stride, k);

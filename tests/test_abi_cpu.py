@@ -221,7 +221,7 @@ def test_fused_gemm_entries_plan_and_reject_without_touching_the_gpu(L):
                     a["out"], None, None)
 
     assert call(t=None) == 1 and call(buf=None) == 1 and call(out=None) == 1 and call(h=None) == 1
-    assert call(n=0) == 3 and call(k=100) == 3 and call(v=0) == 3
+    assert call(n=0) == 3 and call(k=100) == 3 and call(k=56, hs=56, wsd=56) == 3 and call(v=0) == 3
     assert call(hs=2044) == 4 and call(h=0x10008) == 4 and call(buf=0x40010) == 4 and call(hs=1024) == 4
     assert call(nbytes=ws(512, 32000) - 1) == 3 and b"smaller than" in L.lib.pe_attn_last_error()
     sw = L.lib.pe_swiglu_gemm
