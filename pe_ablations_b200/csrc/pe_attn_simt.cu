@@ -157,9 +157,13 @@ __device__ __forceinline__ void store_elem<__nv_bfloat16>(void* base, long long 
   reinterpret_cast<__nv_bfloat16*>(base)[off] = __float2bfloat16_rn(x);
 }
 
-// VC: output columns per thread (stride 16), the smallest of 2, 4, 8 with 16 VC >= d_v
-template <typename T, bool ROUND, int VC>
+// VC: output columns per thread (stride 16), the smallest of 2, 4, 8 with 16 VC >= d_v.
+// RI: query rows per thread (stride 16): a CTA owns 16 RI query rows, 64 normally, 32 when the
+// launch would otherwise leave most SMs without a CTA (configuration 1: 64 CTAs on 148 SMs; the
+// longest CTA sets the run time, and half the rows halve its QK and PV work).
+template <typename T, bool ROUND, int VC, int RI>
 __global__ void __launch_bounds__(NTHREADS) pe_attn_simt_kernel(const KParams p) {
+  constexpr int BMQ = 16 * RI;
   extern __shared__ __align__(16) float smem[];
   const int dqk = p.d_qk, dv = p.d_v;
   const int dqk4 = round4(dqk), ld = dqk4 + 4, dvs = round4(dv);
@@ -172,11 +176,11 @@ __global__ void __launch_bounds__(NTHREADS) pe_attn_simt_kernel(const KParams p)
 
   const int tid = threadIdx.x;
   const int ty = tid >> 4, tx = tid & 15;
-  const int n_qblk = (p.Sq + BM - 1) / BM;
+  const int n_qblk = (p.Sq + BMQ - 1) / BMQ;
   const int qblk = n_qblk - 1 - (int)blockIdx.x;  // heaviest (last) query blocks first
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / p.groups;
-  const int m0 = qblk * BM;
+  const int m0 = qblk * BMQ;
 
   if (p.variant == PE_ATTN_POPE) {
     for (int c = tid; c < p.d_r; c += NTHREADS) {
@@ -185,11 +189,13 @@ __global__ void __launch_bounds__(NTHREADS) pe_attn_simt_kernel(const KParams p)
     }
     __syncthreads();
   }
-  build_operand_tile<T, ROUND>(p, Qs, ld, p.q, p.qr, b, h, m0, p.Sq, p.q_pos0, false, freq_s, delta_s);
+  // rows past this CTA's own are left zero (the tile builder works on 64 rows)
+  build_operand_tile<T, ROUND>(p, Qs, ld, p.q, p.qr, b, h, m0, (m0 + BMQ < p.Sq ? m0 + BMQ : p.Sq), p.q_pos0, false, freq_s,
+                               delta_s);
 
-  float m_run[4], l_run[4], o_acc[4][VC];
+  float m_run[RI], l_run[RI], o_acc[RI][VC];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < RI; ++i) {
     m_run[i] = -INFINITY;
     l_run[i] = 0.f;
 #pragma unroll
@@ -197,7 +203,7 @@ __global__ void __launch_bounds__(NTHREADS) pe_attn_simt_kernel(const KParams p)
   }
   const float slope = (p.variant == PE_ATTN_ALIBI) ? p.slopes[h] : 0.f;
 
-  int k_end = m0 + BM + p.causal_off;
+  int k_end = m0 + BMQ + p.causal_off;
   if (k_end > p.Sk) k_end = p.Sk;
   for (int n0 = 0; n0 < k_end; n0 += BN) {
     __syncthreads();  // previous tile's reads of Ks / Vs / Ps are done (and Qs is complete)
@@ -222,19 +228,19 @@ __global__ void __launch_bounds__(NTHREADS) pe_attn_simt_kernel(const KParams p)
     }
     __syncthreads();
 
-    float s[4][4];
+    float s[RI][4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < RI; ++i)
 #pragma unroll
       for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
     for (int kk = 0; kk < dqk4; kk += 4) {
-      float4 a[4], bb[4];
+      float4 a[RI], bb[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) a[i] = *reinterpret_cast<const float4*>(&Qs[(ty + 16 * i) * ld + kk]);
+      for (int i = 0; i < RI; ++i) a[i] = *reinterpret_cast<const float4*>(&Qs[(ty + 16 * i) * ld + kk]);
 #pragma unroll
       for (int j = 0; j < 4; ++j) bb[j] = *reinterpret_cast<const float4*>(&Ks[(tx + 16 * j) * ld + kk]);
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
+      for (int i = 0; i < RI; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           float acc = s[i][j];
@@ -247,7 +253,7 @@ __global__ void __launch_bounds__(NTHREADS) pe_attn_simt_kernel(const KParams p)
     }
 
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < RI; ++i) {
       const int row = m0 + ty + 16 * i;
       float tmax = -INFINITY;
 #pragma unroll
@@ -281,9 +287,9 @@ __global__ void __launch_bounds__(NTHREADS) pe_attn_simt_kernel(const KParams p)
     __syncthreads();
 
     for (int j = 0; j < BN; j += 4) {
-      float4 a[4];
+      float4 a[RI];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) a[i] = *reinterpret_cast<const float4*>(&Ps[(ty + 16 * i) * P_LD + j]);
+      for (int i = 0; i < RI; ++i) a[i] = *reinterpret_cast<const float4*>(&Ps[(ty + 16 * i) * P_LD + j]);
 #pragma unroll
       for (int jj = 0; jj < 4; ++jj) {
         float vv[VC];
@@ -293,7 +299,7 @@ __global__ void __launch_bounds__(NTHREADS) pe_attn_simt_kernel(const KParams p)
           vv[c] = col < dv ? Vs[(j + jj) * dvs + col] : 0.f;
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < RI; ++i) {
           const float pij = jj == 0 ? a[i].x : jj == 1 ? a[i].y : jj == 2 ? a[i].z : a[i].w;
 #pragma unroll
           for (int c = 0; c < VC; ++c) o_acc[i][c] = fmaf(pij, vv[c], o_acc[i][c]);
@@ -303,7 +309,7 @@ __global__ void __launch_bounds__(NTHREADS) pe_attn_simt_kernel(const KParams p)
   }
 
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < RI; ++i) {
     const int row = m0 + ty + 16 * i;
     if (row >= p.Sq) continue;
     const float inv = 1.f / l_run[i];
@@ -326,27 +332,36 @@ size_t simt_smem_bytes(const KParams& p) {
 }
 
 namespace {
-template <typename T, bool ROUND, int VC>
-cudaError_t launch_simt_instance(const KParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
-  auto kern = pe_attn_simt_kernel<T, ROUND, VC>;
+template <typename T, bool ROUND, int VC, int RI>
+cudaError_t launch_simt_instance(const KParams& p, size_t smem, cudaStream_t stream) {
+  auto kern = pe_attn_simt_kernel<T, ROUND, VC, RI>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
+  dim3 grid((p.Sq + 16 * RI - 1) / (16 * RI), p.H, p.B);
   kern<<<grid, dim3(NTHREADS), smem, stream>>>(p);
   return cudaGetLastError();
 }
+template <typename T, bool ROUND, int VC>
+cudaError_t launch_simt_rows(const KParams& p, size_t smem, cudaStream_t stream) {
+  // 32-row CTAs when 64-row ones would not give every SM at least one and a half CTAs
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long ctas64 = (long long)((p.Sq + BM - 1) / BM) * p.H * p.B;
+  if (2 * ctas64 < 3ll * sms) return launch_simt_instance<T, ROUND, VC, 2>(p, smem, stream);
+  return launch_simt_instance<T, ROUND, VC, 4>(p, smem, stream);
+}
 template <typename T, bool ROUND>
-cudaError_t launch_simt_dv(const KParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
-  if (p.d_v <= 32) return launch_simt_instance<T, ROUND, 2>(p, grid, smem, stream);
-  if (p.d_v <= 64) return launch_simt_instance<T, ROUND, 4>(p, grid, smem, stream);
-  return launch_simt_instance<T, ROUND, MAX_VC>(p, grid, smem, stream);
+cudaError_t launch_simt_dv(const KParams& p, size_t smem, cudaStream_t stream) {
+  if (p.d_v <= 32) return launch_simt_rows<T, ROUND, 2>(p, smem, stream);
+  if (p.d_v <= 64) return launch_simt_rows<T, ROUND, 4>(p, smem, stream);
+  return launch_simt_rows<T, ROUND, MAX_VC>(p, smem, stream);
 }
 }  // namespace
 
 int launch_simt(const KParams& p, int dtype, cudaStream_t stream) {
   const size_t smem = simt_smem_bytes(p);
-  dim3 grid((p.Sq + BM - 1) / BM, p.H, p.B);
-  const cudaError_t e = dtype == PE_ATTN_FP32 ? launch_simt_dv<float, false>(p, grid, smem, stream)
-                                              : launch_simt_dv<__nv_bfloat16, true>(p, grid, smem, stream);
+  const cudaError_t e = dtype == PE_ATTN_FP32 ? launch_simt_dv<float, false>(p, smem, stream)
+                                              : launch_simt_dv<__nv_bfloat16, true>(p, smem, stream);
   if (e != cudaSuccess) {
     set_error("ffma kernel launch failed: %s", cudaGetErrorString(e));
     return PE_ATTN_ERR_LAUNCH;
