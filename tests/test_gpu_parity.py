@@ -213,6 +213,33 @@ def test_determinism_and_unwritten_rows():
     assert torch.equal(outs[0], outs[1])
 
 
+@pytest.mark.parametrize("name,variant,shape,extra", [
+    ("pair_rotary_qknorm_gqa", "rotary", (2, 4096, 16, 4, 128, 0, 128), dict(qk_norm=True)),
+    ("pair_rotary", "rotary", (2, 4096, 8, 8, 128, 0, 128), {}),
+    ("tile4_rotary", "rotary", (4, 2048, 12, 12, 64, 0, 64), {}),
+    ("tile2_nope", "nope", (4, 2048, 12, 12, 64, 0, 64), {}),
+])
+def test_repeated_launches_are_bitwise_identical(name, variant, shape, extra):
+    """Many SMs' worth of blocks, twenty launches: every launch gives the first one's bits.  The
+    hand-offs between warps and between the CTAs of a pair (K rows built in shared memory, P
+    handed over in parts, relaxed arrivals) leave no room for a race to show up as noise."""
+    from pe_ablations_b200 import check_device_status, pe_attention
+    from pe_ablations_b200 import pe as PE
+
+    B, S, H, Hkv, dc, dr, dv = shape
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(91)
+    mk = lambda h, d: torch.randn(B, S, h, d, generator=g).to(torch.bfloat16).to(dev)
+    q, k, v = mk(H, dc), mk(Hkv, dc), mk(Hkv, dv)
+    kw = dict(extra)
+    if variant == "rotary":
+        kw["rotary_table"] = PE.RotaryEmbedding(dc, S, 10000.0).to(dev).freqs_cis
+    first = pe_attention(variant, q, k, v, **kw).clone()
+    for _ in range(20):
+        assert torch.equal(pe_attention(variant, q, k, v, **kw), first)
+    check_device_status()
+
+
 def test_full_size_config4_properties():
     """BASELINE configuration 4 at full size: size-independent properties instead of a CPU oracle.
 
