@@ -81,7 +81,7 @@ struct BCfg {
 
 template <int DQK, int DV, bool ALIBI>
 __global__ void __launch_bounds__(NTHREADS, 1)
-pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+pe_attn_bwd_kernel(const BwdParams p, const int bh_group, const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                    const __grid_constant__ CUtensorMap tmDQ) {
   using C = BCfg<DQK, DV>;
@@ -94,7 +94,16 @@ pe_attn_bwd_kernel(const BwdParams p, const __grid_constant__ CUtensorMap tmQ, c
   auto bar = [&](int idx) -> uint32_t { return smem_base + 8u * (uint32_t)idx; };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int key0 = (int)blockIdx.x * BN, hk = (int)blockIdx.y, b = (int)blockIdx.z;
+  // 1-D grid: key blocks in ascending order (block 0 sees every query block: longest first)
+  // inside groups of ``bh_group`` (batch, K/V head) problems whose Q / dO stay in L2 together
+  const int n_kblk = (p.Sk + BN - 1) / BN;
+  const int n_bh = p.B * p.Hkv;
+  const int per_group = bh_group * n_kblk;
+  const int grp = (int)(blockIdx.x / per_group), in_grp = (int)(blockIdx.x % per_group);
+  const int g_first = grp * bh_group;
+  const int g_size = (n_bh - g_first) < bh_group ? (n_bh - g_first) : bh_group;
+  const int bh = g_first + in_grp % g_size;
+  const int key0 = (in_grp / g_size) * BN, hk = bh % p.Hkv, b = bh / p.Hkv;
   const int n_qblk = (p.Sq + BM - 1) / BM;
   // query row r sees key s iff s <= r + causal_off: the first block with a row that sees key0
   int first_row = key0 - p.causal_off;
@@ -534,8 +543,10 @@ int launch_bwd_instance(const BwdParams& p, cudaStream_t stream) {
   long long dblocks = ((long long)p.B * p.H * p.Sq * (DV / 8) + 255) / 256;
   if (dblocks > 148 * 8) dblocks = 148 * 8;
   bwd_dvec_kernel<DV><<<(unsigned)dblocks, 256, 0, stream>>>(p);
-  dim3 grid((unsigned)((p.Sk + BN - 1) / BN), (unsigned)p.Hkv, (unsigned)p.B), block(NTHREADS);
-  kern<<<grid, block, C::SMEM_BYTES, stream>>>(p, tmQ, tmK, tmV, tmDO, tmDQ);
+  // a CTA streams the Q and dO rows of its K/V head's query heads; heads per group by what L2 holds
+  const int bh_group = balanced_bh_group((long long)p.B * p.Hkv, 2ll * p.Sq * (DQK + DV) * p.groups, 1);
+  dim3 grid((unsigned)((long long)((p.Sk + BN - 1) / BN) * p.Hkv * p.B)), block(NTHREADS);
+  kern<<<grid, block, C::SMEM_BYTES, stream>>>(p, bh_group, tmQ, tmK, tmV, tmDO, tmDQ);
   e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("backward kernel launch failed: %s", cudaGetErrorString(e));
