@@ -188,3 +188,18 @@ def test_attention_input_projections_run_as_one_gemm_and_follow_weight_updates()
     assert "_wcat" not in m.state_dict() and not any("_wcat" in k for k in m.state_dict())
     # doubling v doubles the attention output before wo, hence the module output
     assert (y1.float() - 2.0 * y0.float()).abs().max().item() <= max(y0.float().abs().max().item(), 1.0) * 2 ** -5
+
+
+@pytest.mark.parametrize("bad", [float("nan"), float("inf")])
+def test_lm_head_ce_non_finite_logits_make_the_sum_non_finite(bad):
+    """A NaN or +inf logit is scored and makes the loss sum non-finite, as F.cross_entropy does
+    (and as pe_ce_loss_sums does on stored logits); the count is unaffected."""
+    from pe_ablations_b200.ops import lm_head_ce_loss_sums
+
+    h, w = _rand((300, 128), 51), _rand((700, 128), 52, 0.1)
+    w[13, 5] = bad                               # every row's logit 13 becomes non-finite
+    t = torch.randint(0, 700, (300,), generator=torch.Generator().manual_seed(53)).cuda()
+    out = lm_head_ce_loss_sums(h, w, t)
+    want = F.cross_entropy((h.float() @ w.float().T), t, reduction="sum")
+    assert not torch.isfinite(want).item()
+    assert not torch.isfinite(out[0]).item() and out[1].item() == 300
