@@ -469,7 +469,13 @@ def run_training(args) -> dict:
     dout = torch.randn(Bt, St, Ht, dv, generator=g).to(torch.bfloat16).to(dev)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
+    leaves = (q, k, q_r, k_r, v, coeffs, delta)
+
     def step():
+        # gradients start out absent, as after optimizer.zero_grad(): in a model these tensors are
+        # projection outputs, nothing accumulates into them from one step to the next
+        for t in leaves:
+            t.grad = None
         out = P.pe_attention("pope", q, k, v, q_r=q_r, k_r=k_r, freqs=freqs, fourier_coeffs=coeffs, delta=delta,
                              floor_freq=2 * math.pi / 512)
         out.backward(dout)
