@@ -23,6 +23,41 @@ _VARIANTS = {"nope": _lib.NOPE, "rotary": _lib.ROTARY, "alibi": _lib.ALIBI, "pop
 _status_words: dict[int, torch.Tensor] = {}      # one int32 word per device, for all streams
 
 
+_raw_stream_fn = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
+class _on_device:
+    """``with _on_device(dev) as stream``: makes ``dev`` the current CUDA device for the C call if
+    it is not already (the library launches on the current device) and yields the raw handle of
+    torch's current stream there.  The host side of a call is a few microseconds this way; the
+    generic ``torch.cuda.device`` / ``current_stream`` objects cost several times that, which a
+    training step of small kernels (CPU-bound at the reference's shape) pays per launch.
+
+    Temporaries created inside a wrapper (fp32 copies of parameters, workspaces) are allocated on
+    the same current stream the kernel is launched on, so the caching allocator already orders
+    their reuse behind the kernel: no ``record_stream`` is needed for them."""
+
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, device):
+        self.idx = device.index if device.index is not None else torch.cuda.current_device()
+        self.prev = -1
+
+    def __enter__(self) -> int:
+        cur = torch.cuda.current_device()
+        if cur != self.idx:
+            self.prev = cur
+            torch.cuda.set_device(self.idx)
+        if _raw_stream_fn is not None:
+            return _raw_stream_fn(self.idx)
+        return torch.cuda.current_stream(self.idx).cuda_stream
+
+    def __exit__(self, *exc):
+        if self.prev >= 0:
+            torch.cuda.set_device(self.prev)
+        return False
+
+
 def device_status(device: torch.device) -> torch.Tensor:
     """The int32 word of ``device`` that the tensor-core kernels OR a code into when a bounded
     wait runs out.  One word per device serves every stream (the kernels only ever OR into it).
@@ -331,10 +366,9 @@ def _forward_impl(
     if single_cta:
         flags |= _lib.SINGLE_CTA
     a.flags = flags
-    with torch.cuda.device(dev):
+    with _on_device(dev) as stream:
         if dtype == _lib.BF16 and not simt_check:
             a.device_status = device_status(dev).data_ptr()
-        stream = torch.cuda.current_stream(dev).cuda_stream
         use_split = False
         if split_kv or (split_kv is None and dtype == _lib.BF16 and not simt_check and not single_cta
                         and (H // max(Hkv, 1)) * Sq <= 8 and Sk >= 256):
@@ -357,9 +391,7 @@ def _forward_impl(
             rc = _lib.lib.pe_attn_forward(C.byref(a), C.c_void_p(stream))
     if rc != 0:
         raise _lib.PeAttnError(rc)
-    # parameter tensors created here stay referenced until the stream has used them
-    for t in keep[1:]:
-        t.record_stream(torch.cuda.current_stream(dev))
+    del keep   # parameter copies created here were allocated on the launch stream (see _on_device)
     return out
 
 
@@ -405,14 +437,11 @@ def attention_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: t
         sl = _f32(alibi_slopes.reshape(-1), dev)
         keep.append(sl)
         a.alibi_slopes = sl.data_ptr()
-    with torch.cuda.device(dev):
+    with _on_device(dev) as stream:
         a.device_status = device_status(dev).data_ptr()
-        stream = torch.cuda.current_stream(dev)
-        rc = _lib.lib.pe_attn_backward(C.byref(a), C.c_void_p(stream.cuda_stream))
+        rc = _lib.lib.pe_attn_backward(C.byref(a), C.c_void_p(stream))
     if rc != 0:
         raise _lib.PeAttnError(rc)
-    for t in keep + [dvec]:
-        t.record_stream(stream)
     return dq_accum, dk, dv
 
 
@@ -431,16 +460,12 @@ def pope_expand(x_c: torch.Tensor | None, x_r: torch.Tensor, pos0: int, omega: t
     d_c = 0 if x_c is None else x_c.shape[-1]
     out = torch.empty(B, S, H, d_c + 2 * d_r, dtype=torch.bfloat16, device=x_r.device)
     om, dl = _f32(omega, x_r.device), _f32(delta, x_r.device)
-    with torch.cuda.device(x_r.device):
-        stream = torch.cuda.current_stream(x_r.device)
+    with _on_device(x_r.device) as stream:
         rc = _lib.lib.pe_pope_expand(None if x_c is None else x_c.data_ptr(), _s3(x_c), x_r.data_ptr(), _s3(x_r),
                                      out.data_ptr(), _s3(out), B, S, H, d_c, d_r, int(pos0), om.data_ptr(),
-                                     None if dl is None else dl.data_ptr(), C.c_void_p(stream.cuda_stream))
+                                     None if dl is None else dl.data_ptr(), C.c_void_p(stream))
     if rc != 0:
         raise _lib.PeAttnError(rc)
-    for t in (om, dl):
-        if t is not None:
-            t.record_stream(stream)
     return out
 
 
@@ -453,18 +478,14 @@ def pope_expand_backward(grad: torch.Tensor, x_r: torch.Tensor, d_c: int, pos0: 
     dx_c = torch.empty(B, S, H, d_c, dtype=torch.bfloat16, device=dev) if d_c else None
     dx_r = torch.empty(B, S, H, d_r, dtype=torch.bfloat16, device=dev)
     om, dl = _f32(omega, dev), _f32(delta, dev)
-    with torch.cuda.device(dev):
-        stream = torch.cuda.current_stream(dev)
+    with _on_device(dev) as stream:
         rc = _lib.lib.pe_pope_expand_backward(
             grad.data_ptr(), _dtype_code(grad), _s3(grad), x_r.data_ptr(), _s3(x_r),
             None if dx_c is None else dx_c.data_ptr(), _s3(dx_c), dx_r.data_ptr(), _s3(dx_r), B, S, H, d_c, d_r,
             int(pos0), om.data_ptr(), None if dl is None else dl.data_ptr(), d_omega.data_ptr(),
-            None if d_delta is None else d_delta.data_ptr(), C.c_void_p(stream.cuda_stream))
+            None if d_delta is None else d_delta.data_ptr(), C.c_void_p(stream))
     if rc != 0:
         raise _lib.PeAttnError(rc)
-    for t in (om, dl):
-        if t is not None:
-            t.record_stream(stream)
     return dx_c, dx_r
 
 
@@ -476,8 +497,8 @@ def fope_effective_freqs(base: torch.Tensor, coeffs: torch.Tensor, normalize: bo
     d_r, n_f = coeffs.shape
     flags = (_lib.FOURIER_NORMALIZE if normalize else 0) | (_lib.FOURIER_CEILING if ceil_freq is not None else 0)
     ceil = float(ceil_freq) if ceil_freq is not None else 0.0
-    with torch.cuda.device(coeffs.device):
-        stream = C.c_void_p(torch.cuda.current_stream(coeffs.device).cuda_stream)
+    with _on_device(coeffs.device) as raw_stream:
+        stream = C.c_void_p(raw_stream)
         if d_omega is None:
             omega = torch.empty(d_r, dtype=torch.float32, device=coeffs.device)
             rc = _lib.lib.pe_fope_effective_freqs(base.data_ptr(), coeffs.data_ptr(), d_r, n_f, flags, float(floor_freq),
@@ -503,8 +524,8 @@ def rotary_norm_expand(x: torch.Tensor, table: torch.Tensor | None, table_row0: 
     out = torch.empty(B, S, H, D, dtype=torch.bfloat16, device=x.device)
     rows = 0 if table is None else table.shape[0]
     tptr = None if table is None else table.data_ptr()
-    with torch.cuda.device(x.device):
-        stream = C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
+    with _on_device(x.device) as raw_stream:
+        stream = C.c_void_p(raw_stream)
         if grad is None:
             rc = _lib.lib.pe_rotary_norm_expand(x.data_ptr(), _s3(x), out.data_ptr(), _s3(out), B, S, H, D, tptr,
                                                 int(table_row0), rows, float(mscale), int(qk_norm), float(eps), stream)
@@ -642,10 +663,9 @@ def ce_loss_sums(logits: torch.Tensor, targets: torch.Tensor, out: torch.Tensor 
     dev = logits.device
     if out is None:
         out = torch.zeros(2, dtype=torch.float64, device=dev)
-    with torch.cuda.device(dev):
-        stream = torch.cuda.current_stream(dev)
+    with _on_device(dev) as stream:
         need = _lib.lib.pe_ce_scratch_bytes(n)
-        key = (dev.index if dev.index is not None else torch.cuda.current_device(), stream.cuda_stream)
+        key = (dev.index if dev.index is not None else torch.cuda.current_device(), stream)
         scratch = _ce_scratch.get(key)
         if scratch is None or scratch.numel() < need:
             # zeroed once: the kernel leaves the counter word at zero after every call
@@ -658,10 +678,9 @@ def ce_loss_sums(logits: torch.Tensor, targets: torch.Tensor, out: torch.Tensor 
             _ce_scratch[key] = scratch
         rc = _lib.lib.pe_ce_loss_sums(logits.data_ptr(), dtype, logits.stride(0), targets.data_ptr(), n, vocab,
                                       int(ignore_index), scratch.data_ptr(), out.data_ptr(),
-                                      C.c_void_p(stream.cuda_stream))
+                                      C.c_void_p(stream))
     if rc != 0:
         raise _lib.PeAttnError(rc)
-    targets.record_stream(stream)
     return out
 
 
@@ -752,10 +771,9 @@ def lm_head_ce_loss_sums(hidden: torch.Tensor, weight: torch.Tensor, targets: to
     dev = h.device
     if out is None:
         out = torch.zeros(2, dtype=torch.float64, device=dev)
-    with torch.cuda.device(dev):
-        stream = torch.cuda.current_stream(dev)
+    with _on_device(dev) as stream:
         need = _lib.lib.pe_lm_head_ce_workspace_bytes(n, vocab)
-        key = (dev.index if dev.index is not None else torch.cuda.current_device(), stream.cuda_stream)
+        key = (dev.index if dev.index is not None else torch.cuda.current_device(), stream)
         ws = _head_ws.get(key)
         if ws is None or ws.numel() < need:
             ws = torch.empty(need, dtype=torch.uint8, device=dev)
@@ -766,11 +784,9 @@ def lm_head_ce_loss_sums(hidden: torch.Tensor, weight: torch.Tensor, targets: to
         rc = _lib.lib.pe_lm_head_ce_loss_sums(h.data_ptr(), h.stride(0), w.data_ptr(), w.stride(0), targets.data_ptr(),
                                               n, h.shape[1], vocab, int(ignore_index), ws.data_ptr(), ws.numel(),
                                               out.data_ptr(), device_status(dev).data_ptr(),
-                                              C.c_void_p(stream.cuda_stream))
+                                              C.c_void_p(stream))
     if rc != 0:
         raise _lib.PeAttnError(rc)
-    for t in (h, w, targets):
-        t.record_stream(stream)
     return out
 
 
@@ -783,15 +799,12 @@ def swiglu_gemm(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor) -> to
     if wg.shape != wu.shape or wg.stride(0) != wu.stride(0) or wg.shape[1] != x2.shape[1]:
         raise ValueError("w_gate and w_up must be [ffn_dim, hidden_dim] with equal strides")
     y = torch.empty(x2.shape[0], wg.shape[0], dtype=torch.bfloat16, device=x2.device)
-    with torch.cuda.device(x2.device):
-        stream = torch.cuda.current_stream(x2.device)
+    with _on_device(x2.device) as stream:
         rc = _lib.lib.pe_swiglu_gemm(x2.data_ptr(), x2.stride(0), wg.data_ptr(), wu.data_ptr(), wg.stride(0),
                                      y.data_ptr(), y.stride(0), x2.shape[0], x2.shape[1], wg.shape[0],
-                                     device_status(x2.device).data_ptr(), C.c_void_p(stream.cuda_stream))
+                                     device_status(x2.device).data_ptr(), C.c_void_p(stream))
     if rc != 0:
         raise _lib.PeAttnError(rc)
-    for t in (x2, wg, wu):
-        t.record_stream(stream)
     return y.view(*x.shape[:-1], wg.shape[0])
 
 
@@ -808,16 +821,13 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, residual: torch.Tensor | None = No
         r2 = _bf16_matrix("residual", residual)
         if r2.shape != c.shape:
             raise ValueError("residual must have the shape of the result")
-    with torch.cuda.device(a2.device):
-        stream = torch.cuda.current_stream(a2.device)
+    with _on_device(a2.device) as stream:
         rc = _lib.lib.pe_gemm_nt(a2.data_ptr(), a2.stride(0), b2.data_ptr(), b2.stride(0), c.data_ptr(), c.stride(0),
                                  None if r2 is None else r2.data_ptr(), 0 if r2 is None else r2.stride(0),
                                  a2.shape[0], b2.shape[0], a2.shape[1], device_status(a2.device).data_ptr(),
-                                 C.c_void_p(stream.cuda_stream))
+                                 C.c_void_p(stream))
     if rc != 0:
         raise _lib.PeAttnError(rc)
-    for t in (a2, b2) + (() if r2 is None else (r2,)):
-        t.record_stream(stream)
     return c.view(*a.shape[:-1], b2.shape[0])
 
 
@@ -845,10 +855,9 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     w = weight.detach()
     if w.dtype != torch.float32 or not w.is_contiguous():
         w = w.float().contiguous()
-    with torch.cuda.device(x.device):
+    with _on_device(x.device) as stream:
         rc = _lib.lib.pe_rmsnorm_forward(x2.data_ptr(), w.data_ptr(), y.data_ptr(), _dtype_code(x2), x2.shape[0], dim,
-                                         x2.stride(0), y.stride(0), float(eps),
-                                         C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream))
+                                         x2.stride(0), y.stride(0), float(eps), C.c_void_p(stream))
     if rc != 0:
         raise _lib.PeAttnError(rc)
     return y.view(x.shape)
@@ -862,9 +871,9 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
         raise ValueError("gate and up must have the same shape and dtype")
     g, u = gate.contiguous(), up.contiguous()
     y = torch.empty_like(g)
-    with torch.cuda.device(g.device):
+    with _on_device(g.device) as stream:
         rc = _lib.lib.pe_swiglu_forward(g.data_ptr(), u.data_ptr(), y.data_ptr(), _dtype_code(g), g.numel(),
-                                        C.c_void_p(torch.cuda.current_stream(g.device).cuda_stream))
+                                        C.c_void_p(stream))
     if rc != 0:
         raise _lib.PeAttnError(rc)
     return y
