@@ -244,8 +244,9 @@ int pe_attn_backward(const pe_attn_bwd_args* args, void* stream);
  *   phi = fl(fl((pos0 + s) * omega) + clamp(delta, -2 pi, 0))      (delta null: queries).
  * pe_pope_expand_backward is what autograd derives from it: given grad = d/d out (bf16 or
  * fp32, PE_ATTN_BF16 / PE_ATTN_FP32) it writes d x_c and d x_r (bf16) and ACCUMULATES
- * d_omega[c] += sum pos * d phi and d_delta[c] += sum d phi (fp64 [d_r]; d_delta is the
- * gradient of the CLAMPED bias and may be null; zero both before the first call).
+ * d_omega[c] += sum pos * d phi and d_delta[c] += sum d phi where -2 pi <= delta[c] <= 0 (fp64
+ * [d_r]; d_delta is the gradient of the RAW bias: the clamp passes it on inside the interval
+ * only; it may be null; zero both before the first call).
  * All tensors [B,S,H,*] by element strides (batch, head, seq), 16-byte aligned, strides
  * multiples of 8; d_r 32 or 64, d_c a multiple of 8 (0 = position-only).  omega: the
  * effective frequencies [d_r] fp32. */

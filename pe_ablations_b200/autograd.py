@@ -165,8 +165,7 @@ class FusedAttentionFunction(torch.autograd.Function):
             d_coeffs, d_freqs = fope_effective_freqs(base, coeffs, o["normalize_coeffs"], o["floor_freq"], o["ceil_freq"],
                                                      d_omega=sums[0], want_d_base=bool(ctx.needs_input_grad[7]))
         if delta is not None and ctx.needs_input_grad[8]:
-            inside = (delta >= -_TWO_PI) & (delta <= 0.0)                  # torch.clamp passes the gradient here
-            d_delta = (sums[1].float() * inside).to(delta.dtype)
+            d_delta = sums[1].to(delta.dtype)      # the kernel already zeroes it where the clamp is active
         cast = lambda grad, like: None if grad is None or like is None else grad.to(like.dtype)
         return (None, None, dq, dk, dv if ctx.needs_input_grad[4] else None, dq_r, dk_r,
                 cast(d_freqs, freqs), d_delta, cast(d_coeffs, fourier_coeffs))

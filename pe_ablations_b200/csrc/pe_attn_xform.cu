@@ -162,7 +162,9 @@ __global__ void __launch_bounds__(256) pope_expand_backward_kernel(const XfParam
   __syncthreads();
   for (int i = threadIdx.x; i < DR; i += blockDim.x) {
     atomicAdd(p.d_omega + i, sum_w[i]);
-    if (p.d_delta != nullptr) atomicAdd(p.d_delta + i, sum_d[i]);
+    // gradient of the RAW bias: clamp(delta, -2 pi, 0) passes it on inside the interval only
+    if (p.d_delta != nullptr && p.delta != nullptr && p.delta[i] >= -kTwoPi && p.delta[i] <= 0.0f)
+      atomicAdd(p.d_delta + i, sum_d[i]);
   }
 }
 

@@ -472,7 +472,8 @@ def pope_expand(x_c: torch.Tensor | None, x_r: torch.Tensor, pos0: int, omega: t
 def pope_expand_backward(grad: torch.Tensor, x_r: torch.Tensor, d_c: int, pos0: int, omega: torch.Tensor,
                          delta: torch.Tensor | None, d_omega: torch.Tensor, d_delta: torch.Tensor | None):
     """Gradient of ``pope_expand``: returns (d x_c or None, d x_r) in bf16 and accumulates the
-    frequency / clamped-phase-bias gradients into the fp64 vectors ``d_omega`` / ``d_delta``."""
+    frequency / phase-bias gradients into the fp64 vectors ``d_omega`` / ``d_delta`` (the latter
+    with respect to the raw bias: zero where the clamp to [-2 pi, 0] is active)."""
     B, S, H, d_r = x_r.shape
     dev = x_r.device
     dx_c = torch.empty(B, S, H, d_c, dtype=torch.bfloat16, device=dev) if d_c else None
