@@ -110,9 +110,9 @@ def check_device_status(device: torch.device | None = None) -> None:
 
 
 def _strides(t: torch.Tensor, layout: str) -> tuple[int, int, int]:
-    if t.stride(-1) != 1:
+    sb, s1, s2, s3 = t.stride()
+    if s3 != 1:
         raise ValueError("the last dimension must be contiguous")
-    sb, s1, s2 = t.stride(0), t.stride(1), t.stride(2)
     return (sb, s2, s1) if layout == "bshd" else (sb, s1, s2)
 
 
@@ -124,6 +124,8 @@ def _dims(t: torch.Tensor, layout: str) -> tuple[int, int, int, int]:
 def _f32(t: torch.Tensor | None, device) -> torch.Tensor | None:
     if t is None:
         return None
+    if t.dtype == torch.float32 and t.device == device and t.is_contiguous():
+        return t.detach() if t.requires_grad else t
     return t.detach().to(device=device, dtype=torch.float32).contiguous()
 
 
@@ -306,18 +308,16 @@ def _forward_impl(
         out = torch.empty(shape, dtype=ref.dtype, device=ref.device)
     keep = [out]
 
-    def bind(name, sname, t):
-        if t is None:
-            return
-        setattr(a, name, t.data_ptr())
-        getattr(a, sname)[:] = _strides(t, layout)
-
-    bind("q", "q_stride", q)
-    bind("k", "k_stride", k)
-    bind("v", "v_stride", v)
-    bind("out", "out_stride", out)
-    bind("q_r", "qr_stride", q_r)
-    bind("k_r", "kr_stride", k_r)
+    if q is not None:
+        a.q, a.q_stride[:] = q.data_ptr(), _strides(q, layout)
+    if k is not None:
+        a.k, a.k_stride[:] = k.data_ptr(), _strides(k, layout)
+    a.v, a.v_stride[:] = v.data_ptr(), _strides(v, layout)
+    a.out, a.out_stride[:] = out.data_ptr(), _strides(out, layout)
+    if q_r is not None:
+        a.q_r, a.qr_stride[:] = q_r.data_ptr(), _strides(q_r, layout)
+    if k_r is not None:
+        a.k_r, a.kr_stride[:] = k_r.data_ptr(), _strides(k_r, layout)
     if lse is not None:
         if lse.dtype != torch.float32 or lse.shape != (B, H, Sq) or not lse.is_contiguous() or lse.device != ref.device:
             raise ValueError("lse must be a contiguous fp32 [B, H, Sq] tensor on the inputs' device")
