@@ -85,7 +85,11 @@ __global__ void __launch_bounds__(256) pope_expand_kernel(const XfParams p) {
 }
 
 template <int DR, bool GRAD_F32>
-__global__ void __launch_bounds__(256) pope_expand_backward_kernel(const XfParams p) {
+// Three CTAs per SM (80 registers) and a grid of exactly the CTAs that fit at once: a thread then
+// walks about nine rows, and the per-CTA reduction of the two parameter gradients (shared-memory
+// and global fp64 atomics) happens 444 times instead of 1184 (training shape: 61 -> 51 us for the
+// query side, 38 -> 29 us for the key side).
+__global__ void __launch_bounds__(256, 3) pope_expand_backward_kernel(const XfParams p) {
   constexpr int VPR = DR / 8;
   __shared__ double sum_w[DR], sum_d[DR];
   for (int i = threadIdx.x; i < DR; i += blockDim.x) sum_w[i] = sum_d[i] = 0.0;
@@ -416,7 +420,8 @@ extern "C" int pe_pope_expand_backward(const void* grad, int grad_dtype, const i
   if (d_c > 0) p.dxc = ref_of(dx_c, dxc_stride);
   p.dxr = ref_of(dx_r, dxr_stride);
   p.omega = omega; p.delta = delta; p.d_omega = d_omega; p.d_delta = d_delta;
-  const unsigned grid = grid_for((long long)B * S * H * (d_r / 8));
+  unsigned grid = grid_for((long long)B * S * H * (d_r / 8));
+  if (grid > 148u * 3u) grid = 148u * 3u;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool f32 = grad_dtype == PE_ATTN_FP32;
   if (d_r == 32) {
