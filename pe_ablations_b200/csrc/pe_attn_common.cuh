@@ -87,6 +87,41 @@ __device__ __forceinline__ float effective_freq(const KParams& p, int c) {
   return eff;
 }
 
+// The same value with the Fourier terms of column c dealt to LANES neighbouring lanes of a warp
+// (term j to lane j mod LANES) and the fp64 partial sums joined by shuffles: a chain of
+// 2 n_fourier / LANES dependent fp64 additions instead of 2 n_fourier, for kernel prologues that
+// nothing hides.  Every lane of the warp must make the call (full-mask shuffles); the LANES lanes
+// of a group pass the same c and their index ``sub`` in the group, and all get the result.  The
+// terms are fp32 values and their fp64 sum is exact at these counts, so the rounded result does
+// not depend on the order: bit for bit the value effective_freq() returns.
+template <int LANES>
+__device__ __forceinline__ float effective_freq_lanes(const KParams& p, int c, int sub) {
+  static_assert(LANES == 2 || LANES == 4 || LANES == 8 || LANES == 16 || LANES == 32, "LANES: a power of two <= 32");
+  const float base = p.freqs[c];
+  if (!(p.flags & PE_ATTN_FOURIER_MIX)) return base;
+  const float* a = p.coeffs + (size_t)c * p.n_fourier;
+  const bool normalize = (p.flags & PE_ATTN_FOURIER_NORMALIZE) != 0;
+  float denom = 1.0f;
+  if (normalize) {
+    double s = 0.0;
+    for (int j = sub; j < p.n_fourier; j += LANES) s += fabs((double)a[j]);
+#pragma unroll
+    for (int d = 1; d < LANES; d <<= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+    denom = __fadd_rn((float)s, 1e-8f);
+  }
+  double acc = 0.0;
+  for (int j = sub; j < p.n_fourier; j += LANES) {
+    const float an = normalize ? __fdiv_rn(a[j], denom) : a[j];
+    acc += (double)__fmul_rn(an, __fmul_rn(base, (float)(j + 1)));
+  }
+#pragma unroll
+  for (int d = 1; d < LANES; d <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+  float eff = __fadd_rn((float)acc, base);
+  if (fabsf(eff) < p.floor_freq) eff = 0.0f;
+  if (p.flags & PE_ATTN_FOURIER_CEILING) eff = fminf(fmaxf(eff, -p.ceil_freq), p.ceil_freq);
+  return eff;
+}
+
 // Key phase bias as used: clamp(delta, -2 pi, 0) (src/model/pope.py:172, src/model/fpope.py:328).
 __device__ __forceinline__ float clamped_delta(const KParams& p, int c) {
   if (p.delta == nullptr) return 0.0f;

@@ -98,37 +98,6 @@ __device__ __forceinline__ uint32_t lds_u32(uint32_t a) {
   return v;
 }
 
-// effective_freq() of the common header with the Fourier terms of a column dealt to the four
-// lanes of a quad (term j to lane j mod 4) and the fp64 partial sums joined by shuffles: the
-// prologue of a short CTA is not hidden behind anything, and the serial version is a chain of
-// 2 x n_fourier dependent fp64 additions.  fp64 sums of fp32 terms are exact at these counts,
-// so the rounded result does not depend on the order.
-__device__ __forceinline__ float effective_freq_quad(const KParams& p, int c, int sub) {
-  const float base = p.freqs[c];
-  if (!(p.flags & PE_ATTN_FOURIER_MIX)) return base;
-  const float* a = p.coeffs + (size_t)c * p.n_fourier;
-  const bool normalize = (p.flags & PE_ATTN_FOURIER_NORMALIZE) != 0;
-  float denom = 1.0f;
-  if (normalize) {
-    double s = 0.0;
-    for (int j = sub; j < p.n_fourier; j += 4) s += fabs((double)a[j]);
-    s += __shfl_xor_sync(0xffffffffu, s, 1);
-    s += __shfl_xor_sync(0xffffffffu, s, 2);
-    denom = __fadd_rn((float)s, 1e-8f);
-  }
-  double acc = 0.0;
-  for (int j = sub; j < p.n_fourier; j += 4) {
-    const float an = normalize ? __fdiv_rn(a[j], denom) : a[j];
-    acc += (double)__fmul_rn(an, __fmul_rn(base, (float)(j + 1)));
-  }
-  acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-  acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-  float eff = __fadd_rn((float)acc, base);
-  if (fabsf(eff) < p.floor_freq) eff = 0.0f;
-  if (p.flags & PE_ATTN_FOURIER_CEILING) eff = fminf(fmaxf(eff, -p.ceil_freq), p.ceil_freq);
-  return eff;
-}
-
 // One query row, transformed as the forward kernels transform it (rounded to bf16 once), times
 // scale * log2 e, as fp32 in shared memory.  One warp per row.
 template <int DC, int DR, int MODE>
@@ -228,7 +197,7 @@ pe_attn_decode_kernel(const KParams p, const DecodeParams dp, const __grid_const
   if constexpr (MODE == MODE_POPE) {
     if (tid < 4 * DR) {   // four threads per column (whole warps: 4 DR is 128 or 256)
       const int c = tid >> 2;
-      const float f = effective_freq_quad(p, c, tid & 3);
+      const float f = effective_freq_lanes<4>(p, c, tid & 3);
       if ((tid & 3) == 0) {
         freq_s[c] = f;
         delta_s[c] = clamped_delta(p, c);

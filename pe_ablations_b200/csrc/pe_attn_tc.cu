@@ -146,9 +146,13 @@ pe_attn_tc_kernel(const KParams p, const int bh_group, const __grid_constant__ C
     tmem_relinquish();
   }
   if constexpr (MODE == MODE_POPE) {
-    if (tid >= 128 && tid < 128 + DR) {
-      freq_s[tid - 128] = effective_freq(p, tid - 128);
-      delta_s[tid - 128] = clamped_delta(p, tid - 128);
+    // eight lanes per frequency column (whole warps: 8 DR is a multiple of 32)
+    if (tid < 8 * DR) {
+      const float f = effective_freq_lanes<8>(p, tid >> 3, tid & 7);
+      if ((tid & 7) == 0) {
+        freq_s[tid >> 3] = f;
+        delta_s[tid >> 3] = clamped_delta(p, tid >> 3);
+      }
     }
   }
   tc_fence_before_sync();

@@ -291,31 +291,40 @@ __global__ void __launch_bounds__(256) rotary_norm_kernel(const RnParams p) {
 
 // ---- FoPE frequency mix (src/model/fpope.py:107-146) and its gradient -------------------------
 // One thread per position dimension c; d_r and the number of Fourier terms are tens.
+// one warp per frequency column
 __global__ void fope_freqs_kernel(const KParams p, int d_r, float* omega) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c < d_r) omega[c] = effective_freq(p, c);
+  const int c = (int)((blockIdx.x * blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
+  if (c >= d_r) return;
+  const float f = effective_freq_lanes<32>(p, c, lane);
+  if (lane == 0) omega[c] = f;
 }
 
 // eff = base * W / Z + base with W = sum_j a_j j, Z = sum_j |a_j| + 1e-8 (Z = 1 without
 // normalisation); zero gradient where the floor clip or the ceiling clamp is active.
 __global__ void fope_freqs_backward_kernel(const KParams p, int d_r, const double* d_omega, float* d_coeffs,
                                            float* d_base) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  // one warp per frequency column, the Fourier terms dealt to its lanes
+  const int c = (int)((blockIdx.x * blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
   if (c >= d_r) return;
   const float* a = p.coeffs + (size_t)c * p.n_fourier;
   const bool normalize = (p.flags & PE_ATTN_FOURIER_NORMALIZE) != 0;
-  double Z = 1.0, W = 0.0;
-  if (normalize) {
-    Z = 1e-8;
-    for (int j = 0; j < p.n_fourier; ++j) Z += fabs((double)a[j]);
+  double Zs = 0.0, W = 0.0;
+  for (int j = lane; j < p.n_fourier; j += 32) {
+    Zs += fabs((double)a[j]);
+    W += (double)a[j] * (j + 1);
   }
-  for (int j = 0; j < p.n_fourier; ++j) W += (double)a[j] * (j + 1);
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    Zs += __shfl_xor_sync(0xffffffffu, Zs, d);
+    W += __shfl_xor_sync(0xffffffffu, W, d);
+  }
+  const double Z = normalize ? 1e-8 + Zs : 1.0;
   const double base = p.freqs[c];
   const double eff = base * W / Z + base;
   bool pass = fabs(eff) >= (double)p.floor_freq;
   if ((p.flags & PE_ATTN_FOURIER_CEILING) && fabs(eff) > (double)p.ceil_freq) pass = false;
   const double g = pass ? d_omega[c] : 0.0;
-  for (int j = 0; j < p.n_fourier; ++j) {
+  for (int j = lane; j < p.n_fourier; j += 32) {
     double d = (j + 1) / Z;
     if (normalize) {
       const double sgn = a[j] > 0.f ? 1.0 : (a[j] < 0.f ? -1.0 : 0.0);
@@ -323,7 +332,7 @@ __global__ void fope_freqs_backward_kernel(const KParams p, int d_r, const doubl
     }
     d_coeffs[(size_t)c * p.n_fourier + j] = (float)(g * base * d);
   }
-  if (d_base != nullptr) d_base[c] = (float)(g * (W / Z + 1.0));
+  if (d_base != nullptr && lane == 0) d_base[c] = (float)(g * (W / Z + 1.0));
 }
 
 int check_tensor(const char* name, const void* ptr, const int64_t* s) {
@@ -531,7 +540,7 @@ extern "C" int pe_fope_effective_freqs(const float* base, const float* coeffs, i
     set_error("omega is null");
     return PE_ATTN_ERR_NULL;
   }
-  fope_freqs_kernel<<<(d_r + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(k, d_r, omega);
+  fope_freqs_kernel<<<(d_r * 32 + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(k, d_r, omega);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("pe_fope_effective_freqs launch failed: %s", cudaGetErrorString(e));
@@ -550,7 +559,7 @@ extern "C" int pe_fope_effective_freqs_backward(const float* base, const float* 
     set_error("d_omega and d_coeffs are required");
     return PE_ATTN_ERR_NULL;
   }
-  fope_freqs_backward_kernel<<<(d_r + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(k, d_r, d_omega, d_coeffs,
+  fope_freqs_backward_kernel<<<(d_r * 32 + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(k, d_r, d_omega, d_coeffs,
                                                                                             d_base);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
