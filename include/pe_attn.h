@@ -49,7 +49,7 @@
 extern "C" {
 #endif
 
-#define PE_ATTN_ABI_VERSION 3
+#define PE_ATTN_ABI_VERSION 4
 
 typedef enum pe_attn_variant {
   PE_ATTN_NOPE = 0,   /* no positional transform                                            */
@@ -199,7 +199,7 @@ int pe_attn_selftest_wait_expiry(int32_t* device_status, int64_t limit_cycles, v
 /* ---- attention backward (the gradient autograd derives from the SDPA call) ------------------
  *
  * Gradients of  out = softmax_causal(scale * Q K^T + bias) V  with respect to Q, K and V, for
- * bf16 operands that already carry their positional transform: the quantity PyTorch's
+ * bf16 or fp32 operands that already carry their positional transform: the quantity PyTorch's
  * autograd produces for F.scaled_dot_product_attention at src/model/attention.py:91-96,
  * src/model/fpope_attention.py:171-177 and for the explicit softmax of
  * src/model/alibi.py:145-160 (bias = -slope_h * (t - s) when alibi_slopes is given).  The
@@ -208,14 +208,17 @@ int pe_attn_selftest_wait_expiry(int32_t* device_status, int64_t limit_cycles, v
  * The backward of the positional transform itself is left to the caller (the Python host
  * differentiates its own restatement of the transform).
  *
- * q [B,H,Sq,d_qk], k [B,Hkv,Sk,d_qk], v [B,Hkv,Sk,d_v], out / dout [B,H,Sq,d_v]: bf16, element
- * strides (batch, head, seq), 16-byte aligned, strides multiples of 8.  lse: the forward's
+ * q [B,H,Sq,d_qk], k [B,Hkv,Sk,d_qk], v [B,Hkv,Sk,d_v], out / dout [B,H,Sq,d_v]: ``dtype``,
+ * element strides (batch, head, seq), 16-byte aligned, strides multiples of 8.  lse: the forward's
  * logsumexp output [B,H,Sq] fp32.  dq_accum: fp32 [B,Sq,H,d_qk] contiguous -- cleared and
  * then accumulated into by the call (TMA reductions in an order that is not fixed: bitwise
  * results vary between runs);
- * dk / dv: bf16 outputs shaped and strided like k / v (each written exactly once); dvec:
- * fp32 [B,H,Sq] workspace.  (d_qk, d_v) in {(64,64), (128,64), (128,128)}.  Causal rule as
- * in the forward: key s is visible to query row r iff s <= r + (Sk - Sq). */
+ * dk / dv: outputs of type ``dtype`` shaped and strided like k / v (each written exactly once);
+ * dvec: fp32 [B,H,Sq] workspace.  bf16 with (d_qk, d_v) in {(64,64), (128,64), (128,128)} runs on
+ * the tensor cores; every other multiple of 8 up to (256, 128), and every fp32 call, on the CUDA
+ * cores (fixed summation order; fp32 covers all head dims but (256, 128), whose 64-row tiles
+ * exceed a CTA's shared memory).  Causal rule as in the forward: key s is visible to query row
+ * r iff s <= r + (Sk - Sq). */
 typedef struct pe_attn_bwd_args {
   uint32_t struct_size;       /* sizeof(pe_attn_bwd_args), checked                            */
   int32_t B, H, Hkv, Sq, Sk, d_qk, d_v;
@@ -230,6 +233,7 @@ typedef struct pe_attn_bwd_args {
   int64_t dk_stride[3], dv_stride[3];
   float* dvec;
   int32_t* device_status;     /* as in pe_attn_args; may be null                             */
+  int32_t dtype;              /* pe_attn_dtype of q, k, v, out, dout, dk, dv                  */
 } pe_attn_bwd_args;
 
 int pe_attn_backward(const pe_attn_bwd_args* args, void* stream);

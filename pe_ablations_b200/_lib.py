@@ -68,7 +68,7 @@ class PeAttnBwdArgs(C.Structure):
         ("out_stride", C.c_int64 * 3), ("dout_stride", C.c_int64 * 3),
         ("lse", C.c_void_p), ("alibi_slopes", C.c_void_p), ("dq_accum", C.c_void_p),
         ("dk", C.c_void_p), ("dv", C.c_void_p), ("dk_stride", C.c_int64 * 3), ("dv_stride", C.c_int64 * 3),
-        ("dvec", C.c_void_p), ("device_status", C.c_void_p),
+        ("dvec", C.c_void_p), ("device_status", C.c_void_p), ("dtype", C.c_int32),
     ]
 
 

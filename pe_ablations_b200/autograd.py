@@ -14,10 +14,17 @@ its eager modules (src/model/attention.py:77-96, src/model/alibi.py:137-160,
 src/model/fpope_attention.py:145-177 with src/model/pope.py:124-183 /
 src/model/fpope.py:107-146,266-338, src/model/rope.py:35-57, src/model/normalization.py:44-56).
 
-bf16 only (run the modules under bf16 autocast).  (d_qk, d_v) in {(64, 64), (128, 64), (128, 128)}
--- every YAML configuration of the reference -- take the tensor-core backward kernel; the other
-head dimensions of the bf16 forward, d_qk = 192 / 256 with d_v = 128 (the 1B shape), take the
-FFMA backward kernels.  fp32 calls that need gradients raise; there is no eager fallback.
+bf16 (the modules under bf16 autocast, the precision of the reference's training loop): (d_qk, d_v)
+in {(64, 64), (128, 64), (128, 128)} -- every YAML configuration of the reference -- take the
+tensor-core backward kernel; the other head dimensions of the bf16 forward, d_qk = 192 / 256 with
+d_v = 128 (the 1B shape), take the FFMA backward kernels.
+
+fp32 (the reference's CPU-runnable configuration and its own tests): the forward is the fp32 FFMA
+kernel with the transform in-kernel, the attention core's gradients come from the fp32
+instantiation of the FFMA backward kernels, and the transform's gradient from autograd over
+``transformed_operands`` (ATen operations on the GPU, fp32 throughout: the transform kernels store
+bf16 operands and would throw the precision away).  A parity path, not a throughput path; d_qk + d_v
+<= 320, the bound of the backward's shared-memory tiles.
 """
 
 from __future__ import annotations
@@ -118,7 +125,9 @@ class FusedAttentionFunction(torch.autograd.Function):
 
         q, k, v, q_r, k_r, freqs, delta, fourier_coeffs, out, lse = ctx.saved_tensors
         variant, o = ctx.variant, ctx.o
-        dout = dout.to(torch.bfloat16)
+        dout = dout.to(v.dtype)
+        if v.dtype == torch.float32:
+            return FusedAttentionFunction._backward_fp32(ctx, dout)
         if variant == "pope":
             return FusedAttentionFunction._backward_pope(ctx, dout)
         from .ops import rotary_norm_expand
@@ -136,6 +145,42 @@ class FusedAttentionFunction(torch.autograd.Function):
             dq = rotary_norm_expand(q, *args_q, grad=dqt)
             dk = rotary_norm_expand(k, *args_k, grad=dkt)
         return (None, None, dq, dk, dv if ctx.needs_input_grad[4] else None, None, None, None, None, None)
+
+    @staticmethod
+    def _backward_fp32(ctx, dout):
+        """fp32: kernel for the attention core, autograd over the torch restatement for the transform."""
+        from .ops import attention_backward
+
+        q, k, v, q_r, k_r, freqs, delta, fourier_coeffs, out, lse = ctx.saved_tensors
+        variant, o = ctx.variant, ctx.o
+        need = ctx.needs_input_grad[2:]          # q, k, v, q_r, k_r, freqs, delta, fourier_coeffs
+        plain = variant in ("nope", "alibi") and not o["qk_norm"]
+        leaves = [None] * 8
+        if plain:
+            qt, kt = q, k
+        else:
+            with torch.enable_grad():
+                given = (q, k, None, q_r, k_r, freqs, delta, fourier_coeffs)
+                for i, t in enumerate(given):
+                    if t is not None:
+                        leaves[i] = t.detach().requires_grad_(bool(need[i]))
+                qt, kt = transformed_operands(variant, leaves[0], leaves[1], leaves[3], leaves[4], o, leaves[5],
+                                              leaves[6], leaves[7])
+        dqt, dkt, dv = attention_backward(qt.detach().contiguous(), kt.detach().contiguous(), v, out, dout, lse,
+                                          scale=o["scale"], alibi_slopes=o["alibi_slopes"])
+        grads = [None] * 8
+        if plain:
+            grads[0], grads[1] = dqt, dkt
+        else:
+            wanted = [i for i in range(8) if leaves[i] is not None and leaves[i].requires_grad]
+            pairs = [(t, g) for t, g in ((qt, dqt), (kt, dkt)) if t.requires_grad]
+            if wanted and pairs:
+                got = torch.autograd.grad([t for t, _ in pairs], [leaves[i] for i in wanted], [g for _, g in pairs],
+                                          allow_unused=True)
+                for i, g in zip(wanted, got):
+                    grads[i] = g
+        grads[2] = dv if need[2] else None
+        return (None, None, *grads)
 
     @staticmethod
     def _backward_pope(ctx, dout):

@@ -168,10 +168,12 @@ int pe_attn_backward(const pe_attn_bwd_args* a, void* stream) {
   if (a->H % a->Hkv != 0) return fail(PE_ATTN_ERR_SHAPE, "H=%d is not a multiple of Hkv=%d", a->H, a->Hkv);
   if (a->Sk < a->Sq) return fail(PE_ATTN_ERR_SHAPE, "Sk=%d < Sq=%d", a->Sk, a->Sq);
   if (a->B > 65535 || a->Hkv > 65535) return fail(PE_ATTN_ERR_SHAPE, "B and Hkv must be <= 65535");
-  if (!bwd_supports(a->d_qk, a->d_v) && !bwd_simt_supports(a->d_qk, a->d_v))
+  if (a->dtype != PE_ATTN_BF16 && a->dtype != PE_ATTN_FP32) return fail(PE_ATTN_ERR_VARIANT, "unknown dtype %d", a->dtype);
+  if (!(a->dtype == PE_ATTN_BF16 && bwd_supports(a->d_qk, a->d_v)) && !bwd_simt_supports(a->d_qk, a->d_v, a->dtype))
     return fail(PE_ATTN_ERR_SHAPE,
-                "backward supports (d_qk, d_v) in {(64,64), (128,64), (128,128)} on the tensor cores and any "
-                "multiples of 8 up to (256, 128) on the CUDA cores (got %d, %d)", a->d_qk, a->d_v);
+                "backward supports (d_qk, d_v) in {(64,64), (128,64), (128,128)} on the tensor cores (bf16) and any "
+                "multiples of 8 up to (256, 128) on the CUDA cores -- in fp32 all of those but (256, 128), whose "
+                "tiles do not fit shared memory (got %d, %d, dtype %d)", a->d_qk, a->d_v, a->dtype);
   struct { const char* name; const void* p; const int64_t* s; } ts[] = {
       {"q", a->q, a->q_stride},       {"k", a->k, a->k_stride},   {"v", a->v, a->v_stride},
       {"out", a->out, a->out_stride}, {"dout", a->dout, a->dout_stride},
@@ -205,7 +207,7 @@ int pe_attn_backward(const pe_attn_bwd_args* a, void* stream) {
   p.dv = make_ref(a->dv, a->dv_stride);
   p.lse = a->lse; p.slopes = a->alibi_slopes;
   p.dq_accum = a->dq_accum; p.dvec = a->dvec; p.status = a->device_status;
-  return launch_bwd(p, a->d_qk, a->d_v, a->alibi_slopes != nullptr, static_cast<cudaStream_t>(stream));
+  return launch_bwd(p, a->d_qk, a->d_v, a->dtype, a->alibi_slopes != nullptr, static_cast<cudaStream_t>(stream));
 }
 
 int pe_attn_version(void) { return PE_ATTN_ABI_VERSION; }

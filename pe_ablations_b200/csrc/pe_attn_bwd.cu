@@ -561,9 +561,10 @@ bool bwd_supports(int d_qk, int d_v) {
   return (d_qk == 64 && d_v == 64) || (d_qk == 128 && d_v == 64) || (d_qk == 128 && d_v == 128);
 }
 
-int launch_bwd(const BwdParams& p, int d_qk, int d_v, bool alibi, cudaStream_t stream) {
-  // head dimensions without a tensor-core instantiation (d_qk = 256 above all) run on the CUDA cores
-  if (!bwd_supports(d_qk, d_v)) return launch_bwd_simt(p, d_qk, d_v, alibi, stream);
+int launch_bwd(const BwdParams& p, int d_qk, int d_v, int dtype, bool alibi, cudaStream_t stream) {
+  // fp32 calls, and head dimensions without a tensor-core instantiation (d_qk = 256 above all),
+  // run on the CUDA cores
+  if (dtype != PE_ATTN_BF16 || !bwd_supports(d_qk, d_v)) return launch_bwd_simt(p, d_qk, d_v, dtype, alibi, stream);
   if (d_qk == 64 && d_v == 64)
     return alibi ? launch_bwd_instance<64, 64, true>(p, stream) : launch_bwd_instance<64, 64, false>(p, stream);
   if (d_qk == 128 && d_v == 64)

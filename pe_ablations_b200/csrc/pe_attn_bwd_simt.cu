@@ -2,10 +2,12 @@
 // backward kernel does not have -- above all d_qk = 256 / d_v = 128, the 1B evaluation shape, so
 // that every model the forward serves can also be trained through the drop-in modules.
 //
-// Same contract as the tensor-core kernel: bf16 operands that already carry their positional
+// Same contract as the tensor-core kernel: operands that already carry their positional
 // transform, the forward's logsumexp, gradients of
 //     out = softmax_causal(scale * Q K^T + bias) V
-// with respect to Q (fp32 [B,Sq,H,d_qk]), K and V (bf16, caller's strides).  It is the part of
+// with respect to Q (fp32 [B,Sq,H,d_qk]), K and V (the operands' type, caller's strides).  The
+// kernels are templates over the element type: bf16, and fp32 -- the only backward fp32 calls
+// have (the reference's CPU-runnable configuration and its tests run in fp32).  It is the part of
 // the reference's training step that autograd derives from F.scaled_dot_product_attention
 // (src/model/attention.py:91-96, src/model/fpope_attention.py:171-177, src/model/alibi.py:145-160).
 //
@@ -15,7 +17,7 @@
 //   * query side: one CTA owns 64 query rows of one head and walks over the key blocks it sees:
 //                 dQ = dS K
 // with P = exp(scale S + bias - lse), dS = scale * P o (dO V^T - D), D = rowsum(dO o O).  Tiles
-// are held in shared memory as bf16 rows padded to an odd number of 16-byte slots, products
+// are held in shared memory in the operands' type, rows padded by one 16-byte slot, products
 // run as 4 x 4 (scores) and 4 x 8 / 4 x 16 (gradients) register tiles in fp32.  Nothing here
 // waits on anything but __syncthreads; no atomics, results do not depend on CTA scheduling.
 #include <cuda_bf16.h>
@@ -35,23 +37,57 @@ __device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 
 struct SimtBwdParams {
   BwdParams b;
   int d_qk, d_v;
-  int ldq, ldv;   // bf16 pitches of the d_qk- and d_v-wide tiles: width + 8
+  int ldq, ldv;   // element pitches of the d_qk- and d_v-wide tiles: width + 16 bytes
 };
 
-// rows [row0, row0 + 64) of a [B, H, S, d] bf16 tensor -> shared memory, 16 bytes per thread and step
-__device__ __forceinline__ void load_tile(__nv_bfloat16* dst, int ld, const TensorRef& t, int b, int h, int row0,
-                                          int n_rows, int d) {
-  const int vec = d / 8;
-  const char* base = reinterpret_cast<const char*>(t.ptr) + 2 * ((long long)b * t.sb + (long long)h * t.sh);
+template <typename T>
+struct Elem;
+template <>
+struct Elem<__nv_bfloat16> {
+  static constexpr int PAD = 8;   // elements in 16 bytes
+};
+template <>
+struct Elem<float> {
+  static constexpr int PAD = 4;
+};
+
+// eight consecutive elements (16-byte aligned) as fp32
+__device__ __forceinline__ void load8(const __nv_bfloat16* src, float (&x)[8]) {
+  const uint4 w = *reinterpret_cast<const uint4*>(src);
+  x[0] = bf_lo(w.x); x[1] = bf_hi(w.x); x[2] = bf_lo(w.y); x[3] = bf_hi(w.y);
+  x[4] = bf_lo(w.z); x[5] = bf_hi(w.z); x[6] = bf_lo(w.w); x[7] = bf_hi(w.w);
+}
+__device__ __forceinline__ void load8(const float* src, float (&x)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(src), b = *reinterpret_cast<const float4*>(src + 4);
+  x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+  x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* dst, const float (&x)[8]) {
+  __align__(16) __nv_bfloat16 o[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) o[e] = __float2bfloat16_rn(x[e]);
+  *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(o);
+}
+__device__ __forceinline__ void store8(float* dst, const float (&x)[8]) {
+  *reinterpret_cast<float4*>(dst) = make_float4(x[0], x[1], x[2], x[3]);
+  *reinterpret_cast<float4*>(dst + 4) = make_float4(x[4], x[5], x[6], x[7]);
+}
+
+// rows [row0, row0 + 64) of a [B, H, S, d] tensor -> shared memory, 16 bytes per thread and step
+template <typename T>
+__device__ __forceinline__ void load_tile(T* dst, int ld, const TensorRef& t, int b, int h, int row0, int n_rows, int d) {
+  constexpr int EV = 16 / (int)sizeof(T);
+  const int vec = d / EV;
+  const T* base = reinterpret_cast<const T*>(t.ptr) + (long long)b * t.sb + (long long)h * t.sh;
   for (int idx = threadIdx.x; idx < BT * vec; idx += NTHREADS) {
     const int r = idx / vec, c = idx - r * vec;
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (row0 + r < n_rows) v = *reinterpret_cast<const uint4*>(base + 2 * ((long long)(row0 + r) * t.ss + c * 8));
-    *reinterpret_cast<uint4*>(dst + r * ld + c * 8) = v;
+    if (row0 + r < n_rows) v = *reinterpret_cast<const uint4*>(base + (long long)(row0 + r) * t.ss + c * EV);
+    *reinterpret_cast<uint4*>(dst + r * ld + c * EV) = v;
   }
 }
 
-// acc[i][j] += sum_c A[ty + 16 i][c] * B[tx + 16 j][c] over ``d`` bf16 columns (8 per step)
+// acc[i][j] += sum_c A[ty + 16 i][c] * B[tx + 16 j][c] over ``d`` columns (16 bytes per step)
 __device__ __forceinline__ void dot_tiles(float (&acc)[4][4], const __nv_bfloat16* A, const __nv_bfloat16* Bm, int ld,
                                           int d, int ty, int tx) {
   for (int c = 0; c < d; c += 8) {
@@ -77,12 +113,33 @@ __device__ __forceinline__ void dot_tiles(float (&acc)[4][4], const __nv_bfloat1
     }
   }
 }
+__device__ __forceinline__ void dot_tiles(float (&acc)[4][4], const float* A, const float* Bm, int ld, int d, int ty,
+                                          int tx) {
+  for (int c = 0; c < d; c += 4) {
+    float4 a[4], bb[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) a[i] = *reinterpret_cast<const float4*>(A + (ty + 16 * i) * ld + c);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) bb[j] = *reinterpret_cast<const float4*>(Bm + (tx + 16 * j) * ld + c);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float s = acc[i][j];
+        s = fmaf(a[i].x, bb[j].x, s);
+        s = fmaf(a[i].y, bb[j].y, s);
+        s = fmaf(a[i].z, bb[j].z, s);
+        s = fmaf(a[i].w, bb[j].w, s);
+        acc[i][j] = s;
+      }
+  }
+}
 
 // P and dS of one 64 x 64 (query, key) tile from the tiles in shared memory; thread (ty, tx)
 // owns queries ty + 16 i and keys tx + 16 j.  Writes both to shared memory ([query][key], fp32).
-template <bool ALIBI>
-__device__ __forceinline__ void prob_tile(const SimtBwdParams& sp, const __nv_bfloat16* Qs, const __nv_bfloat16* Ks,
-                                          const __nv_bfloat16* dOs, const __nv_bfloat16* Vs, const float* lse_s,
+template <typename T, bool ALIBI>
+__device__ __forceinline__ void prob_tile(const SimtBwdParams& sp, const T* Qs, const T* Ks, const T* dOs, const T* Vs,
+                                          const float* lse_s,
                                           const float* D_s, float* Ps, float* dSs, int q0, int k0, float slope, int ty,
                                           int tx) {
   const BwdParams& p = sp.b;
@@ -114,30 +171,31 @@ __device__ __forceinline__ void prob_tile(const SimtBwdParams& sp, const __nv_bf
 }
 
 // D[b, h, row] = sum_c dO * O: one warp per row
+template <typename T>
 __global__ void __launch_bounds__(256) rowdot_kernel(const BwdParams p, int d_v) {
   const int warp = (int)((blockIdx.x * 256 + threadIdx.x) >> 5), lane = threadIdx.x & 31;
   const long long n = (long long)p.B * p.H * p.Sq;
   if (warp >= n) return;
   const int row = warp % p.Sq, h = (warp / p.Sq) % p.H, b = warp / ((long long)p.Sq * p.H);
-  const __nv_bfloat16* o = reinterpret_cast<const __nv_bfloat16*>(p.out.ptr) + (long long)b * p.out.sb +
-                           (long long)h * p.out.sh + (long long)row * p.out.ss;
-  const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(p.dout.ptr) + (long long)b * p.dout.sb +
-                           (long long)h * p.dout.sh + (long long)row * p.dout.ss;
+  const T* o = reinterpret_cast<const T*>(p.out.ptr) + (long long)b * p.out.sb + (long long)h * p.out.sh +
+               (long long)row * p.out.ss;
+  const T* g = reinterpret_cast<const T*>(p.dout.ptr) + (long long)b * p.dout.sb + (long long)h * p.dout.sh +
+               (long long)row * p.dout.ss;
   float acc = 0.f;
-  for (int c = lane; c < d_v; c += 32) acc = fmaf(__bfloat162float(o[c]), __bfloat162float(g[c]), acc);
+  for (int c = lane; c < d_v; c += 32) acc = fmaf((float)o[c], (float)g[c], acc);
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
   if (lane == 0) p.dvec[((long long)b * p.H + h) * p.Sq + row] = acc;
 }
 
-template <bool ALIBI>
+template <typename T, bool ALIBI>
 __global__ void __launch_bounds__(NTHREADS) bwd_simt_key_side_kernel(const SimtBwdParams sp) {
   const BwdParams& p = sp.b;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-  __nv_bfloat16* Qs = Ks + BT * sp.ldq;
-  __nv_bfloat16* Vs = Qs + BT * sp.ldq;
-  __nv_bfloat16* dOs = Vs + BT * sp.ldv;
+  T* Ks = reinterpret_cast<T*>(smem_raw);
+  T* Qs = Ks + BT * sp.ldq;
+  T* Vs = Qs + BT * sp.ldq;
+  T* dOs = Vs + BT * sp.ldv;
   float* Ps = reinterpret_cast<float*>(dOs + BT * sp.ldv);
   float* dSs = Ps + BT * P_LD;
   float* lse_s = dSs + BT * P_LD;
@@ -173,7 +231,7 @@ __global__ void __launch_bounds__(NTHREADS) bwd_simt_key_side_kernel(const SimtB
         D_s[tid] = row < p.Sq ? p.dvec[((long long)b * p.H + h) * p.Sq + row] : 0.f;
       }
       __syncthreads();
-      prob_tile<ALIBI>(sp, Qs, Ks, dOs, Vs, lse_s, D_s, Ps, dSs, q0, k0, slope, ty, tx);
+      prob_tile<T, ALIBI>(sp, Qs, Ks, dOs, Vs, lse_s, D_s, Ps, dSs, q0, k0, slope, ty, tx);
       __syncthreads();
       // dV[key][c] += sum_q P[q][key] dO[q][c];  dK[key][c] += sum_q dS[q][key] Q[q][c]
       for (int q = 0; q < BT; ++q) {
@@ -184,8 +242,8 @@ __global__ void __launch_bounds__(NTHREADS) bwd_simt_key_side_kernel(const SimtB
           dsq[i] = dSs[q * P_LD + ty + 16 * i];
         }
         if (tx < n_vg) {
-          const uint4 w = *reinterpret_cast<const uint4*>(dOs + q * sp.ldv + tx * 8);
-          const float x[8] = {bf_lo(w.x), bf_hi(w.x), bf_lo(w.y), bf_hi(w.y), bf_lo(w.z), bf_hi(w.z), bf_lo(w.w), bf_hi(w.w)};
+          float x[8];
+          load8(dOs + q * sp.ldv + tx * 8, x);
 #pragma unroll
           for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -194,8 +252,8 @@ __global__ void __launch_bounds__(NTHREADS) bwd_simt_key_side_kernel(const SimtB
 #pragma unroll
         for (int m = 0; m < 2; ++m) {
           if (tx + 16 * m < n_qg) {
-            const uint4 w = *reinterpret_cast<const uint4*>(Qs + q * sp.ldq + (tx + 16 * m) * 8);
-            const float x[8] = {bf_lo(w.x), bf_hi(w.x), bf_lo(w.y), bf_hi(w.y), bf_lo(w.z), bf_hi(w.z), bf_lo(w.w), bf_hi(w.w)};
+            float x[8];
+            load8(Qs + q * sp.ldq + (tx + 16 * m) * 8, x);
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -205,41 +263,35 @@ __global__ void __launch_bounds__(NTHREADS) bwd_simt_key_side_kernel(const SimtB
       }
     }
   }
-  // bf16 results, 16 bytes per store
+  // results in the operands' type, 16 bytes per store
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int key = k0 + ty + 16 * i;
     if (key >= p.Sk) continue;
     if (tx < n_vg) {
-      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(p.dv.ptr)) + (long long)b * p.dv.sb +
-                           (long long)hk * p.dv.sh + (long long)key * p.dv.ss + tx * 8;
-      __align__(16) __nv_bfloat16 o[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) o[e] = __float2bfloat16_rn(dv_acc[i][e]);
-      *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(o);
+      store8(reinterpret_cast<T*>(const_cast<void*>(p.dv.ptr)) + (long long)b * p.dv.sb + (long long)hk * p.dv.sh +
+                 (long long)key * p.dv.ss + tx * 8,
+             dv_acc[i]);
     }
 #pragma unroll
     for (int m = 0; m < 2; ++m) {
       if (tx + 16 * m < n_qg) {
-        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(p.dk.ptr)) + (long long)b * p.dk.sb +
-                             (long long)hk * p.dk.sh + (long long)key * p.dk.ss + (tx + 16 * m) * 8;
-        __align__(16) __nv_bfloat16 o[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) o[e] = __float2bfloat16_rn(dk_acc[m][i][e]);
-        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(o);
+        store8(reinterpret_cast<T*>(const_cast<void*>(p.dk.ptr)) + (long long)b * p.dk.sb + (long long)hk * p.dk.sh +
+                   (long long)key * p.dk.ss + (tx + 16 * m) * 8,
+               dk_acc[m][i]);
       }
     }
   }
 }
 
-template <bool ALIBI>
+template <typename T, bool ALIBI>
 __global__ void __launch_bounds__(NTHREADS) bwd_simt_query_side_kernel(const SimtBwdParams sp) {
   const BwdParams& p = sp.b;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-  __nv_bfloat16* Qs = Ks + BT * sp.ldq;
-  __nv_bfloat16* Vs = Qs + BT * sp.ldq;
-  __nv_bfloat16* dOs = Vs + BT * sp.ldv;
+  T* Ks = reinterpret_cast<T*>(smem_raw);
+  T* Qs = Ks + BT * sp.ldq;
+  T* Vs = Qs + BT * sp.ldq;
+  T* dOs = Vs + BT * sp.ldv;
   float* Ps = reinterpret_cast<float*>(dOs + BT * sp.ldv);
   float* dSs = Ps + BT * P_LD;
   float* lse_s = dSs + BT * P_LD;
@@ -273,7 +325,7 @@ __global__ void __launch_bounds__(NTHREADS) bwd_simt_query_side_kernel(const Sim
     load_tile(Ks, sp.ldq, p.k, b, hk, k0, p.Sk, sp.d_qk);
     load_tile(Vs, sp.ldv, p.v, b, hk, k0, p.Sk, sp.d_v);
     __syncthreads();
-    prob_tile<ALIBI>(sp, Qs, Ks, dOs, Vs, lse_s, D_s, Ps, dSs, q0, k0, slope, ty, tx);
+    prob_tile<T, ALIBI>(sp, Qs, Ks, dOs, Vs, lse_s, D_s, Ps, dSs, q0, k0, slope, ty, tx);
     __syncthreads();
     // dQ[q][c] += sum_k dS[q][k] K[k][c]: queries ty + 16 i, columns 8 (tx + 16 m) .. + 8
     for (int k = 0; k < BT; ++k) {
@@ -283,8 +335,8 @@ __global__ void __launch_bounds__(NTHREADS) bwd_simt_query_side_kernel(const Sim
 #pragma unroll
       for (int m = 0; m < 2; ++m) {
         if (tx + 16 * m < n_qg) {
-          const uint4 w = *reinterpret_cast<const uint4*>(Ks + k * sp.ldq + (tx + 16 * m) * 8);
-          const float x[8] = {bf_lo(w.x), bf_hi(w.x), bf_lo(w.y), bf_hi(w.y), bf_lo(w.z), bf_hi(w.z), bf_lo(w.w), bf_hi(w.w)};
+          float x[8];
+          load8(Ks + k * sp.ldq + (tx + 16 * m) * 8, x);
 #pragma unroll
           for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -309,23 +361,21 @@ __global__ void __launch_bounds__(NTHREADS) bwd_simt_query_side_kernel(const Sim
   }
 }
 
-}  // namespace
-
-// bf16, d_qk and d_v multiples of 8, d_qk <= 256, d_v <= 128
-bool bwd_simt_supports(int d_qk, int d_v) {
-  return d_qk >= 8 && d_qk <= 256 && d_qk % 8 == 0 && d_v >= 8 && d_v <= 128 && d_v % 8 == 0;
+size_t simt_bwd_smem(int d_qk, int d_v, size_t elem, int pad) {
+  return (size_t)2 * BT * ((d_qk + pad) + (d_v + pad)) * elem + (size_t)(2 * BT * P_LD + 2 * BT) * sizeof(float);
 }
 
-int launch_bwd_simt(const BwdParams& p, int d_qk, int d_v, bool alibi, cudaStream_t stream) {
+template <typename T>
+int launch_bwd_simt_t(const BwdParams& p, int d_qk, int d_v, bool alibi, cudaStream_t stream) {
   SimtBwdParams sp;
   sp.b = p;
   sp.d_qk = d_qk;
   sp.d_v = d_v;
-  sp.ldq = d_qk + 8;
-  sp.ldv = d_v + 8;
-  const size_t smem = (size_t)2 * BT * (sp.ldq + sp.ldv) * sizeof(__nv_bfloat16) + (size_t)(2 * BT * P_LD + 2 * BT) * sizeof(float);
+  sp.ldq = d_qk + Elem<T>::PAD;
+  sp.ldv = d_v + Elem<T>::PAD;
+  const size_t smem = simt_bwd_smem(d_qk, d_v, sizeof(T), Elem<T>::PAD);
   const long long rows = (long long)p.B * p.H * p.Sq;
-  rowdot_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, stream>>>(p, d_v);
+  rowdot_kernel<T><<<(unsigned)((rows * 32 + 255) / 256), 256, 0, stream>>>(p, d_v);
   cudaError_t e = cudaGetLastError();
   auto run = [&](auto key_kernel, auto query_kernel) {
     if (e == cudaSuccess) e = cudaFuncSetAttribute(key_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -337,13 +387,29 @@ int launch_bwd_simt(const BwdParams& p, int d_qk, int d_v, bool alibi, cudaStrea
     query_kernel<<<dim3((p.Sq + BT - 1) / BT, p.H, p.B), NTHREADS, smem, stream>>>(sp);
     e = cudaGetLastError();
   };
-  if (alibi) run(bwd_simt_key_side_kernel<true>, bwd_simt_query_side_kernel<true>);
-  else run(bwd_simt_key_side_kernel<false>, bwd_simt_query_side_kernel<false>);
+  if (alibi) run(bwd_simt_key_side_kernel<T, true>, bwd_simt_query_side_kernel<T, true>);
+  else run(bwd_simt_key_side_kernel<T, false>, bwd_simt_query_side_kernel<T, false>);
   if (e != cudaSuccess) {
     set_error("FFMA backward launch failed: %s", cudaGetErrorString(e));
     return PE_ATTN_ERR_LAUNCH;
   }
   return PE_ATTN_OK;
+}
+
+}  // namespace
+
+// d_qk and d_v multiples of 8, d_qk <= 256, d_v <= 128, and the four operand tiles of 64 rows fit
+// the 227 KB of shared memory a CTA can have (fp32: everything but d_qk 256 with d_v 128)
+bool bwd_simt_supports(int d_qk, int d_v, int dtype) {
+  if (!(d_qk >= 8 && d_qk <= 256 && d_qk % 8 == 0 && d_v >= 8 && d_v <= 128 && d_v % 8 == 0)) return false;
+  const size_t smem = dtype == PE_ATTN_FP32 ? simt_bwd_smem(d_qk, d_v, 4, Elem<float>::PAD)
+                                            : simt_bwd_smem(d_qk, d_v, 2, Elem<__nv_bfloat16>::PAD);
+  return smem <= 227 * 1024;
+}
+
+int launch_bwd_simt(const BwdParams& p, int d_qk, int d_v, int dtype, bool alibi, cudaStream_t stream) {
+  return dtype == PE_ATTN_FP32 ? launch_bwd_simt_t<float>(p, d_qk, d_v, alibi, stream)
+                               : launch_bwd_simt_t<__nv_bfloat16>(p, d_qk, d_v, alibi, stream);
 }
 
 }  // namespace pe_attn

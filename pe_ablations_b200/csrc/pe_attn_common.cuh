@@ -149,9 +149,9 @@ size_t decode_workspace_bytes(const KParams& p);
 int launch_decode(const KParams& p, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 
 bool bwd_supports(int d_qk, int d_v);        // tensor-core backward kernel
-bool bwd_simt_supports(int d_qk, int d_v);   // FFMA backward: any d_qk <= 256, d_v <= 128 in steps of 8
-int launch_bwd_simt(const BwdParams& p, int d_qk, int d_v, bool alibi, cudaStream_t stream);
-int launch_bwd(const BwdParams& p, int d_qk, int d_v, bool alibi, cudaStream_t stream);
+bool bwd_simt_supports(int d_qk, int d_v, int dtype);   // FFMA backward: d_qk <= 256, d_v <= 128 in steps of 8 whose tiles fit shared memory
+int launch_bwd_simt(const BwdParams& p, int d_qk, int d_v, int dtype, bool alibi, cudaStream_t stream);
+int launch_bwd(const BwdParams& p, int d_qk, int d_v, int dtype, bool alibi, cudaStream_t stream);
 
 void set_error(const char* fmt, ...);
 

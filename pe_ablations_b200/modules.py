@@ -11,10 +11,11 @@ Reference classes mirrored (paths inside the reference project):
   FPoPEGroupedQueryAttention  src/model/fpope_attention.py:29-181
   RMSNorm                     src/model/normalization.py:7-27
 
-The fused path is causal-only: a ``mask`` raises.  Under bf16 autocast the modules also
-train: a call that needs gradients goes through ``autograd.FusedAttentionFunction`` (fused
-forward, tensor-core backward kernel); in fp32, or at head dimensions the backward kernel
-does not have, such a call raises -- there is no eager fallback.
+The fused path is causal-only: a ``mask`` raises.  The modules also train: a call that needs
+gradients goes through ``autograd.FusedAttentionFunction`` -- under bf16 autocast the fused
+forward and the tensor-core (or, at the 1B head dims, FFMA) backward kernel, in fp32 the fp32
+FFMA forward and backward kernels; at head dimensions no backward kernel has, such a call
+raises -- there is no eager fallback.
 """
 
 from __future__ import annotations

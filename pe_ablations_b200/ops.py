@@ -205,15 +205,21 @@ def _training_call(variant, q, k, v, q_r, k_r, freqs, delta, fourier_coeffs, lse
 
     if variant not in _VARIANTS:
         raise ValueError(f"unknown variant {variant!r}")
-    if v.dtype != torch.bfloat16 or not v.is_cuda:
-        raise NotImplementedError("gradients are implemented for bf16 CUDA tensors only (run the module under bf16 "
-                                  "autocast); there is no eager fallback")
+    if v.dtype not in (torch.bfloat16, torch.float32) or not v.is_cuda:
+        raise NotImplementedError("gradients are implemented for bf16 and fp32 CUDA tensors; there is no eager "
+                                  "fallback")
     if kw["layout"] != "bshd" or kw["out"] is not None or lse is not None or kw["simt_check"]:
         raise NotImplementedError("a call that needs gradients takes [B, S, H, d] tensors and owns its outputs")
     d_qk = (q.shape[-1] if q is not None else 0) + (2 * q_r.shape[-1] if q_r is not None else 0)
-    if d_qk not in (64, 128, 192, 256) or v.shape[-1] not in (64, 128):
+    if v.dtype == torch.bfloat16 and (d_qk not in (64, 128, 192, 256) or v.shape[-1] not in (64, 128)):
         raise NotImplementedError(f"gradients need d_qk in (64, 128, 192, 256) and d_v in (64, 128) -- the bf16 forward's "
                                   f"head dims; got ({d_qk}, {v.shape[-1]})")
+    if v.dtype == torch.float32:
+        # four 64-row fp32 operand tiles (rows padded by 16 bytes) + the P / dS tiles in 227 KB
+        tiles = 2 * 64 * (d_qk + v.shape[-1] + 8) * 4 + (2 * 64 * 68 + 128) * 4
+        if d_qk % 8 or v.shape[-1] % 8 or d_qk > 256 or v.shape[-1] > 128 or tiles > 227 * 1024:
+            raise NotImplementedError(f"fp32 gradients need d_qk <= 256 and d_v <= 128 in steps of 8 whose backward "
+                                      f"tiles fit shared memory (all but (256, 128)); got ({d_qk}, {v.shape[-1]})")
     dev = v.device
     k_start = kw["start_pos"] if kw["k_start_pos"] is None else kw["k_start_pos"]
     tab = kw["rotary_table"]
@@ -398,19 +404,23 @@ def _forward_impl(
 def attention_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, dout: torch.Tensor,
                        lse: torch.Tensor, *, scale: float, alibi_slopes: torch.Tensor | None = None
                        ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """Gradients of ``softmax_causal(scale q k^T + bias) v`` for transformed bf16 operands.
+    """Gradients of ``softmax_causal(scale q k^T + bias) v`` for transformed operands.
 
-    (d_qk, d_v) in {(64,64), (128,64), (128,128)} run on the tensor cores; any other multiples of 8
-    up to (256, 128) -- the 1B shape's (256, 128) -- on the CUDA cores (FFMA kernels).
+    bf16 with (d_qk, d_v) in {(64,64), (128,64), (128,128)} runs on the tensor cores; any other
+    multiples of 8 up to (256, 128) -- the 1B shape's (256, 128) -- and every fp32 call on the CUDA
+    cores (FFMA kernels; fp32 has every head dim but (256, 128)).
 
-    q [B,Sq,H,d_qk], k [B,Sk,Hkv,d_qk], v [B,Sk,Hkv,d_v], out / dout [B,Sq,H,d_v] (bf16, last
-    dimension contiguous), ``lse`` the forward's [B,H,Sq] logsumexp.  Returns
-    ``(dq fp32 [B,Sq,H,d_qk], dk bf16 like k, dv bf16 like v)``; dq is the accumulation
-    buffer the kernel adds into.
+    q [B,Sq,H,d_qk], k [B,Sk,Hkv,d_qk], v [B,Sk,Hkv,d_v], out / dout [B,Sq,H,d_v] (all bf16 or all
+    fp32, last dimension contiguous), ``lse`` the forward's [B,H,Sq] logsumexp.  Returns
+    ``(dq fp32 [B,Sq,H,d_qk], dk like k, dv like v)``; dq is the accumulation buffer the kernel
+    adds into.
     """
+    dtype = q.dtype
+    if dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError(f"attention_backward needs bf16 or fp32 tensors (got {dtype})")
     for t in (q, k, v, out, dout):
-        if not t.is_cuda or t.dtype != torch.bfloat16:
-            raise TypeError("attention_backward needs bf16 CUDA tensors (there is no other path)")
+        if not t.is_cuda or t.dtype != dtype:
+            raise TypeError("attention_backward needs CUDA tensors of one dtype (there is no other path)")
     B, Sq, H, d_qk = q.shape
     _, Sk, Hkv, d_v = v.shape
     dev = q.device
@@ -425,8 +435,9 @@ def attention_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: t
     a.scale = float(scale)
     dq_accum = torch.empty(B, Sq, H, d_qk, dtype=torch.float32, device=dev)
     dvec = torch.empty(B, H, Sq, dtype=torch.float32, device=dev)
-    dk = torch.empty(B, Sk, Hkv, d_qk, dtype=torch.bfloat16, device=dev)
-    dv = torch.empty(B, Sk, Hkv, d_v, dtype=torch.bfloat16, device=dev)
+    dk = torch.empty(B, Sk, Hkv, d_qk, dtype=dtype, device=dev)
+    dv = torch.empty(B, Sk, Hkv, d_v, dtype=dtype, device=dev)
+    a.dtype = _lib.BF16 if dtype == torch.bfloat16 else _lib.FP32
     for name, sname, t in (("q", "q_stride", q), ("k", "k_stride", k), ("v", "v_stride", v), ("out", "out_stride", out),
                            ("dout", "dout_stride", dout), ("dk", "dk_stride", dk), ("dv", "dv_stride", dv)):
         setattr(a, name, t.data_ptr())

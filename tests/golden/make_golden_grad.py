@@ -6,7 +6,8 @@ parameters, run forward and backward under ``torch.autocast("cpu", dtype=torch.b
 (the precision of its training loop, src/training/trainer.py) with a seeded upstream gradient,
 and the output, the input gradient and every parameter gradient are stored.  The same run in
 fp32 is stored beside it: the distance between the two is the noise floor of bf16 training,
-which the parity test uses to scale its tolerance.
+which the parity test uses to scale its tolerance, and the fp32 output and gradients themselves
+(``y_fp32``, ``grad_fp32/...``) pin the fp32 backward of the drop-in modules.
 
 Run from the repository root:  python tests/golden/make_golden_grad.py --reference <checkout>
 """
@@ -60,8 +61,7 @@ def main():
             y.float().backward(dy)
             grads[mode] = {"x": x.grad.clone()}
             grads[mode].update({n: p.grad.float().clone() for n, p in m.named_parameters() if p.grad is not None})
-            if mode == "bf16":
-                data[f"{spec['name']}/y"] = y.detach().float().numpy()
+            data[f"{spec['name']}/y" + ("" if mode == "bf16" else "_fp32")] = y.detach().float().numpy()
         names = sorted(grads["bf16"])
         data[f"{spec['name']}/grad_names"] = np.array(names)
         worst = 0.0
@@ -69,6 +69,7 @@ def main():
             gb, gf = grads["bf16"][n], grads["fp32"][n]
             keep = gb[::G.TRAIN_ROW_STRIDE] if gb.dim() == 2 else gb
             data[f"{spec['name']}/grad/{n}"] = keep.numpy()
+            data[f"{spec['name']}/grad_fp32/{n}"] = (gf[::G.TRAIN_ROW_STRIDE] if gf.dim() == 2 else gf).numpy()
             # how far bf16 training itself sits from fp32: the scale for the parity tolerance
             data[f"{spec['name']}/bf16_noise/{n}"] = np.array(float((gb - gf).abs().max()))
             data[f"{spec['name']}/fp32_max/{n}"] = np.array(float(gf.abs().max()))

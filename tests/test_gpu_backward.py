@@ -18,9 +18,9 @@ pytestmark = pytest.mark.gpu
 TOL = dict(rtol=1e-2, atol=1e-2)
 
 
-def autograd_core(q, k, v, dout, scale, slopes=None):
-    """out, lse and (dq, dk, dv) of causal softmax attention in fp32; tensors are [B, S, H, d]."""
-    q, k, v = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+def autograd_core(q, k, v, dout, scale, slopes=None, dtype=torch.float32):
+    """out, lse and (dq, dk, dv) of causal softmax attention in ``dtype``; tensors are [B, S, H, d]."""
+    q, k, v = (t.detach().to(dtype).requires_grad_(True) for t in (q, k, v))
     B, Sq, H, _ = q.shape
     Sk, Hkv = k.shape[1], k.shape[2]
     g = H // Hkv
@@ -30,11 +30,11 @@ def autograd_core(q, k, v, dout, scale, slopes=None):
     rows = torch.arange(Sq).view(-1, 1) + (Sk - Sq)
     cols = torch.arange(Sk).view(1, -1)
     if slopes is not None:
-        s = s - slopes.float().view(1, H, 1, 1) * (rows - cols).clamp(min=0).float()
+        s = s - slopes.to(dtype).view(1, H, 1, 1) * (rows - cols).clamp(min=0).to(dtype)
     s = s.masked_fill(cols > rows, float("-inf"))
     lse = torch.logsumexp(s, dim=-1)
     out = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, dim=-1), vv)
-    out.backward(dout.float())
+    out.backward(dout.to(dtype))
     return out.detach(), lse.detach(), q.grad, k.grad, v.grad
 
 
@@ -87,6 +87,53 @@ def test_backward_matches_autograd(case):
     torch.testing.assert_close(dq.float().cpu(), dq_w, **tol)
 
 
+FP32_CASES = [
+    # name, B, H, Hkv, Sq, Sk, d_qk, d_v, alibi
+    ("fp32_config1_128_64", 1, 8, 8, 512, 512, 128, 64, False),
+    ("fp32_d64_gqa_ragged", 2, 4, 2, 300, 300, 64, 64, False),
+    ("fp32_alibi_d64_cached", 1, 4, 2, 131, 264, 64, 64, True),
+    ("fp32_192_128_mqa", 1, 4, 1, 200, 200, 192, 128, False),
+    ("fp32_d24_d40", 1, 2, 2, 70, 70, 24, 40, False),
+    ("fp32_single_row", 1, 2, 2, 1, 1, 64, 64, False),
+]
+
+
+@pytest.mark.parametrize("case", FP32_CASES, ids=lambda c: c[0])
+def test_fp32_backward_matches_autograd(case):
+    """fp32 operands through the FFMA backward kernels against autograd in fp64 (tolerance 1e-4 of
+    each gradient's largest entry: fp32 products and sums in a different order than the checker's)."""
+    from pe_ablations_b200 import check_device_status
+    from pe_ablations_b200.ops import attention_backward
+
+    _, B, H, Hkv, Sq, Sk, dqk, dv, alibi = case
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(4321)
+    mk = lambda s, h, d: torch.randn(B, s, h, d, generator=g)
+    q, k, v, dout = mk(Sq, H, dqk), mk(Sk, Hkv, dqk), mk(Sk, Hkv, dv), mk(Sq, H, dv)
+    scale = dqk ** -0.5
+    slopes = torch.tensor([2.0 ** (-(i + 1) * 8.0 / H) for i in range(H)]) if alibi else None
+    out, lse, dq_w, dk_w, dv_w = autograd_core(q, k, v, dout, scale, slopes, dtype=torch.float64)
+    c = lambda t: t.float().contiguous().to(dev)
+    dq, dk, dv_ = attention_backward(c(q), c(k), c(v), c(out), c(dout), c(lse), scale=scale, alibi_slopes=slopes)
+    torch.cuda.synchronize()
+    check_device_status()
+    assert dk.dtype == torch.float32 and dv_.dtype == torch.float32
+    for have, want, name in ((dq, dq_w, "dq"), (dk, dk_w, "dk"), (dv_, dv_w, "dv")):
+        err = (have.double().cpu() - want).abs().max().item()
+        bound = 1e-4 * max(want.abs().max().item(), 1e-1)    # single row: dq is exactly 0, operands are O(1)
+        assert err <= bound, f"{name}: |diff| {err:.3e} > {bound:.3e}"
+
+
+def test_fp32_backward_refuses_tiles_beyond_shared_memory():
+    from pe_ablations_b200 import _lib
+    from pe_ablations_b200.ops import attention_backward
+
+    dev = torch.device("cuda", 0)
+    mk = lambda d: torch.randn(1, 64, 2, d, device=dev)
+    with pytest.raises(_lib.PeAttnError):
+        attention_backward(mk(256), mk(256), mk(128), mk(128), mk(128), torch.zeros(1, 2, 64, device=dev), scale=0.1)
+
+
 @pytest.mark.parametrize("variant,dims", [("nope", (64, 0, 64)), ("nope", (128, 0, 128)), ("pope", (64, 32, 64)),
                                           ("pope", (128, 64, 128))])
 @pytest.mark.parametrize("S", [200, 1024])
@@ -131,6 +178,12 @@ def _train_cases():
     return list(enumerate(G.TRAIN_CASES))
 
 
+def _train_model_cases_early():
+    from oracle import golden_cases as G
+
+    return list(enumerate(G.TRAIN_MODEL_CASES))
+
+
 @pytest.mark.parametrize("i,spec", _train_cases(), ids=lambda s: s["name"] if isinstance(s, dict) else str(s))
 def test_module_gradients_match_reference_autograd(grads, i, spec):
     """Drop-in module under bf16 autocast, forward + backward, against the reference module's
@@ -173,15 +226,92 @@ def test_module_gradients_match_reference_autograd(grads, i, spec):
         assert err <= bound, f"{name} grad {n}: |diff| {err:.3e} > {bound:.3e}"
 
 
+@pytest.mark.parametrize("i,spec", _train_cases(), ids=lambda s: s["name"] if isinstance(s, dict) else str(s))
+def test_fp32_module_gradients_match_reference_autograd(grads, i, spec):
+    """Drop-in module in fp32, forward + backward, against the reference module's fp32 autograd
+    (``y_fp32`` / ``grad_fp32`` of the fixture): fp32 forward kernel, fp32 FFMA backward kernels,
+    the transform's gradient by autograd over its torch restatement.  Bound per tensor: 2e-4 of
+    its largest entry (parameter gradients sum over every token of the batch)."""
+    from oracle import golden_cases as G
+    from pe_ablations_b200 import check_device_status
+    from tests.test_modules_cpu import build_module
+
+    torch.manual_seed(7000 + i)
+    m = build_module(spec).train()
+    G.fill_parameters(m, 8000 + i)
+    m = m.cuda()
+    g = torch.Generator().manual_seed(9000 + i)
+    x = torch.randn(spec["B"], spec["S"], spec["hidden"], generator=g).cuda().requires_grad_(True)
+    dy = torch.randn(spec["B"], spec["S"], spec["hidden"], generator=g).cuda()
+    y = m(x)
+    assert y.dtype == torch.float32
+    y.backward(dy)
+    torch.cuda.synchronize()
+    check_device_status()
+    name = spec["name"]
+    want_y = torch.from_numpy(grads[f"{name}/y_fp32"])
+    assert (y.detach().cpu() - want_y).abs().max().item() <= 1e-4 * max(1.0, want_y.abs().max().item())
+    got = {"x": x.grad}
+    got.update({n: p.grad for n, p in m.named_parameters() if p.grad is not None})
+    names = [str(n) for n in grads[f"{name}/grad_names"]]
+    assert sorted(got) == names
+    for n in names:
+        want = torch.from_numpy(grads[f"{name}/grad_fp32/{n}"])
+        have = got[n].float().cpu()
+        if have.dim() == 2:
+            have = have[::G.TRAIN_ROW_STRIDE]
+        bound = 2e-4 * max(float(grads[f"{name}/fp32_max/{n}"]), 1e-3)
+        err = (have - want).abs().max().item()
+        assert err <= bound, f"{name} fp32 grad {n}: |diff| {err:.3e} > {bound:.3e}"
+
+
+@pytest.mark.parametrize("i,spec", _train_model_cases_early(), ids=lambda s: s["name"] if isinstance(s, dict) else str(s))
+def test_fp32_transformer_training_step(grads, i, spec):
+    """The Transformer host in fp32: the loss against the reference's fp32 loss, every parameter
+    with a finite gradient whose sample sits within the bf16 noise of the reference's bf16 one."""
+    from oracle import golden_cases as G
+    from pe_ablations_b200 import check_device_status
+    from pe_ablations_b200.model import Transformer, TransformerConfig
+
+    kw = dict(G.TRAIN_MODEL_BASE)
+    kw.update({k: v for k, v in spec.items() if k != "name"})
+    torch.manual_seed(7500 + i)
+    model = Transformer(TransformerConfig(**kw)).train()
+    G.fill_parameters(model, 8500 + i)
+    model = model.cuda()
+    ids = torch.randint(0, kw["vocab_size"], (G.TRAIN_MODEL_BATCH, G.TRAIN_MODEL_SEQ),
+                        generator=torch.Generator().manual_seed(9500 + i)).cuda()
+    out = model(ids, labels=ids)
+    out["loss"].backward()
+    torch.cuda.synchronize()
+    check_device_status()
+    name = spec["name"]
+    assert abs(out["loss"].item() - float(grads[f"{name}/loss_fp32"])) <= 1e-4 * float(grads[f"{name}/loss_fp32"])
+    got = {n: p.grad for n, p in model.named_parameters() if p.grad is not None}
+    assert sorted(got) == [str(n) for n in grads[f"{name}/grad_names"]]
+    for n, gr in got.items():
+        assert torch.isfinite(gr).all(), n
+        want = torch.from_numpy(grads[f"{name}/grad_sample/{n}"])            # the reference's bf16 step
+        have = gr.float().cpu().flatten()[::G.TRAIN_MODEL_SAMPLE_STRIDE]
+        bound = 1e-3 * float(grads[f"{name}/fp32_max/{n}"]) + 1.5 * float(grads[f"{name}/bf16_noise/{n}"])
+        err = (have - want).abs().max().item()
+        assert err <= bound, f"{name} fp32 grad {n}: |diff| {err:.3e} > {bound:.3e}"
+
+
 def test_training_call_refuses_what_the_backward_does_not_cover():
     from pe_ablations_b200 import pe_attention
 
     dev = torch.device("cuda", 0)
     mk = lambda d, dt: torch.randn(1, 64, 2, d, device=dev, dtype=dt, requires_grad=True)
-    with pytest.raises(NotImplementedError):     # fp32 has no backward kernel
-        pe_attention("nope", mk(64, torch.float32), mk(64, torch.float32), mk(64, torch.float32))
-    with torch.no_grad():                        # the same call without gradients is fine
-        pe_attention("nope", mk(64, torch.float32), mk(64, torch.float32), mk(64, torch.float32))
+    with pytest.raises(NotImplementedError):     # fp32 tiles of (256, 128) exceed shared memory
+        pe_attention("nope", mk(256, torch.float32), mk(256, torch.float32), mk(128, torch.float32))
+    with pytest.raises(NotImplementedError):     # bf16 head dims outside the forward's
+        pe_attention("nope", mk(96, torch.bfloat16), mk(96, torch.bfloat16), mk(64, torch.bfloat16))
+    with pytest.raises(NotImplementedError):     # a caller-owned output
+        pe_attention("nope", mk(64, torch.bfloat16), mk(64, torch.bfloat16), mk(64, torch.bfloat16),
+                     out=torch.empty(1, 64, 2, 64, device=dev, dtype=torch.bfloat16))
+    with torch.no_grad():                        # the same calls without gradients are fine
+        pe_attention("nope", mk(256, torch.float32), mk(256, torch.float32), mk(128, torch.float32))
 
 
 @pytest.mark.parametrize("dc,dr", [(128, 64), (128, 32)], ids=["d_qk256", "d_qk192"])
