@@ -80,10 +80,13 @@ __host__ __device__ __forceinline__ int block_tiles(int sblk, int Sk, int causal
   return (kend + BLOCK_N - 1) / BLOCK_N;
 }
 
+constexpr int MAX_K_STAGES = 4;
 enum : int {
-  BAR_QFULL = 0, BAR_KFULL = 2, BAR_KEMPTY = 4, BAR_VFULL = 6, BAR_VEMPTY = 8, BAR_SFULL = 10, BAR_PREADY = 12,
-  BAR_ODONE = 14, BAR_MMADONE = 16, BAR_PHALF = 17, NUM_BARS = 23   // BAR_PHALF: up to three partial hand-offs x two tiles
+  BAR_QFULL = 0, BAR_VFULL = 2, BAR_VEMPTY = 4, BAR_SFULL = 6, BAR_PREADY = 8, BAR_ODONE = 10, BAR_MMADONE = 12,
+  BAR_PHALF = 13,    // up to three partial hand-offs x two tiles
+  BAR_KFULL = 19, BAR_KEMPTY = BAR_KFULL + MAX_K_STAGES, NUM_BARS = BAR_KEMPTY + MAX_K_STAGES
 };
+static_assert(NUM_BARS * 8 <= 256, "the barriers share the first 256 bytes of the tail");
 
 template <int DC, int DR>
 struct Cfg2 {
@@ -95,9 +98,14 @@ struct Cfg2 {
   static constexpr int Q_TILE_BYTES = NCHUNK * Q_CHUNK_BYTES;
   static constexpr int K_STAGE_BYTES = NCHUNK * K_CHUNK_BYTES;   // this CTA's 64 keys
   static constexpr int V_STAGE_BYTES = BLOCK_N * 128;            // 128 keys x this CTA's 64 value columns
+  // K tiles in flight: two where d_qk = 192 / 256 fills the shared memory, four below that -- a
+  // K tile built by the transform warps (wake-up on "stage free", eight passes, proxy fence, an
+  // arrival at the leader's barrier) then has three steps instead of one before the MMA warp
+  // wants it, which at d_qk = 128 (short steps) it did not always make
+  static constexpr int K_STAGES = DQK <= 128 ? MAX_K_STAGES : 2;
   static constexpr int Q_OFF = TAIL_BYTES;
   static constexpr int K_OFF = Q_OFF + Q_TILES * Q_TILE_BYTES;
-  static constexpr int V_OFF = K_OFF + KV_STAGES * K_STAGE_BYTES;
+  static constexpr int V_OFF = K_OFF + K_STAGES * K_STAGE_BYTES;
   static constexpr int SMEM_USED = V_OFF + KV_STAGES * V_STAGE_BYTES;
   static constexpr int SMEM_BYTES = SMEM_USED + 1024;
   static_assert(DQK % 64 == 0 && DQK >= 64 && DQK <= 256, "d_qk must be 64..256 in steps of 64");
@@ -126,6 +134,9 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const int n_top, float* 
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
   const uint32_t rank = cluster_ctarank();          // 0 = leader
   auto lbar = [&](int idx) -> uint32_t { return mapa(bar(idx), 0); };  // the leader's copy of a barrier
+  // stage and barrier phase of key tile j in the ring of K stages
+  auto ks = [](int j) -> int { return j & (C::K_STAGES - 1); };
+  auto kph = [](int j) -> uint32_t { return (uint32_t)((j / C::K_STAGES) & 1); };
 
   // pair (cluster) index -> work item of a (batch, head), longest first within head groups.
   // Items per (batch, head): the n_top longest blocks as two parts each, the others whole.
@@ -209,14 +220,16 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const int n_top, float* 
     const uint32_t n_tma = HAS_TMA_QK ? 1u : 0u;
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(BAR_QFULL + i), 2 * (n_tma + n_xf));   // both CTAs report to the leader's copy
-      mbar_init(bar(BAR_KFULL + i), 2 * (n_tma + n_xf));
       mbar_init(bar(BAR_VFULL + i), 2);
       mbar_init(bar(BAR_PREADY + i), 8);                   // 4 softmax warps x 2 CTAs
       for (int part = 0; part < 3; ++part) mbar_init(bar(BAR_PHALF + 2 * part + i), 8);   // ... for the earlier parts of P
-      mbar_init(bar(BAR_KEMPTY + i), 1);
       mbar_init(bar(BAR_VEMPTY + i), 1);
       mbar_init(bar(BAR_SFULL + i), 1);
       mbar_init(bar(BAR_ODONE + i), 1);
+    }
+    for (int i = 0; i < C::K_STAGES; ++i) {
+      mbar_init(bar(BAR_KFULL + i), 2 * (n_tma + n_xf));
+      mbar_init(bar(BAR_KEMPTY + i), 1);
     }
     mbar_init(bar(BAR_MMADONE), 1);
     mbar_fence_init();
@@ -275,8 +288,8 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const int n_top, float* 
       }
 #pragma unroll 1
       for (int j = 0; j < n_tiles; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (uint32_t)((j >> 1) & 1);
+        const int s = ks(j);
+        const uint32_t ph = kph(j);
         if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_KEMPTY + s), ph ^ 1u))) { fail(ST_WAIT_KEMPTY); break; }
         if (elect_one()) {
           const uint32_t kb = lbar(BAR_KFULL + s);
@@ -321,7 +334,7 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const int n_top, float* 
       if (elect_one()) {
         const uint32_t d = tmem_base + (uint32_t)(i * BLOCK_N);
         uint64_t qd = advance_smem_desc(qdesc0, (uint32_t)(i * C::Q_TILE_BYTES));
-        uint64_t kd = advance_smem_desc(kdesc0, (uint32_t)((j & 1) * C::K_STAGE_BYTES));
+        uint64_t kd = advance_smem_desc(kdesc0, (uint32_t)(ks(j) * C::K_STAGE_BYTES));
 #pragma unroll 1
         for (int c = 0; c < C::NCHUNK; ++c) {
 #pragma unroll
@@ -336,7 +349,7 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const int n_top, float* 
       __syncwarp();
     };
     auto wait_k = [&](int j) -> bool {
-      if (!__all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_KFULL + (j & 1)), (uint32_t)((j >> 1) & 1)))) {
+      if (!__all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_KFULL + ks(j)), kph(j)))) {
         fail(ST_WAIT_KFULL);
         return false;
       }
@@ -411,7 +424,7 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const int n_top, float* 
       if (!ok) break;
       if (elect_one()) {
         tc_commit_pair(bar(BAR_VEMPTY + s), BOTH);
-        if (j + 1 < n_tiles) tc_commit_pair(bar(BAR_KEMPTY + ((j + 1) & 1)), BOTH);
+        if (j + 1 < n_tiles) tc_commit_pair(bar(BAR_KEMPTY + ks(j + 1)), BOTH);
       }
       __syncwarp();
     }
@@ -627,10 +640,10 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const int n_top, float* 
         const int grow = jb * BLOCK_N + rbase + r_in + k * RPP;
         nxt[k] = grow < p.Sk ? ldg_nc_v4(src + 2 * (long long)grow * p.kr.ss) : make_uint4(0, 0, 0, 0);
       }
-      const uint32_t kfull = lbar(BAR_KFULL + 0), kfull1 = lbar(BAR_KFULL + 1);
+      const uint32_t kfull = lbar(BAR_KFULL);
 #pragma unroll 1
       for (int j = 0; j < n_tiles; ++j) {
-        const int s = j & 1;
+        const int s = ks(j);
         uint4 cur[PASSES];
 #pragma unroll
         for (int k = 0; k < PASSES; ++k) cur[k] = nxt[k];
@@ -645,7 +658,7 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const int n_top, float* 
         const float pos0 = (float)(p.k_pos0 + (jb + j) * BLOCK_N + rbase);
 #pragma unroll
         for (int e = 0; e < 8; ++e) sincos_reduced(__fmul_rn(pos0, th[e]), &sb[e], &cb[e]);
-        const bool ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_KEMPTY + s), (uint32_t)(((j >> 1) & 1) ^ 1)));
+        const bool ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_KEMPTY + s), kph(j) ^ 1u));
         if (!ok) { fail(ST_WAIT_KEMPTY); break; }
         const uint32_t kb = k_smem + s * C::K_STAGE_BYTES;
 #pragma unroll
@@ -678,7 +691,7 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const int n_top, float* 
         }
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) PE_TC2_KFULL_ARRIVE(s ? kfull1 : kfull);
+        if (lane == 0) PE_TC2_KFULL_ARRIVE(kfull + 8u * (uint32_t)s);
       }
     } else if constexpr (MODE == MODE_XFORM) {
       // raw rows and table entries of the next tile are requested before the wait for its stage
@@ -689,8 +702,8 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const int n_top, float* 
       if (n_tiles > 0) xform_load_next<DC>(p, xr, cur, p.Sk, BLOCK_N);
 #pragma unroll 1
       for (int j = 0; j < n_tiles; ++j) {
-        const int s = j & 1;
-        const bool ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_KEMPTY + s), (uint32_t)(((j >> 1) & 1) ^ 1)));
+        const int s = ks(j);
+        const bool ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_KEMPTY + s), kph(j) ^ 1u));
         if (!ok) { fail(ST_WAIT_KEMPTY); break; }
         xform_finish<DC>(p, xr, k_smem + s * C::K_STAGE_BYTES, C::K_CHUNK_BYTES, (jb + j) * BLOCK_N + rbase, p.Sk, tg);
         fence_proxy_async_smem();
