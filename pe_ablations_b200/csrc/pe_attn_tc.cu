@@ -378,7 +378,14 @@ pe_attn_tc_kernel(const KParams p, const int bh_group, const __grid_constant__ C
           // logit (log2 units) = s * c2 - slope2 * (row_lim - key)
           const float base = slope2 * (float)(key0 - row_lim);
 #pragma unroll
-          for (int c = 0; c < 64; ++c) t[c] = fmaf(t[c], c2, fmaf((float)c, slope2, base));
+          for (int c = 0; c < 64; c += 2) {
+            // two columns per packed FMA (same roundings as fmaf(t, c2, fmaf(c, slope2, base)) each)
+            const float2 bias = __ffma2_rn(make_float2((float)c, (float)(c + 1)), make_float2(slope2, slope2),
+                                           make_float2(base, base));
+            const float2 r = __ffma2_rn(make_float2(t[c], t[c + 1]), make_float2(c2, c2), bias);
+            t[c] = r.x;
+            t[c + 1] = r.y;
+          }
         }
         const bool need_mask = (key0 + BLOCK_N - 1 > m0 + i * BLOCK_M + p.causal_off) || (key0 + BLOCK_N > p.Sk);
         if (need_mask) {

@@ -488,7 +488,14 @@ pe_attn_tc2_kernel(const KParams p, const int bh_group, const int n_top, float* 
         for (int c = 0; c < BLOCK_N; ++c) t[c] = __uint_as_float(sr[c >> 5][c & 31]);
         if constexpr (ALIBI) {
 #pragma unroll
-          for (int c = 0; c < BLOCK_N; ++c) t[c] = fmaf(t[c], c2, fmaf((float)c, slope2, base_bias));
+          for (int c = 0; c < BLOCK_N; c += 2) {
+            // two columns per packed FMA (same roundings as fmaf(t, c2, fmaf(c, slope2, base)) each)
+            const float2 bias = __ffma2_rn(make_float2((float)c, (float)(c + 1)), make_float2(slope2, slope2),
+                                           make_float2(base_bias, base_bias));
+            const float2 r = __ffma2_rn(make_float2(t[c], t[c + 1]), make_float2(c2, c2), bias);
+            t[c] = r.x;
+            t[c + 1] = r.y;
+          }
         }
         if (need_mask) {
           // columns past the row's last visible key (causal limit, end of the keys): one compare each
