@@ -154,8 +154,11 @@ int pe_attn_forward(const pe_attn_args* args, void* stream);
  * few (batch, head) problems cannot fill the GPU evenly: its longest query blocks decide the run
  * time.  Given this much workspace the CTA-pair kernel cuts those blocks in two along the keys
  * and merges the halves (bit-level results differ from the unsplit kernel by fp32 rounding of
- * the merge; both are within the tolerances).  Without it the call runs unsplit.  The
- * workspace is only used during the call's own kernels (stream-ordered). */
+ * the merge; both are within the tolerances).  Without it the call runs unsplit.  An fp32 call
+ * with a positional transform and at least 128 query rows uses its workspace for the transformed
+ * keys ([B][Hkv][Sk][d_qk] fp32, built once by a kernel in front of the attention kernel instead
+ * of once per query block; identical results).  The workspace is only used during the call's
+ * own kernels (stream-ordered). */
 size_t pe_attn_forward_workspace_bytes(const pe_attn_args* args);
 
 /* Validate only: same checks and return codes as pe_attn_forward, touches no GPU. */

@@ -242,7 +242,8 @@ const char* pe_attn_kernel_name(const pe_attn_args* args) {
 size_t pe_attn_forward_workspace_bytes(const pe_attn_args* args) {
   KParams k;
   if (validate(args, &k) != PE_ATTN_OK) return 0;
-  if (args->dtype != PE_ATTN_BF16 || (args->flags & (PE_ATTN_SIMT_CHECK | PE_ATTN_SINGLE_CTA))) return 0;
+  if (args->dtype == PE_ATTN_FP32) return simt_key_scratch_bytes(k);
+  if (args->flags & (PE_ATTN_SIMT_CHECK | PE_ATTN_SINGLE_CTA)) return 0;
   return (tc2_supports(k) && k.Sq > 256) ? tc2_workspace_bytes(k) : 0;
 }
 

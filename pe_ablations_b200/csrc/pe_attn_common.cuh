@@ -134,6 +134,7 @@ __device__ __forceinline__ float softplus_accurate(float x) {
 }
 
 int launch_simt(const KParams& p, int dtype, cudaStream_t stream);
+size_t simt_key_scratch_bytes(const KParams& p);   // fp32 calls: scratch for keys transformed once, or 0
 int launch_tc(const KParams& p, cudaStream_t stream);
 bool tc_supports(const KParams& p);
 int launch_tc2(const KParams& p, cudaStream_t stream);  // CTA-pair (cta_group::2) variant, d_v = 128

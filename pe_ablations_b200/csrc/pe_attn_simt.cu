@@ -161,8 +161,10 @@ __device__ __forceinline__ void store_elem<__nv_bfloat16>(void* base, long long 
 // RI: query rows per thread (stride 16): a CTA owns 16 RI query rows, 64 normally, 32 when the
 // launch would otherwise leave most SMs without a CTA (configuration 1: 64 CTAs on 148 SMs; the
 // longest CTA sets the run time, and half the rows halve its QK and PV work).
+// ``k_pre``: null, or the transformed keys of every (batch, K/V head) as written by
+// simt_key_pretransform_kernel -- the K tiles are then copied instead of built.
 template <typename T, bool ROUND, int VC, int RI>
-__global__ void __launch_bounds__(NTHREADS) pe_attn_simt_kernel(const KParams p) {
+__global__ void __launch_bounds__(NTHREADS) pe_attn_simt_kernel(const KParams p, const float* const k_pre) {
   constexpr int BMQ = 16 * RI;
   extern __shared__ __align__(16) float smem[];
   const int dqk = p.d_qk, dv = p.d_v;
@@ -207,7 +209,27 @@ __global__ void __launch_bounds__(NTHREADS) pe_attn_simt_kernel(const KParams p)
   if (k_end > p.Sk) k_end = p.Sk;
   for (int n0 = 0; n0 < k_end; n0 += BN) {
     __syncthreads();  // previous tile's reads of Ks / Vs / Ps are done (and Qs is complete)
-    build_operand_tile<T, ROUND>(p, Ks, ld, p.k, p.kr, b, hk, n0, p.Sk, p.k_pos0, true, freq_s, delta_s);
+    if (k_pre != nullptr) {
+      const int vec = dqk4 / 4;
+      const float4* src = reinterpret_cast<const float4*>(k_pre + ((long long)b * p.Hkv + hk) * p.Sk * dqk4);
+      for (int idx0 = tid; idx0 < BN * vec; idx0 += 4 * NTHREADS) {
+        float4 x[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int idx = idx0 + u * NTHREADS;
+          const int r = idx / vec, c = idx - r * vec;
+          x[u] = (idx < BN * vec && n0 + r < p.Sk) ? __ldg(src + (long long)(n0 + r) * vec + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int idx = idx0 + u * NTHREADS;
+          const int r = idx / vec, c = idx - r * vec;
+          if (idx < BN * vec) *reinterpret_cast<float4*>(&Ks[r * ld + 4 * c]) = x[u];
+        }
+      }
+    } else {
+      build_operand_tile<T, ROUND>(p, Ks, ld, p.k, p.kr, b, hk, n0, p.Sk, p.k_pos0, true, freq_s, delta_s);
+    }
     {
       const long long vbase = (long long)b * p.v.sb + (long long)hk * p.v.sh;
       for (int idx0 = tid; idx0 < BN * dv; idx0 += 4 * NTHREADS) {
@@ -323,7 +345,48 @@ __global__ void __launch_bounds__(NTHREADS) pe_attn_simt_kernel(const KParams p)
   }
 }
 
+// The transformed keys of every (batch, K/V head), once: [B][Hkv][Sk][round4(d_qk)] fp32, built by
+// the same code as a K tile inside the attention kernel (bit-identical values).  Every query block
+// of a head needs them, and the accurate softplus / sincos of the PoPE transform is 60 % of a key
+// tile's instructions: with S / 64 (or S / 32) query blocks per head the attention kernel would
+// repeat it that many times.
+template <typename T, bool ROUND>
+__global__ void __launch_bounds__(NTHREADS) simt_key_pretransform_kernel(const KParams p, float* const k_pre) {
+  extern __shared__ __align__(16) float smem[];
+  const int dqk4 = round4(p.d_qk), ld = dqk4 + 4;
+  float* Ks = smem;
+  float* freq_s = Ks + BN * ld;
+  float* delta_s = freq_s + (p.d_r > 0 ? p.d_r : 1);
+  const int tid = threadIdx.x;
+  const int n0 = (int)blockIdx.x * BN, hk = blockIdx.y, b = blockIdx.z;
+  if (p.variant == PE_ATTN_POPE) {
+    for (int c = tid; c < p.d_r; c += NTHREADS) {
+      freq_s[c] = effective_freq(p, c);
+      delta_s[c] = clamped_delta(p, c);
+    }
+    __syncthreads();
+  }
+  build_operand_tile<T, ROUND>(p, Ks, ld, p.k, p.kr, b, hk, n0, p.Sk, p.k_pos0, true, freq_s, delta_s);
+  __syncthreads();
+  const int vec = dqk4 / 4;
+  float4* dst = reinterpret_cast<float4*>(k_pre + ((long long)b * p.Hkv + hk) * p.Sk * dqk4);
+  for (int idx = tid; idx < BN * vec; idx += NTHREADS) {
+    const int r = idx / vec, c = idx - r * vec;
+    if (n0 + r < p.Sk) dst[(long long)(n0 + r) * vec + c] = *reinterpret_cast<const float4*>(&Ks[r * ld + 4 * c]);
+  }
+}
+
 }  // namespace
+
+// Scratch for the transformed keys of an fp32 call, or 0 where building K tiles in place is as
+// good: no transform to repeat (NoPE / ALiBi without QKNorm), fewer than two query blocks per
+// head, or more than 1 GiB.
+size_t simt_key_scratch_bytes(const KParams& p) {
+  const bool transform = p.variant == PE_ATTN_POPE || p.variant == PE_ATTN_ROTARY || (p.flags & PE_ATTN_QK_NORM);
+  if (!transform || p.Sq < 2 * BM) return 0;
+  const size_t bytes = (size_t)p.B * p.Hkv * p.Sk * round4(p.d_qk) * sizeof(float);
+  return bytes <= ((size_t)1 << 30) ? bytes : 0;
+}
 
 size_t simt_smem_bytes(const KParams& p) {
   const size_t ld = round4(p.d_qk) + 4;
@@ -337,8 +400,21 @@ cudaError_t launch_simt_instance(const KParams& p, size_t smem, cudaStream_t str
   auto kern = pe_attn_simt_kernel<T, ROUND, VC, RI>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
+  // fp32 calls that were given scratch transform the keys once, in front of the attention kernel
+  const float* k_pre = nullptr;
+  const size_t need = simt_key_scratch_bytes(p);
+  if (!ROUND && need > 0 && p.workspace != nullptr && p.workspace_bytes >= need) {
+    auto pre = simt_key_pretransform_kernel<T, ROUND>;
+    const size_t pre_smem = ((size_t)BN * (round4(p.d_qk) + 4) + 2 * (size_t)(p.d_r > 0 ? p.d_r : 1)) * sizeof(float);
+    e = cudaFuncSetAttribute(pre, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pre_smem);
+    if (e != cudaSuccess) return e;
+    pre<<<dim3((p.Sk + BN - 1) / BN, p.Hkv, p.B), dim3(NTHREADS), pre_smem, stream>>>(p, p.workspace);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    k_pre = p.workspace;
+  }
   dim3 grid((p.Sq + 16 * RI - 1) / (16 * RI), p.H, p.B);
-  kern<<<grid, dim3(NTHREADS), smem, stream>>>(p);
+  kern<<<grid, dim3(NTHREADS), smem, stream>>>(p, k_pre);
   return cudaGetLastError();
 }
 template <typename T, bool ROUND, int VC>

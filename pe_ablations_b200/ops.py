@@ -389,8 +389,10 @@ def _forward_impl(
             rc = _lib.lib.pe_attn_decode(C.byref(a), C.c_void_p(ws.data_ptr()), C.c_size_t(ws_bytes), C.c_void_p(stream))
         else:
             # few-wave launches of the CTA-pair kernel split their longest query blocks along the
-            # keys when given scratch for the partial results (stream-ordered, from the allocator)
-            fwd_ws = _lib.lib.pe_attn_forward_workspace_bytes(C.byref(a)) if (dtype == _lib.BF16 and split_blocks) else 0
+            # keys when given scratch for the partial results; fp32 calls transform their keys once
+            # into scratch instead of once per query block (stream-ordered, from the allocator)
+            fwd_ws = (_lib.lib.pe_attn_forward_workspace_bytes(C.byref(a))
+                      if ((dtype == _lib.BF16 and split_blocks) or dtype == _lib.FP32) else 0)
             if fwd_ws > 0:
                 ws = torch.empty(fwd_ws, dtype=torch.uint8, device=dev)
                 a.workspace, a.workspace_bytes = ws.data_ptr(), fwd_ws

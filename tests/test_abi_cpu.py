@@ -79,8 +79,11 @@ def test_forward_workspace_is_only_asked_for_few_wave_pair_launches(L):
     # other kernels never use it
     assert L.lib.pe_attn_forward_workspace_bytes(C.byref(_valid_args(L, B=1, H=2, Hkv=2, Sq=8192, Sk=8192,
                                                                   flags=L.SINGLE_CTA))) == 0
+    # fp32: the keys transformed once, [B][Hkv][Sk][d_qk] fp32 -- where there is a transform to repeat
     assert L.lib.pe_attn_forward_workspace_bytes(C.byref(_valid_args(L, B=1, H=2, Hkv=2, Sq=8192, Sk=8192,
-                                                                  dtype=L.FP32))) == 0
+                                                                  dtype=L.FP32))) == 1 * 2 * 8192 * 256 * 4
+    assert L.lib.pe_attn_forward_workspace_bytes(C.byref(_valid_args(L, B=1, H=2, Hkv=2, Sq=64, Sk=8192,
+                                                                  dtype=L.FP32))) == 0      # one query block
     # a misaligned workspace is refused
     bad = _valid_args(L, B=1, H=2, Hkv=2, Sq=8192, Sk=8192, workspace=0x10004, workspace_bytes=n)
     assert L.lib.pe_attn_validate(C.byref(bad)) == 4

@@ -3,6 +3,7 @@
 Tolerances (max abs error on the attention output): 1e-4 for fp32, 2e-2 for bf16.
 """
 
+import math
 import os
 
 import numpy as np
@@ -452,3 +453,37 @@ def test_host_streamed_call_equals_the_device_call(chunks):
     assert (out_host.float() - want).abs().max().item() <= TOL[torch.bfloat16]
     with pytest.raises(ValueError):
         call({**host, "q": host["q"].clone()}, out_host)      # not pinned
+
+@pytest.mark.parametrize("variant", ["pope", "fpope", "rotary_qknorm", "nope_qknorm"])
+def test_fp32_keys_transformed_once_give_identical_results(monkeypatch, variant):
+    """fp32 calls transform their keys once into scratch (the wrapper allocates it); without
+    scratch every query block builds its own K tiles.  Same code, same values: bitwise equal."""
+    from pe_ablations_b200 import _lib, check_device_status, pe_attention
+    from oracle import pe_attention_oracle as O
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(99)
+    B, H, Hkv, Sq, Sk, d, dr = 2, 4, 2, 300, 437, 64, 32
+    mk = lambda s, h, dd: torch.randn(B, s, h, dd, generator=g).to(dev)
+    q, k, v = mk(Sq, H, d), mk(Sk, Hkv, d), mk(Sk, Hkv, d)
+    kw = dict(start_pos=Sk - Sq, k_start_pos=0)
+    name = "nope"
+    if variant in ("pope", "fpope"):
+        name = "pope"
+        kw.update(q_r=mk(Sq, H, dr), k_r=mk(Sk, Hkv, dr), freqs=O.pope_base_freqs(dr), delta=-torch.rand(dr, generator=g) * 3)
+        if variant == "fpope":
+            kw.update(fourier_coeffs=torch.randn(dr, 8, generator=g) * 0.3, floor_freq=2 * math.pi / 512)
+    elif variant == "rotary_qknorm":
+        name = "rotary"
+        kw.update(rotary_table=O.rotary_table(O.pope_base_freqs(d // 2), Sk), table_pos0=0, qk_norm=True)
+    else:
+        kw.update(qk_norm=True)
+    with_scratch = pe_attention(name, q, k, v, **kw)
+    asked = []
+    real = _lib.lib.pe_attn_forward_workspace_bytes
+    monkeypatch.setattr(_lib.lib, "pe_attn_forward_workspace_bytes", lambda a: asked.append(real(a)) or 0)
+    without = pe_attention(name, q, k, v, **kw)
+    torch.cuda.synchronize()
+    check_device_status()
+    assert asked and asked[0] == B * Hkv * Sk * (d + (2 * dr if name == "pope" else 0)) * 4
+    assert torch.equal(with_scratch, without)
