@@ -58,7 +58,7 @@ constexpr int TMEM_COLS = 512;
 constexpr int TAIL = 2048;       // barriers, TMEM slot, per-block lse / D vectors
 constexpr int ST_WAIT_BWD = 1 << 9;
 
-enum : int { BAR_KV = 0, BAR_LDFULL = 1, BAR_LDEMPTY = 3, BAR_S = 5, BAR_P = 6, BAR_DQ = 7, BAR_SFREE = 8, BAR_VEC = 9, BAR_STG = 10, BAR_DRA = 11, BAR_DRB = 12, NUM_BARS = 13 };
+enum : int { BAR_KV = 0, BAR_LDFULL = 1, BAR_LDEMPTY = 3, BAR_S = 5, BAR_P = 6, BAR_DQ = 7, BAR_SFREE = 8, BAR_VEC = 9, BAR_STG = 10, BAR_DRA = 11, BAR_DRB = 12, BAR_PA = 13, NUM_BARS = 14 };
 
 template <int DQK, int DV>
 struct BCfg {
@@ -124,6 +124,7 @@ pe_attn_bwd_kernel(const BwdParams p, const int bh_group, const __grid_constant_
     }
     mbar_init(bar(BAR_S), 1);
     mbar_init(bar(BAR_P), NCOMPUTE / 32);
+    mbar_init(bar(BAR_PA), NCOMPUTE / 32);
     mbar_init(bar(BAR_DQ), 1);
     mbar_init(bar(BAR_SFREE), NDRAIN / 32);
     mbar_init(bar(BAR_VEC), NCOMPUTE / 32);
@@ -228,17 +229,26 @@ pe_attn_bwd_kernel(const BwdParams p, const int bh_group, const __grid_constant_
         tc_commit(bar(BAR_S));
       }
       __syncwarp();
+      // P^T and dS^T arrive in two parts -- the first 32 query columns of each half of the block,
+      // then the rest: the key-side products of the first part run under the softmax of the second
+      auto issue_dv_dk = [&](int kk) {   // 16 query columns per step; packed bf16: 8 TMEM columns
+        const uint32_t acc = (it > 0 || kk > 0) ? 1u : 0u;
+        const uint32_t a_off = (uint32_t)((kk >> 2) * 64 + (kk & 3) * 8);
+        mma_ts(t_dv, t_s + a_off, advance_smem_desc(do_mn, (uint32_t)(kk * 2048)), IDESC_DV, acc);
+        mma_ts(t_dk, t_dp + a_off, advance_smem_desc(q_mn, (uint32_t)(kk * 2048)), IDESC_DK, acc);
+      };
+      ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_PA), ph));
+      if (!ok) { fail(); break; }
+      tc_fence_after_sync();
+      if (elect_one()) {
+        issue_dv_dk(0); issue_dv_dk(1); issue_dv_dk(4); issue_dv_dk(5);
+      }
+      __syncwarp();
       ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_P), ph));
       if (!ok) { fail(); break; }
       tc_fence_after_sync();
       if (elect_one()) {
-#pragma unroll
-        for (int kk = 0; kk < BM / 16; ++kk) {   // 16 query columns per step; packed bf16: 8 TMEM columns
-          const uint32_t acc = (it > 0 || kk > 0) ? 1u : 0u;
-          const uint32_t a_off = (uint32_t)((kk >> 2) * 64 + (kk & 3) * 8);
-          mma_ts(t_dv, t_s + a_off, advance_smem_desc(do_mn, (uint32_t)(kk * 2048)), IDESC_DV, acc);
-          mma_ts(t_dk, t_dp + a_off, advance_smem_desc(q_mn, (uint32_t)(kk * 2048)), IDESC_DK, acc);
-        }
+        issue_dv_dk(2); issue_dv_dk(3); issue_dv_dk(6); issue_dv_dk(7);
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk)     // 16 keys per step
           mma_ss(t_s, advance_smem_desc(ds_mn, (uint32_t)(kk * 2048)), advance_smem_desc(k_mn, (uint32_t)(kk * 2048)),
@@ -403,6 +413,13 @@ pe_attn_bwd_kernel(const BwdParams p, const int bh_group, const __grid_constant_
           // packed bf16 back over columns this thread has already read
           tmem_st16(s_col + (uint32_t)((j >> 1) * 16), pp);
           tmem_st16(d_col + (uint32_t)((j >> 1) * 16), *reinterpret_cast<uint32_t(*)[16]>(&dall[(j >> 1) * 16]));
+          if (j == 1) {
+            // the first 32 query columns of this half are in TMEM: hand them over
+            tmem_wait_st();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(BAR_PA));
+          }
         }
       }
       // dS^T row ``r`` to shared memory (64 query columns = the eight 16-byte slots of chunk hh),
