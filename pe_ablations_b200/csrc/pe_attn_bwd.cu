@@ -58,7 +58,7 @@ constexpr int TMEM_COLS = 512;
 constexpr int TAIL = 2048;       // barriers, TMEM slot, per-block lse / D vectors
 constexpr int ST_WAIT_BWD = 1 << 9;
 
-enum : int { BAR_KV = 0, BAR_LDFULL = 1, BAR_LDEMPTY = 3, BAR_S = 5, BAR_P = 6, BAR_DQ = 7, BAR_SFREE = 8, BAR_VEC = 9, BAR_STG = 10, BAR_DRA = 11, BAR_DRB = 12, BAR_PA = 13, NUM_BARS = 14 };
+enum : int { BAR_KV = 0, BAR_LDFULL = 1, BAR_LDEMPTY = 3, BAR_S = 5, BAR_P = 6, BAR_DQ = 7, BAR_SFREE = 8, BAR_VEC = 9, BAR_STG = 10, BAR_DRA = 11, BAR_DRB = 12, BAR_PA = 13, NUM_BARS = 16 };   // BAR_PA: three partial hand-offs
 
 template <int DQK, int DV>
 struct BCfg {
@@ -124,7 +124,7 @@ pe_attn_bwd_kernel(const BwdParams p, const int bh_group, const __grid_constant_
     }
     mbar_init(bar(BAR_S), 1);
     mbar_init(bar(BAR_P), NCOMPUTE / 32);
-    mbar_init(bar(BAR_PA), NCOMPUTE / 32);
+    for (int part = 0; part < 3; ++part) mbar_init(bar(BAR_PA + part), NCOMPUTE / 32);
     mbar_init(bar(BAR_DQ), 1);
     mbar_init(bar(BAR_SFREE), NDRAIN / 32);
     mbar_init(bar(BAR_VEC), NCOMPUTE / 32);
@@ -237,18 +237,24 @@ pe_attn_bwd_kernel(const BwdParams p, const int bh_group, const __grid_constant_
         mma_ts(t_dv, t_s + a_off, advance_smem_desc(do_mn, (uint32_t)(kk * 2048)), IDESC_DV, acc);
         mma_ts(t_dk, t_dp + a_off, advance_smem_desc(q_mn, (uint32_t)(kk * 2048)), IDESC_DK, acc);
       };
-      ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_PA), ph));
-      if (!ok) { fail(); break; }
-      tc_fence_after_sync();
-      if (elect_one()) {
-        issue_dv_dk(0); issue_dv_dk(1); issue_dv_dk(4); issue_dv_dk(5);
+#pragma unroll
+      for (int part = 0; part < 3 && ok; ++part) {
+        ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_PA + part), ph));
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (elect_one()) {
+          issue_dv_dk(part);
+          issue_dv_dk(4 + part);
+        }
+        __syncwarp();
       }
-      __syncwarp();
+      if (!ok) { fail(); break; }
       ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_P), ph));
       if (!ok) { fail(); break; }
       tc_fence_after_sync();
       if (elect_one()) {
-        issue_dv_dk(2); issue_dv_dk(3); issue_dv_dk(6); issue_dv_dk(7);
+        issue_dv_dk(3);
+        issue_dv_dk(7);
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk)     // 16 keys per step
           mma_ss(t_s, advance_smem_desc(ds_mn, (uint32_t)(kk * 2048)), advance_smem_desc(k_mn, (uint32_t)(kk * 2048)),
@@ -362,7 +368,7 @@ pe_attn_bwd_kernel(const BwdParams p, const int bh_group, const __grid_constant_
       if (!ok) { fail(); break; }
       tc_fence_after_sync();
       // 16 query columns per round, the next round's TMEM loads in flight during the math
-      uint32_t sr[2][16], dr[2][16], pp[16], dall[32];
+      uint32_t sr[2][16], dr[2][16], pp[8], dall[32];
       const uint32_t s_col = tmem_base + lane_sel + (uint32_t)(hh * 64), d_col = s_col + 128u;
       tmem_ld16(s_col, sr[0]);
       tmem_ld16(d_col, dr[0]);
@@ -403,23 +409,21 @@ pe_attn_bwd_kernel(const BwdParams p, const int bh_group, const __grid_constant_
             pv[e] = pe.x; pv[e + 1] = pe.y;
             gv[e] = gg.x; gv[e + 1] = gg.y;
           }
-          const int o = (j & 1) * 8 + (c >> 1);
+          const int o = c >> 1;
           pp[o] = pack_bf16x2(pv[0], pv[1]);
           pp[o + 1] = pack_bf16x2(pv[2], pv[3]);
           dall[j * 8 + (c >> 1)] = pack_bf16x2(gv[0], gv[1]);
           dall[j * 8 + (c >> 1) + 1] = pack_bf16x2(gv[2], gv[3]);
         }
-        if (j & 1) {
-          // packed bf16 back over columns this thread has already read
-          tmem_st16(s_col + (uint32_t)((j >> 1) * 16), pp);
-          tmem_st16(d_col + (uint32_t)((j >> 1) * 16), *reinterpret_cast<uint32_t(*)[16]>(&dall[(j >> 1) * 16]));
-          if (j == 1) {
-            // the first 32 query columns of this half are in TMEM: hand them over
-            tmem_wait_st();
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(BAR_PA));
-          }
+        // packed bf16 back over columns this thread has already read; the round's 16 query
+        // columns are one K step of the key-side products: hand them over
+        tmem_st8(s_col + (uint32_t)(j * 8), pp);
+        tmem_st8(d_col + (uint32_t)(j * 8), *reinterpret_cast<uint32_t(*)[8]>(&dall[j * 8]));
+        if (j < 3) {
+          tmem_wait_st();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(BAR_PA + j));
         }
       }
       // dS^T row ``r`` to shared memory (64 query columns = the eight 16-byte slots of chunk hh),
