@@ -203,15 +203,38 @@ pe_attn_bwd_kernel(const BwdParams p, const int bh_group, const __grid_constant_
     bool ok = n_iter == 0 || __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_KV), 0));
     if (!ok) fail();
 #pragma unroll 1
+    // dP^T = V dO^T of the block in stage ``st`` (the dP^T / dS^T columns).  At d_v = 128 (eight
+    // MMAs) the next block's is issued early, see the end of the loop: 820 -> 868 TFLOP/s at
+    // S 16384; at d_v = 64 it measured 0 to -4 %.
+    constexpr bool EARLY_DP = DV == 128;
+    auto issue_dp = [&](int st) {
+      if (elect_one()) {
+        const uint64_t do_k = advance_smem_desc(do_k0, (uint32_t)st * DO_STAGE);
+#pragma unroll
+        for (int c = 0; c < C::NVC; ++c)
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4)
+            mma_ss(t_dp, advance_smem_desc(v_k, (uint32_t)(c * CH + k4 * 32)),
+                   advance_smem_desc(do_k, (uint32_t)(c * CH + k4 * 32)), IDESC_ST, (c > 0 || k4 > 0) ? 1u : 0u);
+      }
+      __syncwarp();
+    };
     for (int it = 0; it < n_iter && ok; ++it) {
       const uint32_t ph = (uint32_t)(it & 1);
       const int s = it & 1;
-      ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_LDFULL + s), (uint32_t)((it >> 1) & 1)));
+      // with EARLY_DP later blocks' tiles were checked, and their dP^T issued, at the end of the
+      // block before
+      if (it == 0 || !EARLY_DP) {
+        ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_LDFULL + s), (uint32_t)((it >> 1) & 1)));
+        if (!ok) { fail(); break; }
+        tc_fence_after_sync();
+        issue_dp(s);
+      }
       // the S^T columns double as dQ: the previous block's dQ has been read out
-      if (ok && it > 0) ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_SFREE), ph ^ 1u));
+      if (it > 0) ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_SFREE), ph ^ 1u));
       if (!ok) { fail(); break; }
       tc_fence_after_sync();
-      const uint64_t q_k = advance_smem_desc(q_k0, (uint32_t)s * Q_STAGE), do_k = advance_smem_desc(do_k0, (uint32_t)s * DO_STAGE);
+      const uint64_t q_k = advance_smem_desc(q_k0, (uint32_t)s * Q_STAGE);
       const uint64_t q_mn = advance_smem_desc(q_mn0, (uint32_t)s * Q_STAGE), do_mn = advance_smem_desc(do_mn0, (uint32_t)s * DO_STAGE);
       if (elect_one()) {
 #pragma unroll
@@ -220,13 +243,7 @@ pe_attn_bwd_kernel(const BwdParams p, const int bh_group, const __grid_constant_
           for (int k4 = 0; k4 < 4; ++k4)
             mma_ss(t_s, advance_smem_desc(k_k, (uint32_t)(c * CH + k4 * 32)),
                    advance_smem_desc(q_k, (uint32_t)(c * CH + k4 * 32)), IDESC_ST, (c > 0 || k4 > 0) ? 1u : 0u);
-#pragma unroll
-        for (int c = 0; c < C::NVC; ++c)
-#pragma unroll
-          for (int k4 = 0; k4 < 4; ++k4)
-            mma_ss(t_dp, advance_smem_desc(v_k, (uint32_t)(c * CH + k4 * 32)),
-                   advance_smem_desc(do_k, (uint32_t)(c * CH + k4 * 32)), IDESC_ST, (c > 0 || k4 > 0) ? 1u : 0u);
-        tc_commit(bar(BAR_S));
+        tc_commit(bar(BAR_S));   // S^T, and dP^T issued before it
       }
       __syncwarp();
       // P^T and dS^T arrive in two parts -- the first 32 query columns of each half of the block,
@@ -263,6 +280,15 @@ pe_attn_bwd_kernel(const BwdParams p, const int bh_group, const __grid_constant_
         tc_commit(bar(BAR_LDEMPTY + s));
       }
       __syncwarp();
+      // dP^T of the next block now, behind this block's dK product (the last reader of the dS^T
+      // columns; MMAs of one thread execute in issue order): it runs while the drain warps read dQ
+      // out of the S^T columns, which only the next block's S^T product has to wait for
+      if (EARLY_DP && it + 1 < n_iter) {
+        ok = __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_LDFULL + (s ^ 1)), (uint32_t)(((it + 1) >> 1) & 1)));
+        if (!ok) { fail(); break; }
+        tc_fence_after_sync();
+        issue_dp(s ^ 1);
+      }
     }
   }
   } else if (warp >= 8) {
