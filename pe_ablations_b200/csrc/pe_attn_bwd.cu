@@ -202,7 +202,6 @@ pe_attn_bwd_kernel(const BwdParams p, const int bh_group, const __grid_constant_
                    t_dk = tmem_base + 256u + (uint32_t)DV;
     bool ok = n_iter == 0 || __all_sync(0xffffffffu, mbar_wait_spin(bar(BAR_KV), 0));
     if (!ok) fail();
-#pragma unroll 1
     // dP^T = V dO^T of the block in stage ``st`` (the dP^T / dS^T columns).  At d_v = 128 (eight
     // MMAs) the next block's is issued early, see the end of the loop: 820 -> 868 TFLOP/s at
     // S 16384; at d_v = 64 it measured 0 to -4 %.
@@ -219,6 +218,7 @@ pe_attn_bwd_kernel(const BwdParams p, const int bh_group, const __grid_constant_
       }
       __syncwarp();
     };
+#pragma unroll 1
     for (int it = 0; it < n_iter && ok; ++it) {
       const uint32_t ph = (uint32_t)(it & 1);
       const int s = it & 1;
