@@ -219,8 +219,7 @@ int pe_attn_selftest_wait_expiry(int32_t* device_status, int64_t limit_cycles, v
  * dk / dv: outputs of type ``dtype`` shaped and strided like k / v (each written exactly once);
  * dvec: fp32 [B,H,Sq] workspace.  bf16 with (d_qk, d_v) in {(64,64), (128,64), (128,128)} runs on
  * the tensor cores; every other multiple of 8 up to (256, 128), and every fp32 call, on the CUDA
- * cores (fixed summation order; fp32 covers all head dims but (256, 128), whose 64-row tiles
- * exceed a CTA's shared memory).  Causal rule as in the forward: key s is visible to query row
+ * cores (fixed summation order).  Causal rule as in the forward: key s is visible to query row
  * r iff s <= r + (Sk - Sq). */
 typedef struct pe_attn_bwd_args {
   uint32_t struct_size;       /* sizeof(pe_attn_bwd_args), checked                            */

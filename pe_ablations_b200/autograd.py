@@ -23,8 +23,7 @@ fp32 (the reference's CPU-runnable configuration and its own tests): the forward
 kernel with the transform in-kernel, the attention core's gradients come from the fp32
 instantiation of the FFMA backward kernels, and the transform's gradient from autograd over
 ``transformed_operands`` (ATen operations on the GPU, fp32 throughout: the transform kernels store
-bf16 operands and would throw the precision away).  A parity path, not a throughput path; d_qk + d_v
-<= 320, the bound of the backward's shared-memory tiles.
+bf16 operands and would throw the precision away).  A parity path, not a throughput path.
 """
 
 from __future__ import annotations

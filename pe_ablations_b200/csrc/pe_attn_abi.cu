@@ -172,8 +172,8 @@ int pe_attn_backward(const pe_attn_bwd_args* a, void* stream) {
   if (!(a->dtype == PE_ATTN_BF16 && bwd_supports(a->d_qk, a->d_v)) && !bwd_simt_supports(a->d_qk, a->d_v, a->dtype))
     return fail(PE_ATTN_ERR_SHAPE,
                 "backward supports (d_qk, d_v) in {(64,64), (128,64), (128,128)} on the tensor cores (bf16) and any "
-                "multiples of 8 up to (256, 128) on the CUDA cores -- in fp32 all of those but (256, 128), whose "
-                "tiles do not fit shared memory (got %d, %d, dtype %d)", a->d_qk, a->d_v, a->dtype);
+                "multiples of 8 up to (256, 128) on the CUDA cores, bf16 or fp32 (got %d, %d, dtype %d)", a->d_qk, a->d_v,
+                a->dtype);
   struct { const char* name; const void* p; const int64_t* s; } ts[] = {
       {"q", a->q, a->q_stride},       {"k", a->k, a->k_stride},   {"v", a->v, a->v_stride},
       {"out", a->out, a->out_stride}, {"dout", a->dout, a->dout_stride},

@@ -45,10 +45,12 @@ struct Elem;
 template <>
 struct Elem<__nv_bfloat16> {
   static constexpr int PAD = 8;   // elements in 16 bytes
+  static constexpr bool ONE_BUF = false;
 };
 template <>
 struct Elem<float> {
   static constexpr int PAD = 4;
+  static constexpr bool ONE_BUF = true;   // the fp32 operand tiles of d_qk 256 / d_v 128 leave room for one P / dS tile
 };
 
 // eight consecutive elements (16-byte aligned) as fp32
@@ -137,11 +139,13 @@ __device__ __forceinline__ void dot_tiles(float (&acc)[4][4], const float* A, co
 
 // P and dS of one 64 x 64 (query, key) tile from the tiles in shared memory; thread (ty, tx)
 // owns queries ty + 16 i and keys tx + 16 j.  Writes both to shared memory ([query][key], fp32).
-template <typename T, bool ALIBI>
+// PMODE 0: P to ``Ps`` and dS to ``dSs``; 1: P to ``Ps``, dS kept in ``ds_reg`` (the caller writes it
+// over P later: fp32, whose operand tiles leave room for one such tile only); 2: dS to ``dSs`` only.
+template <typename T, bool ALIBI, int PMODE>
 __device__ __forceinline__ void prob_tile(const SimtBwdParams& sp, const T* Qs, const T* Ks, const T* dOs, const T* Vs,
                                           const float* lse_s,
-                                          const float* D_s, float* Ps, float* dSs, int q0, int k0, float slope, int ty,
-                                          int tx) {
+                                          const float* D_s, float* Ps, float* dSs, float (&ds_reg)[4][4], int q0, int k0,
+                                          float slope, int ty, int tx) {
   const BwdParams& p = sp.b;
   float s[4][4], dp[4][4];
 #pragma unroll
@@ -164,8 +168,10 @@ __device__ __forceinline__ void prob_tile(const SimtBwdParams& sp, const T* Qs, 
         if (ALIBI) x += slope * (float)rel;   // -slope * (distance), rel <= 0
         pr = expf(x - lse);
       }
-      Ps[ql * P_LD + kl] = pr;
-      dSs[ql * P_LD + kl] = p.scale * pr * (dp[i][j] - dsum);
+      const float ds = p.scale * pr * (dp[i][j] - dsum);
+      if (PMODE != 2) Ps[ql * P_LD + kl] = pr;
+      if (PMODE == 1) ds_reg[i][j] = ds;
+      else dSs[ql * P_LD + kl] = ds;
     }
   }
 }
@@ -196,8 +202,9 @@ __global__ void __launch_bounds__(NTHREADS) bwd_simt_key_side_kernel(const SimtB
   T* Qs = Ks + BT * sp.ldq;
   T* Vs = Qs + BT * sp.ldq;
   T* dOs = Vs + BT * sp.ldv;
+  constexpr bool ONE_BUF = Elem<T>::ONE_BUF;   // fp32: P and dS take turns in one tile
   float* Ps = reinterpret_cast<float*>(dOs + BT * sp.ldv);
-  float* dSs = Ps + BT * P_LD;
+  float* dSs = ONE_BUF ? Ps : Ps + BT * P_LD;
   float* lse_s = dSs + BT * P_LD;
   float* D_s = lse_s + BT;
 
@@ -231,9 +238,21 @@ __global__ void __launch_bounds__(NTHREADS) bwd_simt_key_side_kernel(const SimtB
         D_s[tid] = row < p.Sq ? p.dvec[((long long)b * p.H + h) * p.Sq + row] : 0.f;
       }
       __syncthreads();
-      prob_tile<T, ALIBI>(sp, Qs, Ks, dOs, Vs, lse_s, D_s, Ps, dSs, q0, k0, slope, ty, tx);
+      float ds_reg[4][4];
+      prob_tile<T, ALIBI, ONE_BUF ? 1 : 0>(sp, Qs, Ks, dOs, Vs, lse_s, D_s, Ps, dSs, ds_reg, q0, k0, slope, ty, tx);
       __syncthreads();
       // dV[key][c] += sum_q P[q][key] dO[q][c];  dK[key][c] += sum_q dS[q][key] Q[q][c]
+      // (one tile for both: first all of dV from P, then dS over it and all of dK)
+      for (int pass = 0; pass < (ONE_BUF ? 2 : 1); ++pass) {
+      if (ONE_BUF && pass == 1) {
+        __syncthreads();   // every thread has read P
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) dSs[(ty + 16 * i) * P_LD + tx + 16 * j] = ds_reg[i][j];
+        __syncthreads();
+      }
+      const bool do_dv = !ONE_BUF || pass == 0, do_dk = !ONE_BUF || pass == 1;
       for (int q = 0; q < BT; ++q) {
         float pq[4], dsq[4];
 #pragma unroll
@@ -241,7 +260,7 @@ __global__ void __launch_bounds__(NTHREADS) bwd_simt_key_side_kernel(const SimtB
           pq[i] = Ps[q * P_LD + ty + 16 * i];
           dsq[i] = dSs[q * P_LD + ty + 16 * i];
         }
-        if (tx < n_vg) {
+        if (do_dv && tx < n_vg) {
           float x[8];
           load8(dOs + q * sp.ldv + tx * 8, x);
 #pragma unroll
@@ -251,7 +270,7 @@ __global__ void __launch_bounds__(NTHREADS) bwd_simt_key_side_kernel(const SimtB
         }
 #pragma unroll
         for (int m = 0; m < 2; ++m) {
-          if (tx + 16 * m < n_qg) {
+          if (do_dk && tx + 16 * m < n_qg) {
             float x[8];
             load8(Qs + q * sp.ldq + (tx + 16 * m) * 8, x);
 #pragma unroll
@@ -261,6 +280,7 @@ __global__ void __launch_bounds__(NTHREADS) bwd_simt_key_side_kernel(const SimtB
           }
         }
       }
+      }  // passes
     }
   }
   // results in the operands' type, 16 bytes per store
@@ -292,8 +312,9 @@ __global__ void __launch_bounds__(NTHREADS) bwd_simt_query_side_kernel(const Sim
   T* Qs = Ks + BT * sp.ldq;
   T* Vs = Qs + BT * sp.ldq;
   T* dOs = Vs + BT * sp.ldv;
+  constexpr bool ONE_BUF = Elem<T>::ONE_BUF;   // fp32: P and dS take turns in one tile
   float* Ps = reinterpret_cast<float*>(dOs + BT * sp.ldv);
-  float* dSs = Ps + BT * P_LD;
+  float* dSs = ONE_BUF ? Ps : Ps + BT * P_LD;
   float* lse_s = dSs + BT * P_LD;
   float* D_s = lse_s + BT;
 
@@ -325,7 +346,8 @@ __global__ void __launch_bounds__(NTHREADS) bwd_simt_query_side_kernel(const Sim
     load_tile(Ks, sp.ldq, p.k, b, hk, k0, p.Sk, sp.d_qk);
     load_tile(Vs, sp.ldv, p.v, b, hk, k0, p.Sk, sp.d_v);
     __syncthreads();
-    prob_tile<T, ALIBI>(sp, Qs, Ks, dOs, Vs, lse_s, D_s, Ps, dSs, q0, k0, slope, ty, tx);
+    float ds_unused[4][4];
+    prob_tile<T, ALIBI, ONE_BUF ? 2 : 0>(sp, Qs, Ks, dOs, Vs, lse_s, D_s, Ps, dSs, ds_unused, q0, k0, slope, ty, tx);
     __syncthreads();
     // dQ[q][c] += sum_k dS[q][k] K[k][c]: queries ty + 16 i, columns 8 (tx + 16 m) .. + 8
     for (int k = 0; k < BT; ++k) {
@@ -361,8 +383,9 @@ __global__ void __launch_bounds__(NTHREADS) bwd_simt_query_side_kernel(const Sim
   }
 }
 
-size_t simt_bwd_smem(int d_qk, int d_v, size_t elem, int pad) {
-  return (size_t)2 * BT * ((d_qk + pad) + (d_v + pad)) * elem + (size_t)(2 * BT * P_LD + 2 * BT) * sizeof(float);
+size_t simt_bwd_smem(int d_qk, int d_v, size_t elem, int pad, bool one_buf) {
+  return (size_t)2 * BT * ((d_qk + pad) + (d_v + pad)) * elem +
+         (size_t)((one_buf ? 1 : 2) * BT * P_LD + 2 * BT) * sizeof(float);
 }
 
 template <typename T>
@@ -373,7 +396,7 @@ int launch_bwd_simt_t(const BwdParams& p, int d_qk, int d_v, bool alibi, cudaStr
   sp.d_v = d_v;
   sp.ldq = d_qk + Elem<T>::PAD;
   sp.ldv = d_v + Elem<T>::PAD;
-  const size_t smem = simt_bwd_smem(d_qk, d_v, sizeof(T), Elem<T>::PAD);
+  const size_t smem = simt_bwd_smem(d_qk, d_v, sizeof(T), Elem<T>::PAD, Elem<T>::ONE_BUF);
   const long long rows = (long long)p.B * p.H * p.Sq;
   rowdot_kernel<T><<<(unsigned)((rows * 32 + 255) / 256), 256, 0, stream>>>(p, d_v);
   cudaError_t e = cudaGetLastError();
@@ -398,12 +421,12 @@ int launch_bwd_simt_t(const BwdParams& p, int d_qk, int d_v, bool alibi, cudaStr
 
 }  // namespace
 
-// d_qk and d_v multiples of 8, d_qk <= 256, d_v <= 128, and the four operand tiles of 64 rows fit
-// the 227 KB of shared memory a CTA can have (fp32: everything but d_qk 256 with d_v 128)
+// d_qk and d_v multiples of 8, d_qk <= 256, d_v <= 128: the four operand tiles of 64 rows then fit
+// the 227 KB of shared memory a CTA can have (fp32 at 256 / 128: 214 KB with a single P / dS tile)
 bool bwd_simt_supports(int d_qk, int d_v, int dtype) {
   if (!(d_qk >= 8 && d_qk <= 256 && d_qk % 8 == 0 && d_v >= 8 && d_v <= 128 && d_v % 8 == 0)) return false;
-  const size_t smem = dtype == PE_ATTN_FP32 ? simt_bwd_smem(d_qk, d_v, 4, Elem<float>::PAD)
-                                            : simt_bwd_smem(d_qk, d_v, 2, Elem<__nv_bfloat16>::PAD);
+  const size_t smem = dtype == PE_ATTN_FP32 ? simt_bwd_smem(d_qk, d_v, 4, Elem<float>::PAD, Elem<float>::ONE_BUF)
+                                            : simt_bwd_smem(d_qk, d_v, 2, Elem<__nv_bfloat16>::PAD, Elem<__nv_bfloat16>::ONE_BUF);
   return smem <= 227 * 1024;
 }
 

@@ -214,12 +214,8 @@ def _training_call(variant, q, k, v, q_r, k_r, freqs, delta, fourier_coeffs, lse
     if v.dtype == torch.bfloat16 and (d_qk not in (64, 128, 192, 256) or v.shape[-1] not in (64, 128)):
         raise NotImplementedError(f"gradients need d_qk in (64, 128, 192, 256) and d_v in (64, 128) -- the bf16 forward's "
                                   f"head dims; got ({d_qk}, {v.shape[-1]})")
-    if v.dtype == torch.float32:
-        # four 64-row fp32 operand tiles (rows padded by 16 bytes) + the P / dS tiles in 227 KB
-        tiles = 2 * 64 * (d_qk + v.shape[-1] + 8) * 4 + (2 * 64 * 68 + 128) * 4
-        if d_qk % 8 or v.shape[-1] % 8 or d_qk > 256 or v.shape[-1] > 128 or tiles > 227 * 1024:
-            raise NotImplementedError(f"fp32 gradients need d_qk <= 256 and d_v <= 128 in steps of 8 whose backward "
-                                      f"tiles fit shared memory (all but (256, 128)); got ({d_qk}, {v.shape[-1]})")
+    if v.dtype == torch.float32 and (d_qk % 8 or v.shape[-1] % 8 or d_qk > 256 or v.shape[-1] > 128):
+        raise NotImplementedError(f"fp32 gradients need d_qk <= 256 and d_v <= 128 in steps of 8; got ({d_qk}, {v.shape[-1]})")
     dev = v.device
     k_start = kw["start_pos"] if kw["k_start_pos"] is None else kw["k_start_pos"]
     tab = kw["rotary_table"]
@@ -410,7 +406,7 @@ def attention_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: t
 
     bf16 with (d_qk, d_v) in {(64,64), (128,64), (128,128)} runs on the tensor cores; any other
     multiples of 8 up to (256, 128) -- the 1B shape's (256, 128) -- and every fp32 call on the CUDA
-    cores (FFMA kernels; fp32 has every head dim but (256, 128)).
+    cores (FFMA kernels).
 
     q [B,Sq,H,d_qk], k [B,Sk,Hkv,d_qk], v [B,Sk,Hkv,d_v], out / dout [B,Sq,H,d_v] (all bf16 or all
     fp32, last dimension contiguous), ``lse`` the forward's [B,H,Sq] logsumexp.  Returns

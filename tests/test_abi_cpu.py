@@ -169,7 +169,7 @@ def test_backward_entry_rejects_bad_arguments_before_touching_the_gpu(L):
     assert b"(64,64), (128,64), (128,128)" in L.lib.pe_attn_last_error()
     assert bwd(C.byref(_bwd_args(L, d_qk=100)), None) == 3                    # not a multiple of 8
     assert bwd(C.byref(_bwd_args(L, dtype=7)), None) == 2                     # unknown dtype
-    assert bwd(C.byref(_bwd_args(L, dtype=1, d_qk=256, d_v=128)), None) == 3  # fp32 tiles beyond shared memory
+    assert bwd(C.byref(_bwd_args(L, dtype=1, d_qk=264)), None) == 3           # fp32: the same head dims
     assert bwd(C.byref(_bwd_args(L, dout=None)), None) == 1
     assert bwd(C.byref(_bwd_args(L, dk=0x10008)), None) == 4
     assert bwd(C.byref(_bwd_args(L, q_stride=(512 * 8 * 128, 130, 8 * 128))), None) == 4
