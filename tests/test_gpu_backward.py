@@ -520,3 +520,27 @@ def test_backward_accepts_a_strided_upstream_gradient():
     out.backward(w.transpose(1, 2).contiguous())
     for a, b_ in zip(g1, (q.grad, k.grad, v.grad)):
         torch.testing.assert_close(a.float(), b_.float(), rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("shape", [(2, 8, 8, 2048, 128, 128), (8, 8, 4, 512, 128, 64), (2, 12, 12, 1024, 64, 64)],
+                         ids=["d128_128", "d128_64_gqa", "d64_64"])
+def test_repeated_backward_launches_give_the_same_dk_dv(shape):
+    """dK and dV are written once per key block in a fixed order of MMAs (P^T / dS^T handed over in
+    parts, the next block's products issued early): bitwise the same on every launch.  dQ is a sum
+    of TMA reductions in an order that is not fixed: equal up to fp32 rounding."""
+    from pe_ablations_b200 import check_device_status
+    from pe_ablations_b200.ops import attention_backward
+
+    B, H, Hkv, S, dqk, dv = shape
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(3)
+    mk = lambda h, d: torch.randn(B, S, h, d, device=dev, generator=g).to(torch.bfloat16)
+    q, k, v, do, o = mk(H, dqk), mk(Hkv, dqk), mk(Hkv, dv), mk(H, dv), mk(H, dv)
+    lse = torch.full((B, H, S), 5.0, device=dev) + torch.log(torch.arange(1, S + 1, device=dev).float())
+    first = [t.clone() for t in attention_backward(q, k, v, o, do, lse, scale=dqk ** -0.5)]
+    for _ in range(10):
+        dq, dk, dv_ = attention_backward(q, k, v, o, do, lse, scale=dqk ** -0.5)
+        assert torch.equal(dk, first[1]) and torch.equal(dv_, first[2])
+        assert (dq - first[0]).abs().max().item() <= 1e-5 * max(first[0].abs().max().item(), 1.0)
+    torch.cuda.synchronize()
+    check_device_status()
